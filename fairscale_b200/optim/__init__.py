@@ -1,0 +1,2 @@
+"""Optimizers and gradient scalers (mirrors fairscale/optim/__init__.py:12-22)."""
+from .oss import OSS  # noqa: F401
