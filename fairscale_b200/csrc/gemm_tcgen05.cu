@@ -1,0 +1,375 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05) with fused epilogues.
+//
+//   C[M,N] = epilogue( sum_k A(m,k) * B(n,k) )        fp32 accumulation in TMEM
+//
+// A and B are bf16 and can each be stored K-major ([rows, K], K contiguous) or MN-major
+// ([K, rows], rows contiguous); this covers the three products of a linear layer without any
+// transposed copy:
+//   forward  Y  = X  W^T : A = X  (K-major),  B = W  (K-major)
+//   dgrad    dX = dY W   : A = dY (K-major),  B = W  (MN-major, stored [N_out... see gemm.py)
+//   wgrad    dW = dY^T X : A = dY (MN-major), B = X  (MN-major)
+//
+// Structure: persistent kernel, one CTA per SM, 192 threads.
+//   warp 0      TMA producer: 128-byte-swizzled 64-wide K slabs of A and B into a 4-stage smem ring
+//   warp 1      allocates TMEM (2 x BLOCK_N fp32 columns) and issues tcgen05.mma (one elected lane)
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp its 32-lane quadrant),
+//               apply bias / GELU / GELU' / residual, convert and store; overlaps the next tile's
+//               main loop because the accumulator is double-buffered in TMEM.
+// All loads are per-CTA TMA loads of this GPU's own memory. Every mbarrier wait is bounded.
+//
+// Replaces the cuBLAS calls behind F.linear in the reference
+// (fairscale/nn/model_parallel/layers.py:290,380 and every nn.Linear of its benchmark models).
+
+#include "sm100.cuh"
+
+namespace fsb {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;   // 64 bf16 = 128 B = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+
+enum Epilogue : int {
+  EPI_NONE = 0,           // C = acc
+  EPI_BIAS = 1,           // C = acc + bias[n]
+  EPI_BIAS_GELU = 2,      // C = gelu(acc + bias[n]);  aux_out (optional) = acc + bias[n]
+  EPI_BIAS_RESIDUAL = 3,  // C = acc + bias[n] + aux[m,n]
+  EPI_DGELU = 4,          // C = acc * gelu'(aux[m,n])
+  EPI_RESIDUAL = 5,       // C = acc + aux[m,n]
+};
+
+struct GemmParams {
+  void* C;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux;
+  __nv_bfloat16* aux_out;
+  int M, N, K;
+  int ldc, ld_aux;
+  int a_mn_major, b_mn_major;
+  int epilogue;
+  int out_f32;       // C is fp32 (else bf16)
+  int accumulate_c;  // C += result (fp32 output only)
+  int* status;
+};
+
+template <int BLOCK_N>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Groups of 16 M-tiles walk N together, so concurrently running CTAs share A and B slabs in L2.
+  constexpr int GROUP_M = 16;
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  using L = SmemLayout<BLOCK_N>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
+  const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BLOCK_N);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BLOCK_M, n0 = tn * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          if (!p.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, true, p.a_mn_major != 0, p.b_mn_major != 0);
+      // K-major: LBO unused, SBO 1024; UMMA_K advance = 32 B inside the swizzle row.
+      // MN-major: LBO = 8192 (next 64 MN elements), SBO 1024; UMMA_K advance = 16 k-rows = 2048 B.
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, b_lbo = p.b_mn_major ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u, b_kstep = p.b_mn_major ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024u);
+            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem slot once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int row = tm * BLOCK_M + quad * 32 + lane;
+      const int n0 = tn * BLOCK_N;
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
+      const bool row_ok = row < p.M;
+      const bool vec_ok = (p.ldc % 8 == 0) && (p.ld_aux % 8 == 0);
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 32), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        const bool full = vec_ok && (col0 + 32 <= p.N);
+        const int epi = p.epilogue;
+        if (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESIDUAL) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+        }
+        if (epi == EPI_BIAS_GELU) {
+          if (p.aux_out != nullptr) {
+            __nv_bfloat16* po = p.aux_out + static_cast<size_t>(row) * p.ld_aux + col0;
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                Vec16<__nv_bfloat16> o;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
+                st16(po + q * 8, o);
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) po[i] = __float2bfloat16_rn(v[i]);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+        } else if (epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU) {
+          const __nv_bfloat16* pa = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
+          float a[32];
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              Vec16<__nv_bfloat16> x = ld16(pa + q * 8);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) a[q * 8 + i] = __bfloat162float(x.v[i]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a[i] = (col0 + i < p.N) ? __bfloat162float(pa[i]) : 0.f;
+          }
+          if (epi == EPI_DGELU) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(a[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += a[i];
+          }
+        }
+        if (p.out_f32) {
+          float* pc = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (p.accumulate_c) {
+            for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] += v[i];
+          } else if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(pc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          } else {
+            for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = v[i];
+          }
+        } else {
+          __nv_bfloat16* pc = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              Vec16<__nv_bfloat16> o;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
+              st16(pc + q * 8, o);
+            }
+          } else {
+            for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = __float2bfloat16_rn(v[i]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait ran out: report, give in-flight TMA copies time to land, then release TMEM and leave
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, FSB_ERR_WAIT_TIMEOUT);
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BLOCK_N);
+  }
+}
+
+}  // namespace fsb
+
+// C ABI ------------------------------------------------------------------------------------------
+// lda / ldb: elements between consecutive rows of the *stored* matrix ([rows,K] when K-major,
+// [K,rows] when MN-major). All leading dimensions must be multiples of 8; pointers 16-byte aligned.
+// Returns 0 on success, a cudaError_t value, or -1 for an argument / tensor-map problem.
+FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
+                          int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
+                          int epilogue, int out_f32, int accumulate_c, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -1;
+  if (accumulate_c && !out_f32) return -1;
+
+  const int block_n = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  bool ok = true;
+  if (!a_mn_major) ok &= fsb_host::encode_2d_16bit(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M);
+  else             ok &= fsb_host::encode_2d_16bit(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BLOCK_K);
+  if (!b_mn_major) ok &= fsb_host::encode_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, block_n);
+  else             ok &= fsb_host::encode_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BLOCK_K);
+  if (!ok) return -1;
+
+  GemmParams p;
+  p.C = C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_aux = ld_aux > 0 ? ld_aux : ldc;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
+  p.status = status;
+
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static int num_sms_cache[64] = {0};
+  static bool attr_set[64][2] = {{false}};
+  const int di = dev & 63;
+  if (num_sms_cache[di] == 0) cudaDeviceGetAttribute(&num_sms_cache[di], cudaDevAttrMultiProcessorCount, dev);
+  const int num_sms = num_sms_cache[di];
+  const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n);
+  int grid = tiles < num_sms ? tiles : num_sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+
+  cudaError_t err;
+  if (block_n == 256) {
+    if (!attr_set[di][0]) {
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);
+      attr_set[di][0] = true;
+    }
+    gemm_bf16_tcgen05_kernel<256><<<grid, GEMM_THREADS, SmemLayout<256>::TOTAL, stream>>>(ta, tb, p);
+  } else {
+    if (!attr_set[di][1]) {
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::TOTAL);
+      attr_set[di][1] = true;
+    }
+    gemm_bf16_tcgen05_kernel<128><<<grid, GEMM_THREADS, SmemLayout<128>::TOTAL, stream>>>(ta, tb, p);
+  }
+  err = cudaGetLastError();
+  return static_cast<int>(err);
+}

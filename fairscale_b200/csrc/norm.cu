@@ -1,0 +1,243 @@
+// LayerNorm / RMSNorm forward and backward for bf16 activations, fp32 statistics.
+//
+// Forward: one CTA per row, the row is read once with 16-byte loads, kept in registers, reduced
+// (mean / variance) and written once; mean and rstd are saved for backward.
+// Backward: same one-pass structure for dx; dgamma / dbeta are accumulated per CTA over a strip of
+// rows into fp32 partials [n_strips, H], reduced by a second small kernel (no atomics, so the
+// result is deterministic).
+// Replaces nn.LayerNorm in the reference's benchmark models (benchmarks/models/transformer_lm.py:109-110).
+
+#include "common.cuh"
+
+namespace fsb {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_VEC = 4;  // up to 4 x 8 bf16 per thread -> H <= 8192
+
+template <bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                                                                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                                                                float* __restrict__ mean_out, float* __restrict__ rstd_out, int H, float eps) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  __nv_bfloat16* yr = y + row * H;
+  const int nvec = H / 8;
+  float v[NORM_MAX_VEC][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_VEC; ++it) {
+    const int j = threadIdx.x + it * NORM_THREADS;
+    if (j < nvec) {
+      const Vec16<__nv_bfloat16> t = ld16(xr + j * 8);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { v[it][k] = __bfloat162float(t.v[k]); sum += v[it][k]; }
+    }
+  }
+  float mean = 0.f;
+  if (!RMS) mean = block_sum(sum, scratch) / H;
+  float sq = 0.f;
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_VEC; ++it) {
+    const int j = threadIdx.x + it * NORM_THREADS;
+    if (j < nvec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { const float d = v[it][k] - mean; sq += d * d; }
+    }
+  }
+  const float var = block_sum(sq, scratch) / H;
+  const float rstd = rsqrtf(var + eps);
+  if (threadIdx.x == 0) {
+    if (!RMS && mean_out != nullptr) mean_out[row] = mean;
+    if (rstd_out != nullptr) rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_VEC; ++it) {
+    const int j = threadIdx.x + it * NORM_THREADS;
+    if (j < nvec) {
+      const Vec16<__nv_bfloat16> g = ld16(gamma + j * 8);
+      Vec16<__nv_bfloat16> o;
+      if (!RMS && beta != nullptr) {
+        const Vec16<__nv_bfloat16> b = ld16(beta + j * 8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          o.v[k] = __float2bfloat16_rn((v[it][k] - mean) * rstd * __bfloat162float(g.v[k]) + __bfloat162float(b.v[k]));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn((v[it][k] - mean) * rstd * __bfloat162float(g.v[k]));
+      }
+      st16(yr + j * 8, o);
+    }
+  }
+}
+
+// dx for one row per CTA iteration; each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps
+// running dgamma/dbeta sums for its columns in registers, flushed to partials at the end.
+template <bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                                const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                                                float* __restrict__ dgamma_part, float* __restrict__ dbeta_part,
+                                                                long long rows, int H) {
+  __shared__ float scratch[32];
+  const int nvec = H / 8;
+  float dg[NORM_MAX_VEC][8], db[NORM_MAX_VEC][8], gam[NORM_MAX_VEC][8];
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_VEC; ++it) {
+    const int j = threadIdx.x + it * NORM_THREADS;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { dg[it][k] = 0.f; db[it][k] = 0.f; gam[it][k] = 0.f; }
+    if (j < nvec) {
+      const Vec16<__nv_bfloat16> g = ld16(gamma + j * 8);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) gam[it][k] = __bfloat162float(g.v[k]);
+    }
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[NORM_MAX_VEC][8], wdy[NORM_MAX_VEC][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < NORM_MAX_VEC; ++it) {
+      const int j = threadIdx.x + it * NORM_THREADS;
+      if (j < nvec) {
+        const Vec16<__nv_bfloat16> tx = ld16(x + row * H + j * 8);
+        const Vec16<__nv_bfloat16> td = ld16(dy + row * H + j * 8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float d = __bfloat162float(td.v[k]);
+          xh[it][k] = (__bfloat162float(tx.v[k]) - mean) * rstd;
+          wdy[it][k] = d * gam[it][k];
+          s1 += wdy[it][k];
+          s2 += wdy[it][k] * xh[it][k];
+          dg[it][k] += d * xh[it][k];
+          db[it][k] += d;
+        }
+      }
+    }
+    if (!RMS) s1 = block_sum(s1, scratch) / H; else s1 = 0.f;
+    s2 = block_sum(s2, scratch) / H;
+#pragma unroll
+    for (int it = 0; it < NORM_MAX_VEC; ++it) {
+      const int j = threadIdx.x + it * NORM_THREADS;
+      if (j < nvec) {
+        Vec16<__nv_bfloat16> o;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(rstd * (wdy[it][k] - s1 - xh[it][k] * s2));
+        st16(dx + row * H + j * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_VEC; ++it) {
+    const int j = threadIdx.x + it * NORM_THREADS;
+    if (j < nvec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        dgamma_part[static_cast<long long>(blockIdx.x) * H + j * 8 + k] = dg[it][k];
+        if (!RMS && dbeta_part != nullptr) dbeta_part[static_cast<long long>(blockIdx.x) * H + j * 8 + k] = db[it][k];
+      }
+    }
+  }
+}
+
+// out[c] = sum_r part[r, c]  (fp32 partials -> bf16 or fp32 result)
+__global__ void column_reduce_kernel(const float* __restrict__ part, int rows, int H, __nv_bfloat16* out_bf16, float* out_f32) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float acc = 0.f;
+  for (int r = 0; r < rows; ++r) acc += part[static_cast<long long>(r) * H + c];
+  if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16_rn(acc);
+  if (out_f32 != nullptr) out_f32[c] = acc;
+}
+
+// Column sums of a bf16 matrix [rows, H] (bias gradient): strip partials then reduce.
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long rows, int H, float* __restrict__ part) {
+  // block = 32 x 8 threads; a block handles 256 columns (8 per thread along x) for a strip of rows
+  const int col0 = (blockIdx.x * 32 + threadIdx.x) * 8;
+  const bool active = col0 < H;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long long r = blockIdx.y * 8 + threadIdx.y; active && r < rows; r += static_cast<long long>(gridDim.y) * 8) {
+    const Vec16<__nv_bfloat16> t = ld16(x + r * H + col0);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] += __bfloat162float(t.v[k]);
+  }
+  __shared__ float red[8][32][9];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[threadIdx.y][threadIdx.x][k] = acc[k];
+  __syncthreads();
+  if (threadIdx.y == 0 && active) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float s = 0.f;
+#pragma unroll
+      for (int y = 0; y < 8; ++y) s += red[y][threadIdx.x][k];
+      part[static_cast<long long>(blockIdx.y) * H + col0 + k] = s;
+    }
+  }
+}
+
+}  // namespace fsb
+
+// H must be a multiple of 8 and <= 8192. mean/rstd are fp32 [rows]. rms != 0 selects RMSNorm
+// (beta and mean ignored).
+FSB_API int fsb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                         long long rows, int H, float eps, int rms, cudaStream_t stream) {
+  using namespace fsb;
+  if (rows <= 0) return 0;
+  if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAX_VEC) return -1;
+  auto* xx = static_cast<const __nv_bfloat16*>(x);
+  auto* gg = static_cast<const __nv_bfloat16*>(gamma);
+  auto* bb = static_cast<const __nv_bfloat16*>(beta);
+  auto* yy = static_cast<__nv_bfloat16*>(y);
+  if (rms) norm_fwd_kernel<true><<<static_cast<unsigned>(rows), NORM_THREADS, 0, stream>>>(xx, gg, bb, yy, mean, rstd, H, eps);
+  else     norm_fwd_kernel<false><<<static_cast<unsigned>(rows), NORM_THREADS, 0, stream>>>(xx, gg, bb, yy, mean, rstd, H, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+FSB_API int fsb_norm_bwd_num_strips(long long rows) {
+  const long long cap = 148 * 4;
+  return static_cast<int>(rows < cap ? rows : cap);
+}
+
+// partials: fp32 workspace of 2 * n_strips * H floats (n_strips from fsb_norm_bwd_num_strips).
+// dgamma / dbeta are bf16 [H] outputs (dbeta may be null, and is ignored for RMSNorm).
+FSB_API int fsb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                         void* dgamma, void* dbeta, float* partials, long long rows, int H, int rms, cudaStream_t stream) {
+  using namespace fsb;
+  if (rows <= 0) return 0;
+  if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAX_VEC) return -1;
+  const int strips = fsb_norm_bwd_num_strips(rows);
+  float* pg = partials;
+  float* pb = partials + static_cast<long long>(strips) * H;
+  auto* d = static_cast<const __nv_bfloat16*>(dy);
+  auto* xx = static_cast<const __nv_bfloat16*>(x);
+  auto* gg = static_cast<const __nv_bfloat16*>(gamma);
+  auto* o = static_cast<__nv_bfloat16*>(dx);
+  if (rms) norm_bwd_kernel<true><<<strips, NORM_THREADS, 0, stream>>>(d, xx, gg, mean, rstd, o, pg, nullptr, rows, H);
+  else     norm_bwd_kernel<false><<<strips, NORM_THREADS, 0, stream>>>(d, xx, gg, mean, rstd, o, pg, pb, rows, H);
+  const int threads = 256, blocks = (H + threads - 1) / threads;
+  column_reduce_kernel<<<blocks, threads, 0, stream>>>(pg, strips, H, static_cast<__nv_bfloat16*>(dgamma), nullptr);
+  if (!rms && dbeta != nullptr)
+    column_reduce_kernel<<<blocks, threads, 0, stream>>>(pb, strips, H, static_cast<__nv_bfloat16*>(dbeta), nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+FSB_API int fsb_colsum_num_strips(long long rows) {
+  const long long want = (rows + 63) / 64;
+  return static_cast<int>(want < 1 ? 1 : (want > 256 ? 256 : want));
+}
+
+// out[c] = sum_r x[r, c]; x bf16 [rows, H] (H % 8 == 0); partials fp32 [n_strips, H]; out bf16 [H].
+FSB_API int fsb_colsum(const void* x, long long rows, int H, float* partials, void* out, cudaStream_t stream) {
+  using namespace fsb;
+  if (rows <= 0 || H <= 0) return 0;
+  if (H % 8 != 0) return -1;
+  const int strips = fsb_colsum_num_strips(rows);
+  dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
+  colsum_partial_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, H, partials);
+  const int threads = 256, blocks = (H + threads - 1) / threads;
+  column_reduce_kernel<<<blocks, threads, 0, stream>>>(partials, strips, H, static_cast<__nv_bfloat16*>(out), nullptr);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,6 @@
+from .checkpoint_activations import (  # noqa: F401
+    checkpoint_wrapper,
+    disable_checkpointing,
+    is_checkpointing,
+    is_recomputing,
+)

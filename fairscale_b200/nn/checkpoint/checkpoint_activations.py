@@ -1,0 +1,249 @@
+"""Activation checkpointing as a module wrapper.
+
+Parity: fairscale/nn/checkpoint/checkpoint_activations.py:25-353 — ``checkpoint_wrapper``
+keeps only a block's inputs in forward and recomputes the block in backward; it accepts
+keyword arguments and non-tensor outputs, restores RNG and autocast state for the
+recomputation, and can park the saved inputs in host memory.
+
+Host offload uses pinned staging buffers and a dedicated copy stream with events, so the
+device→host copy of one block's input overlaps the next block's compute, and the
+host→device copy is issued ahead of the recomputation.
+"""
+
+from __future__ import annotations
+
+import functools
+import threading
+import weakref
+from contextlib import contextmanager, nullcontext
+from typing import Any, Dict, Generator, List, Optional, Tuple
+
+import torch
+import torch.utils.checkpoint as torch_checkpoint
+from torch import Tensor, nn
+
+from ...internal.containers import pack_kwargs, split_non_tensors, unpack_kwargs, unpack_non_tensors
+from .checkpoint_utils import patch_batchnorm
+
+
+class _Flags(threading.local):
+    def __init__(self) -> None:
+        self.is_checkpointing = False
+        self.is_recomputing = False
+        self.is_checkpointing_disabled = False
+
+
+thread_local = _Flags()
+
+
+@contextmanager
+def _flag(name: str, value: bool = True) -> Generator[None, None, None]:
+    prev = getattr(thread_local, name)
+    setattr(thread_local, name, value)
+    try:
+        yield
+    finally:
+        setattr(thread_local, name, prev)
+
+
+def disable_checkpointing() -> Any:
+    """Context in which wrapped modules run as if they were not checkpointed."""
+    return _flag("is_checkpointing_disabled")
+
+
+def enable_checkpointing() -> Any:
+    return _flag("is_checkpointing")
+
+
+def enable_recomputing() -> Any:
+    return _flag("is_recomputing")
+
+
+def is_checkpointing() -> bool:
+    """True inside the first (no-grad) forward of a checkpointed module."""
+    return thread_local.is_checkpointing
+
+
+def is_recomputing() -> bool:
+    """True inside the backward-time recomputation; use it to avoid repeating side effects."""
+    return thread_local.is_recomputing
+
+
+def checkpoint_wrapper(module: nn.Module, offload_to_cpu: bool = False) -> nn.Module:
+    """Make every later call of ``module`` activation-checkpointed; returns the same object.
+
+    Inner activations are dropped and recomputed; with ``offload_to_cpu`` the saved
+    inputs (the "outer" activations) additionally live in pinned host memory between
+    forward and backward.  No-op under ``torch.no_grad()`` and inside
+    :func:`disable_checkpointing`.
+    """
+    patch_batchnorm(module)
+    # a weak reference avoids the module ↔ bound-partial cycle that would keep it alive forever
+    module.forward = functools.partial(  # type: ignore[method-assign]
+        _checkpointed_forward, type(module).forward, weakref.ref(module), offload_to_cpu
+    )
+    return module
+
+
+def _checkpointed_forward(original_forward: Any, weak_self: Any, offload_to_cpu: bool, *args: Any, **kwargs: Any) -> Any:
+    module = weak_self()
+    if not torch.is_grad_enabled() or thread_local.is_checkpointing_disabled:
+        return original_forward(module, *args, **kwargs)
+
+    kwarg_keys, flat_args = pack_kwargs(module, *args, **kwargs)
+    shared: Dict[str, Any] = {"offload": offload_to_cpu}
+    # the dummy input guarantees the Function node is part of the graph even if no input needs grad
+    out = CheckpointFunction.apply(torch.tensor([], requires_grad=True), original_forward, shared, kwarg_keys, *flat_args)
+    needs_grad = shared["output_requires_grad"]
+    if isinstance(out, torch.Tensor):
+        return out if needs_grad else out.detach()
+    out = [t if needs_grad else t.detach() for t in out]
+    packed = shared["packed_non_tensor_outputs"]
+    return unpack_non_tensors(tuple(out), packed) if packed else out
+
+
+def get_rng_state() -> Dict[str, Any]:
+    state = {"torch_rng_state": torch.get_rng_state()}
+    if torch.cuda.is_available():
+        state["cuda_rng_state"] = torch.cuda.get_rng_state()
+    return state
+
+
+def set_rng_state(state: Dict[str, Any]) -> None:
+    torch.set_rng_state(state["torch_rng_state"])
+    if torch.cuda.is_available():
+        torch.cuda.set_rng_state(state["cuda_rng_state"])
+
+
+def _autocast_snapshot() -> Optional[Dict[str, Any]]:
+    if torch.is_autocast_enabled("cuda"):
+        return {"device_type": "cuda", "dtype": torch.get_autocast_dtype("cuda")}
+    if torch.is_autocast_enabled("cpu"):
+        return {"device_type": "cpu", "dtype": torch.get_autocast_dtype("cpu")}
+    return None
+
+
+class _HostParking:
+    """Device→pinned-host and back, on a side stream ordered by events."""
+
+    _streams: Dict[int, Any] = {}
+
+    @classmethod
+    def _stream(cls, device: torch.device) -> Any:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        if idx not in cls._streams:
+            cls._streams[idx] = torch.cuda.Stream(device=idx)
+        return cls._streams[idx]
+
+    @classmethod
+    def park(cls, t: Tensor) -> Tuple[Tensor, Any]:
+        if not t.is_cuda:
+            return t.to("cpu"), None
+        side = cls._stream(t.device)
+        side.wait_stream(torch.cuda.current_stream(t.device))
+        host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        with torch.cuda.stream(side):
+            host.copy_(t, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(side)
+        t.record_stream(side)
+        return host, done
+
+    @classmethod
+    def fetch(cls, host: Tensor, done: Any, device: torch.device) -> Tensor:
+        if device.type != "cuda":
+            return host.to(device)
+        side = cls._stream(device)
+        if done is not None:
+            side.wait_event(done)
+        with torch.cuda.stream(side):
+            dev = host.to(device, non_blocking=True)
+        torch.cuda.current_stream(device).wait_stream(side)
+        dev.record_stream(torch.cuda.current_stream(device))
+        return dev
+
+
+class CheckpointFunction(torch.autograd.Function):
+    """Autograd node that runs ``run_function`` without grad and replays it in backward.
+
+    Non-tensor outputs travel through ``parent_ctx_dict`` (autograd Functions can only
+    return tensors); the caller merges them back.
+    """
+
+    @staticmethod
+    def forward(  # type: ignore[override]
+        ctx: Any,
+        dummy_tensor_requires_grad: Tensor,
+        run_function: Any,
+        parent_ctx_dict: Dict[str, Any],
+        kwarg_keys: Tuple[str, ...],
+        *args: Any,
+    ) -> Any:
+        torch_checkpoint.check_backward_validity(args)
+        ctx.run_function = run_function
+        ctx.kwarg_keys = kwarg_keys
+        ctx.fwd_rng_state = get_rng_state()
+        ctx.autocast = _autocast_snapshot()
+
+        tensor_inputs, packed_inputs = split_non_tensors(args)
+        if parent_ctx_dict["offload"]:
+            ctx.fwd_device = tuple(t.device for t in tensor_inputs)
+            ctx.grad_requirements = tuple(t.requires_grad for t in tensor_inputs)
+            parked = [_HostParking.park(t) for t in tensor_inputs]
+            ctx.park_events = [ev for _, ev in parked]
+            tensor_inputs = tuple(h for h, _ in parked)
+        else:
+            ctx.fwd_device, ctx.grad_requirements, ctx.park_events = None, None, None
+        ctx.save_for_backward(*tensor_inputs)
+        ctx.packed_non_tensor_inputs = packed_inputs
+
+        with torch.no_grad(), enable_checkpointing():
+            f_args, f_kwargs = unpack_kwargs(kwarg_keys, args)
+            outputs = run_function(*f_args, **f_kwargs)
+            the_module = f_args[0]
+
+        # flattened modules expose their weights as plain views, not nn.Parameters
+        params: List[Any] = list(the_module.parameters())
+        params += getattr(the_module, "_unflattened_param_views", [])
+        grad_src = ctx.grad_requirements if ctx.grad_requirements is not None else [t.requires_grad for t in tensor_inputs]
+        parent_ctx_dict["output_requires_grad"] = any(p.requires_grad for p in params) or any(grad_src)
+
+        if not isinstance(outputs, torch.Tensor):
+            outputs, packed_outputs = split_non_tensors(outputs)
+            parent_ctx_dict["packed_non_tensor_outputs"] = packed_outputs
+        return outputs
+
+    @staticmethod
+    def backward(ctx: Any, *grads: Any) -> Tuple[Optional[Tensor], ...]:
+        if not torch.autograd._is_checkpoint_valid():
+            raise RuntimeError("Checkpointing is not compatible with .grad(), please use .backward() if possible")
+
+        saved: Tuple[Tensor, ...] = ctx.saved_tensors
+        if ctx.fwd_device is not None:
+            restored = []
+            for t, dev, ev, need in zip(saved, ctx.fwd_device, ctx.park_events, ctx.grad_requirements):
+                d = _HostParking.fetch(t, ev, dev).detach()
+                d.requires_grad = need
+                restored.append(d)
+            tensor_inputs: Tuple[Tensor, ...] = tuple(restored)
+        else:
+            tensor_inputs = torch_checkpoint.detach_variable(saved)
+        inputs = unpack_non_tensors(tensor_inputs, ctx.packed_non_tensor_inputs)
+
+        # replay under the forward's RNG state so dropout masks match, then put the current state back
+        rng_now = get_rng_state()
+        set_rng_state(ctx.fwd_rng_state)
+        amp = torch.autocast(**ctx.autocast) if ctx.autocast is not None else nullcontext()
+        with torch.enable_grad(), enable_recomputing(), amp:
+            f_args, f_kwargs = unpack_kwargs(ctx.kwarg_keys, inputs)
+            outputs = ctx.run_function(*f_args, **f_kwargs)
+            tensor_outputs, _ = split_non_tensors(outputs)
+        set_rng_state(rng_now)
+
+        live = [(o, g) for o, g in zip(tensor_outputs, grads) if o.requires_grad]
+        if not live:
+            raise RuntimeError("None of the outputs have requires_grad=True, this checkpoint() is not necessary")
+        torch.autograd.backward([o for o, _ in live], [g for _, g in live])
+
+        in_grads = tuple(x.grad if isinstance(x, torch.Tensor) else None for x in inputs)
+        return (None, None, None, None) + in_grads

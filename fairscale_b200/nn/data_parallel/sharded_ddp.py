@@ -21,7 +21,7 @@ import contextlib
 import logging
 from collections import deque
 from itertools import chain
-from typing import Any, Callable, Deque, Dict, Generator, List, Optional, Union
+from typing import TYPE_CHECKING, Any, Callable, Deque, Dict, Generator, List, Optional, Union
 
 import torch
 import torch.distributed as dist
@@ -29,9 +29,12 @@ from torch import nn
 from torch.autograd import Variable, profiler
 
 from ...internal.params import Workhandle, get_global_rank
-from ...optim.oss import OSS
 from ...parallel import comm
 from ..misc.param_bucket import GradBucket
+
+
+if TYPE_CHECKING:
+    from ...optim.oss import OSS
 
 
 def _trainable(p: torch.Tensor) -> bool:
@@ -102,7 +105,7 @@ class ShardedDataParallel(nn.Module):
     def __init__(
         self,
         module: nn.Module,
-        sharded_optimizer: Union[OSS, List[OSS]],
+        sharded_optimizer: Union["OSS", List["OSS"]],
         process_group: Any = None,
         broadcast_buffers: bool = True,
         sync_models_at_startup: bool = True,

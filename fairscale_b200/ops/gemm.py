@@ -1,0 +1,167 @@
+"""bf16 matrix products on the tcgen05 kernel (``csrc/gemm_tcgen05.cu``) and the autograd linear built on it.
+
+Storage convention: every operand is a row-major 2-D bf16 tensor.  ``gemm(a, b, trans_a, trans_b)``
+computes ``op(a) @ op(b)^T``-style products without materialising transposes by telling the kernel
+which operand dimension is contiguous:
+
+* ``linear_forward``  ``y[M,N] = x[M,K] @ w[N,K]^T``      (A K-major, B K-major)
+* ``linear_dgrad``    ``dx[M,K] = dy[M,N] @ w[N,K]``      (A K-major, B MN-major)
+* ``linear_wgrad``    ``dw[N,K] = dy[M,N]^T @ x[M,K]``    (A MN-major, B MN-major)
+
+On CPU tensors (unit tests without a GPU) the same functions run a PyTorch reference.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _bind
+
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_DGELU, EPI_RESIDUAL = range(6)
+
+
+def _as_2d(t: torch.Tensor) -> torch.Tensor:
+    t2 = t.reshape(-1, t.shape[-1])
+    return t2 if t2.is_contiguous() else t2.contiguous()
+
+
+def _launch(
+    a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool, epilogue: int = EPI_NONE,
+    bias: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
+    accumulate: bool = False, max_ctas: int = 0,
+) -> None:
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and c.stride(-1) == 1
+    ld_aux = 0
+    if aux is not None:
+        ld_aux = aux.stride(0)
+    elif aux_out is not None:
+        ld_aux = aux_out.stride(0)
+    _bind.call(
+        "fsb_gemm_bf16",
+        a.data_ptr(), b.data_ptr(), c.data_ptr(), _bind.ptr(bias), _bind.ptr(aux), _bind.ptr(aux_out),
+        M, N, K, a.stride(0), b.stride(0), c.stride(0), ld_aux, int(a_mn), int(b_mn), epilogue,
+        int(c.dtype == torch.float32), int(accumulate), max_ctas, _bind.status_ptr(a.device), _bind.stream_ptr(a.device),
+    )
+
+
+def linear_forward(
+    x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, gelu: bool = False,
+    residual: Optional[torch.Tensor] = None, save_pre_activation: bool = False, out_dtype: Optional[torch.dtype] = None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``y = act(x @ w^T + bias) (+ residual)``; returns ``(y, pre_activation or None)``.
+
+    ``x``: [..., K] bf16, ``w``: [N, K] bf16.  With ``gelu`` and ``save_pre_activation`` the kernel
+    also writes ``x @ w^T + bias`` (needed by the backward) in the same pass.
+    """
+    x2 = _as_2d(x)
+    M, K = x2.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or torch.bfloat16
+    if not _bind.use_native(x2, w):
+        pre = torch.nn.functional.linear(x2.float(), w.float(), None if bias is None else bias.float())
+        y = torch.nn.functional.gelu(pre) if gelu else pre
+        if residual is not None:
+            y = y + _as_2d(residual).float()
+        pre_out = pre.to(x.dtype) if (gelu and save_pre_activation) else None
+        return y.to(out_dtype if x.dtype == torch.bfloat16 else x.dtype).view(*x.shape[:-1], N), pre_out
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    pre_out = None
+    w = w if w.is_contiguous() else w.contiguous()
+    if gelu:
+        assert bias is not None and residual is None
+        if save_pre_activation:
+            pre_out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        _launch(x2, w, y, M, N, K, False, False, EPI_BIAS_GELU, bias=bias, aux_out=pre_out)
+    elif residual is not None:
+        r2 = _as_2d(residual)
+        _launch(x2, w, y, M, N, K, False, False, EPI_BIAS_RESIDUAL if bias is not None else EPI_RESIDUAL, bias=bias, aux=r2)
+    else:
+        _launch(x2, w, y, M, N, K, False, False, EPI_BIAS if bias is not None else EPI_NONE, bias=bias)
+    return y.view(*x.shape[:-1], N), pre_out
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, *, dgelu_pre: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``dx = dy @ w`` (optionally multiplied by ``gelu'(dgelu_pre)`` in the epilogue).  ``dy``: [M, N], ``w``: [N, K]."""
+    dy2 = _as_2d(dy)
+    M, N = dy2.shape
+    K = w.shape[1]
+    if not _bind.use_native(dy2, w):
+        dx = dy2.float() @ w.float()
+        if dgelu_pre is not None:
+            p = _as_2d(dgelu_pre).float()
+            cdf = 0.5 * (1 + torch.erf(p * 0.7071067811865476))
+            pdf = torch.exp(-0.5 * p * p) * 0.3989422804014327
+            dx = dx * (cdf + p * pdf)
+        return dx.to(dy.dtype)
+    dx = torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
+    w = w if w.is_contiguous() else w.contiguous()
+    # output dim of this product is K (rows of the MN-major operand w[N, K]); reduction runs over N
+    if dgelu_pre is not None:
+        _launch(dy2, w, dx, M, K, N, False, True, EPI_DGELU, aux=_as_2d(dgelu_pre))
+    else:
+        _launch(dy2, w, dx, M, K, N, False, True)
+    return dx
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """``dw[N, K] = dy[M, N]^T @ x[M, K]``.  ``out`` may be an fp32 buffer to accumulate into (``accumulate=True``)."""
+    dy2, x2 = _as_2d(dy), _as_2d(x)
+    M, N = dy2.shape
+    K = x2.shape[1]
+    if not _bind.use_native(dy2, x2):
+        dw = dy2.float().t() @ x2.float()
+        if out is not None:
+            out.copy_(out + dw if accumulate else dw)
+            return out
+        return dw.to(dy.dtype)
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.bfloat16, device=dy.device)
+    _launch(dy2, x2, out, N, K, M, True, True, accumulate=accumulate)
+    return out
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``a[M,K] @ b[N,K]^T`` for 2-D bf16 tensors."""
+    y, _ = linear_forward(a, b, None, out_dtype=out_dtype)
+    return y
+
+
+class _LinearFn(torch.autograd.Function):
+    """``y = x w^T + b`` with optional fused GELU or residual; backward uses the dgrad / wgrad products."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, gelu: bool, residual):  # type: ignore[override]
+        need_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, w, bias, residual))
+        y, pre = linear_forward(x, w, bias, gelu=gelu, residual=residual, save_pre_activation=gelu and need_grad)
+        ctx.gelu = gelu
+        ctx.has_bias = bias is not None
+        ctx.has_residual = residual is not None
+        ctx.save_for_backward(x, w, pre)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x, w, pre = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        d_res = dy if ctx.has_residual else None
+        if ctx.gelu:
+            from .activations import gelu_backward
+
+            dy2 = gelu_backward(dy2, pre)
+        dx = linear_dgrad(dy2, w).view_as(x) if ctx.needs_input_grad[0] else None
+        dw = linear_wgrad(dy2, x) if ctx.needs_input_grad[1] else None
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .reduce import column_sum
+
+            db = column_sum(dy2)
+        return dx, dw, db, None, d_res
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, gelu: bool = False,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Differentiable fused linear: ``gelu(x w^T + b)`` or ``x w^T + b + residual``."""
+    return _LinearFn.apply(x, w, bias, gelu, residual)
