@@ -151,12 +151,25 @@ def build_reference(args: argparse.Namespace, device: torch.device):
     torch.manual_seed(0)
     model = build_reference_fsdp_gpt(CFG["vocab"], CFG["d_model"], CFG["n_heads"], args.layers, CFG["ffn"], args.seq, device)
     # the reference's fused Adam accepts only fp32/fp16 parameters and is not built by its default install
-    opt = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, fused=True)
+    params = list(model.parameters())
+    world_is_one = dist.get_world_size() == 1
+    for p in params:
+        p.grad_dtype = None
+    opt = torch.optim.Adam(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, fused=True)
 
     def step(tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         logits = model(tokens)
         loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.view(-1))
         loss.backward()
+        if world_is_one:
+            # With a single rank the reference leaves compute-dtype (bf16) gradients on its fp32 master parameters
+            # (its cast happens in the reduce-scatter callback, which only runs for sharded parameters), and no torch
+            # optimizer accepts that; cast them as a user of the reference would have to.
+            for p in params:
+                if p.grad is not None and p.grad.dtype != p.dtype:
+                    g = p.grad.to(p.dtype)
+                    p.grad = None
+                    p.grad = g
         opt.step()
         opt.zero_grad(set_to_none=True)
         return loss
@@ -255,7 +268,7 @@ def main() -> None:
                 "seq_len": S,
                 "parallelism": f"fsdp{world} full-shard, bf16 compute / fp32 master, checkpoint per block, fused Adam",
                 "l2_policy": "per-step working set (>25 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2",
-                "final_loss": float(last_loss) if last_loss is not None else None,
+                "final_loss": float(last_loss.detach()) if last_loss is not None else None,
                 "peak_mem_gb": round(peak_gb, 2),
             },
             "clocks": clocks,

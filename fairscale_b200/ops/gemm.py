@@ -134,7 +134,7 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, bias, gelu: bool, residual):  # type: ignore[override]
-        need_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, w, bias, residual))
+        need_grad = any(ctx.needs_input_grad)  # all False under no_grad
         y, pre = linear_forward(x, w, bias, gelu=gelu, residual=residual, save_pre_activation=gelu and need_grad)
         ctx.gelu = gelu
         ctx.has_bias = bias is not None

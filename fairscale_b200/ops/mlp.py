@@ -18,9 +18,7 @@ from .reduce import column_sum
 class _MLPFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, residual):  # type: ignore[override]
-        need_grad = torch.is_grad_enabled() and any(
-            t is not None and t.requires_grad for t in (x, w1, b1, w2, b2, residual)
-        )
+        need_grad = any(ctx.needs_input_grad)  # all False under no_grad (e.g. the first pass of a checkpointed block)
         h, pre = linear_forward(x, w1, b1, gelu=True, save_pre_activation=need_grad)
         y, _ = linear_forward(h, w2, b2, residual=residual)
         ctx.has_residual = residual is not None

@@ -250,26 +250,49 @@ def test_fused_adam_mixed_precision_copy_and_noop():
     torch.testing.assert_close(p.detach(), before)
 
 
+def _torch_gpt_loss(sd, cfg, tokens, targets):
+    """Plain torch fp32 evaluation of the GPT defined by state dict ``sd`` (independent of this library's ops)."""
+    import torch.nn.functional as F
+
+    d, H = cfg.d_model, cfg.n_heads
+    B, S = tokens.shape
+    x = sd["embed.wte"][tokens] + sd["embed.wpe"][:S]
+    for i in range(cfg.n_layers):
+        g = lambda n: sd[f"blocks.{i}.{n}"]  # noqa: E731
+        h = F.layer_norm(x, (d,), g("ln1.weight"), g("ln1.bias"), cfg.ln_eps)
+        q, k, v = F.linear(h, g("qkv_w"), g("qkv_b")).view(B, S, 3, H, d // H).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, d)
+        x = x + F.linear(a, g("proj_w"), g("proj_b"))
+        h = F.layer_norm(x, (d,), g("ln2.weight"), g("ln2.bias"), cfg.ln_eps)
+        x = x + F.linear(F.gelu(F.linear(h, g("fc1_w"), g("fc1_b"))), g("fc2_w"), g("fc2_b"))
+    x = F.layer_norm(x, (d,), sd["head.ln_f.weight"], sd["head.ln_f.bias"], cfg.ln_eps)
+    logits = F.linear(x, sd["head.weight"])
+    return F.cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1))
+
+
 def test_gpt_forward_backward_matches_torch():
     """Whole tiny GPT through the native kernels vs. the same weights evaluated by plain fp32 torch ops."""
     from fairscale_b200.models.gpt import GPT, GPTConfig
 
     torch.manual_seed(9)
     cfg = GPTConfig.tiny(vocab=512, d_model=128, n_heads=2, n_layers=2, ffn=512, max_seq=128)
-    ref = GPT(cfg)  # CPU fp32: reference code paths
+    cfg.init_std = 0.08  # larger weights so that activation derivatives are far from constant
     dev = GPT(cfg).to(_dev()).bfloat16()
-    dev.load_state_dict({k: v.to(_dev()).bfloat16() for k, v in ref.state_dict().items()})
-    # keep reference weights equal to the bf16-rounded ones
-    ref.load_state_dict({k: v.float().cpu() for k, v in dev.state_dict().items()})
-    tok = torch.randint(0, cfg.vocab_size, (2, 129))
-    lr_ = ref(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
+    with torch.no_grad():
+        for n, p in dev.named_parameters():
+            if n.endswith("_b") or n.endswith("bias"):
+                p.normal_(0, 0.1)
+    ref_sd = {k: v.detach().float().clone().requires_grad_() for k, v in dev.state_dict().items()}
+    tok = torch.randint(0, cfg.vocab_size, (2, 129), device=_dev())
+    inp, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    lr_ = _torch_gpt_loss(ref_sd, cfg, inp, tgt)
     lr_.backward()
-    td = tok.to(_dev())
-    ld = dev(td[:, :-1].contiguous(), td[:, 1:].contiguous())
+    ld = dev(inp, tgt)
     ld.backward()
     assert abs(ld.item() - lr_.item()) < 3e-2, (ld.item(), lr_.item())
-    for (n, a), (_, b) in zip(dev.named_parameters(), ref.named_parameters()):
-        assert _rel_err(a.grad.cpu(), b.grad) < 8e-2, (n, _rel_err(a.grad.cpu(), b.grad))
+    for n, a in dev.named_parameters():
+        err = _rel_err(a.grad, ref_sd[n].grad)
+        assert err < 6e-2, (n, err)
     _status_ok()
 
 
