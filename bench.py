@@ -131,6 +131,7 @@ def build_ours(args: argparse.Namespace, device: torch.device):
     torch.manual_seed(0)
     model = build_fsdp_gpt(cfg, device)
     opt = FusedAdam(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8)
+    model.attach_optimizer(opt)  # the Adam kernel also writes the bf16 compute shards
 
     def step(tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         loss = model(tokens, targets)

@@ -22,6 +22,8 @@
 
 #include "sm100.cuh"
 
+#include <cstdlib>
+
 namespace fsb {
 
 constexpr int BLOCK_M = 128;
@@ -72,6 +74,96 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   const int r = tile - g * per_group;
   tm = first_m + r % rows;
   tn = r / rows;
+}
+
+// Drain one accumulator (this warp's 32 lanes x BLOCK_N columns starting at TMEM address t_base) through the
+// fused epilogue into global memory. `row` is the global output row owned by this thread.
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_rows(uint32_t t_base, int row, int n0, const GemmParams& p) {
+  const bool row_ok = row < p.M;
+  const bool vec_ok = (p.ldc % 8 == 0) && (p.ld_aux % 8 == 0);
+#pragma unroll 1
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 32), r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (!row_ok || col0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    const bool full = vec_ok && (col0 + 32 <= p.N);
+    const int epi = p.epilogue;
+    if (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESIDUAL) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+    }
+    if (epi == EPI_BIAS_GELU) {
+      if (p.aux_out != nullptr) {
+        __nv_bfloat16* po = p.aux_out + static_cast<size_t>(row) * p.ld_aux + col0;
+        if (full) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            Vec16<__nv_bfloat16> o;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
+            st16(po + q * 8, o);
+          }
+        } else {
+          for (int i = 0; i < 32 && col0 + i < p.N; ++i) po[i] = __float2bfloat16_rn(v[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+    } else if (epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU) {
+      const __nv_bfloat16* pa = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
+      float a[32];
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          Vec16<__nv_bfloat16> x = ld16(pa + q * 8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[q * 8 + i] = __bfloat162float(x.v[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) a[i] = (col0 + i < p.N) ? __bfloat162float(pa[i]) : 0.f;
+      }
+      if (epi == EPI_DGELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(a[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += a[i];
+      }
+    }
+    if (p.out_f32) {
+      float* pc = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+      if (p.accumulate_c) {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] += v[i];
+      } else if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(pc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = v[i];
+      }
+    } else {
+      __nv_bfloat16* pc = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          Vec16<__nv_bfloat16> o;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
+          st16(pc + q * 8, o);
+        }
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  }
 }
 
 template <int BLOCK_N>
@@ -202,90 +294,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
-      const bool row_ok = row < p.M;
-      const bool vec_ok = (p.ldc % 8 == 0) && (p.ld_aux % 8 == 0);
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 32), r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        const bool full = vec_ok && (col0 + 32 <= p.N);
-        const int epi = p.epilogue;
-        if (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESIDUAL) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
-        }
-        if (epi == EPI_BIAS_GELU) {
-          if (p.aux_out != nullptr) {
-            __nv_bfloat16* po = p.aux_out + static_cast<size_t>(row) * p.ld_aux + col0;
-            if (full) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                Vec16<__nv_bfloat16> o;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
-                st16(po + q * 8, o);
-              }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) po[i] = __float2bfloat16_rn(v[i]);
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
-        } else if (epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU) {
-          const __nv_bfloat16* pa = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
-          float a[32];
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              Vec16<__nv_bfloat16> x = ld16(pa + q * 8);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) a[q * 8 + i] = __bfloat162float(x.v[i]);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) a[i] = (col0 + i < p.N) ? __bfloat162float(pa[i]) : 0.f;
-          }
-          if (epi == EPI_DGELU) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(a[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += a[i];
-          }
-        }
-        if (p.out_f32) {
-          float* pc = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-          if (p.accumulate_c) {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] += v[i];
-          } else if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<float4*>(pc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-          } else {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = v[i];
-          }
-        } else {
-          __nv_bfloat16* pc = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              Vec16<__nv_bfloat16> o;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
-              st16(pc + q * 8, o);
-            }
-          } else {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = __float2bfloat16_rn(v[i]);
-          }
-        }
-      }
+      epilogue_rows<BLOCK_N>(t_base, row, n0, p);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
@@ -308,6 +317,189 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 2 * BLOCK_N);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (two SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2. Each CTA stages only its 128 rows of A and its 128 columns of B, so the
+// shared-memory traffic per MMA drops by a third and 6 stages fit. CTA 0 (the leader) issues the MMAs;
+// both CTAs load with their own per-CTA TMA (nothing is broadcast), and both drain their half of the
+// accumulator. Barriers: full[] lives in the leader and counts both CTAs' bytes; empty[] and tmem_full[]
+// exist in both CTAs and are signalled by two commits (local + peer); tmem_empty[] lives in the leader
+// and collects the 8 epilogue warps of the pair.
+// ------------------------------------------------------------------------------------------------
+constexpr int PAIR_BLOCK_N = 256;
+constexpr int PAIR_HALF_N = 128;
+constexpr int PAIR_STAGES = 6;
+
+struct PairSmem {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;      // 16 KB: this CTA's 128 rows
+  static constexpr int B_BYTES = PAIR_HALF_N * BLOCK_K * 2;  // 16 KB: this CTA's 128 columns
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  using L = PairSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + PAIR_STAGES;
+  uint64_t* tmem_full_bar = empty_bar + PAIR_STAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
+  const int tiles_n = (p.N + PAIR_BLOCK_N - 1) / PAIR_BLOCK_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 8);  // 4 epilogue warps in each CTA of the pair
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 2 * PAIR_BLOCK_N);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
+        const int n0 = tn * PAIR_BLOCK_N + static_cast<int>(rank) * PAIR_HALF_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * L::STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          const int k0 = kb * BLOCK_K;
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tmap_a, bar, m0 + j * 64, k0);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < PAIR_HALF_N / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tmap_b, bar, n0 + j * 64, k0);
+          }
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_f16(2 * BLOCK_M, PAIR_BLOCK_N, true, p.a_mn_major != 0, p.b_mn_major != 0);
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, b_lbo = p.b_mn_major ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u, b_kstep = p.b_mn_major ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024u);
+            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          umma_commit_pair(map_to_cta(eb, 0));
+          umma_commit_pair(map_to_cta(eb, 1));
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
+        umma_commit_pair(map_to_cta(fb, 0));
+        umma_commit_pair(map_to_cta(fb, 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int row = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M + quad * 32 + lane;
+      const int n0 = tn * PAIR_BLOCK_N;
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
+      epilogue_rows<PAIR_BLOCK_N>(t_base, row, n0, p);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, FSB_ERR_WAIT_TIMEOUT);
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();  // neither CTA leaves while its partner may still signal its barriers or read its smem
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 2 * PAIR_BLOCK_N);
   }
 }
 
@@ -357,6 +549,25 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
 
   cudaError_t err;
+  static int pair_mode = -1;  // FSB_GEMM_PAIR=0 disables the CTA-pair kernel
+  if (pair_mode < 0) {
+    const char* e = getenv("FSB_GEMM_PAIR");
+    pair_mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (pair_mode == 1 && M >= 256 && N >= 256 && max_ctas == 0) {
+    // the B map's box is this CTA's 128 columns (K-major) / 64 (MN-major, unchanged)
+    if (!b_mn_major && !fsb_host::encode_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, PAIR_HALF_N)) return -1;
+    static bool pair_attr_set[64] = {false};
+    if (!pair_attr_set[di]) {
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL);
+      pair_attr_set[di] = true;
+    }
+    const int pair_tiles = ((M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((N + PAIR_BLOCK_N - 1) / PAIR_BLOCK_N);
+    const int max_pairs = num_sms / 2;
+    const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+    gemm_bf16_tcgen05_pair_kernel<<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, stream>>>(ta, tb, p);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (block_n == 256) {
     if (!attr_set[di][0]) {
       cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);

@@ -12,7 +12,151 @@
 namespace fsb {
 
 constexpr int NORM_THREADS = 256;
-constexpr int NORM_MAX_VEC = 4;  // up to 4 x 8 bf16 per thread -> H <= 8192
+constexpr int NORM_MAX_VEC = 4;  // block-per-row path: up to 4 x 8 bf16 per thread -> H <= 8192
+constexpr int NORM_WARPS = 4;    // warp-per-row path: rows handled per CTA
+
+// ---- warp-per-row kernels (H <= 4096): a lane keeps VPL 16-byte vectors of the row in registers, all
+// reductions are warp shuffles, no shared memory and no block barriers.
+template <bool RMS, int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32) norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                                                                        const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                                                                        float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                        long long rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = H / 8;
+  const __nv_bfloat16* xr = x + row * H;
+  float v[VPL][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int it = 0; it < VPL; ++it) {
+    const int j = lane + it * 32;
+    if (j < nvec) {
+      const Vec16<__nv_bfloat16> t = ld16(xr + j * 8);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { v[it][k] = __bfloat162float(t.v[k]); sum += v[it][k]; }
+    }
+  }
+  const float mean = RMS ? 0.f : warp_sum(sum) / H;
+  float sq = 0.f;
+#pragma unroll
+  for (int it = 0; it < VPL; ++it) {
+    const int j = lane + it * 32;
+    if (j < nvec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { const float d = v[it][k] - mean; sq += d * d; }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / H + eps);
+  if (lane == 0) {
+    if (!RMS && mean_out != nullptr) mean_out[row] = mean;
+    if (rstd_out != nullptr) rstd_out[row] = rstd;
+  }
+  __nv_bfloat16* yr = y + row * H;
+#pragma unroll
+  for (int it = 0; it < VPL; ++it) {
+    const int j = lane + it * 32;
+    if (j < nvec) {
+      const Vec16<__nv_bfloat16> g = ld16(gamma + j * 8);
+      Vec16<__nv_bfloat16> o;
+      if (!RMS && beta != nullptr) {
+        const Vec16<__nv_bfloat16> b = ld16(beta + j * 8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          o.v[k] = __float2bfloat16_rn((v[it][k] - mean) * rstd * __bfloat162float(g.v[k]) + __bfloat162float(b.v[k]));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn((v[it][k] - mean) * rstd * __bfloat162float(g.v[k]));
+      }
+      st16(yr + j * 8, o);
+    }
+  }
+}
+
+// dx only (dgamma / dbeta come from norm_dparam_partial_kernel)
+template <bool RMS, int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32) norm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                           const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                                           const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                                                           long long rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = H / 8;
+  const float mean = RMS ? 0.f : mean_in[row];
+  const float rstd = rstd_in[row];
+  float xh[VPL][8], wdy[VPL][8];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int it = 0; it < VPL; ++it) {
+    const int j = lane + it * 32;
+    if (j < nvec) {
+      const Vec16<__nv_bfloat16> tx = ld16(x + row * H + j * 8);
+      const Vec16<__nv_bfloat16> td = ld16(dy + row * H + j * 8);
+      const Vec16<__nv_bfloat16> tg = ld16(gamma + j * 8);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        xh[it][k] = (__bfloat162float(tx.v[k]) - mean) * rstd;
+        wdy[it][k] = __bfloat162float(td.v[k]) * __bfloat162float(tg.v[k]);
+        s1 += wdy[it][k];
+        s2 += wdy[it][k] * xh[it][k];
+      }
+    }
+  }
+  s1 = RMS ? 0.f : warp_sum(s1) / H;
+  s2 = warp_sum(s2) / H;
+#pragma unroll
+  for (int it = 0; it < VPL; ++it) {
+    const int j = lane + it * 32;
+    if (j < nvec) {
+      Vec16<__nv_bfloat16> o;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(rstd * (wdy[it][k] - s1 - xh[it][k] * s2));
+      st16(dx + row * H + j * 8, o);
+    }
+  }
+}
+
+// Partial column sums of dy * xhat (-> dgamma) and dy (-> dbeta) over a strip of rows.
+// grid = (ceil(H / 256), strips), block = (32, 8): a thread owns 8 consecutive columns.
+template <bool RMS>
+__global__ void __launch_bounds__(256) norm_dparam_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                  const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                                                  float* __restrict__ dgamma_part, float* __restrict__ dbeta_part,
+                                                                  long long rows, int H) {
+  const int col0 = (blockIdx.x * 32 + threadIdx.x) * 8;
+  const bool active = col0 < H;
+  float dg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, db[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (long long r = blockIdx.y * 8 + threadIdx.y; active && r < rows; r += static_cast<long long>(gridDim.y) * 8) {
+    const float mean = RMS ? 0.f : mean_in[r];
+    const float rstd = rstd_in[r];
+    const Vec16<__nv_bfloat16> tx = ld16(x + r * H + col0);
+    const Vec16<__nv_bfloat16> td = ld16(dy + r * H + col0);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float d = __bfloat162float(td.v[k]);
+      dg[k] += d * (__bfloat162float(tx.v[k]) - mean) * rstd;
+      db[k] += d;
+    }
+  }
+  __shared__ float red[2][8][32][9];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { red[0][threadIdx.y][threadIdx.x][k] = dg[k]; red[1][threadIdx.y][threadIdx.x][k] = db[k]; }
+  __syncthreads();
+  if (threadIdx.y < 2 && active) {
+    const int which = threadIdx.y;
+    if (which == 1 && (RMS || dbeta_part == nullptr)) return;
+    float* out = (which == 0 ? dgamma_part : dbeta_part) + static_cast<long long>(blockIdx.y) * H + col0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float s = 0.f;
+#pragma unroll
+      for (int yy = 0; yy < 8; ++yy) s += red[which][yy][threadIdx.x][k];
+      out[k] = s;
+    }
+  }
+}
 
 template <bool RMS>
 __global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
@@ -71,73 +215,44 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const __nv_bfloa
   }
 }
 
-// dx for one row per CTA iteration; each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps
-// running dgamma/dbeta sums for its columns in registers, flushed to partials at the end.
+// Block-per-row dx (H > 4096).
 template <bool RMS>
-__global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                                                                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
-                                                                const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-                                                                float* __restrict__ dgamma_part, float* __restrict__ dbeta_part,
-                                                                long long rows, int H) {
+__global__ void __launch_bounds__(NORM_THREADS) norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                   const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                                   const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx, int H) {
   __shared__ float scratch[32];
   const int nvec = H / 8;
-  float dg[NORM_MAX_VEC][8], db[NORM_MAX_VEC][8], gam[NORM_MAX_VEC][8];
-#pragma unroll
-  for (int it = 0; it < NORM_MAX_VEC; ++it) {
-    const int j = threadIdx.x + it * NORM_THREADS;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { dg[it][k] = 0.f; db[it][k] = 0.f; gam[it][k] = 0.f; }
-    if (j < nvec) {
-      const Vec16<__nv_bfloat16> g = ld16(gamma + j * 8);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) gam[it][k] = __bfloat162float(g.v[k]);
-    }
-  }
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float mean = RMS ? 0.f : mean_in[row];
-    const float rstd = rstd_in[row];
-    float xh[NORM_MAX_VEC][8], wdy[NORM_MAX_VEC][8];
-    float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-    for (int it = 0; it < NORM_MAX_VEC; ++it) {
-      const int j = threadIdx.x + it * NORM_THREADS;
-      if (j < nvec) {
-        const Vec16<__nv_bfloat16> tx = ld16(x + row * H + j * 8);
-        const Vec16<__nv_bfloat16> td = ld16(dy + row * H + j * 8);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float d = __bfloat162float(td.v[k]);
-          xh[it][k] = (__bfloat162float(tx.v[k]) - mean) * rstd;
-          wdy[it][k] = d * gam[it][k];
-          s1 += wdy[it][k];
-          s2 += wdy[it][k] * xh[it][k];
-          dg[it][k] += d * xh[it][k];
-          db[it][k] += d;
-        }
-      }
-    }
-    if (!RMS) s1 = block_sum(s1, scratch) / H; else s1 = 0.f;
-    s2 = block_sum(s2, scratch) / H;
-#pragma unroll
-    for (int it = 0; it < NORM_MAX_VEC; ++it) {
-      const int j = threadIdx.x + it * NORM_THREADS;
-      if (j < nvec) {
-        Vec16<__nv_bfloat16> o;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(rstd * (wdy[it][k] - s1 - xh[it][k] * s2));
-        st16(dx + row * H + j * 8, o);
-      }
-    }
-  }
+  const long long row = blockIdx.x;
+  const float mean = RMS ? 0.f : mean_in[row];
+  const float rstd = rstd_in[row];
+  float xh[NORM_MAX_VEC][8], wdy[NORM_MAX_VEC][8];
+  float s1 = 0.f, s2 = 0.f;
 #pragma unroll
   for (int it = 0; it < NORM_MAX_VEC; ++it) {
     const int j = threadIdx.x + it * NORM_THREADS;
     if (j < nvec) {
+      const Vec16<__nv_bfloat16> tx = ld16(x + row * H + j * 8);
+      const Vec16<__nv_bfloat16> td = ld16(dy + row * H + j * 8);
+      const Vec16<__nv_bfloat16> tg = ld16(gamma + j * 8);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        dgamma_part[static_cast<long long>(blockIdx.x) * H + j * 8 + k] = dg[it][k];
-        if (!RMS && dbeta_part != nullptr) dbeta_part[static_cast<long long>(blockIdx.x) * H + j * 8 + k] = db[it][k];
+        xh[it][k] = (__bfloat162float(tx.v[k]) - mean) * rstd;
+        wdy[it][k] = __bfloat162float(td.v[k]) * __bfloat162float(tg.v[k]);
+        s1 += wdy[it][k];
+        s2 += wdy[it][k] * xh[it][k];
       }
+    }
+  }
+  if (!RMS) s1 = block_sum(s1, scratch) / H; else s1 = 0.f;
+  s2 = block_sum(s2, scratch) / H;
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_VEC; ++it) {
+    const int j = threadIdx.x + it * NORM_THREADS;
+    if (j < nvec) {
+      Vec16<__nv_bfloat16> o;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(rstd * (wdy[it][k] - s1 - xh[it][k] * s2));
+      st16(dx + row * H + j * 8, o);
     }
   }
 }
@@ -182,6 +297,31 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
 
 // H must be a multiple of 8 and <= 8192. mean/rstd are fp32 [rows]. rms != 0 selects RMSNorm
 // (beta and mean ignored).
+template <bool RMS>
+static void launch_norm_fwd(const __nv_bfloat16* x, const __nv_bfloat16* g, const __nv_bfloat16* b, __nv_bfloat16* y, float* mean,
+                            float* rstd, long long rows, int H, float eps, cudaStream_t stream) {
+  using namespace fsb;
+  const unsigned grid = static_cast<unsigned>((rows + NORM_WARPS - 1) / NORM_WARPS);
+  const int vpl = (H / 8 + 31) / 32;
+  if (vpl <= 2)       norm_fwd_warp_kernel<RMS, 2><<<grid, NORM_WARPS * 32, 0, stream>>>(x, g, b, y, mean, rstd, rows, H, eps);
+  else if (vpl <= 4)  norm_fwd_warp_kernel<RMS, 4><<<grid, NORM_WARPS * 32, 0, stream>>>(x, g, b, y, mean, rstd, rows, H, eps);
+  else if (vpl <= 8)  norm_fwd_warp_kernel<RMS, 8><<<grid, NORM_WARPS * 32, 0, stream>>>(x, g, b, y, mean, rstd, rows, H, eps);
+  else if (vpl <= 16) norm_fwd_warp_kernel<RMS, 16><<<grid, NORM_WARPS * 32, 0, stream>>>(x, g, b, y, mean, rstd, rows, H, eps);
+  else norm_fwd_kernel<RMS><<<static_cast<unsigned>(rows), NORM_THREADS, 0, stream>>>(x, g, b, y, mean, rstd, H, eps);
+}
+
+template <bool RMS>
+static void launch_norm_bwd_dx(const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* g, const float* mean,
+                               const float* rstd, __nv_bfloat16* dx, long long rows, int H, cudaStream_t stream) {
+  using namespace fsb;
+  const unsigned grid = static_cast<unsigned>((rows + NORM_WARPS - 1) / NORM_WARPS);
+  const int vpl = (H / 8 + 31) / 32;
+  if (vpl <= 2)       norm_bwd_dx_warp_kernel<RMS, 2><<<grid, NORM_WARPS * 32, 0, stream>>>(dy, x, g, mean, rstd, dx, rows, H);
+  else if (vpl <= 4)  norm_bwd_dx_warp_kernel<RMS, 4><<<grid, NORM_WARPS * 32, 0, stream>>>(dy, x, g, mean, rstd, dx, rows, H);
+  else if (vpl <= 8)  norm_bwd_dx_warp_kernel<RMS, 8><<<grid, NORM_WARPS * 32, 0, stream>>>(dy, x, g, mean, rstd, dx, rows, H);
+  else norm_bwd_dx_kernel<RMS><<<static_cast<unsigned>(rows), NORM_THREADS, 0, stream>>>(dy, x, g, mean, rstd, dx, H);
+}
+
 FSB_API int fsb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
                          long long rows, int H, float eps, int rms, cudaStream_t stream) {
   using namespace fsb;
@@ -191,14 +331,14 @@ FSB_API int fsb_norm_fwd(const void* x, const void* gamma, const void* beta, voi
   auto* gg = static_cast<const __nv_bfloat16*>(gamma);
   auto* bb = static_cast<const __nv_bfloat16*>(beta);
   auto* yy = static_cast<__nv_bfloat16*>(y);
-  if (rms) norm_fwd_kernel<true><<<static_cast<unsigned>(rows), NORM_THREADS, 0, stream>>>(xx, gg, bb, yy, mean, rstd, H, eps);
-  else     norm_fwd_kernel<false><<<static_cast<unsigned>(rows), NORM_THREADS, 0, stream>>>(xx, gg, bb, yy, mean, rstd, H, eps);
+  if (rms) launch_norm_fwd<true>(xx, gg, bb, yy, mean, rstd, rows, H, eps, stream);
+  else     launch_norm_fwd<false>(xx, gg, bb, yy, mean, rstd, rows, H, eps, stream);
   return static_cast<int>(cudaGetLastError());
 }
 
 FSB_API int fsb_norm_bwd_num_strips(long long rows) {
-  const long long cap = 148 * 4;
-  return static_cast<int>(rows < cap ? rows : cap);
+  const long long want = (rows + 7) / 8;
+  return static_cast<int>(want < 1 ? 1 : (want > 48 ? 48 : want));
 }
 
 // partials: fp32 workspace of 2 * n_strips * H floats (n_strips from fsb_norm_bwd_num_strips).
@@ -215,18 +355,24 @@ FSB_API int fsb_norm_bwd(const void* dy, const void* x, const void* gamma, const
   auto* xx = static_cast<const __nv_bfloat16*>(x);
   auto* gg = static_cast<const __nv_bfloat16*>(gamma);
   auto* o = static_cast<__nv_bfloat16*>(dx);
-  if (rms) norm_bwd_kernel<true><<<strips, NORM_THREADS, 0, stream>>>(d, xx, gg, mean, rstd, o, pg, nullptr, rows, H);
-  else     norm_bwd_kernel<false><<<strips, NORM_THREADS, 0, stream>>>(d, xx, gg, mean, rstd, o, pg, pb, rows, H);
-  const int threads = 256, blocks = (H + threads - 1) / threads;
+  const bool want_beta = !rms && dbeta != nullptr;
+  dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
+  if (rms) {
+    launch_norm_bwd_dx<true>(d, xx, gg, mean, rstd, o, rows, H, stream);
+    norm_dparam_partial_kernel<true><<<grid, block, 0, stream>>>(d, xx, mean, rstd, pg, nullptr, rows, H);
+  } else {
+    launch_norm_bwd_dx<false>(d, xx, gg, mean, rstd, o, rows, H, stream);
+    norm_dparam_partial_kernel<false><<<grid, block, 0, stream>>>(d, xx, mean, rstd, pg, want_beta ? pb : nullptr, rows, H);
+  }
+  const int threads = 128, blocks = (H + threads - 1) / threads;
   column_reduce_kernel<<<blocks, threads, 0, stream>>>(pg, strips, H, static_cast<__nv_bfloat16*>(dgamma), nullptr);
-  if (!rms && dbeta != nullptr)
-    column_reduce_kernel<<<blocks, threads, 0, stream>>>(pb, strips, H, static_cast<__nv_bfloat16*>(dbeta), nullptr);
+  if (want_beta) column_reduce_kernel<<<blocks, threads, 0, stream>>>(pb, strips, H, static_cast<__nv_bfloat16*>(dbeta), nullptr);
   return static_cast<int>(cudaGetLastError());
 }
 
 FSB_API int fsb_colsum_num_strips(long long rows) {
   const long long want = (rows + 63) / 64;
-  return static_cast<int>(want < 1 ? 1 : (want > 256 ? 256 : want));
+  return static_cast<int>(want < 1 ? 1 : (want > 48 ? 48 : want));
 }
 
 // out[c] = sum_r x[r, c]; x bf16 [rows, H] (H % 8 == 0); partials fp32 [n_strips, H]; out bf16 [H].
@@ -237,7 +383,7 @@ FSB_API int fsb_colsum(const void* x, long long rows, int H, float* partials, vo
   const int strips = fsb_colsum_num_strips(rows);
   dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
   colsum_partial_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, H, partials);
-  const int threads = 256, blocks = (H + threads - 1) / threads;
+  const int threads = 128, blocks = (H + threads - 1) / threads;
   column_reduce_kernel<<<blocks, threads, 0, stream>>>(partials, strips, H, static_cast<__nv_bfloat16*>(out), nullptr);
   return static_cast<int>(cudaGetLastError());
 }

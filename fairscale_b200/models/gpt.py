@@ -138,7 +138,7 @@ def build_fsdp_gpt(cfg: GPTConfig, device: torch.device, process_group: Any = No
     from ..nn.data_parallel import FullyShardedDataParallel as FSDP
 
     kw = dict(process_group=process_group, mixed_precision=True, compute_dtype=compute_dtype, reshard_after_forward=True,
-              flatten_parameters=True, compute_device=device)
+              flatten_parameters=True, compute_device=device, keep_low_precision_grads=True, persistent_compute_shards=True)
     kw.update(fsdp_kwargs)
 
     def wrap_block(m: nn.Module) -> nn.Module:

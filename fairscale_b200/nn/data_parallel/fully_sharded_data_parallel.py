@@ -68,6 +68,7 @@ from ...internal.parallel import (
 from ...internal.params import calc_grad_norm, get_global_rank, recursive_copy_to_device
 from ...internal.reduce_scatter_bucketer import ReduceScatterBucketer
 from ...internal.state_dict import replace_by_prefix_
+from ...ops.cast import cast_into
 from ...parallel import comm
 from ..misc import flatten_params_wrapper as _fpw
 from ..misc.flatten_params_wrapper import FlattenParamsWrapper
@@ -209,6 +210,12 @@ class FullyShardedDataParallel(nn.Module):
             ``world/this`` after (default: smallest power of two ≥ sqrt(world)).
         allow_reset_parameters: permit ``reset_parameters`` on the wrapper.
         prefetch: overlap the next unit's all-gather with the current unit's forward.
+        keep_low_precision_grads: leave ``p.grad`` in ``compute_dtype`` (no cast to the master dtype after
+            the reduction); pair with an optimizer that accepts mixed gradient / parameter dtypes.
+        persistent_compute_shards: keep the ``compute_dtype`` copy of every shard resident (2 bytes per
+            local parameter) instead of re-casting the master shard before each all-gather.  With
+            :meth:`attach_optimizer` a fused optimizer refreshes that copy in its own update pass, so the
+            cast disappears entirely.
     """
 
     def __init__(
@@ -237,6 +244,8 @@ class FullyShardedDataParallel(nn.Module):
         gradient_predivide_factor: Optional[float] = None,
         allow_reset_parameters: bool = False,
         prefetch: bool = True,
+        keep_low_precision_grads: bool = False,
+        persistent_compute_shards: bool = False,
     ):
         t0 = time.time()
         super().__init__()
@@ -281,6 +290,8 @@ class FullyShardedDataParallel(nn.Module):
         self.gradient_postdivide_factor: float = self.world_size / self.gradient_predivide_factor
         self.allow_reset_parameters = allow_reset_parameters
         self.prefetch = prefetch
+        self.keep_low_precision_grads = keep_low_precision_grads and mixed_precision
+        self.persistent_compute_shards = persistent_compute_shards and mixed_precision and not self.move_params_to_cpu
         self.numel_padded_per_param: List[int] = []
         self._tstart = time.time()
 
@@ -622,6 +633,8 @@ class FullyShardedDataParallel(nn.Module):
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         self._lazy_init()
+        for p in self.params:
+            p._fp16_shard_current = False  # type: ignore[attr-defined]
         return self.module.load_state_dict(state_dict, strict)
 
     def load_state_dict(self, state_dict: Any, strict: bool = True) -> NamedTuple:  # type: ignore[override]
@@ -730,6 +743,7 @@ class FullyShardedDataParallel(nn.Module):
                     if not volatile:
                         shard, _ = self._get_shard(full)
                         p._fp32_shard.copy_(shard.view_as(p._fp32_shard))  # type: ignore[attr-defined]
+                        p._fp16_shard_current = False  # type: ignore[attr-defined]
                     if can_free:
                         free_storage_(full)
                 self.has_full_params = False
@@ -789,12 +803,25 @@ class FullyShardedDataParallel(nn.Module):
                 p._fp32_shard = p._fp32_shard.pin_memory()  # type: ignore[attr-defined]
             p.data = p._fp32_shard  # type: ignore[attr-defined]
         if self.move_params_to_cpu or self.mixed_precision:
-            p._fp16_shard = torch.zeros_like(  # type: ignore[attr-defined]
-                p._fp32_shard, device=self.compute_device, dtype=self.compute_dtype  # type: ignore[attr-defined]
+            old = getattr(p, "_fp16_shard", None)
+            reuse = (
+                self.persistent_compute_shards and old is not None and old.dtype == self.compute_dtype
+                and old.numel() == p._fp32_shard.numel() and old.device == self.compute_device  # type: ignore[attr-defined]
             )
-            free_storage_(p._fp16_shard)  # type: ignore[attr-defined]
+            if not reuse:
+                p._fp16_shard = torch.zeros_like(  # type: ignore[attr-defined]
+                    p._fp32_shard, device=self.compute_device, dtype=self.compute_dtype  # type: ignore[attr-defined]
+                )
+                p._fp16_shard_current = False  # type: ignore[attr-defined]
+                if not self.persistent_compute_shards:
+                    free_storage_(p._fp16_shard)  # type: ignore[attr-defined]
         else:
             p._fp16_shard = None  # type: ignore[attr-defined]
+        if self.keep_low_precision_grads:
+            try:
+                p.grad_dtype = None  # type: ignore[attr-defined]  # gradients stay in the compute dtype
+            except Exception:
+                pass
         if p._is_sharded:  # type: ignore[attr-defined]
             p._full_param_padded = torch.zeros(  # type: ignore[attr-defined]
                 p.data.numel() * self.world_size, device=self.compute_device, dtype=self.compute_dtype
@@ -1041,7 +1068,9 @@ class FullyShardedDataParallel(nn.Module):
             else:
                 assert self.world_size == 1
                 grad = param.grad.data
-                if grad.dtype != param.dtype or getattr(param, "_saved_grad_shard", None) is not None:
+                if (grad.dtype != param.dtype and not self.keep_low_precision_grads) or getattr(
+                    param, "_saved_grad_shard", None
+                ) is not None:
                     param.grad = None
                     self._post_reduction_hook(param, grad)
                 else:
@@ -1058,9 +1087,9 @@ class FullyShardedDataParallel(nn.Module):
             if self.move_grads_to_cpu:
                 param._cpu_grad.copy_(reduced_grad, non_blocking=True)  # type: ignore[attr-defined]
             return
-        if reduced_grad.dtype != param.dtype:
+        if reduced_grad.dtype != param.dtype and not self.keep_low_precision_grads:
             low = reduced_grad
-            reduced_grad = reduced_grad.to(dtype=param.dtype)
+            reduced_grad = cast_into(torch.empty_like(low, dtype=param.dtype), low)
             _record_stream(low, self._streams["post_backward"])
         reduced_grad = reduced_grad.view_as(param._fp32_shard) if reduced_grad.numel() == param._fp32_shard.numel() else reduced_grad  # type: ignore[attr-defined]
         saved = getattr(param, "_saved_grad_shard", None)
@@ -1373,18 +1402,60 @@ class FullyShardedDataParallel(nn.Module):
         with _on_stream(cast_stream):
             for p in self.params if params is None else params:
                 assert p._fp16_shard is not None  # type: ignore[attr-defined]
-                alloc_storage_(p._fp16_shard, size=p._fp32_shard.size())  # type: ignore[attr-defined]
-                p._fp16_shard.copy_(p._fp32_shard, non_blocking=True)  # type: ignore[attr-defined]
+                fresh = self.persistent_compute_shards and getattr(p, "_fp16_shard_current", False)
+                if not fresh:
+                    alloc_storage_(p._fp16_shard, size=p._fp32_shard.size())  # type: ignore[attr-defined]
+                    cast_into(p._fp16_shard, p._fp32_shard)  # type: ignore[attr-defined]
+                    p._fp16_shard_current = self.persistent_compute_shards  # type: ignore[attr-defined]
                 p.data = p._fp16_shard  # type: ignore[attr-defined]
         _current_stream(self.compute_device).wait_stream(cast_stream)
 
     @torch.no_grad()
     def _free_fp16_param_shard(self, params: Optional[List[Parameter]] = None) -> None:
+        if self.persistent_compute_shards:
+            return
         cur = _current_stream(self.compute_device)
         for p in self.params if params is None else params:
             if p._fp16_shard is not None:  # type: ignore[attr-defined]
                 _record_stream(p._fp16_shard, cur)  # type: ignore[attr-defined]
                 free_storage_(p._fp16_shard)  # type: ignore[attr-defined]
+
+    def invalidate_compute_shards(self) -> None:
+        """Call after modifying master shards by hand (``persistent_compute_shards`` only): the resident
+        compute-dtype copies are re-derived from the master shards at the next forward."""
+        for m in get_fsdp_instances(self):
+            for p in m.params:
+                p._fp16_shard_current = False  # type: ignore[attr-defined]
+
+    def attach_optimizer(self, optim: torch.optim.Optimizer) -> None:
+        """Let a fused optimizer refresh the resident compute-dtype shards in its update pass.
+
+        Requires ``persistent_compute_shards`` and an optimizer exposing ``param_copies`` (this library's
+        :class:`~fairscale_b200.optim.Adam`): after every ``optim.step()`` the compute shards are current and
+        the master->compute cast before the next all-gather is skipped.
+        """
+        self._lazy_init()
+        copies = getattr(optim, "param_copies", None)
+        if copies is None:
+            raise TypeError("optimizer has no `param_copies`; use fairscale_b200.optim.Adam")
+        tracked = []
+        for m in get_fsdp_instances(self):
+            for p in m.params:
+                m._init_param_attributes(p)
+            if not m.persistent_compute_shards:
+                continue
+            for p in m.params:
+                if p._fp16_shard is None or not p.requires_grad:  # type: ignore[attr-defined]
+                    continue
+                copies[p] = p._fp16_shard  # type: ignore[attr-defined]
+                tracked.append(p)
+
+        def mark_current(*_: Any) -> None:
+            for p in tracked:
+                if p.grad is not None:
+                    p._fp16_shard_current = True  # type: ignore[attr-defined]
+
+        optim.register_step_post_hook(mark_current)
 
     def assert_state(self, state: Union[TrainingState, List[TrainingState]]) -> None:
         if isinstance(state, TrainingState):

@@ -89,6 +89,22 @@ class FlatParameter(nn.Parameter):
             raise ValueError(f"Incorrect numel of supplied data: got {src.numel()} but expected {total}")
         return (piece.view(shape) for piece, shape in zip(src.split(self._param_numels), self._param_shapes))
 
+    def get_param_views_for_forward(self) -> Iterator[Tensor]:
+        """Views for the wrapped module's forward.  When a gradient will be needed they come from
+        :class:`_FlatViews` and carry their :class:`GradArena` window, so weight gradients can be written
+        straight into the flat gradient."""
+        if not (self.requires_grad and torch.is_grad_enabled()) or self.data.numel() != self.full_numel:
+            return self.get_param_views()
+        arena = getattr(self, "_grad_arena", None)
+        if arena is None or arena.total != self.full_numel:
+            arena = self._grad_arena = GradArena(self.full_numel)
+        views = _FlatViews.apply(self, self._param_numels, self._param_shapes, arena)
+        off = 0
+        for v, n, shp in zip(views, self._param_numels, self._param_shapes):
+            v._fsb_grad_slot = (arena, off, shp)
+            off += n
+        return iter(views)
+
     def metadata(self) -> Tuple[List[str], List[torch.Size], List[int]]:
         """``(names, shapes, numels)`` of the original parameters, names relative to the wrapped module."""
         names = [f"{path}.{attr}" if path else attr for path, _, attr in self._param_infos]
@@ -107,6 +123,79 @@ class FlatParameter(nn.Parameter):
             ([self.data], self.requires_grad),
             (self._param_numels, self._param_shapes, self._param_infos, self._shared_param_infos),
         )
+
+
+class GradArena:
+    """Per-flat-parameter landing zone for weight gradients.
+
+    Views handed to the wrapped module carry ``_fsb_grad_slot = (arena, offset, shape)``.  A kernel that
+    produces the gradient of such a view (e.g. the wgrad GEMM) asks :meth:`slot` for the matching window of
+    one flat buffer and writes there directly; when autograd later assembles the flat parameter's gradient,
+    windows that were filled in place need no copy, which removes the ``torch.cat`` of all per-parameter
+    gradients (one full read+write of the gradient per unit per step).
+    """
+
+    def __init__(self, total: int):
+        self.total = total
+        self.buffer: Optional[Tensor] = None
+        self.claimed: Set[int] = set()
+
+    def slot(self, offset: int, shape: torch.Size, dtype: torch.dtype, device: torch.device) -> Optional[Tensor]:
+        """Window for the gradient of the view at ``offset`` — at most once per backward (a second use of the
+        same weight must go through autograd's own accumulation)."""
+        if offset in self.claimed:
+            return None
+        if self.buffer is None:
+            self.buffer = torch.empty(self.total, dtype=dtype, device=device)
+        elif self.buffer.dtype != dtype or self.buffer.device != device:
+            return None
+        self.claimed.add(offset)
+        return self.buffer[offset : offset + shape.numel()].view(shape)
+
+    def take(self, dtype: torch.dtype, device: torch.device) -> Tensor:
+        buf = self.buffer
+        if buf is None or buf.dtype != dtype or buf.device != device:
+            buf = torch.empty(self.total, dtype=dtype, device=device)
+        self.buffer = None
+        self.claimed = set()
+        return buf
+
+
+def grad_slot_for(weight: Tensor) -> Optional[Tensor]:
+    """The in-place gradient window of ``weight`` if it is a view handed out by a flat parameter, else None."""
+    info = getattr(weight, "_fsb_grad_slot", None)
+    if info is None:
+        return None
+    arena, offset, shape = info
+    return arena.slot(offset, shape, weight.dtype, weight.device)
+
+
+class _FlatViews(torch.autograd.Function):
+    """flat parameter -> per-parameter views; backward gathers the views' gradients into one flat buffer,
+    skipping those already written in place through the :class:`GradArena`."""
+
+    @staticmethod
+    def forward(ctx: Any, flat: Tensor, numels: List[int], shapes: List[torch.Size], arena: GradArena):  # type: ignore[override]
+        ctx.numels, ctx.shapes, ctx.arena = numels, shapes, arena
+        ctx.flat_meta = (flat.dtype, flat.device)
+        return tuple(t.view(s) for t, s in zip(flat.split(numels), shapes))
+
+    @staticmethod
+    def backward(ctx: Any, *grads: Any):  # type: ignore[override]
+        dtype, device = ctx.flat_meta
+        claimed = set(ctx.arena.claimed)
+        buf = ctx.arena.take(dtype, device)
+        off = 0
+        for g, n in zip(grads, ctx.numels):
+            window = buf[off : off + n]
+            if g is None:
+                window.zero_()
+            elif off in claimed and g.data_ptr() == window.data_ptr() and g.dtype == dtype:
+                pass  # produced in place
+            else:
+                window.copy_(g.reshape(-1))
+            off += n
+        return buf, None, None, None
 
 
 ParamGroups = Optional[Union[List[List[nn.Parameter]], List[nn.Parameter]]]
@@ -258,7 +347,8 @@ class FlattenParamsWrapper(nn.Module):
         """(Re)point the original attribute names at views of the current flat data."""
         assert self.is_flattened
         views: List[Tensor] = []
-        for (_, mod, attr), v in zip(self._param_infos, self.get_param_views()):
+        fwd_views = chain.from_iterable(p.get_param_views_for_forward() for p in self.flat_params)  # type: ignore[attr-defined]
+        for (_, mod, attr), v in zip(self._param_infos, fwd_views):
             setattr(mod, attr, v)  # plain attribute: the view is not an nn.Parameter
             views.append(v)
         # checkpoint_wrapper consults this to decide whether outputs need grad

@@ -123,6 +123,22 @@ def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tenso
     return out
 
 
+def grad_slot_info(weight: torch.Tensor):
+    """Forward-time capture of a weight's flat-gradient window descriptor (None for ordinary tensors)."""
+    return getattr(weight, "_fsb_grad_slot", None)
+
+
+def wgrad_into_slot(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, slot_info=None) -> torch.Tensor:
+    """``dw`` for ``weight``; written straight into the flat-gradient window of ``weight`` when it has one."""
+    slot = None
+    info = slot_info if slot_info is not None else getattr(weight, "_fsb_grad_slot", None)
+    if info is not None and dy.is_cuda and weight.dtype == torch.bfloat16:
+        arena, offset, shape = info
+        if (offset * 2) % 16 == 0:
+            slot = arena.slot(offset, shape, weight.dtype, weight.device)
+    return linear_wgrad(dy, x, out=slot)
+
+
 def matmul_nt(a: torch.Tensor, b: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``a[M,K] @ b[N,K]^T`` for 2-D bf16 tensors."""
     y, _ = linear_forward(a, b, None, out_dtype=out_dtype)
@@ -139,6 +155,7 @@ class _LinearFn(torch.autograd.Function):
         ctx.gelu = gelu
         ctx.has_bias = bias is not None
         ctx.has_residual = residual is not None
+        ctx.w_slot = grad_slot_info(w)
         ctx.save_for_backward(x, w, pre)
         return y
 
@@ -152,7 +169,7 @@ class _LinearFn(torch.autograd.Function):
 
             dy2 = gelu_backward(dy2, pre)
         dx = linear_dgrad(dy2, w).view_as(x) if ctx.needs_input_grad[0] else None
-        dw = linear_wgrad(dy2, x) if ctx.needs_input_grad[1] else None
+        dw = wgrad_into_slot(dy2, x, w, ctx.w_slot) if ctx.needs_input_grad[1] else None
         db = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             from .reduce import column_sum

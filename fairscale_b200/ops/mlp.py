@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from .gemm import linear_dgrad, linear_forward, linear_wgrad
+from .gemm import grad_slot_info, linear_dgrad, linear_forward, wgrad_into_slot
 from .reduce import column_sum
 
 
@@ -22,6 +22,7 @@ class _MLPFn(torch.autograd.Function):
         h, pre = linear_forward(x, w1, b1, gelu=True, save_pre_activation=need_grad)
         y, _ = linear_forward(h, w2, b2, residual=residual)
         ctx.has_residual = residual is not None
+        ctx.slots = (grad_slot_info(w1), grad_slot_info(w2))
         ctx.save_for_backward(x, w1, w2, pre, h)
         return y
 
@@ -30,10 +31,10 @@ class _MLPFn(torch.autograd.Function):
         x, w1, w2, pre, h = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         d_pre = linear_dgrad(dy2, w2, dgelu_pre=pre)          # [M, ffn], already multiplied by gelu'(pre)
-        dw2 = linear_wgrad(dy2, h)
+        dw2 = wgrad_into_slot(dy2, h, w2, ctx.slots[1])
         db2 = column_sum(dy2)
         dx = linear_dgrad(d_pre, w1).view_as(x)
-        dw1 = linear_wgrad(d_pre, x)
+        dw1 = wgrad_into_slot(d_pre, x, w1, ctx.slots[0])
         db1 = column_sum(d_pre)
         return dx, dw1, db1, dw2, db2, (dy if ctx.has_residual else None)
 

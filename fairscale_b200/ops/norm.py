@@ -63,7 +63,7 @@ def norm_backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, mean:
     db = torch.empty(H, dtype=torch.bfloat16, device=x.device) if (has_bias and not rms) else None
     _bind.call("fsb_norm_bwd", dy2.data_ptr(), x2.data_ptr(), weight.data_ptr(), _bind.ptr(mean), rstd.data_ptr(), dx.data_ptr(),
                dw.data_ptr(), _bind.ptr(db), partials.data_ptr(), rows, H, int(rms), _bind.stream_ptr(x.device),
-               launches=3 if db is not None else 2)
+               launches=4 if db is not None else 3)
     return dx.view_as(x), dw, db
 
 
