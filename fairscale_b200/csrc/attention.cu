@@ -1,0 +1,772 @@
+// Causal flash attention (forward + backward) on tcgen05 / TMEM for packed QKV.
+//
+//   qkv : bf16 [B, S, 3, H, D]   (the output of the fused QKV projection, untouched)
+//   o   : bf16 [B, S, H, D]      lse : fp32 [B, H, S]   (natural-log sum-exp of the scaled scores)
+//
+// All tiles are fetched straight from the packed tensor with per-CTA TMA loads (no permute / contiguous /
+// cat glue kernels) and every product runs on the tensor cores with fp32 accumulators in TMEM:
+//
+//   forward (one CTA per 128 query rows)       S = Q K^T -> online softmax -> O += P V
+//   backward dQ (one CTA per 128 query rows)   S = Q K^T, dP = dO V^T -> dS -> dQ += dS K
+//   backward dK/dV (one CTA per 128 key rows)  S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T -> dV += P^T dO, dK += dS^T Q
+//
+// Thread roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM allocation), warps 2..5
+// "softmax" threads that own one accumulator row each (TMEM lane == row), do the exponentials in registers and
+// hand the bf16 probabilities back to the tensor cores through 128-byte-swizzled shared memory.
+// A K-major tile [rows, 64] and an MN-major tile of the same bytes differ only in the MMA descriptor, so each
+// streamed tile is loaded once and used both as a "transposed" and a "plain" operand.
+// Every mbarrier wait is bounded (see sm100.cuh).
+//
+// Replaces nn.MultiheadAttention / bmm+softmax in the reference's models
+// (benchmarks/models/transformer_lm.py:107,150-152,169-183).
+
+#include "sm100.cuh"
+
+namespace fsb {
+
+constexpr int ATT_THREADS = 192;
+constexpr int ATT_BM = 128;  // rows owned by a CTA (TMEM lanes)
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+struct AttnParams {
+  int B, S, H, D;
+  float scale;        // softmax scale (1/sqrt(D))
+  __nv_bfloat16* o;   // fwd out / bwd in   [B*S, H*D]
+  float* lse;         // [B, H, S]
+  const float* delta; // [B, H, S]  rowsum(dO * O)
+  __nv_bfloat16* dqkv;  // [B*S, 3*H*D]
+  int* status;
+};
+
+// byte offset of (row, 16-byte chunk) inside a 128-byte-swizzled [rows x 64 bf16] slab
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// K-major operand descriptor for k-step `ks` (16 elements) of a tile made of [rows x 64] slabs of `slab_bytes`
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int ks, uint32_t slab_bytes) {
+  return make_smem_desc(base + static_cast<uint32_t>(ks >> 2) * slab_bytes + static_cast<uint32_t>(ks & 3) * 32u, 16u, 1024u);
+}
+// MN-major operand descriptor: the tile is [k_rows x 64] slabs (one per 64 MN elements, `slab_bytes` apart);
+// k-step `ks` covers 16 k_rows = 2048 bytes.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int ks, uint32_t slab_bytes) {
+  return make_smem_desc(base + static_cast<uint32_t>(ks) * 2048u, slab_bytes, 1024u);
+}
+
+struct AttnBars {
+  uint64_t stat_full;     // stationary tiles landed
+  uint64_t str_full[2];   // streamed stage landed (first operand)
+  uint64_t str2_full[2];  // streamed stage landed (second operand)
+  uint64_t str_empty[2];  // streamed stage free again
+  uint64_t s_full[2];     // score accumulator(s) ready in TMEM
+  uint64_t s_empty[2];    // score accumulator(s) drained by the softmax threads
+  uint64_t p_full;        // probabilities / dS written to shared memory
+  uint64_t acc_done;      // accumulate-type MMAs of the iteration finished (P buffer + accumulators free)
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void attn_init_bars(AttnBars* b) {
+  mbar_init(&b->stat_full, 1);
+  for (int i = 0; i < 2; ++i) {
+    mbar_init(&b->str_full[i], 1);
+    mbar_init(&b->str2_full[i], 1);
+    mbar_init(&b->str_empty[i], 1);
+    mbar_init(&b->s_full[i], 1);
+    mbar_init(&b->s_empty[i], 4);
+  }
+  mbar_init(&b->p_full, 4);
+  mbar_init(&b->acc_done, 1);
+  b->abort_flag = 0;
+  fence_barrier_init();
+}
+
+__device__ __forceinline__ void attn_teardown(AttnBars* bars, int warp, uint32_t tmem_base, uint32_t ncols, int* status) {
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->abort_flag) {
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, FSB_ERR_WAIT_TIMEOUT);
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, ncols);
+  }
+}
+
+// =================================================================================================
+// Forward
+// =================================================================================================
+template <int D>
+struct FwdSmem {
+  static constexpr int TILE = ATT_BM * D * 2;  // one [128 x D] bf16 tile
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = TILE;           // 2 stages
+  static constexpr int V_OFF = 3 * TILE;       // 2 stages
+  static constexpr int P_OFF = 5 * TILE;       // [128 x 128] bf16
+  static constexpr int BAR_OFF = P_OFF + ATT_BM * 128 * 2;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
+  using L = FwdSmem<D>;
+  constexpr int SLABS = D / 64;
+  constexpr uint32_t SLAB = ATT_BM * 128;  // bytes of a [128 x 64] slab
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  AttnBars* bars = reinterpret_cast<AttnBars*>(smem + L::BAR_OFF);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = p.S / ATT_BM;
+  const int qt = n_qt - 1 - blockIdx.x;  // heavy (long) rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_kv = qt + 1;
+  const int HD = p.H * D;
+  const int row0 = b * p.S + qt * ATT_BM;
+  constexpr uint32_t TMEM_COLS = 512;  // S0 [0,128) S1 [128,256) O [256, 256+D)
+
+  if (threadIdx.x == 0) {
+    attn_init_bars(bars);
+    tma_prefetch_desc(&tm_qkv);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->stat_full, L::TILE);
+#pragma unroll
+      for (int c = 0; c < SLABS; ++c) tma_load_2d(smem + L::Q_OFF + c * SLAB, &tm_qkv, &bars->stat_full, h * D + c * 64, row0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&bars->str_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        const int krow = b * p.S + j * ATT_BM;
+        mbar_expect_tx(&bars->str_full[st], L::TILE);
+#pragma unroll
+        for (int c = 0; c < SLABS; ++c)
+          tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], HD + h * D + c * 64, krow);
+        mbar_expect_tx(&bars->str2_full[st], L::TILE);
+#pragma unroll
+        for (int c = 0; c < SLABS; ++c)
+          tma_load_2d(smem + L::V_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str2_full[st], 2 * HD + h * D + c * 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(ATT_BM, 128, true, false, false);  // Q K^T : both K-major
+      const uint32_t idesc_o = make_idesc_f16(ATT_BM, D, true, false, true);     // P V   : V is MN-major
+      const uint32_t sq = smem_u32(smem + L::Q_OFF), sp = smem_u32(smem + L::P_OFF);
+      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars->s_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base + st * 128, desc_kmajor(sq, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
+        umma_commit(&bars->s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) { if (!issue_s(j + 1)) { ok = false; break; } }
+        const int st = j & 1;
+        if (!mbar_wait(&bars->p_full, j & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&bars->str2_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < 128 / 16; ++ks)
+          umma_f16_ss(tmem_base + 256, desc_kmajor(sp, ks, SLAB), desc_mnmajor(sv, ks, SLAB), idesc_o, (j | ks) != 0);
+        umma_commit(&bars->str_empty[st]);
+        umma_commit(&bars->acc_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;  // row inside the tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    float m_run = -INFINITY, l_run = 0.f;
+    uint8_t* sp = smem + L::P_OFF;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int st = j & 1;
+      if (!mbar_wait(&bars->s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t ts = tmem_base + st * 128 + lane_off;
+      const bool diag = (j == qt);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(ts + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float v = __uint_as_float(r[i]);
+          if (!diag || (c * 32 + i) <= row) mx = fmaxf(mx, v);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * sl2);
+      const float mb = m_new * sl2;
+      // pass 2: probabilities (packed bf16 in registers)
+      uint32_t pk[64];
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(ts + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(r[i]) * sl2 - mb);
+          float p1 = exp2f(__uint_as_float(r[i + 1]) * sl2 - mb);
+          if (diag) {
+            if (c * 32 + i > row) p0 = 0.f;
+            if (c * 32 + i + 1 > row) p1 = 0.f;
+          }
+          rs += p0 + p1;
+          pk[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[st]);
+      // O and the P buffer belong to the previous P V product until it has completed
+      if (j > 0) {
+        if (!mbar_wait(&bars->acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + 256 + lane_off + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { lo[i] = r[i]; hi[i] = r[16 + i]; }
+            tmem_st_32x16(tmem_base + 256 + lane_off + c * 32, lo);
+            tmem_st_32x16(tmem_base + 256 + lane_off + c * 32 + 16, hi);
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {  // 16 chunks of 8 bf16 = this row of P
+        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(sp + (ch >> 3) * SLAB + swz(row, ch & 7)) = v;
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full);
+      l_run = l_run * alpha + rs;
+      m_run = m_new;
+    }
+    if (ok && mbar_wait(&bars->acc_done, (n_kv - 1) & 1, abort_flag)) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* orow = p.o + static_cast<size_t>(row0 + row) * HD + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + 256 + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv);
+          v.y = pack_bf16(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv);
+          v.z = pack_bf16(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv);
+          v.w = pack_bf16(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
+        }
+      }
+      if (p.lse != nullptr)
+        p.lse[(static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row] = (m_run * sl2 + log2f(l_run)) * LN2;
+    }
+  }
+  attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
+}
+
+// =================================================================================================
+// Backward, dQ: one CTA per 128 query rows; streams K and V tiles.
+// =================================================================================================
+template <int D>
+struct DqSmem {
+  static constexpr int TILE = ATT_BM * D * 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int DO_OFF = TILE;
+  static constexpr int K_OFF = 2 * TILE;   // 2 stages
+  static constexpr int V_OFF = 4 * TILE;   // 2 stages
+  static constexpr int DS_OFF = 6 * TILE;  // [128 x 128] bf16
+  static constexpr int BAR_OFF = DS_OFF + ATT_BM * 128 * 2;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, AttnParams p) {
+  using L = DqSmem<D>;
+  constexpr int SLABS = D / 64;
+  constexpr uint32_t SLAB = ATT_BM * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  AttnBars* bars = reinterpret_cast<AttnBars*>(smem + L::BAR_OFF);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = p.S / ATT_BM;
+  const int qt = n_qt - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_kv = qt + 1;
+  const int HD = p.H * D;
+  const int row0 = b * p.S + qt * ATT_BM;
+  constexpr uint32_t TMEM_COLS = 512;  // S [0,128) dP [128,256) dQ [256, 256+D)
+
+  if (threadIdx.x == 0) {
+    attn_init_bars(bars);
+    tma_prefetch_desc(&tm_qkv);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->stat_full, 2 * L::TILE);
+#pragma unroll
+      for (int c = 0; c < SLABS; ++c) {
+        tma_load_2d(smem + L::Q_OFF + c * SLAB, &tm_qkv, &bars->stat_full, h * D + c * 64, row0);
+        tma_load_2d(smem + L::DO_OFF + c * SLAB, &tm_do, &bars->stat_full, h * D + c * 64, row0);
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&bars->str_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        const int krow = b * p.S + j * ATT_BM;
+        mbar_expect_tx(&bars->str_full[st], 2 * L::TILE);
+#pragma unroll
+        for (int c = 0; c < SLABS; ++c) {
+          tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], HD + h * D + c * 64, krow);
+          tma_load_2d(smem + L::V_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], 2 * HD + h * D + c * 64, krow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(ATT_BM, 128, true, false, false);
+      const uint32_t idesc_q = make_idesc_f16(ATT_BM, D, true, false, true);  // dS K : K tile read MN-major
+      const uint32_t sq = smem_u32(smem + L::Q_OFF), sdo = smem_u32(smem + L::DO_OFF), sds = smem_u32(smem + L::DS_OFF);
+      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&bars->s_empty[0], (j & 1) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
+        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base, desc_kmajor(sq, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base + 128, desc_kmajor(sdo, ks, SLAB), desc_kmajor(sv, ks, SLAB), idesc_s, ks != 0);
+        umma_commit(&bars->s_full[0]);
+        if (!mbar_wait(&bars->p_full, j & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 128 / 16; ++ks)
+          umma_f16_ss(tmem_base + 256, desc_kmajor(sds, ks, SLAB), desc_mnmajor(sk, ks, SLAB), idesc_q, (j | ks) != 0);
+        umma_commit(&bars->str_empty[st]);
+        umma_commit(&bars->acc_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    const size_t stat_idx = (static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row;
+    const float lse2 = p.lse[stat_idx] * LOG2E;
+    const float delta = p.delta[stat_idx];
+    uint8_t* sds = smem + L::DS_OFF;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (!mbar_wait(&bars->s_full[0], j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const bool diag = (j == qt);
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_base + lane_off + c * 32, rs);
+        tmem_ld_32x32(tmem_base + 128 + lane_off + c * 32, rp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
+          if (diag) {
+            if (c * 32 + i > row) p0 = 0.f;
+            if (c * 32 + i + 1 > row) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(rp[i]) - delta) * p.scale;
+          const float d1 = p1 * (__uint_as_float(rp[i + 1]) - delta) * p.scale;
+          pk[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[0]);
+      if (j > 0) {
+        if (!mbar_wait(&bars->acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(sds + (ch >> 3) * SLAB + swz(row, ch & 7)) = v;
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full);
+    }
+    if (ok && mbar_wait(&bars->acc_done, (n_kv - 1) & 1, abort_flag)) {
+      tc_fence_after_sync();
+      __nv_bfloat16* drow = p.dqkv + static_cast<size_t>(row0 + row) * (3 * HD) + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + 256 + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+          v.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+          v.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+          v.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+          *reinterpret_cast<uint4*>(drow + c * 32 + q * 8) = v;
+        }
+      }
+    }
+  }
+  attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
+}
+
+// =================================================================================================
+// Backward, dK / dV: one CTA per 128 key rows; streams 64-row Q / dO sub-tiles.
+// =================================================================================================
+constexpr int KV_QSUB = 64;
+
+template <int D>
+struct DkvSmem {
+  static constexpr int TILE = ATT_BM * D * 2;     // K or V tile
+  static constexpr int QTILE = KV_QSUB * D * 2;   // Q or dO sub-tile
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = TILE;
+  static constexpr int Q_OFF = 2 * TILE;                 // 2 stages
+  static constexpr int DO_OFF = 2 * TILE + 2 * QTILE;    // 2 stages
+  static constexpr int PT_OFF = 2 * TILE + 4 * QTILE;    // [128 keys x 64 q] bf16
+  static constexpr int DST_OFF = PT_OFF + ATT_BM * KV_QSUB * 2;
+  static constexpr int BAR_OFF = DST_OFF + ATT_BM * KV_QSUB * 2;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
+                    const __grid_constant__ CUtensorMap tm_do, AttnParams p) {
+  using L = DkvSmem<D>;
+  constexpr int SLABS = D / 64;
+  constexpr uint32_t SLAB = ATT_BM * 128;    // [128 x 64] slab of K / V / P^T / dS^T
+  constexpr uint32_t QSLAB = KV_QSUB * 128;  // [64 x 64] slab of Q / dO
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  AttnBars* bars = reinterpret_cast<AttnBars*>(smem + L::BAR_OFF);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;  // key tile; small kt = many query sub-tiles = heavy, scheduled first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int HD = p.H * D;
+  const int krow0 = b * p.S + kt * ATT_BM;
+  const int first_sub = kt * (ATT_BM / KV_QSUB);
+  const int n_sub = p.S / KV_QSUB - first_sub;
+  constexpr uint32_t TMEM_COLS = 512;  // S^T [0,64) dP^T [64,128) dV [128,128+D) dK [256,256+D)
+
+  if (threadIdx.x == 0) {
+    attn_init_bars(bars);
+    tma_prefetch_desc(&tm_kv);
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->stat_full, 2 * L::TILE);
+#pragma unroll
+      for (int c = 0; c < SLABS; ++c) {
+        tma_load_2d(smem + L::K_OFF + c * SLAB, &tm_kv, &bars->stat_full, HD + h * D + c * 64, krow0);
+        tma_load_2d(smem + L::V_OFF + c * SLAB, &tm_kv, &bars->stat_full, 2 * HD + h * D + c * 64, krow0);
+      }
+      for (int t = 0; t < n_sub; ++t) {
+        const int st = t & 1;
+        if (!mbar_wait(&bars->str_empty[st], ((t >> 1) & 1) ^ 1u, abort_flag)) break;
+        const int qrow = b * p.S + (first_sub + t) * KV_QSUB;
+        mbar_expect_tx(&bars->str_full[st], 2 * L::QTILE);
+#pragma unroll
+        for (int c = 0; c < SLABS; ++c) {
+          tma_load_2d(smem + L::Q_OFF + st * L::QTILE + c * QSLAB, &tm_q, &bars->str_full[st], h * D + c * 64, qrow);
+          tma_load_2d(smem + L::DO_OFF + st * L::QTILE + c * QSLAB, &tm_do, &bars->str_full[st], h * D + c * 64, qrow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(ATT_BM, KV_QSUB, true, false, false);  // K Q^T, V dO^T
+      const uint32_t idesc_a = make_idesc_f16(ATT_BM, D, true, false, true);         // P^T dO, dS^T Q (B MN-major)
+      const uint32_t sk = smem_u32(smem + L::K_OFF), sv = smem_u32(smem + L::V_OFF);
+      const uint32_t spt = smem_u32(smem + L::PT_OFF), sdst = smem_u32(smem + L::DST_OFF);
+      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
+      for (int t = 0; t < n_sub && ok; ++t) {
+        const int st = t & 1;
+        if (!mbar_wait(&bars->str_full[st], (t >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&bars->s_empty[0], (t & 1) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sq = smem_u32(smem + L::Q_OFF + st * L::QTILE);
+        const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base, desc_kmajor(sk, ks, SLAB), desc_kmajor(sq, ks, QSLAB), idesc_s, ks != 0);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base + 64, desc_kmajor(sv, ks, SLAB), desc_kmajor(sdo, ks, QSLAB), idesc_s, ks != 0);
+        umma_commit(&bars->s_full[0]);
+        if (!mbar_wait(&bars->p_full, t & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < KV_QSUB / 16; ++ks)
+          umma_f16_ss(tmem_base + 128, desc_kmajor(spt, ks, SLAB), desc_mnmajor(sdo, ks, QSLAB), idesc_a, (t | ks) != 0);
+#pragma unroll
+        for (int ks = 0; ks < KV_QSUB / 16; ++ks)
+          umma_f16_ss(tmem_base + 256, desc_kmajor(sdst, ks, SLAB), desc_mnmajor(sq, ks, QSLAB), idesc_a, (t | ks) != 0);
+        umma_commit(&bars->str_empty[st]);
+        umma_commit(&bars->acc_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;  // key row inside the tile
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    const float* lse_bh = p.lse + (static_cast<size_t>(b) * p.H + h) * p.S;
+    const float* delta_bh = p.delta + (static_cast<size_t>(b) * p.H + h) * p.S;
+    uint8_t* spt = smem + L::PT_OFF;
+    uint8_t* sdst = smem + L::DST_OFF;
+    bool ok = true;
+    for (int t = 0; t < n_sub && ok; ++t) {
+      if (!mbar_wait(&bars->s_full[0], t & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int q0 = (first_sub + t) * KV_QSUB;       // first query row of the sub-tile (sequence index)
+      const int key = kt * ATT_BM + row;              // this thread's key (sequence index)
+      const bool diag = q0 < (kt + 1) * ATT_BM;       // sub-tile overlaps the diagonal block
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_base + lane_off + c * 32, rs);
+        tmem_ld_32x32(tmem_base + 64 + lane_off + c * 32, rp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int qa = q0 + c * 32 + i;
+          const float l0 = __ldg(lse_bh + qa) * LOG2E, l1 = __ldg(lse_bh + qa + 1) * LOG2E;
+          const float e0 = __ldg(delta_bh + qa), e1 = __ldg(delta_bh + qa + 1);
+          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - l0);
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - l1);
+          if (diag) {
+            if (key > qa) p0 = 0.f;
+            if (key > qa + 1) p1 = 0.f;
+          }
+          pp[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+          pd[c * 16 + (i >> 1)] = pack_bf16(p0 * (__uint_as_float(rp[i]) - e0) * p.scale,
+                                            p1 * (__uint_as_float(rp[i + 1]) - e1) * p.scale);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[0]);
+      if (t > 0) {
+        if (!mbar_wait(&bars->acc_done, (t - 1) & 1, abort_flag)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {  // 64 query columns = 8 chunks of 8 bf16
+        *reinterpret_cast<uint4*>(spt + swz(row, ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(sdst + swz(row, ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full);
+    }
+    if (ok && mbar_wait(&bars->acc_done, (n_sub - 1) & 1, abort_flag)) {
+      tc_fence_after_sync();
+      __nv_bfloat16* base = p.dqkv + static_cast<size_t>(krow0 + row) * (3 * HD) + h * D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {  // 0: dK (TMEM cols 256..), 1: dV (cols 128..)
+        const uint32_t tcol = which == 0 ? 256u : 128u;
+        __nv_bfloat16* drow = base + (which == 0 ? HD : 2 * HD);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + tcol + lane_off + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+            *reinterpret_cast<uint4*>(drow + c * 32 + q * 8) = v;
+          }
+        }
+      }
+    }
+  }
+  attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
+}
+
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                  int B, int S, int H, int D) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * H;
+  if (w >= total) return;
+  const long long tok = w / H;
+  const int h = static_cast<int>(w - tok * H);
+  const __nv_bfloat16* po = o + (tok * H + h) * D;
+  const __nv_bfloat16* pd = d_o + (tok * H + h) * D;
+  float acc = 0.f;
+  for (int j = lane * 8; j < D; j += 32 * 8) {
+    const Vec16<__nv_bfloat16> a = ld16(po + j), c = ld16(pd + j);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += __bfloat162float(a.v[k]) * __bfloat162float(c.v[k]);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const long long bb = tok / S, s = tok - bb * S;
+    delta[(bb * H + h) * S + s] = acc;
+  }
+}
+
+}  // namespace fsb
+
+// ------------------------------------------------------------------------------------------------
+// C ABI.  S must be a multiple of 128, D in {64, 128}; all tensors contiguous, 16-byte aligned.
+// ------------------------------------------------------------------------------------------------
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  return static_cast<int>(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+// Each CTA allocates all 512 TMEM columns, so two CTAs must never share an SM: ask for more than half of the
+// SM's shared memory even when the tiles need less (D = 64).
+static constexpr int kMinSmem = 120 * 1024;
+static inline int one_cta_smem(int bytes) { return bytes < kMinSmem ? kMinSmem : bytes; }
+
+FSB_API int fsb_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int H, int D, float scale, int* status,
+                         cudaStream_t stream) {
+  using namespace fsb;
+  if (S % ATT_BM != 0 || (D != 64 && D != 128)) return -1;
+  CUtensorMap tm;
+  if (!fsb_host::encode_2d_16bit(&tm, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, ATT_BM)) return -1;
+  AttnParams p{};
+  p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
+  p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = status;
+  dim3 grid(S / ATT_BM, H, B);
+  if (D == 128) {
+    set_smem(attn_fwd_kernel<128>, FwdSmem<128>::TOTAL);
+    attn_fwd_kernel<128><<<grid, ATT_THREADS, FwdSmem<128>::TOTAL, stream>>>(tm, p);
+  } else {
+    set_smem(attn_fwd_kernel<64>, one_cta_smem(FwdSmem<64>::TOTAL));
+    attn_fwd_kernel<64><<<grid, ATT_THREADS, one_cta_smem(FwdSmem<64>::TOTAL), stream>>>(tm, p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dqkv receives dQ, dK and dV in the packed layout of qkv.  delta: fp32 workspace [B, H, S].
+FSB_API int fsb_attn_bwd(const void* qkv, const void* o, const void* d_o, const float* lse, float* delta, void* dqkv, int B, int S,
+                         int H, int D, float scale, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (S % ATT_BM != 0 || (D != 64 && D != 128)) return -1;
+  CUtensorMap tm_qkv128, tm_do128, tm_qkv64, tm_do64;
+  bool ok = true;
+  ok &= fsb_host::encode_2d_16bit(&tm_qkv128, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, ATT_BM);
+  ok &= fsb_host::encode_2d_16bit(&tm_do128, d_o, (uint64_t)H * D, (uint64_t)B * S, (uint64_t)H * D, 64, ATT_BM);
+  ok &= fsb_host::encode_2d_16bit(&tm_qkv64, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, KV_QSUB);
+  ok &= fsb_host::encode_2d_16bit(&tm_do64, d_o, (uint64_t)H * D, (uint64_t)B * S, (uint64_t)H * D, 64, KV_QSUB);
+  if (!ok) return -1;
+  AttnParams p{};
+  p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
+  p.o = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(o));
+  p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = static_cast<__nv_bfloat16*>(dqkv); p.status = status;
+  {
+    const long long warps = static_cast<long long>(B) * S * H;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
+                                                                             static_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, D);
+  }
+  dim3 grid(S / ATT_BM, H, B);
+  if (D == 128) {
+    set_smem(attn_bwd_dq_kernel<128>, DqSmem<128>::TOTAL);
+    set_smem(attn_bwd_dkv_kernel<128>, DkvSmem<128>::TOTAL);
+    attn_bwd_dkv_kernel<128><<<grid, ATT_THREADS, DkvSmem<128>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
+    attn_bwd_dq_kernel<128><<<grid, ATT_THREADS, DqSmem<128>::TOTAL, stream>>>(tm_qkv128, tm_do128, p);
+  } else {
+    set_smem(attn_bwd_dq_kernel<64>, one_cta_smem(DqSmem<64>::TOTAL));
+    set_smem(attn_bwd_dkv_kernel<64>, one_cta_smem(DkvSmem<64>::TOTAL));
+    attn_bwd_dkv_kernel<64><<<grid, ATT_THREADS, one_cta_smem(DkvSmem<64>::TOTAL), stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
+    attn_bwd_dq_kernel<64><<<grid, ATT_THREADS, one_cta_smem(DqSmem<64>::TOTAL), stream>>>(tm_qkv128, tm_do128, p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}

@@ -301,3 +301,27 @@ def test_smoke_entry():
     import __graft_entry__ as g
 
     g.smoke()
+
+
+@pytest.mark.parametrize("B,S,H,D", [(1, 128, 1, 128), (2, 384, 3, 128), (2, 256, 4, 64), (1, 1024, 2, 128)])
+def test_flash_attention_fwd_bwd(B, S, H, D):
+    from fairscale_b200.ops import attention
+    from fairscale_b200.ops.attention import causal_attention
+
+    torch.manual_seed(11)
+    qkv = (torch.randn(B, S, 3 * H * D, device=_dev()) * 0.7).bfloat16().requires_grad_()
+    o = causal_attention(qkv, H)
+    assert attention.BACKEND == "tcgen05"
+    go = torch.randn_like(o)
+    o.backward(go)
+    _status_ok()
+    ref_in = qkv.detach().float().requires_grad_()
+    q, k, v = ref_in.view(B, S, 3, H, D).permute(2, 0, 3, 1, 4)
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(D)
+    s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device=_dev()).triu(1), float("-inf"))
+    oref = (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, H * D)
+    oref.backward(go.float())
+    assert _rel_err(o, oref) < 2e-2, _rel_err(o, oref)
+    g, gr = qkv.grad.view(B, S, 3, H, D), ref_in.grad.view(B, S, 3, H, D)
+    for i, name in enumerate("qkv"):
+        assert _rel_err(g[:, :, i], gr[:, :, i]) < 3e-2, (name, _rel_err(g[:, :, i], gr[:, :, i]))
