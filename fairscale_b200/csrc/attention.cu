@@ -713,6 +713,8 @@ static int set_smem(K kernel, int bytes) {
 static constexpr int kMinSmem = 120 * 1024;
 static inline int one_cta_smem(int bytes) { return bytes < kMinSmem ? kMinSmem : bytes; }
 
+FSB_API int fsb_last_tensor_map_result() { return fsb_host::last_encode_result(); }
+
 FSB_API int fsb_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int H, int D, float scale, int* status,
                          cudaStream_t stream) {
   using namespace fsb;
@@ -739,12 +741,10 @@ FSB_API int fsb_attn_bwd(const void* qkv, const void* o, const void* d_o, const 
   using namespace fsb;
   if (S % ATT_BM != 0 || (D != 64 && D != 128)) return -1;
   CUtensorMap tm_qkv128, tm_do128, tm_qkv64, tm_do64;
-  bool ok = true;
-  ok &= fsb_host::encode_2d_16bit(&tm_qkv128, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, ATT_BM);
-  ok &= fsb_host::encode_2d_16bit(&tm_do128, d_o, (uint64_t)H * D, (uint64_t)B * S, (uint64_t)H * D, 64, ATT_BM);
-  ok &= fsb_host::encode_2d_16bit(&tm_qkv64, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, KV_QSUB);
-  ok &= fsb_host::encode_2d_16bit(&tm_do64, d_o, (uint64_t)H * D, (uint64_t)B * S, (uint64_t)H * D, 64, KV_QSUB);
-  if (!ok) return -1;
+  if (!fsb_host::encode_2d_16bit(&tm_qkv128, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, ATT_BM)) return -2;
+  if (!fsb_host::encode_2d_16bit(&tm_do128, d_o, (uint64_t)H * D, (uint64_t)B * S, (uint64_t)H * D, 64, ATT_BM)) return -3;
+  if (!fsb_host::encode_2d_16bit(&tm_qkv64, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, KV_QSUB)) return -4;
+  if (!fsb_host::encode_2d_16bit(&tm_do64, d_o, (uint64_t)H * D, (uint64_t)B * S, (uint64_t)H * D, 64, KV_QSUB)) return -5;
   AttnParams p{};
   p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
   p.o = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(o));

@@ -264,7 +264,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+inline int& last_encode_result() {
+  static int r = 0;
+  return r;
+}
+
 inline EncodeTiledFn encode_tiled_fn() {
+  // The driver entry point needs a current context in the calling thread; autograd worker threads may not
+  // have touched the runtime yet, so bind the primary context once per thread.
+  thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (fn == nullptr) {
     void* p = nullptr;
@@ -290,6 +302,7 @@ inline bool encode_2d_16bit(CUtensorMap* map, const void* base, uint64_t inner, 
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  last_encode_result() = static_cast<int>(r);
   return r == CUDA_SUCCESS;
 }
 
