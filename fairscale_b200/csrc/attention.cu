@@ -214,34 +214,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
       tc_fence_after_sync();
       const uint32_t ts = tmem_base + st * 128 + lane_off;
       const bool diag = (j == qt);
-      // pass 1: row maximum
+      // the whole score row in registers: four TMEM loads in flight, one wait
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, sr[c]);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[i]);
+          const float v = __uint_as_float(sr[c][i]);
           if (!diag || (c * 32 + i) <= row) mx = fmaxf(mx, v);
         }
       }
       const float m_new = fmaxf(m_run, mx);
       const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * sl2);
       const float mb = m_new * sl2;
-      // pass 2: probabilities (packed bf16 in registers)
       uint32_t pk[64];
       float rs = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(r[i]) * sl2 - mb);
-          float p1 = exp2f(__uint_as_float(r[i + 1]) * sl2 - mb);
+          float p0 = exp2f(__uint_as_float(sr[c][i]) * sl2 - mb);
+          float p1 = exp2f(__uint_as_float(sr[c][i + 1]) * sl2 - mb);
           if (diag) {
             if (c * 32 + i > row) p0 = 0.f;
             if (c * 32 + i + 1 > row) p1 = 0.f;
@@ -426,22 +423,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
       const bool diag = (j == qt);
       uint32_t pk[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + lane_off + c * 32, rs);
-        tmem_ld_32x32(tmem_base + 128 + lane_off + c * 32, rp);
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t rs[2][32], rp[2][32];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          tmem_ld_32x32(tmem_base + lane_off + (cc * 2 + u) * 32, rs[u]);
+          tmem_ld_32x32(tmem_base + 128 + lane_off + (cc * 2 + u) * 32, rp[u]);
+        }
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
-          if (diag) {
-            if (c * 32 + i > row) p0 = 0.f;
-            if (c * 32 + i + 1 > row) p1 = 0.f;
+        for (int u = 0; u < 2; ++u) {
+          const int c = cc * 2 + u;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = exp2f(__uint_as_float(rs[u][i]) * sl2 - lse2);
+            float p1 = exp2f(__uint_as_float(rs[u][i + 1]) * sl2 - lse2);
+            if (diag) {
+              if (c * 32 + i > row) p0 = 0.f;
+              if (c * 32 + i + 1 > row) p1 = 0.f;
+            }
+            const float d0 = p0 * (__uint_as_float(rp[u][i]) - delta) * p.scale;
+            const float d1 = p1 * (__uint_as_float(rp[u][i + 1]) - delta) * p.scale;
+            pk[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
           }
-          const float d0 = p0 * (__uint_as_float(rp[i]) - delta) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rp[i + 1]) - delta) * p.scale;
-          pk[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
         }
       }
       tc_fence_before_sync();
@@ -609,26 +613,31 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
       const int key = kt * ATT_BM + row;              // this thread's key (sequence index)
       const bool diag = q0 < (kt + 1) * ATT_BM;       // sub-tile overlaps the diagonal block
       uint32_t pp[32], pd[32];
+      {
+        uint32_t rs[2][32], rp[2][32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + lane_off + c * 32, rs);
-        tmem_ld_32x32(tmem_base + 64 + lane_off + c * 32, rp);
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32(tmem_base + lane_off + c * 32, rs[c]);
+          tmem_ld_32x32(tmem_base + 64 + lane_off + c * 32, rp[c]);
+        }
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int qa = q0 + c * 32 + i;
-          const float l0 = __ldg(lse_bh + qa) * LOG2E, l1 = __ldg(lse_bh + qa + 1) * LOG2E;
-          const float e0 = __ldg(delta_bh + qa), e1 = __ldg(delta_bh + qa + 1);
-          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - l0);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - l1);
-          if (diag) {
-            if (key > qa) p0 = 0.f;
-            if (key > qa + 1) p1 = 0.f;
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int qa = q0 + c * 32 + i;
+            const float2 l2v = __ldg(reinterpret_cast<const float2*>(lse_bh + qa));
+            const float2 e2v = __ldg(reinterpret_cast<const float2*>(delta_bh + qa));
+            float p0 = exp2f(__uint_as_float(rs[c][i]) * sl2 - l2v.x * LOG2E);
+            float p1 = exp2f(__uint_as_float(rs[c][i + 1]) * sl2 - l2v.y * LOG2E);
+            if (diag) {
+              if (key > qa) p0 = 0.f;
+              if (key > qa + 1) p1 = 0.f;
+            }
+            pp[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+            pd[c * 16 + (i >> 1)] = pack_bf16(p0 * (__uint_as_float(rp[c][i]) - e2v.x) * p.scale,
+                                              p1 * (__uint_as_float(rp[c][i + 1]) - e2v.y) * p.scale);
           }
-          pp[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
-          pd[c * 16 + (i >> 1)] = pack_bf16(p0 * (__uint_as_float(rp[i]) - e0) * p.scale,
-                                            p1 * (__uint_as_float(rp[i + 1]) - e1) * p.scale);
         }
       }
       tc_fence_before_sync();

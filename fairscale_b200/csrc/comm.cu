@@ -1,0 +1,436 @@
+// Collectives over NVLink 5 / NVSwitch peer memory, issued from inside the kernels (no NCCL).
+//
+// Every rank owns a "symmetric" buffer that all peers have mapped; a kernel receives the table of peer
+// pointers and moves data with plain 16-byte loads / stores over NVLink.  Synchronisation between GPUs uses
+// one 32-bit flag per (channel, source rank) in a symmetric signal pad: a rank publishes the call's epoch to
+// every peer with st.release.sys and polls its own pad with ld.acquire.sys.  Each collective is ONE kernel:
+//
+//   entry barrier (peers' inputs are ready)  ->  pull / push over NVLink  ->  exit barrier (peers are done
+//   with my buffer), so that in-stream ordering on every GPU is enough for the callers.
+//
+// All polls are bounded: after kCommWaitNs without progress the kernel writes FSB_ERR_WAIT_TIMEOUT to its
+// status word and returns; the host raises.  No TMA cluster multicast is used anywhere; remote data is read
+// with ordinary loads (L1-bypassing) by the CTA that needs it.
+//
+// These kernels replace the c10d calls of the reference: _all_gather_base / _reduce_scatter_base
+// (fairscale/nn/data_parallel/fully_sharded_data_parallel.py:2032-2037,
+// fairscale/internal/reduce_scatter_bucketer.py:38-45), all_reduce (nn/model_parallel/mappings.py:42) and
+// all_to_all_single (nn/moe/moe_layer.py:29), and fuse the element-wise work that follows them
+// (pre/post-divide, fp32 cast, gradient accumulation; MoE slot scatter / weighted combine).
+
+#include "common.cuh"
+
+namespace fsb {
+
+constexpr int kMaxRanks = 8;
+constexpr uint64_t kCommWaitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+constexpr int COMM_THREADS = 512;
+
+struct CommCtx {
+  int rank, world;
+  uint32_t epoch;             // strictly increasing per call on a channel pair
+  int channel;                // base channel; the kernel uses channel (entry) and channel + 1 (exit / mid)
+  uint32_t* pads[kMaxRanks];  // peer signal pads: pads[p][channel * kMaxRanks + src]
+  unsigned int* counter;      // local scratch counter (zero before the call, left at zero)
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {  // L1-bypassing 16-byte load
+  return __ldcg(reinterpret_cast<const uint4*>(p));
+}
+
+// Tell every peer that this rank reached `epoch` on `channel` (one thread per peer).
+__device__ __forceinline__ void signal_peers(const CommCtx& c, int channel) {
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.pads[threadIdx.x] + channel * kMaxRanks + c.rank, c.epoch);
+  }
+}
+// Wait until every peer reached `epoch` on `channel`. Returns false on timeout (status word set).
+__device__ __forceinline__ bool wait_peers(const CommCtx& c, int channel) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t* mine = c.pads[c.rank] + channel * kMaxRanks + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    // epochs wrap: compare as signed distance
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - c.epoch) < 0) {
+      if (globaltimer_ns() - t0 > kCommWaitNs) {
+        ok_flag = 0;
+        if (c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+// Grid-wide completion: the last CTA to arrive signals the peers on `channel` and waits for theirs.
+__device__ __forceinline__ void exit_barrier(const CommCtx& c, int channel) {
+  __shared__ int last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(c.counter, 1u);
+    last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (last) *c.counter = 0;
+  }
+  __syncthreads();
+  if (last) {
+    signal_peers(c, channel);
+    wait_peers(c, channel);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS) barrier_kernel(CommCtx c) {
+  signal_peers(c, c.channel);
+  wait_peers(c, c.channel);
+}
+
+// out[p * n16 + i] = src_p[i] for every rank p; src pointers address each rank's shard (16-byte units)
+struct PtrTable { const void* p[kMaxRanks]; };
+
+__global__ void __launch_bounds__(COMM_THREADS) all_gather_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);
+  if (!wait_peers(c, c.channel)) return;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int k = 0; k < c.world; ++k) {
+    const int p = (c.rank + k) % c.world;  // start with the local shard, then walk the ring
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[p]);
+    uint4* d = out + static_cast<long long>(p) * n16;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) d[i] = ld_peer16(s + i);
+  }
+  exit_barrier(c, c.channel + 1);
+}
+
+// out[p-th chunk] = src_p[my chunk]: equal-split all-to-all, chunk = n16 16-byte units
+__global__ void __launch_bounds__(COMM_THREADS) all_to_all_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);
+  if (!wait_peers(c, c.channel)) return;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int k = 0; k < c.world; ++k) {
+    const int p = (c.rank + k) % c.world;
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[p]) + static_cast<long long>(c.rank) * n16;
+    uint4* d = out + static_cast<long long>(p) * n16;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) d[i] = ld_peer16(s + i);
+  }
+  exit_barrier(c, c.channel + 1);
+}
+
+template <typename T> struct Acc8;  // 16 bytes of T accumulated in fp32
+template <> struct Acc8<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void add(float (&a)[8], const uint4& v) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { a[2 * i] += __low2float(h[i]); a[2 * i + 1] += __high2float(h[i]); }
+  }
+};
+template <> struct Acc8<__half> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void add(float (&a)[8], const uint4& v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { a[2 * i] += __low2float(h[i]); a[2 * i + 1] += __high2float(h[i]); }
+  }
+};
+template <> struct Acc8<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void add(float (&a)[8], const uint4& v) {
+    const float* f = reinterpret_cast<const float*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] += f[i];
+  }
+};
+
+// Reduce-scatter with fused scale / cast / accumulate:
+//   out[i] = (accumulate ? out[i] : 0) + scale * sum_p src_p[rank * n + i]
+// TI: gradient dtype in the peers' buffers; TO: output dtype (fp32 master-precision shard or TI).
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(COMM_THREADS) reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n, float scale, int accumulate) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);
+  if (!wait_peers(c, c.channel)) return;
+  constexpr int E = Acc8<TI>::N;
+  const long long nvec = n / E;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    uint4 v[kMaxRanks];
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q)  // all peers' loads in flight together
+      if (q < c.world) v[q] = ld_peer16(reinterpret_cast<const TI*>(src.p[q]) + static_cast<long long>(c.rank) * n + i * E);
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // fixed summation order (rank 0, 1, ...): the result does not depend on timing
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q)
+      if (q < c.world) Acc8<TI>::add(a, v[q]);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      float r = a[e] * scale;
+      TO* o = out + i * E + e;
+      if (accumulate) r += to_f32<TO>(*o);
+      *o = from_f32<TO>(r);
+    }
+  }
+  // ragged tail (n not a multiple of the vector width)
+  for (long long i = nvec * E + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float a = 0.f;
+    for (int q = 0; q < c.world; ++q) a += to_f32<TI>(reinterpret_cast<const TI*>(src.p[q])[static_cast<long long>(c.rank) * n + i]);
+    float r = a * scale;
+    if (accumulate) r += to_f32<TO>(out[i]);
+    out[i] = from_f32<TO>(r);
+  }
+  exit_barrier(c, c.channel + 1);
+}
+
+// In-place all-reduce (sum) of every rank's symmetric buffer of n elements, two-shot:
+// reduce my chunk from all peers into my buffer, cross-GPU barrier, then pull the other chunks from their owners.
+// The grid must be fully resident (its CTAs wait for one another).
+template <typename T>
+__global__ void __launch_bounds__(COMM_THREADS) all_reduce_kernel(CommCtx c, PtrTable bufs, long long n) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);
+  if (!wait_peers(c, c.channel)) return;
+  constexpr int E = Acc8<T>::N;
+  const long long chunk = ((n / E + c.world - 1) / c.world);  // vectors per chunk
+  const long long nvec = n / E;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  T* mine = reinterpret_cast<T*>(const_cast<void*>(bufs.p[c.rank]));
+  const long long lo = min(static_cast<long long>(c.rank) * chunk, nvec), hi = min(lo + chunk, nvec);
+  for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += stride) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q)
+      if (q < c.world) Acc8<T>::add(a, ld_peer16(reinterpret_cast<const T*>(bufs.p[q]) + i * E));
+    T r[8];
+#pragma unroll
+    for (int e = 0; e < E; ++e) r[e] = from_f32<T>(a[e]);
+    *reinterpret_cast<uint4*>(mine + i * E) = *reinterpret_cast<const uint4*>(r);
+  }
+  // elements past the last full vector are reduced by rank 0 and fetched by the others below
+  if (c.rank == 0) {
+    for (long long i = nvec * E + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+      float a = 0.f;
+      for (int q = 0; q < c.world; ++q) a += to_f32<T>(reinterpret_cast<const T*>(bufs.p[q])[i]);
+      mine[i] = from_f32<T>(a);
+    }
+  }
+  exit_barrier(c, c.channel + 1);  // every rank's chunk is final and nobody still reads stale chunks
+  // all CTAs must observe the barrier that the last CTA completed: spin on the pad (monotonic epochs)
+  if (!wait_peers(c, c.channel + 1)) return;
+  for (int k = 1; k < c.world; ++k) {
+    const int p = (c.rank + k) % c.world;
+    const long long plo = min(static_cast<long long>(p) * chunk, nvec), phi = min(plo + chunk, nvec);
+    const T* s = reinterpret_cast<const T*>(bufs.p[p]);
+    for (long long i = plo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < phi; i += stride)
+      *reinterpret_cast<uint4*>(mine + i * E) = ld_peer16(s + i * E);
+  }
+  if (c.rank != 0) {
+    const T* s = reinterpret_cast<const T*>(bufs.p[0]);
+    for (long long i = nvec * E + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) mine[i] = s[i];
+  }
+  exit_barrier(c, c.channel + 2);
+}
+
+// ------------------------------------------------------------------------------------------------
+// MoE routing over peer memory.
+// scatter: row t of `x` [T, M] is stored (scaled by w[t] if given) into row dst_row[t] of rank dst_rank[t]'s
+//          buffer (remote 16-byte stores); rows with dst_rank < 0 are dropped.
+// gather : out[t] (+)= w[t] * row src_row[t] of rank src_rank[t]'s buffer (remote loads).
+// One warp moves one row; M % 8 == 0 (bf16).
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS) moe_scatter_rows_kernel(CommCtx c, PtrTable dst, const __nv_bfloat16* __restrict__ x,
+                                                                        const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
+                                                                        const float* __restrict__ w, long long T, int rows_per_token, int M) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);  // destinations are zeroed / free
+  if (!wait_peers(c, c.channel)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    const int r = dst_rank[t];
+    if (r < 0) continue;
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dst.p[r])) + static_cast<long long>(dst_row[t]) * M;
+    const __nv_bfloat16* s = x + (t / rows_per_token) * M;
+    const float scale = (w != nullptr) ? w[t] : 1.f;
+    for (int j = lane * 8; j < M; j += 256) {
+      Vec16<__nv_bfloat16> v = ld16(s + j);
+      if (w != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v.v[k] = __float2bfloat16_rn(__bfloat162float(v.v[k]) * scale);
+      }
+      st16(d + j, v);
+    }
+  }
+  exit_barrier(c, c.channel + 1);  // all rows of all ranks have landed
+}
+
+// out[token] = sum over its `rows_per_token` routes of w[t] * peer_row(t); dot[t] (optional) = <peer_row(t), g[token]>
+__global__ void __launch_bounds__(COMM_THREADS) moe_gather_rows_kernel(CommCtx c, PtrTable src, __nv_bfloat16* __restrict__ out,
+                                                                       const int* __restrict__ src_rank, const int* __restrict__ src_row,
+                                                                       const float* __restrict__ w, const __nv_bfloat16* __restrict__ g,
+                                                                       float* __restrict__ dot, long long tokens, int rows_per_token, int M) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);  // sources are complete
+  if (!wait_peers(c, c.channel)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long tok = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; tok < tokens; tok += warps) {
+    float dots[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = lane * 8; j < M; j += 256) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      Vec16<__nv_bfloat16> gv;
+      if (g != nullptr) gv = ld16(g + tok * M + j);
+      for (int k = 0; k < rows_per_token && k < 4; ++k) {
+        const long long t = tok * rows_per_token + k;
+        const int r = src_rank[t];
+        if (r < 0) continue;
+        const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + static_cast<long long>(src_row[t]) * M + j;
+        Vec16<__nv_bfloat16> v;
+        v.raw = ld_peer16(s);
+        const float wt = (w != nullptr) ? w[t] : 1.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float f = __bfloat162float(v.v[e]);
+          acc[e] += wt * f;
+          if (g != nullptr) dots[k] += f * __bfloat162float(gv.v[e]);
+        }
+      }
+      if (out != nullptr) {
+        Vec16<__nv_bfloat16> o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16_rn(acc[e]);
+        st16(out + tok * M + j, o);
+      }
+    }
+    if (dot != nullptr) {
+      for (int k = 0; k < rows_per_token && k < 4; ++k) {
+        const float d = warp_sum(dots[k]);
+        if (lane == 0) dot[tok * rows_per_token + k] = d;
+      }
+    }
+  }
+  exit_barrier(c, c.channel + 1);  // peers may reuse their buffers
+}
+
+}  // namespace fsb
+
+// ------------------------------------------------------------------------------------------------
+// C ABI. `pads` / `ptrs`: host arrays of `world` device pointers (peer-mapped). `counter`: zeroed device uint.
+// dtype codes: 0 fp32, 1 fp16, 2 bf16. All data pointers 16-byte aligned.
+// ------------------------------------------------------------------------------------------------
+static fsb::CommCtx make_ctx(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, int* status) {
+  fsb::CommCtx c{};
+  c.rank = rank; c.world = world; c.epoch = epoch; c.channel = channel;
+  for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) c.pads[i] = static_cast<uint32_t*>(pads[i]);
+  c.counter = static_cast<unsigned int*>(counter);
+  c.status = status;
+  return c;
+}
+static fsb::PtrTable make_table(void* const* ptrs, int world) {
+  fsb::PtrTable t{};
+  for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) t.p[i] = ptrs[i];
+  return t;
+}
+static int comm_grid(long long work_items, int max_blocks) {
+  long long b = (work_items + fsb::COMM_THREADS - 1) / fsb::COMM_THREADS;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return static_cast<int>(b);
+}
+
+FSB_API int fsb_comm_max_ranks() { return fsb::kMaxRanks; }
+
+FSB_API int fsb_comm_barrier(int rank, int world, unsigned epoch, int channel, void* const* pads, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks) return -1;
+  fsb::barrier_kernel<<<1, fsb::COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch, channel, pads, nullptr, status));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[world * nbytes] <- every rank's shard (src[p], nbytes each, multiple of 16)
+FSB_API int fsb_comm_all_gather(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* src,
+                                void* out, long long nbytes, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || nbytes % 16) return -1;
+  const long long n16 = nbytes / 16;
+  fsb::all_gather_kernel<<<comm_grid(n16, 148 * 2), fsb::COMM_THREADS, 0, stream>>>(
+      make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), n16);
+  return static_cast<int>(cudaGetLastError());
+}
+
+FSB_API int fsb_comm_all_to_all(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* src,
+                                void* out, long long chunk_bytes, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || chunk_bytes % 16) return -1;
+  const long long n16 = chunk_bytes / 16;
+  fsb::all_to_all_kernel<<<comm_grid(n16, 148 * 2), fsb::COMM_THREADS, 0, stream>>>(
+      make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), n16);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[n] (out_dtype) = (accumulate ? out : 0) + scale * sum_p src[p][rank * n + i]   (src in in_dtype)
+FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                                    void* const* src, int in_dtype, void* out, int out_dtype, long long n, float scale, int accumulate,
+                                    int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world > kMaxRanks) return -1;
+  if ((n * (in_dtype == FSB_F32 ? 4 : 2)) % 16) return -1;  // each rank's chunk must start 16-byte aligned
+  const CommCtx c = make_ctx(rank, world, epoch, channel, pads, counter, status);
+  const PtrTable t = make_table(src, world);
+  const int grid = comm_grid(n / 8, 148 * 2);
+#define FSB_RS(IC, IT, OC, OT)                                                                                          \
+  if (in_dtype == IC && out_dtype == OC) {                                                                              \
+    reduce_scatter_kernel<IT, OT><<<grid, COMM_THREADS, 0, stream>>>(c, t, static_cast<OT*>(out), n, scale, accumulate); \
+    return static_cast<int>(cudaGetLastError());                                                                        \
+  }
+  FSB_RS(FSB_BF16, __nv_bfloat16, FSB_F32, float)
+  FSB_RS(FSB_BF16, __nv_bfloat16, FSB_BF16, __nv_bfloat16)
+  FSB_RS(FSB_F16, __half, FSB_F32, float)
+  FSB_RS(FSB_F16, __half, FSB_F16, __half)
+  FSB_RS(FSB_F32, float, FSB_F32, float)
+#undef FSB_RS
+  return -1;
+}
+
+// in-place sum over ranks of every rank's symmetric buffer bufs[p] (n elements)
+FSB_API int fsb_comm_all_reduce(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* bufs,
+                                int dtype, long long n, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world > kMaxRanks) return -1;
+  const CommCtx c = make_ctx(rank, world, epoch, channel, pads, counter, status);
+  const PtrTable t = make_table(bufs, world);
+  const int grid = comm_grid(n / 8 / world + 1, 132);  // fully resident: CTAs wait for one another
+  if (dtype == FSB_BF16) all_reduce_kernel<__nv_bfloat16><<<grid, COMM_THREADS, 0, stream>>>(c, t, n);
+  else if (dtype == FSB_F16) all_reduce_kernel<__half><<<grid, COMM_THREADS, 0, stream>>>(c, t, n);
+  else if (dtype == FSB_F32) all_reduce_kernel<float><<<grid, COMM_THREADS, 0, stream>>>(c, t, n);
+  else return -1;
+  return static_cast<int>(cudaGetLastError());
+}
+
+FSB_API int fsb_comm_moe_scatter_rows(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                                      void* const* dst, const void* x, const int* dst_rank, const int* dst_row, const float* w,
+                                      long long T, int rows_per_token, int M, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world > kMaxRanks || M % 8) return -1;
+  moe_scatter_rows_kernel<<<comm_grid(T * 32, 148 * 2), COMM_THREADS, 0, stream>>>(
+      make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(dst, world), static_cast<const __nv_bfloat16*>(x),
+      dst_rank, dst_row, w, T, rows_per_token, M);
+  return static_cast<int>(cudaGetLastError());
+}
+
+FSB_API int fsb_comm_moe_gather_rows(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                                     void* const* src, void* out, const int* src_rank, const int* src_row, const float* w,
+                                     const void* g, float* dot, long long tokens, int rows_per_token, int M, int* status,
+                                     cudaStream_t stream) {
+  using namespace fsb;
+  if (world > kMaxRanks || M % 8 || rows_per_token > 4) return -1;
+  moe_gather_rows_kernel<<<comm_grid(tokens * 32, 148 * 2), COMM_THREADS, 0, stream>>>(
+      make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<__nv_bfloat16*>(out), src_rank,
+      src_row, w, static_cast<const __nv_bfloat16*>(g), dot, tokens, rows_per_token, M);
+  return static_cast<int>(cudaGetLastError());
+}

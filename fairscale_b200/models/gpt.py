@@ -131,11 +131,25 @@ class GPT(nn.Module):
 
 
 def build_fsdp_gpt(cfg: GPTConfig, device: torch.device, process_group: Any = None, *, checkpoint_blocks: bool = True,
-                   compute_dtype: torch.dtype = torch.bfloat16, **fsdp_kwargs: Any) -> nn.Module:
+                   compute_dtype: torch.dtype = torch.bfloat16, nvlink_heap: bool = True, **fsdp_kwargs: Any) -> nn.Module:
     """The flagship training setup: every block is ``FSDP(checkpoint_wrapper(block))``, embedding and head are
     their own FSDP units, and a root FSDP ties them together (full shard, bf16 compute, fp32 master shards)."""
     from ..nn.checkpoint import checkpoint_wrapper
     from ..nn.data_parallel import FullyShardedDataParallel as FSDP
+
+    import torch.distributed as dist
+
+    from ..internal.parallel import ProcessGroupName, get_process_group_cached
+    from ..parallel import nvlink, symm
+
+    if process_group is None:
+        process_group = get_process_group_cached()
+    world = process_group.size()
+    if nvlink_heap and world > 1 and device.type == "cuda" and nvlink.available() and symm.workspace_for(process_group) is None:
+        # the compute-dtype shards live in the symmetric heap so peers all-gather them without staging
+        shard_mb = (2 * cfg.num_params() // world >> 20) + 64
+        ws = nvlink.enable(process_group, device, staging_mb=256, heap_mb=shard_mb)
+        symm.register_workspace(get_process_group_cached(ProcessGroupName.reduce_scatter), ws)
 
     kw = dict(process_group=process_group, mixed_precision=True, compute_dtype=compute_dtype, reshard_after_forward=True,
               flatten_parameters=True, compute_device=device, keep_low_precision_grads=True, persistent_compute_shards=True)

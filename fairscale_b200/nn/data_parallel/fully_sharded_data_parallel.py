@@ -69,7 +69,7 @@ from ...internal.params import calc_grad_norm, get_global_rank, recursive_copy_t
 from ...internal.reduce_scatter_bucketer import ReduceScatterBucketer
 from ...internal.state_dict import replace_by_prefix_
 from ...ops.cast import cast_into
-from ...parallel import comm
+from ...parallel import comm, symm
 from ..misc import flatten_params_wrapper as _fpw
 from ..misc.flatten_params_wrapper import FlattenParamsWrapper
 from ..wrap import auto_wrap, config_auto_wrap_policy, enable_wrap
@@ -809,9 +809,14 @@ class FullyShardedDataParallel(nn.Module):
                 and old.numel() == p._fp32_shard.numel() and old.device == self.compute_device  # type: ignore[attr-defined]
             )
             if not reuse:
-                p._fp16_shard = torch.zeros_like(  # type: ignore[attr-defined]
-                    p._fp32_shard, device=self.compute_device, dtype=self.compute_dtype  # type: ignore[attr-defined]
-                )
+                ws = symm.workspace_for(self.process_group) if (self.persistent_compute_shards and p._is_sharded) else None  # type: ignore[attr-defined]
+                if ws is not None and comm.comm_mode() == "fused":
+                    # resident in the symmetric heap: peers pull it directly during the all-gather
+                    p._fp16_shard = ws.alloc_tensor(tuple(p._fp32_shard.shape), self.compute_dtype)  # type: ignore[attr-defined]
+                else:
+                    p._fp16_shard = torch.zeros_like(  # type: ignore[attr-defined]
+                        p._fp32_shard, device=self.compute_device, dtype=self.compute_dtype  # type: ignore[attr-defined]
+                    )
                 p._fp16_shard_current = False  # type: ignore[attr-defined]
                 if not self.persistent_compute_shards:
                     free_storage_(p._fp16_shard)  # type: ignore[attr-defined]
@@ -1055,7 +1060,33 @@ class FullyShardedDataParallel(nn.Module):
                 param.grad.data = param.grad.data.to(param.dtype)
             if self.gradient_predivide_factor > 1:
                 param.grad.data.div_(self.gradient_predivide_factor)
-            if param._is_sharded:  # type: ignore[attr-defined]
+            ws = symm.workspace_for(self.process_group_reduce_scatter) if param._is_sharded else None  # type: ignore[attr-defined]
+            if (
+                ws is not None
+                and comm.comm_mode() == "fused"
+                and param.grad.is_cuda
+                and param.grad.numel() * param.grad.element_size() > (self.bucket_cap_mb << 20) // max(self.world_size, 1)
+                and ws.can_reduce_scatter(param._fp32_shard, param.grad.data)  # type: ignore[attr-defined]
+                and param.grad.numel() * param.grad.element_size() <= ws.lanes[2].staging_bytes
+            ):
+                # one NVLink kernel: pull-reduce this rank's slice from every peer, apply the complete 1/world
+                # averaging, land in the gradient dtype the optimizer sees and accumulate into an earlier shard
+                grad = param.grad.data
+                param.grad = None
+                if self.gradient_predivide_factor > 1:
+                    grad.mul_(self.gradient_predivide_factor)  # undo the pre-division applied above
+                out_dtype = grad.dtype if self.keep_low_precision_grads else param.dtype
+                saved = getattr(param, "_saved_grad_shard", None)
+                accumulate = saved is not None and saved.dtype == out_dtype
+                out = saved if accumulate else torch.empty_like(param._fp32_shard, dtype=out_dtype)  # type: ignore[attr-defined]
+                comm._COUNTERS["reduce_scatter"] += 1
+                ws.reduce_scatter(out.view(-1), grad.view(-1), scale=1.0 / self.world_size, accumulate=accumulate)
+                if saved is not None and not accumulate:
+                    out.add_(saved.to(out.dtype))
+                param._saved_grad_shard = out  # type: ignore[attr-defined]
+                if self.move_grads_to_cpu:
+                    param._cpu_grad.copy_(out, non_blocking=True)  # type: ignore[attr-defined]
+            elif param._is_sharded:  # type: ignore[attr-defined]
                 assert self._reducer is not None
                 grad = param.grad.data
                 param.grad = None
