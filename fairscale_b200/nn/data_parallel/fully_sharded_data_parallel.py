@@ -1435,7 +1435,8 @@ class FullyShardedDataParallel(nn.Module):
                 assert p._fp16_shard is not None  # type: ignore[attr-defined]
                 fresh = self.persistent_compute_shards and getattr(p, "_fp16_shard_current", False)
                 if not fresh:
-                    alloc_storage_(p._fp16_shard, size=p._fp32_shard.size())  # type: ignore[attr-defined]
+                    if not self.persistent_compute_shards:
+                        alloc_storage_(p._fp16_shard, size=p._fp32_shard.size())  # type: ignore[attr-defined]
                     cast_into(p._fp16_shard, p._fp32_shard)  # type: ignore[attr-defined]
                     p._fp16_shard_current = self.persistent_compute_shards  # type: ignore[attr-defined]
                 p.data = p._fp16_shard  # type: ignore[attr-defined]
