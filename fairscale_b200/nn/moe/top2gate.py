@@ -1,0 +1,127 @@
+"""Top-2 gating (GShard) in index form.
+
+Behavioural parity with fairscale/nn/moe/top2gate.py:37-130: fp32 softmax, top-1 by probability, second
+expert by Gumbel-max on the logits with the first masked out, slot assignment by token order with the second
+choices queued behind all first choices, capacity ``2*S/E``, auxiliary loss ``mean(me * ce)``, gates
+renormalised over the kept experts.
+
+The reference materialises one-hot ``[S, E, C]`` tensors (537 MB fp32 for S=8192, E=64, C=256) and dispatches
+with dense einsums.  Here routing is kept as per-token ``(expert, slot, gate)`` triples (:class:`Top2Route`);
+the dense ``(l_aux, combine_weights, dispatch_mask)`` contract is still available from :func:`top2gating` for
+code that wants it and is what ``Top2Gate.forward`` returns.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Dict, NamedTuple, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+gumbel_map: Dict[torch.device, Callable] = {}
+
+
+def gumbel_rsample(shape: Tuple, device: torch.device) -> Tensor:
+    sampler = gumbel_map.get(device)
+    if sampler is None:
+        one = torch.tensor(1.0, device=device)
+        zero = torch.tensor(0.0, device=device)
+        sampler = torch.distributions.gumbel.Gumbel(zero, one).rsample  # type: ignore[assignment]
+        gumbel_map[device] = sampler
+    return sampler(shape)
+
+
+def one_hot(tensor: torch.Tensor, num_classes: int) -> Tensor:
+    assert num_classes > 0, "num_classes must be a positive integer"
+    ret = torch.zeros(tensor.shape + (num_classes,), device=tensor.device, dtype=tensor.dtype)
+    ret.scatter_(-1, tensor.unsqueeze(-1), 1)
+    return ret
+
+
+class Top2Route(NamedTuple):
+    """Routing of ``S`` tokens to ``E`` experts with ``capacity`` slots each.
+
+    ``expert[s, k]`` / ``slot[s, k]``: k-th choice of token s and its position in that expert's buffer;
+    ``keep[s, k]``: False when the choice overflowed the capacity; ``gate[s, k]``: normalised weight (0 if
+    dropped, differentiable w.r.t. the logits); ``l_aux``: load-balancing loss.
+    """
+
+    l_aux: Tensor
+    expert: Tensor
+    slot: Tensor
+    keep: Tensor
+    gate: Tensor
+    capacity: int
+    num_experts: int
+
+
+def top2_route(logits: torch.Tensor, noise: Optional[Tensor] = None) -> Top2Route:
+    """Index-form top-2 routing; ``noise`` (Gumbel, same shape as ``logits``) can be supplied for reproducibility."""
+    gates = F.softmax(logits, dim=1, dtype=torch.float)
+    S, E = gates.shape
+    capacity = 2 * S // E
+    assert S % E == 0
+    idx1 = torch.argmax(gates, dim=1)
+    if noise is None:
+        noise = gumbel_rsample(logits.shape, device=logits.device)
+    noisy = (logits + noise).scatter(1, idx1.unsqueeze(1), float("-inf"))
+    idx2 = torch.argmax(noisy, dim=1)
+
+    mask1 = one_hot(idx1, E)
+    mask2 = one_hot(idx2, E)
+    # position of each token among the tokens that chose the same expert, in token order
+    loc1 = (torch.cumsum(mask1, dim=0) - 1).gather(1, idx1.unsqueeze(1)).squeeze(1)
+    loc2 = (torch.cumsum(mask2, dim=0) - 1 + mask1.sum(dim=0, keepdim=True)).gather(1, idx2.unsqueeze(1)).squeeze(1)
+
+    me = gates.mean(dim=0)
+    ce = mask1.float().mean(dim=0)
+    l_aux = torch.mean(me * ce)
+
+    keep1, keep2 = loc1 < capacity, loc2 < capacity
+    g1 = gates.gather(1, idx1.unsqueeze(1)).squeeze(1) * keep1
+    g2 = gates.gather(1, idx2.unsqueeze(1)).squeeze(1) * keep2
+    denom = torch.clamp(g1 + g2, min=torch.finfo(g1.dtype).eps)
+    gate = torch.stack([g1 / denom, g2 / denom], dim=1)
+    expert = torch.stack([idx1, idx2], dim=1)
+    slot = torch.stack([loc1 * keep1, loc2 * keep2], dim=1)
+    keep = torch.stack([keep1, keep2], dim=1)
+    return Top2Route(l_aux.to(logits.dtype), expert, slot, keep, gate, capacity, E)
+
+
+def dense_from_route(route: Top2Route, dtype: torch.dtype) -> Tuple[Tensor, Tensor]:
+    """``combine_weights [S, E, C]`` and ``dispatch_mask [S, E, C]`` (bool) from index-form routing."""
+    S = route.expert.shape[0]
+    combine = torch.zeros((S, route.num_experts, route.capacity), dtype=route.gate.dtype, device=route.gate.device)
+    rows = torch.arange(S, device=route.expert.device)
+    for k in range(2):
+        w = route.gate[:, k] * route.keep[:, k]
+        combine = combine.index_put((rows, route.expert[:, k], route.slot[:, k]), w, accumulate=True)
+    return combine.to(dtype), combine.bool()
+
+
+def top2gating(logits: torch.Tensor) -> Tuple[Tensor, Tensor, Tensor]:
+    """Dense Top-2 gating: ``(l_aux, combine_weights[S,E,C], dispatch_mask[S,E,C])``."""
+    route = top2_route(logits)
+    combine, mask = dense_from_route(route, logits.dtype)
+    return route.l_aux, combine, mask
+
+
+class Top2Gate(torch.nn.Module):
+    """Gate network ``wg: model_dim -> num_experts`` followed by top-2 routing.
+
+    ``forward`` returns the dense triple of the reference; :meth:`route` returns the index form that
+    :class:`~fairscale_b200.nn.moe.MOELayer` uses for its scatter / gather fast path.
+    """
+
+    wg: torch.nn.Linear
+
+    def __init__(self, model_dim: int, num_experts: int) -> None:
+        super().__init__()
+        self.wg = torch.nn.Linear(model_dim, num_experts, bias=False)
+
+    def route(self, input: torch.Tensor) -> Top2Route:
+        return top2_route(self.wg(input))
+
+    def forward(self, input: torch.Tensor) -> Tuple[Tensor, Tensor, Tensor]:  # type: ignore[override]
+        return top2gating(self.wg(input))

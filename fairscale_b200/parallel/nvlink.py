@@ -97,6 +97,14 @@ class NvlinkWorkspace:
         self._bump = off + nbytes
         return self.heap[off : off + nbytes]
 
+    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Named, reusable heap tensor (allocated on first use; the same name and size returns the same window)."""
+        key = (name, tuple(shape), dtype)
+        cache = self.__dict__.setdefault("_scratch", {})
+        if key not in cache:
+            cache[key] = self.alloc_tensor(tuple(shape), dtype)
+        return cache[key]
+
     def alloc_tensor(self, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         n = 1
         for s in shape:

@@ -1,0 +1,104 @@
+"""Top-2 gating numerics and MOELayer (index path == dense einsum path) on CPU / gloo."""
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from fairscale_b200.fair_dev.testing.testing import spawn_ranks
+from fairscale_b200.nn.moe import MOELayer, Top2Gate, top2gating
+from fairscale_b200.nn.moe.top2gate import dense_from_route, top2_route
+
+
+def test_top2gating_reference_values():
+    # same construction as the reference's unit test: 12 tokens, 4 experts, uniform logits except a bump
+    torch.manual_seed(3)
+    logits = torch.rand(12, 4)
+    l_aux, combine, mask = top2gating(logits)
+    assert combine.shape == (12, 4, 6) and mask.shape == (12, 4, 6)
+    assert mask.dtype == torch.bool
+    # every kept (token, expert) pair owns exactly one slot and no slot is used twice
+    assert (mask.sum(dim=(1, 2)) <= 2).all()
+    assert (mask.sum(dim=0) <= 1).all()
+    # weights of a token sum to 1 when both choices were kept
+    sums = combine.sum(dim=(1, 2))
+    both = mask.sum(dim=(1, 2)) == 2
+    torch.testing.assert_close(sums[both], torch.ones_like(sums[both]))
+    assert 0.0 < l_aux.item() < 1.0
+
+
+def test_capacity_overflow_drops_tokens():
+    logits = torch.zeros(8, 4)
+    logits[:, 0] = 10.0  # everyone wants expert 0 first; capacity is 4
+    route = top2_route(logits, noise=torch.zeros_like(logits))
+    assert route.capacity == 4
+    assert route.keep[:, 0].sum().item() == 4
+    assert (route.slot[route.keep[:, 0], 0] == torch.arange(4)).all()  # token order decides the slots
+    combine, mask = dense_from_route(route, torch.float32)
+    assert mask[:, 0].sum().item() == 4
+
+
+class _Expert(nn.Module):
+    def __init__(self, d, scale):
+        super().__init__()
+        self.fc = nn.Linear(d, d, bias=False)
+        with torch.no_grad():
+            self.fc.weight.copy_(torch.eye(d) * scale)
+
+    def forward(self, x):
+        return self.fc(x)
+
+
+class _DenseGate(nn.Module):
+    """Wraps a Top2Gate but only exposes the dense contract (forces the einsum path)."""
+
+    def __init__(self, inner):
+        super().__init__()
+        self.inner = inner
+        self.noise = None
+
+    def forward(self, x):
+        route = top2_route(self.inner.wg(x), noise=self.noise)
+        c, m = dense_from_route(route, x.dtype)
+        return route.l_aux, c, m
+
+
+class _IndexGate(Top2Gate):
+    noise = None
+
+    def route(self, x):
+        return top2_route(self.wg(x), noise=self.noise)
+
+
+def _moe(rank, world):
+    torch.manual_seed(0)
+    d, n_local = 8, 2
+    E = world * n_local
+    gate = _IndexGate(d, E)
+    dist.broadcast(gate.wg.weight.data, 0)
+    experts = nn.ModuleList([_Expert(d, 1.0 + rank * n_local + i) for i in range(n_local)])
+    fast = MOELayer(gate, experts)
+    dense_gate = _DenseGate(gate)
+    slow = MOELayer(dense_gate, experts)
+    for p in experts.parameters():
+        assert p.expert is True
+    torch.manual_seed(10 + rank)
+    x = torch.randn(4, 4, d, requires_grad=True)  # 16 tokens, divisible by E
+    noise = torch.randn(16, E)
+    gate.noise = noise
+    dense_gate.noise = noise
+    y_fast = fast(x)
+    g = torch.randn_like(y_fast)
+    gx_fast, gw_fast = torch.autograd.grad(y_fast, [x, gate.wg.weight], g, retain_graph=True)
+    ge_fast = torch.autograd.grad(y_fast, list(experts.parameters()), g)
+    y_slow = slow(x)
+    gx_slow, gw_slow = torch.autograd.grad(y_slow, [x, gate.wg.weight], g, retain_graph=True)
+    ge_slow = torch.autograd.grad(y_slow, list(experts.parameters()), g)
+    torch.testing.assert_close(y_fast, y_slow, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(gx_fast, gx_slow, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(gw_fast, gw_slow, atol=1e-5, rtol=1e-5)
+    for a, b in zip(ge_fast, ge_slow):
+        torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(fast.l_aux, slow.l_aux)
+
+
+def test_moe_index_path_matches_dense_path():
+    spawn_ranks(_moe, 2, (), backend="gloo")
