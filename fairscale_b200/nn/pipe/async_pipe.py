@@ -1,0 +1,154 @@
+"""Multi-process pipeline: one stage per rank, activations and gradients over NCCL / gloo p2p.
+
+Capability parity with fairscale/nn/pipe/async_pipe.py:65-401 (``AsyncPipe(module, balance, group=...,
+chunks=..., checkpoint=...)``, lazy per-rank construction with ``LazyModule``, idle ranks beyond
+``len(balance)``, ``back_helper`` on non-final stages).  The schedule is GPipe's: a stage forwards its
+micro-batches in order as they arrive and backwards them in reverse; sends are asynchronous so a stage
+computes micro-batch *i+1* while micro-batch *i* is on the wire.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Any, Iterable, List, Optional, Sequence, Tuple, Union
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from . import microbatch
+from .batchnorm import DeferredBatchNorm
+from .messages import SendRecvTransport
+from .types import LazyModule
+
+Tensors = Tuple[Tensor, ...]
+TensorOrTensors = Union[Tensor, Tensors]
+
+
+class _RecvBoundary(torch.autograd.Function):
+    """Identity on a received activation whose backward ships the gradient to the previous stage."""
+
+    @staticmethod
+    def forward(ctx: Any, x: Tensor, transport: SendRecvTransport, prev_rank: int) -> Tensor:  # type: ignore[override]
+        ctx.transport, ctx.prev_rank = transport, prev_rank
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx: Any, grad: Tensor):  # type: ignore[override]
+        ctx.transport.send(grad, ctx.prev_rank)
+        return grad, None, None
+
+
+class AsyncPipe(nn.Module):
+    """Args:
+        module: ``nn.Sequential`` (every rank builds everything and keeps its slice) or a list of
+            :class:`LazyModule` (every rank builds only its slice).
+        balance: layers per stage; stage ``r`` runs on group rank ``r``; further ranks stay idle.
+        group: pipeline process group (default: the pipeline group of ``initialize_model_parallel`` if
+            initialised, else WORLD).
+        chunks / checkpoint / deferred_batch_norm: as for :class:`Pipe`.
+    """
+
+    def __init__(self, module: Union[nn.Sequential, List[LazyModule]], balance: Iterable[int], *, group: Any = None,
+                 worker_map: Optional[Any] = None, input_device: Optional[torch.device] = None, chunks: int = 1,
+                 checkpoint: str = "except_last", deferred_batch_norm: bool = False) -> None:
+        super().__init__()
+        if chunks <= 0:
+            raise ValueError("number of chunks must be positive integer")
+        if checkpoint not in ["always", "except_last", "never"]:
+            raise ValueError("checkpoint is not one of 'always', 'except_last', or 'never'")
+        if group is None:
+            from ..model_parallel import initialize as mpi
+
+            group = mpi.get_pipeline_parallel_group() if mpi.model_parallel_is_initialized() else dist.group.WORLD
+        self.group = group
+        self.balance = list(balance)
+        self.chunks = chunks
+        self.checkpoint = checkpoint
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if len(self.balance) > self.world:
+            raise IndexError(f"too few ranks to hold given partitions (ranks: {self.world}, partitions: {len(self.balance)})")
+        n_layers = len(module)
+        if sum(self.balance) != n_layers:
+            raise ValueError(f"module and sum of balance have different length (module: {n_layers}, sum of balance: {sum(self.balance)})")
+        self.final_stage = len(self.balance) - 1
+        if self.rank >= len(self.balance):
+            logging.warning(f"AsyncPipe: rank {self.rank} has no partition and stays idle")
+            self.partition: Optional[nn.Sequential] = None
+        else:
+            lo = sum(self.balance[: self.rank])
+            layers = list(module)[lo : lo + self.balance[self.rank]] if isinstance(module, nn.Sequential) else module[lo : lo + self.balance[self.rank]]
+            built = [l() if isinstance(l, LazyModule) else l for l in layers]
+            part = nn.Sequential(*built)
+            if deferred_batch_norm:
+                part = DeferredBatchNorm.convert_deferred_batch_norm(part, chunks)
+            self.partition = part
+        if input_device is None:
+            input_device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+        self.input_device = input_device
+        if self.partition is not None:
+            self.partition.to(self.input_device)
+        self.transport = SendRecvTransport(group, self.input_device)
+        self._outputs: List[Tensor] = []
+
+    def __len__(self) -> int:
+        return 0 if self.partition is None else len(self.partition)
+
+    def _run_stage(self, x: TensorOrTensors, use_checkpoint: bool) -> TensorOrTensors:
+        assert self.partition is not None
+        if use_checkpoint and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint as torch_ckpt
+
+            return torch_ckpt(self.partition, x, use_reentrant=False)
+        return self.partition(x)
+
+    def forward(self, input: Optional[TensorOrTensors] = None) -> Optional[TensorOrTensors]:  # type: ignore[override]
+        """Stage 0 consumes ``input``; the final stage returns the gathered output; other stages return the list
+        of their micro-batch outputs (pass it to :meth:`back_helper` to run their share of backward)."""
+        if self.partition is None:
+            return None
+        first, last = self.rank == 0, self.rank == self.final_stage
+        if first:
+            assert input is not None
+            microbatch.check(input)
+            batches = [b.tensor_or_tensors for b in microbatch.scatter(input, self.chunks)]
+            n = len(batches)
+            if not last:
+                self.transport.send(torch.tensor([n], dtype=torch.int64, device=self.input_device), self.rank + 1)
+        else:
+            n = int(self.transport.recv(self.rank - 1).item())
+            if not last:
+                self.transport.send(torch.tensor([n], dtype=torch.int64, device=self.input_device), self.rank + 1)
+        stop = {"always": n, "except_last": n - 1, "never": 0}[self.checkpoint] if self.training else 0
+        outs: List[Tensor] = []
+        for i in range(n):
+            if first:
+                x = batches[i]
+            else:
+                x = self.transport.recv(self.rank - 1)
+                if x.requires_grad and torch.is_grad_enabled():
+                    x = _RecvBoundary.apply(x, self.transport, self.rank - 1)
+            y = self._run_stage(x, i < stop)
+            assert isinstance(y, Tensor), "stages of AsyncPipe exchange single tensors"
+            if not last:
+                self.transport.send(y, self.rank + 1)
+            outs.append(y)
+        self._outputs = outs
+        if last:
+            return torch.cat(outs)
+        return outs  # type: ignore[return-value]
+
+    def back_helper(self, output: Optional[List[Tensor]] = None) -> None:
+        """Run backward on a non-final stage: receive each micro-batch's output gradient from the next stage
+        (reverse order) and back-propagate; gradients for the previous stage leave through the recv boundary."""
+        if self.partition is None or self.rank == self.final_stage:
+            self.transport.flush()
+            return
+        outs = self._outputs if output is None else output
+        grads = [self.transport.recv(self.rank + 1) for _ in outs]  # next stage emits them in its backward order
+        # the final stage back-propagates torch.cat(outs): gradients arrive in autograd's (reverse) order
+        for y, g in zip(reversed(outs), grads):
+            if y.requires_grad:
+                torch.autograd.backward(y, g)
+        self.transport.flush()

@@ -1,0 +1,75 @@
+"""Drive a multi-process pipeline from rank 0 over ``torch.distributed.rpc`` (parity: fairscale/nn/pipe/rpc.py:85-285).
+
+Control plane only: rank 0 tells every worker to construct its :class:`AsyncPipe` stage, to run forward for a
+batch and to run its share of backward; tensors travel between stages over p2p as in :class:`AsyncPipe`.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from .async_pipe import AsyncPipe
+
+_PIPES: Dict[int, AsyncPipe] = {}
+_NEXT_ID = 0
+
+
+def _build(pipe_id: int, module_factory: Callable[[], nn.Sequential], args: tuple, kwargs: dict) -> None:
+    _PIPES[pipe_id] = AsyncPipe(module_factory(), *args, **kwargs)
+
+
+def _forward(pipe_id: int, training: bool) -> None:
+    pipe = _PIPES[pipe_id]
+    pipe.train(training)
+    pipe(None)
+
+
+def _backward(pipe_id: int) -> None:
+    _PIPES[pipe_id].back_helper()
+
+
+def _call(pipe_id: int, fn: Callable[[AsyncPipe], Any]) -> Any:
+    return fn(_PIPES[pipe_id])
+
+
+class PipeRPCWrapper(nn.Module):
+    """Rank 0 owns the object; workers are addressed by the names in ``worker_map`` (group rank -> rpc name)."""
+
+    def __init__(self, module_factory: Callable[[], nn.Sequential], *args: Any, worker_map: Optional[Dict[int, str]] = None, **kwargs: Any):
+        super().__init__()
+        from torch.distributed import rpc
+
+        global _NEXT_ID
+        self.pipe_id = _NEXT_ID
+        _NEXT_ID += 1
+        self.worker_map = worker_map or {r: f"Test{r}" for r in range(dist.get_world_size())}
+        self.rpc = rpc
+        futs = [rpc.rpc_async(name, _build, args=(self.pipe_id, module_factory, args, kwargs)) for r, name in self.worker_map.items() if r != 0]
+        _build(self.pipe_id, module_factory, args, kwargs)
+        for f in futs:
+            f.wait()
+        self.model = _PIPES[self.pipe_id]
+
+    def foreach_worker(self, callback: Callable[[AsyncPipe], Any], include_self: bool = False) -> List[Any]:
+        futs = [self.rpc.rpc_async(name, _call, args=(self.pipe_id, callback)) for r, name in self.worker_map.items() if r != 0]
+        out = [callback(self.model)] if include_self else []
+        return out + [f.wait() for f in futs]
+
+    def forward(self, tensor: Tensor) -> Any:  # type: ignore[override]
+        futs = [self.rpc.rpc_async(name, _forward, args=(self.pipe_id, self.training)) for r, name in self.worker_map.items() if r != 0]
+        out = self.model(tensor)
+        self._pending = futs
+        return out
+
+    def backward(self) -> None:
+        """Run backward on every non-final stage (call after the final stage's ``loss.backward()``)."""
+        for f in getattr(self, "_pending", []):
+            f.wait()
+        futs = [self.rpc.rpc_async(name, _backward, args=(self.pipe_id,)) for r, name in self.worker_map.items() if r != 0]
+        self.model.back_helper()
+        for f in futs:
+            f.wait()
