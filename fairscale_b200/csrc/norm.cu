@@ -387,3 +387,69 @@ FSB_API int fsb_colsum(const void* x, long long rows, int H, float* partials, vo
   column_reduce_kernel<<<blocks, threads, 0, stream>>>(partials, strips, H, static_cast<__nv_bfloat16*>(out), nullptr);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free column sum (declared in fsb_no_alloc.h; no counterpart in the reference library).
+// The strip partials go to a fixed array in device memory instead of a workspace from the caller.
+// ---------------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "fsb_no_alloc.h"
+
+namespace {
+constexpr int kStaticStrips = 48;   // upper bound of fsb_colsum_num_strips
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) float g_colsum_scratch[kStaticStrips * FSB_COLSUM_STATIC_MAX_H];
+float* g_colsum_scratch_ptr[kMaxDevices] = {};
+std::mutex g_colsum_scratch_mutex;
+
+// Device address of the scratch array on the current device; resolved once per device.
+int colsum_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return FSB_NOALLOC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_colsum_scratch_mutex);
+  if (g_colsum_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_colsum_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return FSB_NOALLOC_ERR_SYMBOL;
+    }
+    g_colsum_scratch_ptr[dev] = p;
+  }
+  *out = g_colsum_scratch_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+FSB_API int fsb_colsum_static_max_h(void) { return FSB_COLSUM_STATIC_MAX_H; }
+
+FSB_API const char* fsb_colsum_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case FSB_NOALLOC_ERR_SHAPE: return "fsb_colsum_static: H must be a multiple of 8";
+    case FSB_NOALLOC_ERR_TOO_LARGE: return "fsb_colsum_static: H exceeds FSB_COLSUM_STATIC_MAX_H (8192); call fsb_colsum with a caller-provided workspace";
+    case FSB_NOALLOC_ERR_DEVICE: return "fsb_colsum_static: device ordinal beyond the 64 devices the library tracks";
+    case FSB_NOALLOC_ERR_SYMBOL: return "fsb_colsum_static: could not resolve the built-in workspace on this device";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "fsb_colsum_static: unknown error";
+  }
+}
+
+FSB_API int fsb_colsum_static(const void* x, long long rows, int H, void* out, cudaStream_t stream) {
+  using namespace fsb;
+  if (rows <= 0 || H <= 0) return 0;
+  if (H % 8 != 0) return FSB_NOALLOC_ERR_SHAPE;
+  if (H > FSB_COLSUM_STATIC_MAX_H) return FSB_NOALLOC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = colsum_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  const int strips = fsb_colsum_num_strips(rows);  // <= kStaticStrips
+  dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
+  // every (strip, column < H) element read by the reduction below is written here first: no clearing needed
+  colsum_partial_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, H, scratch);
+  const int threads = 128, blocks = (H + threads - 1) / threads;
+  column_reduce_kernel<<<blocks, threads, 0, stream>>>(scratch, strips, H, static_cast<__nv_bfloat16*>(out), nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
