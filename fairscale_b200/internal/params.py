@@ -48,5 +48,11 @@ def calc_grad_norm(parameters: Union[torch.Tensor, List[torch.nn.Parameter]], p:
     p = float(p)
     if p == inf:
         return max(q.grad.detach().abs().max() for q in with_grad)  # type: ignore[union-attr,return-value]
+    grads = [q.grad.detach() for q in with_grad]  # type: ignore[union-attr]
+    if p == 2.0 and grads[0].is_cuda:
+        from ..ops import multi_tensor
+
+        if multi_tensor.supported(grads):  # one launch per dtype, result stays on the device
+            return multi_tensor.l2_norm(grads).to(dtype=with_grad[0].dtype)
     per_param = torch.stack([torch.norm(q.grad.detach(), p, dtype=torch.float32) for q in with_grad])  # type: ignore[union-attr]
     return torch.norm(per_param, p).to(dtype=with_grad[0].dtype)
