@@ -1,0 +1,1 @@
+"""Experimental components; APIs here may change without notice."""
