@@ -26,6 +26,26 @@ import torch.distributed as dist
 _COUNTERS = {"all_gather": 0, "reduce_scatter": 0, "all_reduce": 0, "all_to_all": 0, "broadcast": 0, "reduce": 0}
 
 
+_LISTENERS: list = []
+
+
+def add_listener(fn: Any) -> None:
+    """Register ``fn(kind, group, out, inp)``; called before every collective issued through this module
+    (``kind`` is a key of :func:`counters`).  Used by memory / traffic trackers."""
+    if fn not in _LISTENERS:
+        _LISTENERS.append(fn)
+
+
+def remove_listener(fn: Any) -> None:
+    if fn in _LISTENERS:
+        _LISTENERS.remove(fn)
+
+
+def _notify(kind: str, group: Any, out: Any, inp: Any) -> None:
+    for fn in list(_LISTENERS):
+        fn(kind, group, out, inp)
+
+
 def counters() -> dict:
     """Number of collectives issued through this front-end since import (test instrumentation)."""
     return dict(_COUNTERS)
@@ -78,6 +98,8 @@ def _symm_for(group: Any, *tensors: torch.Tensor):
 def all_gather_into(out: torch.Tensor, shard: torch.Tensor, group: Any = None, async_op: bool = False):
     """``out[r*n:(r+1)*n] = shard of rank r`` for a flat ``out`` of ``world*n`` elements."""
     _COUNTERS["all_gather"] += 1
+    if _LISTENERS:
+        _notify("all_gather", group, out, shard)
     world = group_size(group)
     if world == 1 or not _is_real_group(group):
         out.view(-1)[: shard.numel()].copy_(shard.reshape(-1))
@@ -92,6 +114,8 @@ def all_gather_into(out: torch.Tensor, shard: torch.Tensor, group: Any = None, a
 def reduce_scatter_into(out: torch.Tensor, flat_in: torch.Tensor, group: Any = None, async_op: bool = False):
     """Sum ``flat_in`` (``world*n`` elements) over ranks; rank r keeps elements ``[r*n,(r+1)*n)``."""
     _COUNTERS["reduce_scatter"] += 1
+    if _LISTENERS:
+        _notify("reduce_scatter", group, out, flat_in)
     world = group_size(group)
     if world == 1 or not _is_real_group(group):
         out.copy_(flat_in.view(-1)[: out.numel()].view_as(out))
