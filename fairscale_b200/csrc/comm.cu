@@ -18,79 +18,9 @@
 // all_to_all_single (nn/moe/moe_layer.py:29), and fuse the element-wise work that follows them
 // (pre/post-divide, fp32 cast, gradient accumulation; MoE slot scatter / weighted combine).
 
-#include "common.cuh"
+#include "comm_dev.cuh"
 
 namespace fsb {
-
-constexpr int kMaxRanks = 8;
-constexpr uint64_t kCommWaitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
-constexpr int COMM_THREADS = 512;
-
-struct CommCtx {
-  int rank, world;
-  uint32_t epoch;             // strictly increasing per call on a channel pair
-  int channel;                // base channel; the kernel uses channel (entry) and channel + 1 (exit / mid)
-  uint32_t* pads[kMaxRanks];  // peer signal pads: pads[p][channel * kMaxRanks + src]
-  unsigned int* counter;      // local scratch counter (zero before the call, left at zero)
-  int* status;
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_peer16(const void* p) {  // L1-bypassing 16-byte load
-  return __ldcg(reinterpret_cast<const uint4*>(p));
-}
-
-// Tell every peer that this rank reached `epoch` on `channel` (one thread per peer).
-__device__ __forceinline__ void signal_peers(const CommCtx& c, int channel) {
-  if (threadIdx.x < c.world) {
-    __threadfence_system();
-    st_release_sys(c.pads[threadIdx.x] + channel * kMaxRanks + c.rank, c.epoch);
-  }
-}
-// Wait until every peer reached `epoch` on `channel`. Returns false on timeout (status word set).
-__device__ __forceinline__ bool wait_peers(const CommCtx& c, int channel) {
-  __shared__ int ok_flag;
-  if (threadIdx.x == 0) ok_flag = 1;
-  __syncthreads();
-  if (threadIdx.x < c.world) {
-    const uint32_t* mine = c.pads[c.rank] + channel * kMaxRanks + threadIdx.x;
-    const uint64_t t0 = globaltimer_ns();
-    // epochs wrap: compare as signed distance
-    while (static_cast<int32_t>(ld_acquire_sys(mine) - c.epoch) < 0) {
-      if (globaltimer_ns() - t0 > kCommWaitNs) {
-        ok_flag = 0;
-        if (c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
-  __syncthreads();
-  return ok_flag != 0;
-}
-// Grid-wide completion: the last CTA to arrive signals the peers on `channel` and waits for theirs.
-__device__ __forceinline__ void exit_barrier(const CommCtx& c, int channel) {
-  __shared__ int last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(c.counter, 1u);
-    last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (last) *c.counter = 0;
-  }
-  __syncthreads();
-  if (last) {
-    signal_peers(c, channel);
-    wait_peers(c, channel);
-  }
-}
 
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(COMM_THREADS) barrier_kernel(CommCtx c) {
@@ -99,7 +29,6 @@ __global__ void __launch_bounds__(COMM_THREADS) barrier_kernel(CommCtx c) {
 }
 
 // out[p * n16 + i] = src_p[i] for every rank p; src pointers address each rank's shard (16-byte units)
-struct PtrTable { const void* p[kMaxRanks]; };
 
 __global__ void __launch_bounds__(COMM_THREADS) all_gather_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);

@@ -1,0 +1,456 @@
+// Tensor-parallel GEMMs fused with their collective, one kernel each, over NVLink peer memory.
+//
+//   ag_gemm :  C[M, N] = concat_r(A_r)[M, K] * B[N, K]^T           all-gather -> GEMM
+//              (A is sharded by rows: rank r owns the Mc = M / world rows of chunk r)
+//   gemm_rs :  Out[Mc, N] = sum_r ( A_r[M, Kr] * B_r[N, Kr]^T )[rows of my chunk]     GEMM -> reduce-scatter
+//
+// Both are persistent kernels whose first `n_comm` CTAs move data while the remaining CTAs run the tcgen05
+// main loop of gemm_tcgen05.cu (TMA producer warp / MMA warp / 4 epilogue warps, accumulators double-buffered
+// in TMEM).  Tiles are ordered chunk by chunk so that communication of one chunk overlaps the math of another:
+//
+//   ag_gemm  the GEMM CTAs start with the rows this rank already owns; meanwhile the copy CTAs pull the peers'
+//            chunks (16-byte L1-bypassing peer loads, remote chunks in ring order) into the local gather
+//            buffer and publish one counter per chunk; a producer warp waits for that counter (bounded) before
+//            the first TMA load of a chunk.  Every remote byte crosses NVLink once; TMA only ever reads this
+//            GPU's own memory.  The gather buffer is kept: backward needs the gathered activations.
+//   gemm_rs  rank r computes the chunks in the order r+1, r+2, ..., r (its own last) and writes bf16 partial
+//            tiles to its symmetric staging buffer; the epilogue warp that completes a chunk raises a flag
+//            in the owner's signal pad (st.release.sys).  The owner's reduce CTAs wait for each peer's flag
+//            (bounded), pull that peer's partial chunk and accumulate in fp32, adding their own partial (and the
+//            bias) last.
+//
+// Cross-GPU ordering uses the epoch flags of comm_dev.cuh; an exit barrier keeps a rank's buffers alive until
+// every peer is done reading them.  No TMA multicast, no cluster launch.  Replaces all-gather + F.linear and
+// F.linear + all-reduce of the reference's tensor-parallel layers
+// (fairscale/nn/model_parallel/layers.py:290,380-382; mappings.py:42-78).
+
+#include "comm_dev.cuh"
+#include "gemm_tile.cuh"
+
+namespace fsb {
+
+constexpr int FUSED_BLOCK_N = 256;
+
+struct FusedParams {
+  CommCtx c;
+  PtrTable peer;          // ag: every rank's A shard; rs: every rank's staging buffer [M, N]
+  uint4* gather;          // ag: local gather buffer [M, K]
+  uint32_t* counts;       // per-chunk counters in local memory (monotonic across calls)
+  uint32_t target;        // value a chunk counter reaches when the chunk is complete in this call
+  long long chunk16;      // 16-byte units per chunk (ag: Mc * K * 2 / 16; rs: Mc * N * 2 / 16)
+  float* acc;             // rs: fp32 scratch [Mc * N]
+  __nv_bfloat16* out;     // rs: result [Mc, N]
+  const __nv_bfloat16* out_bias;  // rs: bias added once after the reduction (may be null)
+  int n_comm;             // CTAs [0, n_comm) communicate, the rest compute
+  int Mc;                 // rows per chunk
+};
+
+__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  while (static_cast<int32_t>(ld_acquire_gpu(ctr) - target) < 0) {
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > kCommWaitNs) {
+      *abort_flag = 1;
+      return false;
+    }
+    __nanosleep(128);
+  }
+  return true;
+}
+
+// The tcgen05 main loop shared by both kernels.  MODE 0: ag_gemm, MODE 1: gemm_rs.
+template <int MODE>
+__device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                               const GemmParams& p, const FusedParams& f, uint8_t* smem) {
+  constexpr int BLOCK_N = FUSED_BLOCK_N;
+  using L = SmemLayout<BLOCK_N>;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = blockIdx.x - f.n_comm, G = gridDim.x - f.n_comm;
+  const int world = f.c.world, rank = f.c.rank;
+
+  const int tiles_mc = f.Mc / BLOCK_M;
+  const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int tiles_per_chunk = tiles_mc * tiles_n;
+  const int num_tiles = tiles_per_chunk * world;
+  const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  // chunk visited k-th: ag starts at home, rs ends at home
+  auto chunk_of = [&](int k) { return (rank + k + (MODE == 1 ? 1 : 0)) % world; };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BLOCK_N);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int ready_chunk = -1;
+      for (int tile = g; tile < num_tiles && ok; tile += G) {
+        const int k = tile / tiles_per_chunk;
+        const int chunk = chunk_of(k);
+        int tm, tn;
+        tile_coords(tile - k * tiles_per_chunk, tiles_mc, tiles_n, tm, tn);
+        const int n0 = tn * BLOCK_N;
+        const bool local_a = (MODE == 0) && (chunk == rank);
+        const int m0 = local_a ? tm * BLOCK_M : chunk * f.Mc + tm * BLOCK_M;
+        if (MODE == 0 && !local_a && ready_chunk != chunk) {
+          // the copy CTAs publish a chunk with generic-proxy stores; order them before this thread's TMA reads
+          if (!wait_counter(f.counts + chunk, f.target, abort_flag)) { ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");
+          ready_chunk = chunk;
+        }
+        const CUtensorMap* ta = local_a ? &tmap_a_local : &tmap_a;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          tma_load_2d(sa, ta, &full_bar[stage], k0, m0);
+          if (!p.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, true, false, p.b_mn_major != 0);
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
+      const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = g; tile < num_tiles && ok; tile += G) {
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * 32u, 16u, 1024u);
+            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = g; tile < num_tiles && ok; tile += G) {
+      const int k = tile / tiles_per_chunk;
+      const int chunk = chunk_of(k);
+      int tm, tn;
+      tile_coords(tile - k * tiles_per_chunk, tiles_mc, tiles_n, tm, tn);
+      const int row = chunk * f.Mc + tm * BLOCK_M + quad * 32 + lane;
+      const int n0 = tn * BLOCK_N;
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
+      epilogue_rows<BLOCK_N>(t_base, row, n0, p);
+      tc_fence_before_sync();
+      if (MODE == 1) {
+        // publish this warp's share of the tile; the warp that completes the chunk tells its owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t prev = atomicAdd(f.counts + chunk, 1u);
+          if (prev + 1u == f.target) {
+            __threadfence_system();
+            st_release_sys(f.c.pads[chunk] + f.c.channel * kMaxRanks + rank, f.c.epoch);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, FSB_ERR_WAIT_TIMEOUT);
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BLOCK_N);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ ag_gemm
+__device__ __forceinline__ void ag_copy_cta(const FusedParams& f) {
+  const CommCtx& c = f.c;
+  if (blockIdx.x == 0) signal_peers(c, c.channel);  // my shard is ready (stream order) -> peers may read it
+  if (!wait_peers(c, c.channel)) return;
+  const long long stride = static_cast<long long>(f.n_comm) * blockDim.x;
+  for (int k = 1; k <= c.world; ++k) {
+    const int pr = (c.rank + k) % c.world;  // remote chunks in ring order, the local copy last (nothing waits for it)
+    const uint4* s = reinterpret_cast<const uint4*>(f.peer.p[pr]);
+    uint4* d = f.gather + static_cast<long long>(pr) * f.chunk16;
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 7 * stride < f.chunk16; i += 8 * stride) {  // 8 loads in flight per thread hide the NVLink latency
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = ld_peer16(s + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) d[i + u * stride] = v[u];
+    }
+    for (; i < f.chunk16; i += stride) d[i] = ld_peer16(s + i);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(f.counts + pr, 1u);
+  }
+  exit_barrier_n(c, c.channel + 1, static_cast<unsigned int>(f.n_comm));  // peers are done reading my shard
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ CUtensorMap tmap_a_gather,
+               const __grid_constant__ CUtensorMap tmap_b, GemmParams p, FusedParams f) {
+  extern __shared__ uint8_t smem_raw[];
+  if (static_cast<int>(blockIdx.x) < f.n_comm) {
+    ag_copy_cta(f);
+    return;
+  }
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  fused_gemm_cta<0>(tmap_a_local, tmap_a_gather, tmap_b, p, f, smem);
+}
+
+// ------------------------------------------------------------------------------------------------ gemm_rs
+__device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { o[2 * i] = __low2float(h[i]); o[2 * i + 1] = __high2float(h[i]); }
+}
+
+__device__ __forceinline__ void rs_reduce_cta(const FusedParams& f, int N) {
+  const CommCtx& c = f.c;
+  __shared__ int ok_flag;
+  const long long stride = static_cast<long long>(f.n_comm) * blockDim.x;
+  const int n16_row = N / 8;
+  for (int j = 0; j < c.world; ++j) {
+    const int s = (c.rank - 1 - j + 2 * c.world) % c.world;  // the order in which the peers finish my chunk; myself last
+    if (threadIdx.x == 0) {
+      ok_flag = 1;
+      const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + s;
+      const uint64_t t0 = globaltimer_ns();
+      while (static_cast<int32_t>(ld_acquire_sys(flag) - c.epoch) < 0) {
+        if (globaltimer_ns() - t0 > kCommWaitNs) {
+          ok_flag = 0;
+          if (c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
+          break;
+        }
+        __nanosleep(128);
+      }
+    }
+    __syncthreads();
+    if (!ok_flag) return;
+    const uint4* src = reinterpret_cast<const uint4*>(f.peer.p[s]) + static_cast<long long>(c.rank) * f.chunk16;
+    const bool first = (j == 0), last = (j == c.world - 1);
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < f.chunk16; i += stride) {
+      float v[8];
+      unpack8(ld_peer16(src + i), v);
+      float4* a = reinterpret_cast<float4*>(f.acc) + 2 * i;
+      if (!first) {
+        const float4 a0 = a[0], a1 = a[1];
+        v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
+        v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+      }
+      if (!last) {
+        a[0] = make_float4(v[0], v[1], v[2], v[3]);
+        a[1] = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+        if (f.out_bias != nullptr) {
+          float b[8];
+          unpack8(*reinterpret_cast<const uint4*>(f.out_bias + static_cast<int>(i % n16_row) * 8), b);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] += b[u];
+        }
+        Vec16<__nv_bfloat16> o;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) o.v[u] = __float2bfloat16_rn(v[u]);
+        st16(f.out + i * 8, o);
+      }
+    }
+    __syncthreads();
+  }
+  exit_barrier_n(c, c.channel + 1, static_cast<unsigned int>(f.n_comm));  // peers are done reading my staging buffer
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p, FusedParams f) {
+  extern __shared__ uint8_t smem_raw[];
+  if (static_cast<int>(blockIdx.x) < f.n_comm) {
+    rs_reduce_cta(f, p.N);
+    return;
+  }
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  fused_gemm_cta<1>(tmap_a, tmap_a, tmap_b, p, f, smem);
+}
+
+}  // namespace fsb
+
+// C ABI ------------------------------------------------------------------------------------------
+static fsb::CommCtx fused_ctx(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, int* status) {
+  fsb::CommCtx c{};
+  c.rank = rank; c.world = world; c.epoch = epoch; c.channel = channel;
+  for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) c.pads[i] = static_cast<uint32_t*>(pads[i]);
+  c.counter = static_cast<unsigned int*>(counter);
+  c.status = status;
+  return c;
+}
+
+static int fused_grid(int n_comm, int tiles, int* grid_out) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_comm < 1 || n_comm >= sms) return -1;
+  int gemm_ctas = sms - n_comm;  // every CTA must be resident at once: the compute CTAs wait for the copy CTAs
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  *grid_out = n_comm + gemm_ctas;
+  return 0;
+}
+
+// C[M, N] (bf16, ldc) = epilogue( gather(A)[M, K] * B^T ).  a_peers[r]: rank r's shard [Mc, K] (contiguous, in the
+// symmetric heap); a_local: this rank's shard; gather: local [M, K] buffer that receives every chunk.
+// B is [N, K] (K-major) or [K, N] (b_mn_major).  counts: `world` uint32 in local memory, zero at first use;
+// target: cumulative n_comm * (number of calls that used `counts`), this call included.
+FSB_API int fsb_ag_gemm_bf16(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                             void* const* a_peers, const void* a_local, void* gather, const void* B, void* C, const void* bias,
+                             void* aux_out, int M, int N, int K, int ldb, int ldc, int b_mn_major, int epilogue, void* counts,
+                             unsigned target, int n_comm, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world < 1 || world > kMaxRanks || M % world) return -1;
+  const int Mc = M / world;
+  if (Mc % BLOCK_M || K % 8 || ldb % 8 || ldc % 8) return -1;
+  if (epilogue != EPI_NONE && epilogue != EPI_BIAS && epilogue != EPI_BIAS_GELU) return -1;
+  CUtensorMap tl, tg, tb;
+  bool ok = fsb_host::encode_2d_16bit(&tl, a_local, (uint64_t)K, (uint64_t)Mc, (uint64_t)K, BLOCK_K, BLOCK_M);
+  ok &= fsb_host::encode_2d_16bit(&tg, gather, (uint64_t)K, (uint64_t)M, (uint64_t)K, BLOCK_K, BLOCK_M);
+  if (!b_mn_major) ok &= fsb_host::encode_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, FUSED_BLOCK_N);
+  else             ok &= fsb_host::encode_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BLOCK_K);
+  if (!ok) return -1;
+  GemmParams p{};
+  p.C = C; p.bias = static_cast<const __nv_bfloat16*>(bias); p.aux = nullptr; p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ldc; p.a_mn_major = 0; p.b_mn_major = b_mn_major;
+  p.epilogue = epilogue; p.out_f32 = 0; p.accumulate_c = 0; p.status = status;
+  FusedParams f{};
+  f.c = fused_ctx(rank, world, epoch, channel, pads, counter, status);
+  for (int i = 0; i < world; ++i) f.peer.p[i] = a_peers[i];
+  f.gather = static_cast<uint4*>(gather);
+  f.counts = static_cast<uint32_t*>(counts);
+  f.target = target;
+  f.chunk16 = static_cast<long long>(Mc) * K * 2 / 16;
+  f.n_comm = n_comm; f.Mc = Mc;
+  int grid = 0;
+  const int tiles = (M / BLOCK_M) * ((N + FUSED_BLOCK_N - 1) / FUSED_BLOCK_N);
+  if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<FUSED_BLOCK_N>::TOTAL);
+    attr_set = true;
+  }
+  ag_gemm_kernel<<<grid, GEMM_THREADS, SmemLayout<FUSED_BLOCK_N>::TOTAL, stream>>>(tl, tg, tb, p, f);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[Mc, N] (bf16) = sum over ranks of (A[M, K] * B^T)[my chunk's rows] (+ out_bias).  stage_peers[r]: rank r's
+// staging buffer [M, N] bf16 in the symmetric heap (this rank writes stage_peers[rank]); acc: fp32 scratch [Mc * N];
+// counts / target as for ag_gemm but counting 4 * tiles-per-chunk arrivals per call.
+FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                             void* const* stage_peers, const void* A, const void* B, void* out, const void* out_bias, void* acc,
+                             int M, int N, int K, int lda, int ldb, int b_mn_major, void* counts, unsigned target, int n_comm,
+                             int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world < 1 || world > kMaxRanks || M % world) return -1;
+  const int Mc = M / world;
+  if (Mc % BLOCK_M || N % 8 || lda % 8 || ldb % 8) return -1;
+  CUtensorMap ta, tb;
+  bool ok = fsb_host::encode_2d_16bit(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M);
+  if (!b_mn_major) ok &= fsb_host::encode_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, FUSED_BLOCK_N);
+  else             ok &= fsb_host::encode_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BLOCK_K);
+  if (!ok) return -1;
+  GemmParams p{};
+  p.C = const_cast<void*>(stage_peers[rank]);
+  p.M = M; p.N = N; p.K = K; p.ldc = N; p.ld_aux = N; p.a_mn_major = 0; p.b_mn_major = b_mn_major;
+  p.epilogue = EPI_NONE; p.out_f32 = 0; p.accumulate_c = 0; p.status = status;
+  FusedParams f{};
+  f.c = fused_ctx(rank, world, epoch, channel, pads, counter, status);
+  for (int i = 0; i < world; ++i) f.peer.p[i] = stage_peers[i];
+  f.counts = static_cast<uint32_t*>(counts);
+  f.target = target;
+  f.chunk16 = static_cast<long long>(Mc) * N * 2 / 16;
+  f.acc = static_cast<float*>(acc);
+  f.out = static_cast<__nv_bfloat16*>(out);
+  f.out_bias = static_cast<const __nv_bfloat16*>(out_bias);
+  f.n_comm = n_comm; f.Mc = Mc;
+  int grid = 0;
+  const int tiles = (M / BLOCK_M) * ((N + FUSED_BLOCK_N - 1) / FUSED_BLOCK_N);
+  if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<FUSED_BLOCK_N>::TOTAL);
+    attr_set = true;
+  }
+  gemm_rs_kernel<<<grid, GEMM_THREADS, SmemLayout<FUSED_BLOCK_N>::TOTAL, stream>>>(ta, tb, p, f);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// arrivals per chunk and call that fsb_gemm_rs_bf16 counts (the caller accumulates `target` with it)
+FSB_API int fsb_gemm_rs_arrivals(int M, int N, int world) {
+  using namespace fsb;
+  if (world < 1 || M % world || (M / world) % BLOCK_M) return -1;
+  return 4 * (M / world / BLOCK_M) * ((N + FUSED_BLOCK_N - 1) / FUSED_BLOCK_N);
+}

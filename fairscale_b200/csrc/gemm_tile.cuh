@@ -1,0 +1,149 @@
+// Pieces shared by the tcgen05 GEMM kernels: tile constants, the shared-memory layout of the operand ring,
+// the L2-friendly tile order and the fused epilogue that drains one TMEM accumulator into global memory.
+#pragma once
+
+#include "sm100.cuh"
+
+namespace fsb {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;   // 64 bf16 = 128 B = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+
+enum Epilogue : int {
+  EPI_NONE = 0,           // C = acc
+  EPI_BIAS = 1,           // C = acc + bias[n]
+  EPI_BIAS_GELU = 2,      // C = gelu(acc + bias[n]);  aux_out (optional) = acc + bias[n]
+  EPI_BIAS_RESIDUAL = 3,  // C = acc + bias[n] + aux[m,n]
+  EPI_DGELU = 4,          // C = acc * gelu'(aux[m,n])
+  EPI_RESIDUAL = 5,       // C = acc + aux[m,n]
+};
+
+struct GemmParams {
+  void* C;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux;
+  __nv_bfloat16* aux_out;
+  int M, N, K;
+  int ldc, ld_aux;
+  int a_mn_major, b_mn_major;
+  int epilogue;
+  int out_f32;       // C is fp32 (else bf16)
+  int accumulate_c;  // C += result (fp32 output only)
+  int* status;
+};
+
+template <int BLOCK_N>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Groups of 16 M-tiles walk N together, so concurrently running CTAs share A and B slabs in L2.
+  constexpr int GROUP_M = 16;
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+// Drain one accumulator (this warp's 32 lanes x BLOCK_N columns starting at TMEM address t_base) through the
+// fused epilogue into global memory. `row` is the global output row owned by this thread.
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_rows(uint32_t t_base, int row, int n0, const GemmParams& p) {
+  const bool row_ok = row < p.M;
+  const bool vec_ok = (p.ldc % 8 == 0) && (p.ld_aux % 8 == 0);
+#pragma unroll 1
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 32), r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (!row_ok || col0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    const bool full = vec_ok && (col0 + 32 <= p.N);
+    const int epi = p.epilogue;
+    if (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESIDUAL) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+    }
+    if (epi == EPI_BIAS_GELU) {
+      if (p.aux_out != nullptr) {
+        __nv_bfloat16* po = p.aux_out + static_cast<size_t>(row) * p.ld_aux + col0;
+        if (full) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            Vec16<__nv_bfloat16> o;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
+            st16(po + q * 8, o);
+          }
+        } else {
+          for (int i = 0; i < 32 && col0 + i < p.N; ++i) po[i] = __float2bfloat16_rn(v[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+    } else if (epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU) {
+      const __nv_bfloat16* pa = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
+      float a[32];
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          Vec16<__nv_bfloat16> x = ld16(pa + q * 8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[q * 8 + i] = __bfloat162float(x.v[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) a[i] = (col0 + i < p.N) ? __bfloat162float(pa[i]) : 0.f;
+      }
+      if (epi == EPI_DGELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(a[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += a[i];
+      }
+    }
+    if (p.out_f32) {
+      float* pc = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+      if (p.accumulate_c) {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] += v[i];
+      } else if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(pc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = v[i];
+      }
+    } else {
+      __nv_bfloat16* pc = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          Vec16<__nv_bfloat16> o;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[q * 8 + i]);
+          st16(pc + q * 8, o);
+        }
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) pc[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  }
+}
+
+}  // namespace fsb

@@ -1,0 +1,265 @@
+"""Sequence-parallel tensor-parallel linears whose collective runs inside the GEMM kernel.
+
+``all_gather_linear(x_shard, W, b, group)``      : ``y = all_gather(x_shard) @ W^T + b``            (column-parallel)
+``linear_reduce_scatter(x, W, b, group)``        : ``y_shard = reduce_scatter(x @ W^T) + b``        (row-parallel)
+
+With an NVLink workspace for ``group`` (:func:`fairscale_b200.parallel.nvlink.enable`) and bf16 CUDA tensors each
+call is ONE kernel of ``csrc/gemm_comm_tcgen05.cu``: copy / reduce CTAs move chunks over peer memory while the
+tcgen05 CTAs compute the chunks in an order that hides the transfer.  The backward of each is the other fused
+kernel (the gradient of an all-gather is a reduce-scatter and vice versa) plus a local wgrad GEMM on the
+already-gathered operand, so a transformer layer does no stand-alone tensor-parallel collective at all.  The
+reference does these steps as ``all_reduce`` + ``F.linear`` (fairscale/nn/model_parallel/layers.py:290,380-382;
+mappings.py:42-78).
+
+Anywhere else (CPU, gloo, other dtypes, shapes the kernels do not take) the same functions run the collective
+and the matmul separately through :mod:`fairscale_b200.parallel.comm`.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from ..ops import _bind
+from ..ops import gemm as gemm_ops
+from ..ops.reduce import column_sum
+from . import comm, symm
+
+_AG_CHANNEL, _RS_CHANNEL = 16, 18  # signal-pad channels (entry / flags, exit) outside the collective lanes
+_SIGS_DONE = False
+
+
+def _sigs() -> None:
+    global _SIGS_DONE
+    if _SIGS_DONE:
+        return
+    from ctypes import c_int, c_uint, c_void_p
+
+    head = [c_int, c_int, c_uint, c_int, c_void_p, c_void_p]
+    S = _bind._SIGNATURES
+    S["fsb_ag_gemm_bf16"] = head + [c_void_p] * 7 + [c_int] * 7 + [c_void_p, c_uint, c_int, c_void_p, c_void_p]
+    S["fsb_gemm_rs_bf16"] = head + [c_void_p] * 6 + [c_int] * 6 + [c_void_p, c_uint, c_int, c_void_p, c_void_p]
+    S["fsb_gemm_rs_arrivals"] = [c_int, c_int, c_int]
+    _SIGS_DONE = True
+
+
+def comm_ctas() -> int:
+    """CTAs (SMs) of a fused kernel that move data instead of computing (env ``FSB200_FUSED_COMM_CTAS``)."""
+    return int(os.environ.get("FSB200_FUSED_COMM_CTAS", "16"))
+
+
+class _State:
+    """Per-workspace bookkeeping of the fused kernels: epochs, monotonic chunk counters and their targets."""
+
+    def __init__(self, ws: Any):
+        self.ws = ws
+        dev = ws.device
+        self.ag_counts = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.rs_counts = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.ag_target = 0
+        self.rs_target = 0
+        self.ag_epoch = 0
+        self.rs_epoch = 0
+        self.acc: Dict[int, torch.Tensor] = {}
+
+
+_STATES: Dict[int, _State] = {}
+
+
+def _state(ws: Any) -> _State:
+    st = _STATES.get(id(ws))
+    if st is None:
+        _sigs()
+        st = _STATES[id(ws)] = _State(ws)
+    return st
+
+
+def _workspace(group: Any, *tensors: torch.Tensor) -> Optional[Any]:
+    if comm.comm_mode() == "nccl" or not all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors):
+        return None
+    if not _bind.use_native(*tensors):
+        return None
+    return symm.workspace_for(group if group is not None else dist.group.WORLD)
+
+
+def ag_gemm_supported(ws: Any, Mc: int, K: int, N: int) -> bool:
+    return ws is not None and Mc % 128 == 0 and K % 8 == 0 and N % 8 == 0
+
+
+def gemm_rs_supported(ws: Any, M: int, K: int, N: int) -> bool:
+    return ws is not None and M % ws.world == 0 and (M // ws.world) % 128 == 0 and K % 8 == 0 and N % 8 == 0
+
+
+# ---------------------------------------------------------------------------------------------- raw kernels
+def ag_gemm(ws: Any, x_shard: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], *, w_is_kn: bool = False,
+            gelu: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(y[M, N], gathered[M, K])`` with ``M = world * Mc``.  ``w`` is ``[N, K]``, or ``[K, N]`` when ``w_is_kn``."""
+    st = _state(ws)
+    Mc, K = x_shard.shape
+    N = w.shape[1] if w_is_kn else w.shape[0]
+    M = Mc * ws.world
+    dev = x_shard.device
+    window = ws.scratch("ag_in", (Mc, K), torch.bfloat16)
+    if ws.offset_of(x_shard) is None or not x_shard.is_contiguous():
+        window.copy_(x_shard)
+        src_off = ws.offset_of(window)
+    else:
+        src_off = ws.offset_of(x_shard)
+    gathered = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    n_comm = comm_ctas()
+    st.ag_epoch = (st.ag_epoch + 1) & 0x7FFFFFFF
+    st.ag_target = (st.ag_target + n_comm) & 0xFFFFFFFF
+    epi = 0 if bias is None else (2 if gelu else 1)
+    a_local = ws.base + src_off
+    _bind.call(
+        "fsb_ag_gemm_bf16", ws.rank, ws.world, st.ag_epoch, _AG_CHANNEL, ws.pad_ptrs, ws.counters.data_ptr() + 4 * 16,
+        ws.peers(src_off), a_local, gathered.data_ptr(), w.data_ptr(), y.data_ptr(), _bind.ptr(bias), None,
+        M, N, K, w.stride(0), N, int(w_is_kn), epi, st.ag_counts.data_ptr(), st.ag_target, n_comm,
+        _bind.status_ptr(dev), _bind.stream_ptr(dev),
+    )
+    return y, gathered
+
+
+def gemm_rs(ws: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], *, w_is_kn: bool = False) -> torch.Tensor:
+    """``out[Mc, N] = (sum over ranks of x @ w^T)[this rank's rows] + bias``; ``x`` is ``[M, K_local]``."""
+    st = _state(ws)
+    M, K = x.shape
+    N = w.shape[1] if w_is_kn else w.shape[0]
+    Mc = M // ws.world
+    dev = x.device
+    x = x.contiguous()
+    stage = ws.scratch("rs_stage", (M, N), torch.bfloat16)
+    acc = st.acc.get(Mc * N)
+    if acc is None:
+        acc = st.acc[Mc * N] = torch.empty(Mc * N, dtype=torch.float32, device=dev)
+    out = torch.empty((Mc, N), dtype=torch.bfloat16, device=dev)
+    n_comm = comm_ctas()
+    arrivals = _bind.fn("fsb_gemm_rs_arrivals")(M, N, ws.world)
+    st.rs_epoch = (st.rs_epoch + 1) & 0x7FFFFFFF
+    st.rs_target = (st.rs_target + arrivals) & 0xFFFFFFFF
+    _bind.call(
+        "fsb_gemm_rs_bf16", ws.rank, ws.world, st.rs_epoch, _RS_CHANNEL, ws.pad_ptrs, ws.counters.data_ptr() + 4 * 17,
+        ws.peers(ws.offset_of(stage)), x.data_ptr(), w.data_ptr(), out.data_ptr(), _bind.ptr(bias), acc.data_ptr(),
+        M, N, K, x.stride(0), w.stride(0), int(w_is_kn), st.rs_counts.data_ptr(), st.rs_target, n_comm,
+        _bind.status_ptr(dev), _bind.stream_ptr(dev),
+    )
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- unfused path
+def _all_gather_rows(x: torch.Tensor, group: Any) -> torch.Tensor:
+    world = comm.group_size(group)
+    out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    comm.all_gather_into(out.view(-1), x.contiguous().view(-1), group=group)
+    return out
+
+
+def _reduce_scatter_rows(x: torch.Tensor, group: Any) -> torch.Tensor:
+    world = comm.group_size(group)
+    out = torch.empty((x.shape[0] // world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if world > 1 and dist.get_backend(group) == "gloo":  # gloo has no reduce-scatter
+        full = x.contiguous().clone()
+        dist.all_reduce(full, group=group)
+        r = comm.group_rank(group)
+        out.copy_(full[r * out.shape[0] : (r + 1) * out.shape[0]])
+        return out
+    comm.reduce_scatter_into(out.view(-1), x.contiguous().view(-1), group=group)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- autograd
+class _AllGatherLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], group: Any) -> torch.Tensor:  # type: ignore[override]
+        ctx.group = group
+        ws = _workspace(group, x, w)
+        if ag_gemm_supported(ws, x.shape[0], x.shape[1], w.shape[0]):
+            y, gathered = ag_gemm(ws, x, w, bias)
+            ctx.fused = True
+        else:
+            gathered = _all_gather_rows(x, group)
+            y = F.linear(gathered, w, bias)
+            ctx.fused = False
+        ctx.save_for_backward(gathered, w)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, dy: torch.Tensor) -> Any:  # type: ignore[override]
+        gathered, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        ws = _workspace(ctx.group, dy, w) if ctx.fused else None
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            if gemm_rs_supported(ws, dy.shape[0], dy.shape[1], w.shape[1]):
+                dx = gemm_rs(ws, dy, w, None, w_is_kn=True)  # dX = reduce_scatter(dY @ W)
+            else:
+                dx = _reduce_scatter_rows(dy @ w, ctx.group)
+        if ctx.needs_input_grad[1]:
+            dw = gemm_ops.linear_wgrad(dy, gathered).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = column_sum(dy) if _bind.use_native(dy) and dy.dtype == torch.bfloat16 else dy.sum(0)
+        return dx, dw, db, None
+
+
+class _LinearReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], group: Any) -> torch.Tensor:  # type: ignore[override]
+        ctx.group = group
+        ws = _workspace(group, x, w)
+        if gemm_rs_supported(ws, x.shape[0], x.shape[1], w.shape[0]):
+            out = gemm_rs(ws, x, w, bias)
+            ctx.fused = True
+        else:
+            out = _reduce_scatter_rows(F.linear(x, w), group)
+            if bias is not None:
+                out = out + bias
+            ctx.fused = False
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, dout: torch.Tensor) -> Any:  # type: ignore[override]
+        x, w = ctx.saved_tensors
+        dout = dout.contiguous()
+        ws = _workspace(ctx.group, dout, w) if ctx.fused else None
+        dx = dw = db = None
+        if ag_gemm_supported(ws, dout.shape[0], dout.shape[1], w.shape[1]):
+            dx, gathered = ag_gemm(ws, dout, w, None, w_is_kn=True)  # dX = all_gather(dOut) @ W
+        else:
+            gathered = _all_gather_rows(dout, ctx.group)
+            dx = gathered @ w if ctx.needs_input_grad[0] else None
+        if ctx.needs_input_grad[1]:
+            dw = gemm_ops.linear_wgrad(gathered, x).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            # the bias is replicated but every rank saw different tokens: sum its gradient over the group
+            db = (column_sum(dout) if _bind.use_native(dout) and dout.dtype == torch.bfloat16 else dout.sum(0)).clone()
+            if comm.group_size(ctx.group) > 1:
+                comm.all_reduce(db, group=ctx.group)
+        return dx, dw, db, None
+
+
+def _flatten(x: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, ...]]:
+    return x.reshape(-1, x.shape[-1]), tuple(x.shape[:-1])
+
+
+def all_gather_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], group: Any = None) -> torch.Tensor:
+    """``x``: this rank's token shard ``[tokens / world, ..., K]`` (sharded along dim 0); returns ``[tokens, ..., N_local]``."""
+    x2, lead = _flatten(x)
+    y = _AllGatherLinear.apply(x2, weight, bias, group)
+    world = comm.group_size(group)
+    return y.view((lead[0] * world,) + lead[1:] + (y.shape[-1],)) if lead else y
+
+
+def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], group: Any = None) -> torch.Tensor:
+    """``x``: ``[tokens, ..., K_local]``; returns this rank's token shard ``[tokens / world, ..., N]`` of the reduced product."""
+    x2, lead = _flatten(x)
+    y = _LinearReduceScatter.apply(x2, weight, bias, group)
+    world = comm.group_size(group)
+    return y.view((lead[0] // world,) + lead[1:] + (y.shape[-1],)) if lead else y
