@@ -16,8 +16,9 @@
 //   gemm_rs  rank r computes the chunks in the order r+1, r+2, ..., r (its own last) and writes bf16 partial
 //            tiles to its symmetric staging buffer; the epilogue warp that completes a chunk raises a flag
 //            in the owner's signal pad (st.release.sys).  The owner's reduce CTAs wait for each peer's flag
-//            (bounded), pull that peer's partial chunk and accumulate in fp32, adding their own partial (and the
-//            bias) last.
+//            (bounded), pull that peer's partial chunk (8 loads in flight per thread) and accumulate it in an fp32
+//            scratch while the tensor-core CTAs are still busy.  When a CTA of either kind runs out of work it
+//            joins the final pass, out = scratch + own partial + bias, which therefore runs on every SM.
 //
 // Cross-GPU ordering uses the epoch flags of comm_dev.cuh; an exit barrier keeps a rank's buffers alive until
 // every peer is done reading them.  No TMA multicast, no cluster launch.  Replaces all-gather + F.linear and
@@ -37,6 +38,7 @@ struct FusedParams {
   uint4* gather;          // ag: local gather buffer [M, K]
   uint32_t* counts;       // per-chunk counters in local memory (monotonic across calls)
   uint32_t target;        // value a chunk counter reaches when the chunk is complete in this call
+  uint32_t target_comm;   // rs: value counts[kMaxRanks] reaches when every reduce CTA has folded in all peers
   long long chunk16;      // 16-byte units per chunk (ag: Mc * K * 2 / 16; rs: Mc * N * 2 / 16)
   float* acc;             // rs: fp32 scratch [Mc * N]
   __nv_bfloat16* out;     // rs: result [Mc, N]
@@ -275,13 +277,13 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
   for (int i = 0; i < 4; ++i) { o[2 * i] = __low2float(h[i]); o[2 * i + 1] = __high2float(h[i]); }
 }
 
-__device__ __forceinline__ void rs_reduce_cta(const FusedParams& f, int N) {
+// Peers' partials of my chunk -> fp32 scratch (first peer writes, the others add).  Returns false after a timeout.
+__device__ __forceinline__ bool rs_reduce_cta(const FusedParams& f) {
   const CommCtx& c = f.c;
   __shared__ int ok_flag;
   const long long stride = static_cast<long long>(f.n_comm) * blockDim.x;
-  const int n16_row = N / 8;
-  for (int j = 0; j < c.world; ++j) {
-    const int s = (c.rank - 1 - j + 2 * c.world) % c.world;  // the order in which the peers finish my chunk; myself last
+  for (int j = 0; j + 1 < c.world; ++j) {
+    const int s = (c.rank - 1 - j + 2 * c.world) % c.world;  // the order in which the peers finish my chunk
     if (threadIdx.x == 0) {
       ok_flag = 1;
       const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + s;
@@ -296,48 +298,98 @@ __device__ __forceinline__ void rs_reduce_cta(const FusedParams& f, int N) {
       }
     }
     __syncthreads();
-    if (!ok_flag) return;
+    if (!ok_flag) return false;
     const uint4* src = reinterpret_cast<const uint4*>(f.peer.p[s]) + static_cast<long long>(c.rank) * f.chunk16;
-    const bool first = (j == 0), last = (j == c.world - 1);
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < f.chunk16; i += stride) {
-      float v[8];
-      unpack8(ld_peer16(src + i), v);
-      float4* a = reinterpret_cast<float4*>(f.acc) + 2 * i;
+    float4* acc = reinterpret_cast<float4*>(f.acc);
+    const bool first = (j == 0);
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 7 * stride < f.chunk16; i += 8 * stride) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = ld_peer16(src + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        float x[8];
+        unpack8(v[u], x);
+        float4* a = acc + 2 * (i + u * stride);
+        if (!first) {
+          const float4 a0 = a[0], a1 = a[1];
+          x[0] += a0.x; x[1] += a0.y; x[2] += a0.z; x[3] += a0.w;
+          x[4] += a1.x; x[5] += a1.y; x[6] += a1.z; x[7] += a1.w;
+        }
+        a[0] = make_float4(x[0], x[1], x[2], x[3]);
+        a[1] = make_float4(x[4], x[5], x[6], x[7]);
+      }
+    }
+    for (; i < f.chunk16; i += stride) {
+      float x[8];
+      unpack8(ld_peer16(src + i), x);
+      float4* a = acc + 2 * i;
       if (!first) {
         const float4 a0 = a[0], a1 = a[1];
-        v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
-        v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+        x[0] += a0.x; x[1] += a0.y; x[2] += a0.z; x[3] += a0.w;
+        x[4] += a1.x; x[5] += a1.y; x[6] += a1.z; x[7] += a1.w;
       }
-      if (!last) {
-        a[0] = make_float4(v[0], v[1], v[2], v[3]);
-        a[1] = make_float4(v[4], v[5], v[6], v[7]);
-      } else {
-        if (f.out_bias != nullptr) {
-          float b[8];
-          unpack8(*reinterpret_cast<const uint4*>(f.out_bias + static_cast<int>(i % n16_row) * 8), b);
-#pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] += b[u];
-        }
-        Vec16<__nv_bfloat16> o;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) o.v[u] = __float2bfloat16_rn(v[u]);
-        st16(f.out + i * 8, o);
-      }
+      a[0] = make_float4(x[0], x[1], x[2], x[3]);
+      a[1] = make_float4(x[4], x[5], x[6], x[7]);
     }
     __syncthreads();
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) atomicAdd(f.counts + kMaxRanks, 1u);
   exit_barrier_n(c, c.channel + 1, static_cast<unsigned int>(f.n_comm));  // peers are done reading my staging buffer
+  return true;
+}
+
+// out = scratch (the peers' sum) + my own partial chunk + bias, on every CTA of the grid once its other work is done.
+__device__ __forceinline__ void rs_final_pass(const FusedParams& f, int N) {
+  __shared__ int final_ok;
+  if (threadIdx.x == 0) {
+    int dummy_abort = 0;
+    bool ok = wait_counter(f.counts + f.c.rank, f.target, &dummy_abort);               // my own chunk is complete
+    if (ok && f.c.world > 1) ok = wait_counter(f.counts + kMaxRanks, f.target_comm, &dummy_abort);  // peers folded in
+    if (!ok && f.c.status != nullptr) atomicExch(f.c.status, FSB_ERR_WAIT_TIMEOUT);
+    final_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!final_ok) return;
+  const uint4* own = reinterpret_cast<const uint4*>(f.peer.p[f.c.rank]) + static_cast<long long>(f.c.rank) * f.chunk16;
+  const float4* acc = reinterpret_cast<const float4*>(f.acc);
+  const int n16_row = N / 8;
+  const bool have_peers = f.c.world > 1;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < f.chunk16; i += stride) {
+    float v[8];
+    unpack8(__ldcg(own + i), v);
+    if (have_peers) {
+      const float4 a0 = __ldcg(acc + 2 * i), a1 = __ldcg(acc + 2 * i + 1);
+      v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
+      v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+    }
+    if (f.out_bias != nullptr) {
+      float b[8];
+      unpack8(*reinterpret_cast<const uint4*>(f.out_bias + static_cast<int>(i % n16_row) * 8), b);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] += b[u];
+    }
+    Vec16<__nv_bfloat16> o;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) o.v[u] = __float2bfloat16_rn(v[u]);
+    st16(f.out + i * 8, o);
+  }
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p, FusedParams f) {
   extern __shared__ uint8_t smem_raw[];
   if (static_cast<int>(blockIdx.x) < f.n_comm) {
-    rs_reduce_cta(f, p.N);
-    return;
+    if (f.c.world > 1 && !rs_reduce_cta(f)) return;
+  } else {
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    fused_gemm_cta<1>(tmap_a, tmap_a, tmap_b, p, f, smem);
   }
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  fused_gemm_cta<1>(tmap_a, tmap_a, tmap_b, p, f, smem);
+  rs_final_pass(f, p.N);
 }
 
 }  // namespace fsb
@@ -408,11 +460,12 @@ FSB_API int fsb_ag_gemm_bf16(int rank, int world, unsigned epoch, int channel, v
 
 // out[Mc, N] (bf16) = sum over ranks of (A[M, K] * B^T)[my chunk's rows] (+ out_bias).  stage_peers[r]: rank r's
 // staging buffer [M, N] bf16 in the symmetric heap (this rank writes stage_peers[rank]); acc: fp32 scratch [Mc * N];
-// counts / target as for ag_gemm but counting 4 * tiles-per-chunk arrivals per call.
+// counts: kMaxRanks + 1 uint32; target as for ag_gemm but counting 4 * tiles-per-chunk arrivals per call;
+// target_comm: cumulative n_comm over the calls (with world > 1) that used `counts`.
 FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
                              void* const* stage_peers, const void* A, const void* B, void* out, const void* out_bias, void* acc,
-                             int M, int N, int K, int lda, int ldb, int b_mn_major, void* counts, unsigned target, int n_comm,
-                             int* status, cudaStream_t stream) {
+                             int M, int N, int K, int lda, int ldb, int b_mn_major, void* counts, unsigned target,
+                             unsigned target_comm, int n_comm, int* status, cudaStream_t stream) {
   using namespace fsb;
   if (world < 1 || world > kMaxRanks || M % world) return -1;
   const int Mc = M / world;
@@ -431,6 +484,7 @@ FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, v
   for (int i = 0; i < world; ++i) f.peer.p[i] = stage_peers[i];
   f.counts = static_cast<uint32_t*>(counts);
   f.target = target;
+  f.target_comm = target_comm;
   f.chunk16 = static_cast<long long>(Mc) * N * 2 / 16;
   f.acc = static_cast<float*>(acc);
   f.out = static_cast<__nv_bfloat16*>(out);

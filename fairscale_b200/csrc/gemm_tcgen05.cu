@@ -192,16 +192,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 constexpr int PAIR_BLOCK_N = 256;
 constexpr int PAIR_HALF_N = 128;
 constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_EPI_WARPS = 8;                        // two per TMEM lane quadrant, 128 columns each
+constexpr int PAIR_THREADS = 64 + 32 * PAIR_EPI_WARPS;   // producer warp + MMA warp + epilogue warps
 
 struct PairSmem {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;      // 16 KB: this CTA's 128 rows
   static constexpr int B_BYTES = PAIR_HALF_N * BLOCK_K * 2;  // 16 KB: this CTA's 128 columns
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = PAIR_STAGES * STAGE_BYTES;           // 4 KB of staging per epilogue warp
+  static constexpr int BAR_OFFSET = EPI_OFFSET + PAIR_EPI_WARPS * 4096;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
   using L = PairSmem;
   extern __shared__ uint8_t smem_raw[];
@@ -234,7 +237,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], 8);  // 4 epilogue warps in each CTA of the pair
+      mbar_init(&tmem_empty_bar[a], 2 * PAIR_EPI_WARPS);  // the epilogue warps of both CTAs of the pair
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -325,19 +328,24 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (both CTAs)
-    const int quad = warp & 3;
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;     // which 128 columns of the 256 this warp drains
+    uint8_t* stage = smem + L::EPI_OFFSET + (warp - 2) * 4096;
+    const bool coalesce = epilogue_can_coalesce(p);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      const int row = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M + quad * 32 + lane;
-      const int n0 = tn * PAIR_BLOCK_N;
+      const int row0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M + quad * 32;
+      const int n0 = tn * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2);
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_rows<PAIR_BLOCK_N>(t_base, row, n0, p);
+      const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2)) +
+                              (static_cast<uint32_t>(quad * 32) << 16);
+      if (coalesce) epilogue_rows_coalesced(t_base, row0, n0, PAIR_BLOCK_N / 2, p, stage, lane);
+      else          epilogue_rows<PAIR_BLOCK_N / 2>(t_base, row0 + lane, n0, p);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
@@ -425,7 +433,7 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
     const int pair_tiles = ((M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((N + PAIR_BLOCK_N - 1) / PAIR_BLOCK_N);
     const int max_pairs = num_sms / 2;
     const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
-    gemm_bf16_tcgen05_pair_kernel<<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, stream>>>(ta, tb, p);
+    gemm_bf16_tcgen05_pair_kernel<<<2 * pairs, PAIR_THREADS, PairSmem::TOTAL, stream>>>(ta, tb, p);
     return static_cast<int>(cudaGetLastError());
   }
   if (block_n == 256) {

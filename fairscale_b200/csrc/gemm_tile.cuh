@@ -146,4 +146,117 @@ __device__ __forceinline__ void epilogue_rows(uint32_t t_base, int row, int n0, 
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Coalesced epilogue for bf16 outputs.  A warp owns 32 accumulator rows (one TMEM lane quadrant) and walks its
+// columns in slabs of 64.  Thread = row when it reads TMEM and does the math, but global memory is touched
+// with 8 lanes per row (8 x 16 B = one 128-byte line, 4 rows per instruction): the slab is transposed through a
+// warp-private, XOR-swizzled 4 KB staging buffer in shared memory, in both directions (aux in, C / aux_out out).
+// `stage` is this warp's buffer; ncols is a multiple of 64.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t epi_swz(int row, int chunk) {  // byte offset of 16-byte chunk `chunk` of `row`
+  return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// global [32 rows x 64 cols] bf16 slab -> staging (coalesced reads)
+__device__ __forceinline__ void epi_slab_load(uint8_t* stage, const __nv_bfloat16* g, int ld, int row0, int col0, int M, int N, int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row0 + rr < M && col0 + cc * 8 < N) v = *reinterpret_cast<const uint4*>(g + static_cast<size_t>(row0 + rr) * ld + col0 + cc * 8);
+    *reinterpret_cast<uint4*>(stage + epi_swz(rr, cc)) = v;
+  }
+}
+// staging -> global [32 rows x 64 cols] bf16 slab (coalesced writes)
+__device__ __forceinline__ void epi_slab_store(const uint8_t* stage, __nv_bfloat16* g, int ld, int row0, int col0, int M, int N, int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3);
+    if (row0 + rr < M && col0 + cc * 8 < N)
+      *reinterpret_cast<uint4*>(g + static_cast<size_t>(row0 + rr) * ld + col0 + cc * 8) = *reinterpret_cast<const uint4*>(stage + epi_swz(rr, cc));
+  }
+}
+// this thread's row of the slab: 64 floats -> staging as bf16
+__device__ __forceinline__ void epi_row_to_stage(uint8_t* stage, const float (&v)[64], int lane) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    Vec16<__nv_bfloat16> o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = __float2bfloat16_rn(v[c * 8 + i]);
+    *reinterpret_cast<uint4*>(stage + epi_swz(lane, c)) = o.raw;
+  }
+}
+
+__device__ __forceinline__ void epilogue_rows_coalesced(uint32_t t_base, int row0, int n0, int ncols, const GemmParams& p, uint8_t* stage, int lane) {
+  const int epi = p.epilogue;
+  for (int c0 = 0; c0 < ncols; c0 += 64) {
+    const int col0 = n0 + c0;
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32(t_base + static_cast<uint32_t>(c0), r0);
+    tmem_ld_32x32(t_base + static_cast<uint32_t>(c0 + 32), r1);
+    const bool needs_aux = (epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU);
+    if (needs_aux && col0 < p.N) epi_slab_load(stage, p.aux, p.ld_aux, row0, col0, p.M, p.N, lane);  // overlaps the TMEM load
+    tmem_ld_wait();
+    if (col0 >= p.N) continue;  // warp-uniform
+    float v[64];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { v[i] = __uint_as_float(r0[i]); v[32 + i] = __uint_as_float(r1[i]); }
+    if (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESIDUAL) {
+      if ((reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          if (col0 + c * 8 < p.N) {
+            const Vec16<__nv_bfloat16> b = ld16(p.bias + col0 + c * 8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[c * 8 + i] += __bfloat162float(b.v[i]);
+          }
+        }
+      } else {  // a bias that is a view into a flat parameter may start at any element
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+      }
+    }
+    if (needs_aux) {
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        Vec16<__nv_bfloat16> a;
+        a.raw = *reinterpret_cast<const uint4*>(stage + epi_swz(lane, c));
+        if (epi == EPI_DGELU) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[c * 8 + i] *= gelu_erf_grad(__bfloat162float(a.v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[c * 8 + i] += __bfloat162float(a.v[i]);
+        }
+      }
+      __syncwarp();
+    }
+    if (epi == EPI_BIAS_GELU) {
+      if (p.aux_out != nullptr) {
+        epi_row_to_stage(stage, v, lane);
+        __syncwarp();
+        epi_slab_store(stage, p.aux_out, p.ld_aux, row0, col0, p.M, p.N, lane);
+        __syncwarp();
+      }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) v[i] = gelu_erf(v[i]);
+    }
+    epi_row_to_stage(stage, v, lane);
+    __syncwarp();
+    epi_slab_store(stage, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc, row0, col0, p.M, p.N, lane);
+    __syncwarp();
+  }
+}
+
+// bf16 output with 16-byte aligned rows: the layouts the coalesced epilogue handles
+__device__ __forceinline__ bool epilogue_can_coalesce(const GemmParams& p) {
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.aux) | reinterpret_cast<uintptr_t>(p.aux_out);
+  return !p.out_f32 && (p.ldc % 8 == 0) && (p.ld_aux % 8 == 0) && (p.N % 8 == 0) && (ptrs & 15u) == 0;
+}
+
 }  // namespace fsb

@@ -42,14 +42,24 @@ def _sigs() -> None:
     head = [c_int, c_int, c_uint, c_int, c_void_p, c_void_p]
     S = _bind._SIGNATURES
     S["fsb_ag_gemm_bf16"] = head + [c_void_p] * 7 + [c_int] * 7 + [c_void_p, c_uint, c_int, c_void_p, c_void_p]
-    S["fsb_gemm_rs_bf16"] = head + [c_void_p] * 6 + [c_int] * 6 + [c_void_p, c_uint, c_int, c_void_p, c_void_p]
+    S["fsb_gemm_rs_bf16"] = head + [c_void_p] * 6 + [c_int] * 6 + [c_void_p, c_uint, c_uint, c_int, c_void_p, c_void_p]
     S["fsb_gemm_rs_arrivals"] = [c_int, c_int, c_int]
     _SIGS_DONE = True
 
 
-def comm_ctas() -> int:
-    """CTAs (SMs) of a fused kernel that move data instead of computing (env ``FSB200_FUSED_COMM_CTAS``)."""
-    return int(os.environ.get("FSB200_FUSED_COMM_CTAS", "16"))
+def comm_ctas(remote_bytes: float = 0.0, flops: float = 0.0, world: int = 2) -> int:
+    """CTAs (SMs) of a fused kernel that move data instead of computing.
+
+    Enough of them to move ``remote_bytes`` over NVLink while the remaining SMs spend ``flops`` on the chunks that do
+    not depend on the transfer; one copy CTA sustains roughly 45 GB/s of peer loads.  ``FSB200_FUSED_COMM_CTAS`` overrides."""
+    env = os.environ.get("FSB200_FUSED_COMM_CTAS")
+    if env:
+        return int(env)
+    if remote_bytes <= 0 or flops <= 0:
+        return 16
+    overlap_s = flops / 1.2e15 * max(world - 1, 1) / world
+    need = remote_bytes / max(overlap_s, 1e-6) / 45e9
+    return int(min(32, max(4, -(-need // 1))))
 
 
 class _State:
@@ -58,10 +68,11 @@ class _State:
     def __init__(self, ws: Any):
         self.ws = ws
         dev = ws.device
-        self.ag_counts = torch.zeros(8, dtype=torch.int32, device=dev)
-        self.rs_counts = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.ag_counts = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.rs_counts = torch.zeros(16, dtype=torch.int32, device=dev)
         self.ag_target = 0
         self.rs_target = 0
+        self.rs_target_comm = 0
         self.ag_epoch = 0
         self.rs_epoch = 0
         self.acc: Dict[int, torch.Tensor] = {}
@@ -111,7 +122,7 @@ def ag_gemm(ws: Any, x_shard: torch.Tensor, w: torch.Tensor, bias: Optional[torc
         src_off = ws.offset_of(x_shard)
     gathered = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
     y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    n_comm = comm_ctas()
+    n_comm = comm_ctas((ws.world - 1) * Mc * K * 2.0, 2.0 * M * N * K, ws.world)
     st.ag_epoch = (st.ag_epoch + 1) & 0x7FFFFFFF
     st.ag_target = (st.ag_target + n_comm) & 0xFFFFFFFF
     epi = 0 if bias is None else (2 if gelu else 1)
@@ -138,14 +149,16 @@ def gemm_rs(ws: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     if acc is None:
         acc = st.acc[Mc * N] = torch.empty(Mc * N, dtype=torch.float32, device=dev)
     out = torch.empty((Mc, N), dtype=torch.bfloat16, device=dev)
-    n_comm = comm_ctas()
+    n_comm = comm_ctas((ws.world - 1) * Mc * N * 2.0, 2.0 * M * N * K, ws.world)
     arrivals = _bind.fn("fsb_gemm_rs_arrivals")(M, N, ws.world)
     st.rs_epoch = (st.rs_epoch + 1) & 0x7FFFFFFF
     st.rs_target = (st.rs_target + arrivals) & 0xFFFFFFFF
+    if ws.world > 1:
+        st.rs_target_comm = (st.rs_target_comm + n_comm) & 0xFFFFFFFF
     _bind.call(
         "fsb_gemm_rs_bf16", ws.rank, ws.world, st.rs_epoch, _RS_CHANNEL, ws.pad_ptrs, ws.counters.data_ptr() + 4 * 17,
         ws.peers(ws.offset_of(stage)), x.data_ptr(), w.data_ptr(), out.data_ptr(), _bind.ptr(bias), acc.data_ptr(),
-        M, N, K, x.stride(0), w.stride(0), int(w_is_kn), st.rs_counts.data_ptr(), st.rs_target, n_comm,
+        M, N, K, x.stride(0), w.stride(0), int(w_is_kn), st.rs_counts.data_ptr(), st.rs_target, st.rs_target_comm, n_comm,
         _bind.status_ptr(dev), _bind.stream_ptr(dev),
     )
     return out
