@@ -34,13 +34,19 @@ struct AttnParams {
   float scale;        // softmax scale (1/sqrt(D))
   __nv_bfloat16* o;   // fwd out / bwd in   [B*S, H*D]
   float* lse;         // [B, H, S]
-  const float* delta; // [B, H, S]  rowsum(dO * O)
+  const float* delta; // [2, B, H, S]: scale * rowsum(dO * O), then the base-2 lse (both written by attn_delta_kernel)
   __nv_bfloat16* dqkv;  // [B*S, 3*H*D]
   int* status;
 };
 
 // byte offset of (row, 16-byte chunk) inside a 128-byte-swizzled [rows x 64 bf16] slab
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
+
+__device__ __forceinline__ float ex2_approx(float x) {  // 2^x on the MUFU pipe, one instruction
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -99,6 +105,46 @@ __device__ __forceinline__ void attn_teardown(AttnBars* bars, int warp, uint32_t
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, ncols);
   }
+}
+
+// Row maximum / exponentials of one 128-column score row held in registers.  Eight independent accumulators keep
+// the dependent chains short (a softmax warp runs alone on its scheduler, so latency is not hidden by other warps).
+template <bool DIAG>
+__device__ __forceinline__ float fwd_row_max(const uint32_t (&sr)[4][32], int row) {
+  float m[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) m[k] = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float v = __uint_as_float(sr[c][i]);
+      if (!DIAG || (c * 32 + i) <= row) m[i & 7] = fmaxf(m[i & 7], v);
+    }
+  }
+  return fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
+}
+
+template <bool DIAG>
+__device__ __forceinline__ float fwd_row_exp(const uint32_t (&sr)[4][32], int row, float sl2, float mb, uint32_t (&pk)[64]) {
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), sl2, -mb));
+      float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), sl2, -mb));
+      if (DIAG) {
+        if (c * 32 + i > row) p0 = 0.f;
+        if (c * 32 + i + 1 > row) p1 = 0.f;
+      }
+      acc[(i >> 1) & 7] += p0 + p1;
+      pk[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+    }
+  }
+  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
 }
 
 // =================================================================================================
@@ -219,34 +265,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, sr[c]);
       tmem_ld_wait();
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(sr[c][i]);
-          if (!diag || (c * 32 + i) <= row) mx = fmaxf(mx, v);
-        }
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * sl2);
+      // Tiles below the diagonal need no mask; only the last tile of a CTA pays for the comparisons.
+      float mx;
+      if (!diag) mx = fwd_row_max<false>(sr, row); else mx = fwd_row_max<true>(sr, row);
+      // Keep the old maximum while the new one is at most 2^8 above it: the probabilities stay well inside the
+      // bf16 / fp32 range and O needs no rescaling (the final 1 / l normalisation uses the same maximum).
+      float m_new = fmaxf(m_run, mx);
+      if (m_run != -INFINITY && (m_new - m_run) * sl2 <= 8.f) m_new = m_run;
+      const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - m_new) * sl2);
       const float mb = m_new * sl2;
       uint32_t pk[64];
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(sr[c][i]) * sl2 - mb);
-          float p1 = exp2f(__uint_as_float(sr[c][i + 1]) * sl2 - mb);
-          if (diag) {
-            if (c * 32 + i > row) p0 = 0.f;
-            if (c * 32 + i + 1 > row) p1 = 0.f;
-          }
-          rs += p0 + p1;
-          pk[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
-        }
-      }
+      float rs;
+      if (!diag) rs = fwd_row_exp<false>(sr, row, sl2, mb, pk); else rs = fwd_row_exp<true>(sr, row, sl2, mb, pk);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[st]);
@@ -307,6 +337,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
     }
   }
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
+}
+
+// dS for 64 columns of one row: P = 2^(s * sl2 - lse2), dS = P * (dP * scale - delta * scale)
+template <bool DIAG>
+__device__ __forceinline__ void dq_half_row(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], int cc, int row, float sl2,
+                                            float lse2, float scale, float delta_s, uint32_t (&pk)[64]) {
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int c = cc * 2 + u;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = ex2_approx(fmaf(__uint_as_float(rs[u][i]), sl2, -lse2));
+      float p1 = ex2_approx(fmaf(__uint_as_float(rs[u][i + 1]), sl2, -lse2));
+      if (DIAG) {
+        if (c * 32 + i > row) p0 = 0.f;
+        if (c * 32 + i + 1 > row) p1 = 0.f;
+      }
+      pk[c * 16 + (i >> 1)] = pack_bf16(p0 * fmaf(__uint_as_float(rp[u][i]), scale, -delta_s),
+                                        p1 * fmaf(__uint_as_float(rp[u][i + 1]), scale, -delta_s));
+    }
+  }
 }
 
 // =================================================================================================
@@ -413,8 +464,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
     const size_t stat_idx = (static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row;
-    const float lse2 = p.lse[stat_idx] * LOG2E;
-    const float delta = p.delta[stat_idx];
+    const float lse2 = p.delta[static_cast<size_t>(p.B) * p.H * p.S + stat_idx];  // base-2 lse, written by the delta kernel
+    const float delta_s = p.delta[stat_idx];                                       // scale * rowsum(dO * O)
     uint8_t* sds = smem + L::DS_OFF;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
@@ -431,22 +482,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
           tmem_ld_32x32(tmem_base + 128 + lane_off + (cc * 2 + u) * 32, rp[u]);
         }
         tmem_ld_wait();
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c = cc * 2 + u;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = exp2f(__uint_as_float(rs[u][i]) * sl2 - lse2);
-            float p1 = exp2f(__uint_as_float(rs[u][i + 1]) * sl2 - lse2);
-            if (diag) {
-              if (c * 32 + i > row) p0 = 0.f;
-              if (c * 32 + i + 1 > row) p1 = 0.f;
-            }
-            const float d0 = p0 * (__uint_as_float(rp[u][i]) - delta) * p.scale;
-            const float d1 = p1 * (__uint_as_float(rp[u][i + 1]) - delta) * p.scale;
-            pk[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
-          }
-        }
+        if (!diag) dq_half_row<false>(rs, rp, cc, row, sl2, lse2, p.scale, delta_s, pk);
+        else       dq_half_row<true>(rs, rp, cc, row, sl2, lse2, p.scale, delta_s, pk);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -485,6 +522,34 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     }
   }
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
+}
+
+// P^T and dS^T for one key row against 64 queries; the per-query statistics come in 16-byte broadcast loads.
+template <bool DIAG>
+__device__ __forceinline__ void dkv_row(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], const float* __restrict__ lse2,
+                                        const float* __restrict__ delta_s, int q0, int key, float sl2, float scale,
+                                        uint32_t (&pp)[32], uint32_t (&pd)[32]) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 l = __ldg(reinterpret_cast<const float4*>(lse2 + c * 32 + i));
+      const float4 e = __ldg(reinterpret_cast<const float4*>(delta_s + c * 32 + i));
+      const float lv[4] = {l.x, l.y, l.z, l.w}, ev[4] = {e.x, e.y, e.z, e.w};
+      float pr[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        pr[k] = ex2_approx(fmaf(__uint_as_float(rs[c][i + k]), sl2, -lv[k]));
+        if (DIAG && key > q0 + c * 32 + i + k) pr[k] = 0.f;
+      }
+      pp[c * 16 + (i >> 1)] = pack_bf16(pr[0], pr[1]);
+      pp[c * 16 + (i >> 1) + 1] = pack_bf16(pr[2], pr[3]);
+      pd[c * 16 + (i >> 1)] = pack_bf16(pr[0] * fmaf(__uint_as_float(rp[c][i]), scale, -ev[0]),
+                                        pr[1] * fmaf(__uint_as_float(rp[c][i + 1]), scale, -ev[1]));
+      pd[c * 16 + (i >> 1) + 1] = pack_bf16(pr[2] * fmaf(__uint_as_float(rp[c][i + 2]), scale, -ev[2]),
+                                            pr[3] * fmaf(__uint_as_float(rp[c][i + 3]), scale, -ev[3]));
+    }
+  }
 }
 
 // =================================================================================================
@@ -601,8 +666,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
     const int row = quad * 32 + lane;  // key row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    const float* lse_bh = p.lse + (static_cast<size_t>(b) * p.H + h) * p.S;
-    const float* delta_bh = p.delta + (static_cast<size_t>(b) * p.H + h) * p.S;
+    const float* delta_bh = p.delta + (static_cast<size_t>(b) * p.H + h) * p.S;   // scale * rowsum(dO * O)
+    const float* lse2_bh = delta_bh + static_cast<size_t>(p.B) * p.H * p.S;        // base-2 lse
     uint8_t* spt = smem + L::PT_OFF;
     uint8_t* sdst = smem + L::DST_OFF;
     bool ok = true;
@@ -621,24 +686,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
           tmem_ld_32x32(tmem_base + 64 + lane_off + c * 32, rp[c]);
         }
         tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const int qa = q0 + c * 32 + i;
-            const float2 l2v = __ldg(reinterpret_cast<const float2*>(lse_bh + qa));
-            const float2 e2v = __ldg(reinterpret_cast<const float2*>(delta_bh + qa));
-            float p0 = exp2f(__uint_as_float(rs[c][i]) * sl2 - l2v.x * LOG2E);
-            float p1 = exp2f(__uint_as_float(rs[c][i + 1]) * sl2 - l2v.y * LOG2E);
-            if (diag) {
-              if (key > qa) p0 = 0.f;
-              if (key > qa + 1) p1 = 0.f;
-            }
-            pp[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
-            pd[c * 16 + (i >> 1)] = pack_bf16(p0 * (__uint_as_float(rp[c][i]) - e2v.x) * p.scale,
-                                              p1 * (__uint_as_float(rp[c][i + 1]) - e2v.y) * p.scale);
-          }
-        }
+        if (!diag) dkv_row<false>(rs, rp, lse2_bh + q0, delta_bh + q0, q0, key, sl2, p.scale, pp, pd);
+        else       dkv_row<true>(rs, rp, lse2_bh + q0, delta_bh + q0, q0, key, sl2, p.scale, pp, pd);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -684,9 +733,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
 }
 
-// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head)
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                                  int B, int S, int H, int D) {
+// delta[b, h, s] = scale * sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head).
+// Also writes the base-2 log-sum-exp right behind it: delta[B*H*S + i] = lse[i] * log2(e).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
+                                  float* __restrict__ delta, float scale, int B, int S, int H, int D) {
   const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long total = static_cast<long long>(B) * S * H;
@@ -704,7 +754,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   acc = warp_sum(acc);
   if (lane == 0) {
     const long long bb = tok / S, s = tok - bb * S;
-    delta[(bb * H + h) * S + s] = acc;
+    const long long idx = (bb * H + h) * S + s;
+    delta[idx] = acc * scale;
+    delta[total + idx] = lse[idx] * LOG2E;
   }
 }
 
@@ -763,7 +815,7 @@ FSB_API int fsb_attn_bwd(const void* qkv, const void* o, const void* d_o, const 
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
     attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
-                                                                             static_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, D);
+                                                                             static_cast<const __nv_bfloat16*>(d_o), lse, delta, scale, B, S, H, D);
   }
   dim3 grid(S / ATT_BM, H, B);
   if (D == 128) {

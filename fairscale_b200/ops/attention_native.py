@@ -43,7 +43,7 @@ class _FlashAttnFn(torch.autograd.Function):
         D = three_hd // (3 * H)
         d_o = d_o.contiguous()
         dqkv = torch.empty_like(qkv)
-        delta = torch.empty_like(lse)
+        delta = torch.empty((2,) + tuple(lse.shape), dtype=torch.float32, device=lse.device)  # scale*delta, then base-2 lse
         _bind.call("fsb_attn_bwd", qkv.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(), delta.data_ptr(), dqkv.data_ptr(),
                    B, S, H, D, ctx.scale, _bind.status_ptr(qkv.device), _bind.stream_ptr(qkv.device), launches=3)
         return dqkv, None, None
