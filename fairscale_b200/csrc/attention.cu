@@ -10,9 +10,10 @@
 //   backward dQ (one CTA per 128 query rows)   S = Q K^T, dP = dO V^T -> dS -> dQ += dS K
 //   backward dK/dV (one CTA per 128 key rows)  S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T -> dV += P^T dO, dK += dS^T Q
 //
-// Thread roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM allocation), warps 2..5
-// "softmax" threads that own one accumulator row each (TMEM lane == row), do the exponentials in registers and
-// hand the bf16 probabilities back to the tensor cores through 128-byte-swizzled shared memory.
+// Thread roles per CTA (320 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM allocation), warps 2..9
+// "softmax" threads: two threads per accumulator row (TMEM lane == row; warps w and w+4 share a lane quadrant and
+// take half of the columns each, so every scheduler has two warps to interleave), which do the exponentials in
+// registers and hand the bf16 probabilities back to the tensor cores through 128-byte-swizzled shared memory.
 // A K-major tile [rows, 64] and an MN-major tile of the same bytes differ only in the MMA descriptor, so each
 // streamed tile is loaded once and used both as a "transposed" and a "plain" operand.
 // Every mbarrier wait is bounded (see sm100.cuh).
@@ -24,7 +25,7 @@
 
 namespace fsb {
 
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;  // TMA warp + MMA warp + 8 compute warps (two per TMEM lane quadrant, half the columns each)
 constexpr int ATT_BM = 128;  // rows owned by a CTA (TMEM lanes)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -76,6 +77,38 @@ struct AttnBars {
   int abort_flag;
 };
 
+struct PairXch {            // forward only: row statistics exchanged between the two threads of a row
+  float xch[2][2][ATT_BM];  // [parity][column half][row]
+  int xflag[2][2][ATT_BM];  // sequence number of the value in xch (0 = nothing yet)
+};
+
+// The two threads of a row swap one float through shared memory.  `seq` (> 0) must differ between consecutive uses of
+// a parity slot.  The wait is a bounded poll, not a hardware barrier, so a thread that gave up after a timeout
+// elsewhere cannot strand its partner.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool pair_exchange(PairXch* bars, int parity, int half, int row, int seq, float mine, float& other,
+                                              volatile int* abort_flag) {
+  *reinterpret_cast<volatile float*>(&bars->xch[parity][half][row]) = mine;
+  __threadfence_block();
+  *reinterpret_cast<volatile int*>(&bars->xflag[parity][half][row]) = seq;
+  const volatile int* theirs = &bars->xflag[parity][half ^ 1][row];
+  if (*theirs != seq) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (*theirs != seq) {
+      if (((++spins) & 127u) == 0u) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+          *abort_flag = 1;
+          return false;
+        }
+      }
+    }
+  }
+  __threadfence_block();
+  other = *reinterpret_cast<volatile float*>(&bars->xch[parity][half ^ 1][row]);
+  return true;
+}
+
 __device__ __forceinline__ void attn_init_bars(AttnBars* b) {
   mbar_init(&b->stat_full, 1);
   for (int i = 0; i < 2; ++i) {
@@ -83,9 +116,9 @@ __device__ __forceinline__ void attn_init_bars(AttnBars* b) {
     mbar_init(&b->str2_full[i], 1);
     mbar_init(&b->str_empty[i], 1);
     mbar_init(&b->s_full[i], 1);
-    mbar_init(&b->s_empty[i], 4);
+    mbar_init(&b->s_empty[i], 8);
   }
-  mbar_init(&b->p_full, 4);
+  mbar_init(&b->p_full, 8);
   mbar_init(&b->acc_done, 1);
   b->abort_flag = 0;
   fence_barrier_init();
@@ -107,38 +140,38 @@ __device__ __forceinline__ void attn_teardown(AttnBars* bars, int warp, uint32_t
   }
 }
 
-// Row maximum / exponentials of one 128-column score row held in registers.  Eight independent accumulators keep
-// the dependent chains short (a softmax warp runs alone on its scheduler, so latency is not hidden by other warps).
+// Row maximum / exponentials of 64 columns (starting at column `col0`) of a score row held in registers.  Eight
+// independent accumulators keep the dependent chains short.
 template <bool DIAG>
-__device__ __forceinline__ float fwd_row_max(const uint32_t (&sr)[4][32], int row) {
+__device__ __forceinline__ float fwd_row_max(const uint32_t (&sr)[2][32], int col0, int row) {
   float m[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) m[k] = -INFINITY;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < 2; ++c) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const float v = __uint_as_float(sr[c][i]);
-      if (!DIAG || (c * 32 + i) <= row) m[i & 7] = fmaxf(m[i & 7], v);
+      if (!DIAG || (col0 + c * 32 + i) <= row) m[i & 7] = fmaxf(m[i & 7], v);
     }
   }
   return fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
 }
 
 template <bool DIAG>
-__device__ __forceinline__ float fwd_row_exp(const uint32_t (&sr)[4][32], int row, float sl2, float mb, uint32_t (&pk)[64]) {
+__device__ __forceinline__ float fwd_row_exp(const uint32_t (&sr)[2][32], int col0, int row, float sl2, float mb, uint32_t (&pk)[32]) {
   float acc[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) acc[k] = 0.f;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < 2; ++c) {
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
       float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), sl2, -mb));
       float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), sl2, -mb));
       if (DIAG) {
-        if (c * 32 + i > row) p0 = 0.f;
-        if (c * 32 + i + 1 > row) p1 = 0.f;
+        if (col0 + c * 32 + i > row) p0 = 0.f;
+        if (col0 + c * 32 + i + 1 > row) p1 = 0.f;
       }
       acc[(i >> 1) & 7] += p0 + p1;
       pk[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
@@ -158,7 +191,8 @@ struct FwdSmem {
   static constexpr int V_OFF = 3 * TILE;       // 2 stages
   static constexpr int P_OFF = 5 * TILE;       // [128 x 128] bf16
   static constexpr int BAR_OFF = P_OFF + ATT_BM * 128 * 2;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int XCH_OFF = BAR_OFF + 256;
+  static constexpr int TOTAL = XCH_OFF + 4096 + 1024;
 };
 
 template <int D>
@@ -185,6 +219,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
     attn_init_bars(bars);
     tma_prefetch_desc(&tm_qkv);
   }
+  PairXch* xch = reinterpret_cast<PairXch*>(smem + L::XCH_OFF);
+  for (int i = threadIdx.x; i < 2 * 2 * ATT_BM; i += ATT_THREADS) (&xch->xflag[0][0][0])[i] = 0;
   if (warp == 1) {
     tmem_alloc(&bars->tmem_slot, TMEM_COLS);
     tmem_relinquish();
@@ -248,35 +284,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;   // which 64 of the 128 score columns (and which D/2 of the output columns)
     const int row = quad * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's share of the row sum
     uint8_t* sp = smem + L::P_OFF;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int st = j & 1;
       if (!mbar_wait(&bars->s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t ts = tmem_base + st * 128 + lane_off;
+      const uint32_t ts = tmem_base + st * 128 + half * 64 + lane_off;
       const bool diag = (j == qt);
-      // the whole score row in registers: four TMEM loads in flight, one wait
-      uint32_t sr[4][32];
+      uint32_t sr[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, sr[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32(ts + c * 32, sr[c]);
       tmem_ld_wait();
       // Tiles below the diagonal need no mask; only the last tile of a CTA pays for the comparisons.
-      float mx;
-      if (!diag) mx = fwd_row_max<false>(sr, row); else mx = fwd_row_max<true>(sr, row);
+      float mx, other;
+      if (!diag) mx = fwd_row_max<false>(sr, half * 64, row); else mx = fwd_row_max<true>(sr, half * 64, row);
+      if (!__all_sync(0xffffffffu, pair_exchange(xch, j & 1, half, row, j + 1, mx, other, abort_flag))) { ok = false; break; }
+      mx = fmaxf(mx, other);
       // Keep the old maximum while the new one is at most 2^8 above it: the probabilities stay well inside the
       // bf16 / fp32 range and O needs no rescaling (the final 1 / l normalisation uses the same maximum).
       float m_new = fmaxf(m_run, mx);
       if (m_run != -INFINITY && (m_new - m_run) * sl2 <= 8.f) m_new = m_run;
       const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - m_new) * sl2);
       const float mb = m_new * sl2;
-      uint32_t pk[64];
+      uint32_t pk[32];
       float rs;
-      if (!diag) rs = fwd_row_exp<false>(sr, row, sl2, mb, pk); else rs = fwd_row_exp<true>(sr, row, sl2, mb, pk);
+      if (!diag) rs = fwd_row_exp<false>(sr, half * 64, row, sl2, mb, pk); else rs = fwd_row_exp<true>(sr, half * 64, row, sl2, mb, pk);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[st]);
@@ -286,25 +324,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < D / 64; ++c) {
+            const uint32_t to = tmem_base + 256 + lane_off + half * (D / 2) + c * 32;
             uint32_t r[32];
-            tmem_ld_32x32(tmem_base + 256 + lane_off + c * 32, r);
+            tmem_ld_32x32(to, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
             uint32_t lo[16], hi[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) { lo[i] = r[i]; hi[i] = r[16 + i]; }
-            tmem_st_32x16(tmem_base + 256 + lane_off + c * 32, lo);
-            tmem_st_32x16(tmem_base + 256 + lane_off + c * 32 + 16, hi);
+            tmem_st_32x16(to, lo);
+            tmem_st_32x16(to + 16, hi);
           }
           tmem_st_wait();
         }
       }
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {  // 16 chunks of 8 bf16 = this row of P
+      for (int ch = 0; ch < 8; ++ch) {  // this thread's 8 chunks of 8 bf16 = its half of the row of P
         const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sp + (ch >> 3) * SLAB + swz(row, ch & 7)) = v;
+        *reinterpret_cast<uint4*>(sp + half * SLAB + swz(row, ch)) = v;
       }
       fence_proxy_async();
       tc_fence_before_sync();
@@ -315,12 +354,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
     }
     if (ok && mbar_wait(&bars->acc_done, (n_kv - 1) & 1, abort_flag)) {
       tc_fence_after_sync();
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* orow = p.o + static_cast<size_t>(row0 + row) * HD + h * D;
+      float l_other = 0.f;
+      const bool got = __all_sync(0xffffffffu, pair_exchange(xch, n_kv & 1, half, row, n_kv + 1, l_run, l_other, abort_flag));
+      const float l_tot = l_run + l_other;
+      const float inv = got ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* orow = p.o + static_cast<size_t>(row0 + row) * HD + h * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + 256 + lane_off + c * 32, r);
+        tmem_ld_32x32(tmem_base + 256 + lane_off + half * (D / 2) + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -332,29 +374,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
           *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
         }
       }
-      if (p.lse != nullptr)
-        p.lse[(static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row] = (m_run * sl2 + log2f(l_run)) * LN2;
+      if (half == 0 && p.lse != nullptr)
+        p.lse[(static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row] = (m_run * sl2 + log2f(l_tot)) * LN2;
     }
   }
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
 }
 
-// dS for 64 columns of one row: P = 2^(s * sl2 - lse2), dS = P * (dP * scale - delta * scale)
+// dS for 64 columns (starting at column `col0`) of one row: P = 2^(s * sl2 - lse2), dS = P * (dP * scale - delta * scale)
 template <bool DIAG>
-__device__ __forceinline__ void dq_half_row(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], int cc, int row, float sl2,
-                                            float lse2, float scale, float delta_s, uint32_t (&pk)[64]) {
+__device__ __forceinline__ void dq_half_row(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], int col0, int row, float sl2,
+                                            float lse2, float scale, float delta_s, uint32_t (&pk)[32]) {
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
-    const int c = cc * 2 + u;
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
       float p0 = ex2_approx(fmaf(__uint_as_float(rs[u][i]), sl2, -lse2));
       float p1 = ex2_approx(fmaf(__uint_as_float(rs[u][i + 1]), sl2, -lse2));
       if (DIAG) {
-        if (c * 32 + i > row) p0 = 0.f;
-        if (c * 32 + i + 1 > row) p1 = 0.f;
+        if (col0 + u * 32 + i > row) p0 = 0.f;
+        if (col0 + u * 32 + i + 1 > row) p1 = 0.f;
       }
-      pk[c * 16 + (i >> 1)] = pack_bf16(p0 * fmaf(__uint_as_float(rp[u][i]), scale, -delta_s),
+      pk[u * 16 + (i >> 1)] = pack_bf16(p0 * fmaf(__uint_as_float(rp[u][i]), scale, -delta_s),
                                         p1 * fmaf(__uint_as_float(rp[u][i + 1]), scale, -delta_s));
     }
   }
@@ -460,6 +501,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 score columns / which D/2 output columns
     const int row = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
@@ -472,18 +514,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
       if (!mbar_wait(&bars->s_full[0], j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const bool diag = (j == qt);
-      uint32_t pk[64];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      uint32_t pk[32];
+      {
         uint32_t rs[2][32], rp[2][32];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          tmem_ld_32x32(tmem_base + lane_off + (cc * 2 + u) * 32, rs[u]);
-          tmem_ld_32x32(tmem_base + 128 + lane_off + (cc * 2 + u) * 32, rp[u]);
+          tmem_ld_32x32(tmem_base + lane_off + half * 64 + u * 32, rs[u]);
+          tmem_ld_32x32(tmem_base + 128 + lane_off + half * 64 + u * 32, rp[u]);
         }
         tmem_ld_wait();
-        if (!diag) dq_half_row<false>(rs, rp, cc, row, sl2, lse2, p.scale, delta_s, pk);
-        else       dq_half_row<true>(rs, rp, cc, row, sl2, lse2, p.scale, delta_s, pk);
+        if (!diag) dq_half_row<false>(rs, rp, half * 64, row, sl2, lse2, p.scale, delta_s, pk);
+        else       dq_half_row<true>(rs, rp, half * 64, row, sl2, lse2, p.scale, delta_s, pk);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -492,9 +533,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
         if (!mbar_wait(&bars->acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
+      for (int ch = 0; ch < 8; ++ch) {
         const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sds + (ch >> 3) * SLAB + swz(row, ch & 7)) = v;
+        *reinterpret_cast<uint4*>(sds + half * SLAB + swz(row, ch)) = v;
       }
       fence_proxy_async();
       tc_fence_before_sync();
@@ -503,11 +544,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     }
     if (ok && mbar_wait(&bars->acc_done, (n_kv - 1) & 1, abort_flag)) {
       tc_fence_after_sync();
-      __nv_bfloat16* drow = p.dqkv + static_cast<size_t>(row0 + row) * (3 * HD) + h * D;
+      __nv_bfloat16* drow = p.dqkv + static_cast<size_t>(row0 + row) * (3 * HD) + h * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + 256 + lane_off + c * 32, r);
+        tmem_ld_32x32(tmem_base + 256 + lane_off + half * (D / 2) + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -524,31 +565,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
 }
 
-// P^T and dS^T for one key row against 64 queries; the per-query statistics come in 16-byte broadcast loads.
+// P^T and dS^T for one key row against 32 queries (`qa0` = sequence index of the first); the per-query statistics come
+// in 16-byte broadcast loads.
 template <bool DIAG>
-__device__ __forceinline__ void dkv_row(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], const float* __restrict__ lse2,
-                                        const float* __restrict__ delta_s, int q0, int key, float sl2, float scale,
-                                        uint32_t (&pp)[32], uint32_t (&pd)[32]) {
+__device__ __forceinline__ void dkv_row(const uint32_t (&rs)[32], const uint32_t (&rp)[32], const float* __restrict__ lse2,
+                                        const float* __restrict__ delta_s, int qa0, int key, float sl2, float scale,
+                                        uint32_t (&pp)[16], uint32_t (&pd)[16]) {
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int i = 0; i < 32; i += 4) {
+    const float4 l = __ldg(reinterpret_cast<const float4*>(lse2 + i));
+    const float4 e = __ldg(reinterpret_cast<const float4*>(delta_s + i));
+    const float lv[4] = {l.x, l.y, l.z, l.w}, ev[4] = {e.x, e.y, e.z, e.w};
+    float pr[4];
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      const float4 l = __ldg(reinterpret_cast<const float4*>(lse2 + c * 32 + i));
-      const float4 e = __ldg(reinterpret_cast<const float4*>(delta_s + c * 32 + i));
-      const float lv[4] = {l.x, l.y, l.z, l.w}, ev[4] = {e.x, e.y, e.z, e.w};
-      float pr[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        pr[k] = ex2_approx(fmaf(__uint_as_float(rs[c][i + k]), sl2, -lv[k]));
-        if (DIAG && key > q0 + c * 32 + i + k) pr[k] = 0.f;
-      }
-      pp[c * 16 + (i >> 1)] = pack_bf16(pr[0], pr[1]);
-      pp[c * 16 + (i >> 1) + 1] = pack_bf16(pr[2], pr[3]);
-      pd[c * 16 + (i >> 1)] = pack_bf16(pr[0] * fmaf(__uint_as_float(rp[c][i]), scale, -ev[0]),
-                                        pr[1] * fmaf(__uint_as_float(rp[c][i + 1]), scale, -ev[1]));
-      pd[c * 16 + (i >> 1) + 1] = pack_bf16(pr[2] * fmaf(__uint_as_float(rp[c][i + 2]), scale, -ev[2]),
-                                            pr[3] * fmaf(__uint_as_float(rp[c][i + 3]), scale, -ev[3]));
+    for (int k = 0; k < 4; ++k) {
+      pr[k] = ex2_approx(fmaf(__uint_as_float(rs[i + k]), sl2, -lv[k]));
+      if (DIAG && key > qa0 + i + k) pr[k] = 0.f;
     }
+    pp[i >> 1] = pack_bf16(pr[0], pr[1]);
+    pp[(i >> 1) + 1] = pack_bf16(pr[2], pr[3]);
+    pd[i >> 1] = pack_bf16(pr[0] * fmaf(__uint_as_float(rp[i]), scale, -ev[0]), pr[1] * fmaf(__uint_as_float(rp[i + 1]), scale, -ev[1]));
+    pd[(i >> 1) + 1] = pack_bf16(pr[2] * fmaf(__uint_as_float(rp[i + 2]), scale, -ev[2]), pr[3] * fmaf(__uint_as_float(rp[i + 3]), scale, -ev[3]));
   }
 }
 
@@ -663,6 +700,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 32 of the 64 queries of a sub-tile / which D/2 output columns
     const int row = quad * 32 + lane;  // key row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
@@ -674,20 +712,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
     for (int t = 0; t < n_sub && ok; ++t) {
       if (!mbar_wait(&bars->s_full[0], t & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      const int q0 = (first_sub + t) * KV_QSUB;       // first query row of the sub-tile (sequence index)
-      const int key = kt * ATT_BM + row;              // this thread's key (sequence index)
-      const bool diag = q0 < (kt + 1) * ATT_BM;       // sub-tile overlaps the diagonal block
-      uint32_t pp[32], pd[32];
+      const int qa0 = (first_sub + t) * KV_QSUB + half * 32;  // first query (sequence index) this thread handles
+      const int key = kt * ATT_BM + row;                      // this thread's key (sequence index)
+      const bool diag = qa0 < (kt + 1) * ATT_BM;              // may overlap the diagonal block
+      uint32_t pp[16], pd[16];
       {
-        uint32_t rs[2][32], rp[2][32];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld_32x32(tmem_base + lane_off + c * 32, rs[c]);
-          tmem_ld_32x32(tmem_base + 64 + lane_off + c * 32, rp[c]);
-        }
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_base + lane_off + half * 32, rs);
+        tmem_ld_32x32(tmem_base + 64 + lane_off + half * 32, rp);
         tmem_ld_wait();
-        if (!diag) dkv_row<false>(rs, rp, lse2_bh + q0, delta_bh + q0, q0, key, sl2, p.scale, pp, pd);
-        else       dkv_row<true>(rs, rp, lse2_bh + q0, delta_bh + q0, q0, key, sl2, p.scale, pp, pd);
+        if (!diag) dkv_row<false>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
+        else       dkv_row<true>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -696,9 +731,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
         if (!mbar_wait(&bars->acc_done, (t - 1) & 1, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {  // 64 query columns = 8 chunks of 8 bf16
-        *reinterpret_cast<uint4*>(spt + swz(row, ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sdst + swz(row, ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
+      for (int ch = 0; ch < 4; ++ch) {  // 32 query columns = 4 chunks of 8 bf16
+        *reinterpret_cast<uint4*>(spt + swz(row, half * 4 + ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(sdst + swz(row, half * 4 + ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
       }
       fence_proxy_async();
       tc_fence_before_sync();
@@ -707,13 +742,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
     }
     if (ok && mbar_wait(&bars->acc_done, (n_sub - 1) & 1, abort_flag)) {
       tc_fence_after_sync();
-      __nv_bfloat16* base = p.dqkv + static_cast<size_t>(krow0 + row) * (3 * HD) + h * D;
+      __nv_bfloat16* base = p.dqkv + static_cast<size_t>(krow0 + row) * (3 * HD) + h * D + half * (D / 2);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {  // 0: dK (TMEM cols 256..), 1: dV (cols 128..)
-        const uint32_t tcol = which == 0 ? 256u : 128u;
+        const uint32_t tcol = (which == 0 ? 256u : 128u) + static_cast<uint32_t>(half * (D / 2));
         __nv_bfloat16* drow = base + (which == 0 ? HD : 2 * HD);
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + tcol + lane_off + c * 32, r);
           tmem_ld_wait();
