@@ -38,7 +38,12 @@ struct AttnParams {
   const float* delta; // [2, B, H, S]: scale * rowsum(dO * O), then the base-2 lse (both written by attn_delta_kernel)
   __nv_bfloat16* dqkv;  // [B*S, 3*H*D]
   int* status;
+  unsigned long long* trace;  // optional timeline of CTA (0,0,0) of the forward kernel: [role][iteration][4] ns stamps
 };
+
+#define ATT_TRACE(role, j, k)                                                                                       \
+  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64)                     \
+    p.trace[((role) * 64 + (j)) * 4 + (k)] = globaltimer_ns();
 
 // byte offset of (row, 16-byte chunk) inside a 128-byte-swizzled [rows x 64 bf16] slab
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
@@ -68,7 +73,8 @@ struct AttnBars {
   uint64_t stat_full;     // stationary tiles landed
   uint64_t str_full[2];   // streamed stage landed (first operand)
   uint64_t str2_full[2];  // streamed stage landed (second operand)
-  uint64_t str_empty[2];  // streamed stage free again
+  uint64_t str_empty[2];  // streamed stage free again (forward: the V half of the stage)
+  uint64_t k_empty[2];    // forward: K half of the stage free again (released as soon as S = Q K^T has read it)
   uint64_t s_full[2];     // score accumulator(s) ready in TMEM
   uint64_t s_empty[2];    // score accumulator(s) drained by the softmax threads
   uint64_t p_full;        // probabilities / dS written to shared memory
@@ -115,6 +121,7 @@ __device__ __forceinline__ void attn_init_bars(AttnBars* b) {
     mbar_init(&b->str_full[i], 1);
     mbar_init(&b->str2_full[i], 1);
     mbar_init(&b->str_empty[i], 1);
+    mbar_init(&b->k_empty[i], 1);
     mbar_init(&b->s_full[i], 1);
     mbar_init(&b->s_empty[i], 8);
   }
@@ -237,12 +244,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
       for (int c = 0; c < SLABS; ++c) tma_load_2d(smem + L::Q_OFF + c * SLAB, &tm_qkv, &bars->stat_full, h * D + c * 64, row0);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
-        if (!mbar_wait(&bars->str_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        if (!mbar_wait(&bars->k_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        ATT_TRACE(0, j, 0)
         const int krow = b * p.S + j * ATT_BM;
         mbar_expect_tx(&bars->str_full[st], L::TILE);
 #pragma unroll
         for (int c = 0; c < SLABS; ++c)
           tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], HD + h * D + c * 64, krow);
+        if (!mbar_wait(&bars->str_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        ATT_TRACE(0, j, 1)
         mbar_expect_tx(&bars->str2_full[st], L::TILE);
 #pragma unroll
         for (int c = 0; c < SLABS; ++c)
@@ -258,13 +268,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) return false;
+        ATT_TRACE(1, j, 0)
         if (!mbar_wait(&bars->s_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) return false;
+        ATT_TRACE(1, j, 1)
         tc_fence_after_sync();
         const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
           umma_f16_ss(tmem_base + st * 128, desc_kmajor(sq, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
         umma_commit(&bars->s_full[st]);
+        umma_commit(&bars->k_empty[st]);  // the K tile can be refilled while the softmax and P V of this step run
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -272,7 +285,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
         if (j + 1 < n_kv) { if (!issue_s(j + 1)) { ok = false; break; } }
         const int st = j & 1;
         if (!mbar_wait(&bars->p_full, j & 1, abort_flag)) { ok = false; break; }
+        ATT_TRACE(1, j, 2)
         if (!mbar_wait(&bars->str2_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        ATT_TRACE(1, j, 3)
         tc_fence_after_sync();
         const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
 #pragma unroll
@@ -294,6 +309,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
     for (int j = 0; j < n_kv && ok; ++j) {
       const int st = j & 1;
       if (!mbar_wait(&bars->s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, j, 0) }
       tc_fence_after_sync();
       const uint32_t ts = tmem_base + st * 128 + half * 64 + lane_off;
       const bool diag = (j == qt);
@@ -301,10 +317,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) tmem_ld_32x32(ts + c * 32, sr[c]);
       tmem_ld_wait();
+      if (warp == 2 && lane == 0) { ATT_TRACE(3, j, 0) }
       // Tiles below the diagonal need no mask; only the last tile of a CTA pays for the comparisons.
       float mx, other;
       if (!diag) mx = fwd_row_max<false>(sr, half * 64, row); else mx = fwd_row_max<true>(sr, half * 64, row);
+      if (warp == 2 && lane == 0) { ATT_TRACE(3, j, 1) }
       if (!__all_sync(0xffffffffu, pair_exchange(xch, j & 1, half, row, j + 1, mx, other, abort_flag))) { ok = false; break; }
+      if (warp == 2 && lane == 0) { ATT_TRACE(3, j, 2) }
       mx = fmaxf(mx, other);
       // Keep the old maximum while the new one is at most 2^8 above it: the probabilities stay well inside the
       // bf16 / fp32 range and O needs no rescaling (the final 1 / l normalisation uses the same maximum).
@@ -318,9 +337,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[st]);
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, j, 1) }
       // O and the P buffer belong to the previous P V product until it has completed
       if (j > 0) {
         if (!mbar_wait(&bars->acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
+        if (warp == 2 && lane == 0) { ATT_TRACE(2, j, 2) }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
@@ -349,6 +370,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, j, 3) }
       l_run = l_run * alpha + rs;
       m_run = m_new;
     }
@@ -811,6 +833,14 @@ static inline int one_cta_smem(int bytes) { return bytes < kMinSmem ? kMinSmem :
 
 FSB_API int fsb_last_tensor_map_result() { return fsb_host::last_encode_result(); }
 
+// Debug aid: when set to a device buffer of 4 * 64 * 4 uint64, the forward kernel's CTA (0,0,0) records nanosecond
+// time stamps of its producer / MMA / softmax roles per key tile.  Pass nullptr to switch it off again.
+static unsigned long long* g_attn_trace = nullptr;
+FSB_API int fsb_attn_set_trace(void* buf) {
+  g_attn_trace = static_cast<unsigned long long*>(buf);
+  return 0;
+}
+
 FSB_API int fsb_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int H, int D, float scale, int* status,
                          cudaStream_t stream) {
   using namespace fsb;
@@ -819,7 +849,7 @@ FSB_API int fsb_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int
   if (!fsb_host::encode_2d_16bit(&tm, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, ATT_BM)) return -1;
   AttnParams p{};
   p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
-  p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = status;
+  p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = status; p.trace = g_attn_trace;
   dim3 grid(S / ATT_BM, H, B);
   if (D == 128) {
     set_smem(attn_fwd_kernel<128>, FwdSmem<128>::TOTAL);
