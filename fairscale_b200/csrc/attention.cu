@@ -71,9 +71,9 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int ks, uint32_t
 
 struct AttnBars {
   uint64_t stat_full;     // stationary tiles landed
-  uint64_t str_full[2];   // streamed stage landed (first operand)
+  uint64_t str_full[3];   // streamed stage landed (first operand)
   uint64_t str2_full[2];  // streamed stage landed (second operand)
-  uint64_t str_empty[2];  // streamed stage free again (forward: the V half of the stage)
+  uint64_t str_empty[3];  // streamed stage free again (forward: the V half of the stage)
   uint64_t k_empty[2];    // forward: K half of the stage free again (released as soon as S = Q K^T has read it)
   uint64_t s_full[2];     // score accumulator(s) ready in TMEM
   uint64_t s_empty[2];    // score accumulator(s) drained by the softmax threads
@@ -117,6 +117,8 @@ __device__ __forceinline__ bool pair_exchange(PairXch* bars, int parity, int hal
 
 __device__ __forceinline__ void attn_init_bars(AttnBars* b) {
   mbar_init(&b->stat_full, 1);
+  mbar_init(&b->str_full[2], 1);
+  mbar_init(&b->str_empty[2], 1);
   for (int i = 0; i < 2; ++i) {
     mbar_init(&b->str_full[i], 1);
     mbar_init(&b->str2_full[i], 1);
@@ -622,9 +624,10 @@ struct DkvSmem {
   static constexpr int QTILE = KV_QSUB * D * 2;   // Q or dO sub-tile
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = TILE;
-  static constexpr int Q_OFF = 2 * TILE;                 // 2 stages
-  static constexpr int DO_OFF = 2 * TILE + 2 * QTILE;    // 2 stages
-  static constexpr int PT_OFF = 2 * TILE + 4 * QTILE;    // [128 keys x 64 q] bf16
+  static constexpr int STAGES = 3;                             // Q / dO sub-tiles in flight
+  static constexpr int Q_OFF = 2 * TILE;
+  static constexpr int DO_OFF = 2 * TILE + STAGES * QTILE;
+  static constexpr int PT_OFF = 2 * TILE + 2 * STAGES * QTILE;  // [128 keys x 64 q] bf16
   static constexpr int DST_OFF = PT_OFF + ATT_BM * KV_QSUB * 2;
   static constexpr int BAR_OFF = DST_OFF + ATT_BM * KV_QSUB * 2;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
@@ -650,7 +653,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
   const int krow0 = b * p.S + kt * ATT_BM;
   const int first_sub = kt * (ATT_BM / KV_QSUB);
   const int n_sub = p.S / KV_QSUB - first_sub;
-  constexpr uint32_t TMEM_COLS = 512;  // S^T [0,64) dP^T [64,128) dV [128,128+D) dK [256,256+D)
+  // S^T / dP^T are double-buffered so the products of sub-tile t+1 run while the threads work on sub-tile t:
+  // buffer 0: S^T [0,64) dP^T [64,128); buffer 1: S^T [384,448) dP^T [448,512); dV [128,128+D); dK [256,256+D)
+  constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
     attn_init_bars(bars);
@@ -676,8 +681,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
         tma_load_2d(smem + L::V_OFF + c * SLAB, &tm_kv, &bars->stat_full, 2 * HD + h * D + c * 64, krow0);
       }
       for (int t = 0; t < n_sub; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(&bars->str_empty[st], ((t >> 1) & 1) ^ 1u, abort_flag)) break;
+        const int st = t % L::STAGES;
+        if (!mbar_wait(&bars->str_empty[st], ((t / L::STAGES) & 1) ^ 1u, abort_flag)) break;
         const int qrow = b * p.S + (first_sub + t) * KV_QSUB;
         mbar_expect_tx(&bars->str_full[st], 2 * L::QTILE);
 #pragma unroll
@@ -694,20 +699,30 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
       const uint32_t sk = smem_u32(smem + L::K_OFF), sv = smem_u32(smem + L::V_OFF);
       const uint32_t spt = smem_u32(smem + L::PT_OFF), sdst = smem_u32(smem + L::DST_OFF);
       bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
-      for (int t = 0; t < n_sub && ok; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(&bars->str_full[st], (t >> 1) & 1, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(&bars->s_empty[0], (t & 1) ^ 1u, abort_flag)) { ok = false; break; }
+      // S^T(t) = K Q_t^T and dP^T(t) = V dO_t^T into accumulator buffer t & 1
+      auto issue_sp = [&](int t) -> bool {
+        const int st = t % L::STAGES, buf = t & 1;
+        if (!mbar_wait(&bars->str_full[st], (t / L::STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars->s_empty[buf], ((t >> 1) & 1) ^ 1u, abort_flag)) return false;
         tc_fence_after_sync();
         const uint32_t sq = smem_u32(smem + L::Q_OFF + st * L::QTILE);
         const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
+        const uint32_t t_s = tmem_base + (buf ? 384u : 0u), t_p = tmem_base + (buf ? 448u : 64u);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
-          umma_f16_ss(tmem_base, desc_kmajor(sk, ks, SLAB), desc_kmajor(sq, ks, QSLAB), idesc_s, ks != 0);
+          umma_f16_ss(t_s, desc_kmajor(sk, ks, SLAB), desc_kmajor(sq, ks, QSLAB), idesc_s, ks != 0);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
-          umma_f16_ss(tmem_base + 64, desc_kmajor(sv, ks, SLAB), desc_kmajor(sdo, ks, QSLAB), idesc_s, ks != 0);
-        umma_commit(&bars->s_full[0]);
+          umma_f16_ss(t_p, desc_kmajor(sv, ks, SLAB), desc_kmajor(sdo, ks, QSLAB), idesc_s, ks != 0);
+        umma_commit(&bars->s_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sp(0);
+      for (int t = 0; t < n_sub && ok; ++t) {
+        if (t + 1 < n_sub) { if (!issue_sp(t + 1)) { ok = false; break; } }
+        const int st = t % L::STAGES;
+        const uint32_t sq = smem_u32(smem + L::Q_OFF + st * L::QTILE);
+        const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
         if (!mbar_wait(&bars->p_full, t & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
@@ -732,7 +747,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
     uint8_t* sdst = smem + L::DST_OFF;
     bool ok = true;
     for (int t = 0; t < n_sub && ok; ++t) {
-      if (!mbar_wait(&bars->s_full[0], t & 1, abort_flag)) { ok = false; break; }
+      const int buf = t & 1;
+      if (!mbar_wait(&bars->s_full[buf], (t >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const int qa0 = (first_sub + t) * KV_QSUB + half * 32;  // first query (sequence index) this thread handles
       const int key = kt * ATT_BM + row;                      // this thread's key (sequence index)
@@ -740,15 +756,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
       uint32_t pp[16], pd[16];
       {
         uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + lane_off + half * 32, rs);
-        tmem_ld_32x32(tmem_base + 64 + lane_off + half * 32, rp);
+        tmem_ld_32x32(tmem_base + (buf ? 384u : 0u) + lane_off + half * 32, rs);
+        tmem_ld_32x32(tmem_base + (buf ? 448u : 64u) + lane_off + half * 32, rp);
         tmem_ld_wait();
         if (!diag) dkv_row<false>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
         else       dkv_row<true>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[0]);
+      if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
       if (t > 0) {
         if (!mbar_wait(&bars->acc_done, (t - 1) & 1, abort_flag)) { ok = false; break; }
       }
