@@ -79,6 +79,7 @@ struct AttnBars {
   uint64_t s_empty[2];    // score accumulator(s) drained by the softmax threads
   uint64_t p_full;        // probabilities / dS written to shared memory
   uint64_t acc_done;      // accumulate-type MMAs of the iteration finished (P buffer + accumulators free)
+  uint64_t acc_done2[2];  // dQ kernel: the same, alternating with the double-buffered dS tile
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -129,6 +130,8 @@ __device__ __forceinline__ void attn_init_bars(AttnBars* b) {
   }
   mbar_init(&b->p_full, 8);
   mbar_init(&b->acc_done, 1);
+  mbar_init(&b->acc_done2[0], 1);
+  mbar_init(&b->acc_done2[1], 1);
   b->abort_flag = 0;
   fence_barrier_init();
 }
@@ -405,28 +408,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, AttnParams p) {
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
 }
 
-// dS for 64 columns (starting at column `col0`) of one row: P = 2^(s * sl2 - lse2), dS = P * (dP * scale - delta * scale)
+// dS for 32 columns (starting at key column `col0` of the 128-key tile) of one row:
+// P = 2^(s * sl2 - lse2), dS = P * (dP * scale - delta * scale)
 template <bool DIAG>
-__device__ __forceinline__ void dq_half_row(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], int col0, int row, float sl2,
-                                            float lse2, float scale, float delta_s, uint32_t (&pk)[32]) {
+__device__ __forceinline__ void dq_cols32(const uint32_t (&rs)[32], const uint32_t (&rp)[32], int col0, int row, float sl2,
+                                          float lse2, float scale, float delta_s, uint32_t (&pk)[16]) {
 #pragma unroll
-  for (int u = 0; u < 2; ++u) {
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float p0 = ex2_approx(fmaf(__uint_as_float(rs[u][i]), sl2, -lse2));
-      float p1 = ex2_approx(fmaf(__uint_as_float(rs[u][i + 1]), sl2, -lse2));
-      if (DIAG) {
-        if (col0 + u * 32 + i > row) p0 = 0.f;
-        if (col0 + u * 32 + i + 1 > row) p1 = 0.f;
-      }
-      pk[u * 16 + (i >> 1)] = pack_bf16(p0 * fmaf(__uint_as_float(rp[u][i]), scale, -delta_s),
-                                        p1 * fmaf(__uint_as_float(rp[u][i + 1]), scale, -delta_s));
+  for (int i = 0; i < 32; i += 2) {
+    float p0 = ex2_approx(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
+    float p1 = ex2_approx(fmaf(__uint_as_float(rs[i + 1]), sl2, -lse2));
+    if (DIAG) {
+      if (col0 + i > row) p0 = 0.f;
+      if (col0 + i + 1 > row) p1 = 0.f;
     }
+    pk[i >> 1] = pack_bf16(p0 * fmaf(__uint_as_float(rp[i]), scale, -delta_s), p1 * fmaf(__uint_as_float(rp[i + 1]), scale, -delta_s));
   }
 }
 
 // =================================================================================================
-// Backward, dQ: one CTA per 128 query rows; streams K and V tiles.
+// Backward, dQ: one CTA per 128 query rows; streams K and V tiles and consumes them in two steps of 64 keys, so that
+// S / dP fit TMEM twice and the products of step u+1 overlap the exponentials of step u.
 // =================================================================================================
 template <int D>
 struct DqSmem {
@@ -435,7 +436,7 @@ struct DqSmem {
   static constexpr int DO_OFF = TILE;
   static constexpr int K_OFF = 2 * TILE;   // 2 stages
   static constexpr int V_OFF = 4 * TILE;   // 2 stages
-  static constexpr int DS_OFF = 6 * TILE;  // [128 x 128] bf16
+  static constexpr int DS_OFF = 6 * TILE;  // two [128 x 64] bf16 buffers
   static constexpr int BAR_OFF = DS_OFF + ATT_BM * 128 * 2;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
@@ -458,7 +459,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
   const int n_kv = qt + 1;
   const int HD = p.H * D;
   const int row0 = b * p.S + qt * ATT_BM;
-  constexpr uint32_t TMEM_COLS = 512;  // S [0,128) dP [128,256) dQ [256, 256+D)
+  constexpr uint32_t TMEM_COLS = 512;  // buffer b: S [128 b, +64) dP [128 b + 64, +64); dQ [256, 256+D)
 
   if (threadIdx.x == 0) {
     attn_init_bars(bars);
@@ -496,31 +497,40 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(ATT_BM, 128, true, false, false);
+      const uint32_t idesc_s = make_idesc_f16(ATT_BM, 64, true, false, false);
       const uint32_t idesc_q = make_idesc_f16(ATT_BM, D, true, false, true);  // dS K : K tile read MN-major
       const uint32_t sq = smem_u32(smem + L::Q_OFF), sdo = smem_u32(smem + L::DO_OFF), sds = smem_u32(smem + L::DS_OFF);
+      const int n_steps = 2 * n_kv;
       bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(&bars->s_empty[0], (j & 1) ^ 1u, abort_flag)) { ok = false; break; }
+      // step u = key tile u / 2, keys [64 (u & 1), +64) of it; S and dP of step u go to accumulator buffer u & 1
+      auto issue_sp = [&](int u) -> bool {
+        const int j = u >> 1, hh = u & 1, st = j & 1, buf = u & 1;
+        if (hh == 0 && !mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars->s_empty[buf], ((u >> 1) & 1) ^ 1u, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE) + hh * 8192u;  // rows 64 hh .. of every slab
+        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE) + hh * 8192u;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base + buf * 128, desc_kmajor(sq, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_f16_ss(tmem_base + buf * 128 + 64, desc_kmajor(sdo, ks, SLAB), desc_kmajor(sv, ks, SLAB), idesc_s, ks != 0);
+        umma_commit(&bars->s_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sp(0);
+      for (int u = 0; u < n_steps && ok; ++u) {
+        if (u + 1 < n_steps) { if (!issue_sp(u + 1)) { ok = false; break; } }
+        const int j = u >> 1, hh = u & 1, st = j & 1, buf = u & 1;
+        if (!mbar_wait(&bars->p_full, u & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
-        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          umma_f16_ss(tmem_base, desc_kmajor(sq, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          umma_f16_ss(tmem_base + 128, desc_kmajor(sdo, ks, SLAB), desc_kmajor(sv, ks, SLAB), idesc_s, ks != 0);
-        umma_commit(&bars->s_full[0]);
-        if (!mbar_wait(&bars->p_full, j & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 128 / 16; ++ks)
-          umma_f16_ss(tmem_base + 256, desc_kmajor(sds, ks, SLAB), desc_mnmajor(sk, ks, SLAB), idesc_q, (j | ks) != 0);
-        umma_commit(&bars->str_empty[st]);
-        umma_commit(&bars->acc_done);
+        for (int ks = 0; ks < 64 / 16; ++ks)
+          umma_f16_ss(tmem_base + 256, desc_kmajor(sds + buf * 16384u, ks, SLAB), desc_mnmajor(sk, hh * 4 + ks, SLAB), idesc_q, (u | ks) != 0);
+        if (hh == 1) umma_commit(&bars->str_empty[st]);
+        umma_commit(&bars->acc_done2[buf]);
       }
     }
   } else {
@@ -533,40 +543,39 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     const float lse2 = p.delta[static_cast<size_t>(p.B) * p.H * p.S + stat_idx];  // base-2 lse, written by the delta kernel
     const float delta_s = p.delta[stat_idx];                                       // scale * rowsum(dO * O)
     uint8_t* sds = smem + L::DS_OFF;
+    const int n_steps = 2 * n_kv;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      if (!mbar_wait(&bars->s_full[0], j & 1, abort_flag)) { ok = false; break; }
+    for (int u = 0; u < n_steps && ok; ++u) {
+      const int j = u >> 1, hh = u & 1, buf = u & 1;
+      if (!mbar_wait(&bars->s_full[buf], (u >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const bool diag = (j == qt);
-      uint32_t pk[32];
+      uint32_t pk[16];
       {
-        uint32_t rs[2][32], rp[2][32];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          tmem_ld_32x32(tmem_base + lane_off + half * 64 + u * 32, rs[u]);
-          tmem_ld_32x32(tmem_base + 128 + lane_off + half * 64 + u * 32, rp[u]);
-        }
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_base + buf * 128 + lane_off + half * 32, rs);
+        tmem_ld_32x32(tmem_base + buf * 128 + 64 + lane_off + half * 32, rp);
         tmem_ld_wait();
-        if (!diag) dq_half_row<false>(rs, rp, half * 64, row, sl2, lse2, p.scale, delta_s, pk);
-        else       dq_half_row<true>(rs, rp, half * 64, row, sl2, lse2, p.scale, delta_s, pk);
+        if (!diag) dq_cols32<false>(rs, rp, hh * 64 + half * 32, row, sl2, lse2, p.scale, delta_s, pk);
+        else       dq_cols32<true>(rs, rp, hh * 64 + half * 32, row, sl2, lse2, p.scale, delta_s, pk);
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[0]);
-      if (j > 0) {
-        if (!mbar_wait(&bars->acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
+      if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
+      if (u >= 2) {  // the dQ product that read this dS buffer two steps ago
+        if (!mbar_wait(&bars->acc_done2[buf], ((u >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sds + half * SLAB + swz(row, ch)) = v;
+        *reinterpret_cast<uint4*>(sds + buf * 16384 + swz(row, half * 4 + ch)) = v;
       }
       fence_proxy_async();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
     }
-    if (ok && mbar_wait(&bars->acc_done, (n_kv - 1) & 1, abort_flag)) {
+    if (ok && mbar_wait(&bars->acc_done2[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_flag)) {
       tc_fence_after_sync();
       __nv_bfloat16* drow = p.dqkv + static_cast<size_t>(row0 + row) * (3 * HD) + h * D + half * (D / 2);
 #pragma unroll 1
