@@ -506,7 +506,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
       auto issue_sp = [&](int u) -> bool {
         const int j = u >> 1, hh = u & 1, st = j & 1, buf = u & 1;
         if (hh == 0 && !mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) return false;
+        ATT_TRACE(1, u, 0)
         if (!mbar_wait(&bars->s_empty[buf], ((u >> 1) & 1) ^ 1u, abort_flag)) return false;
+        ATT_TRACE(1, u, 1)
         tc_fence_after_sync();
         const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE) + hh * 8192u;  // rows 64 hh .. of every slab
         const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE) + hh * 8192u;
@@ -524,6 +526,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
         if (u + 1 < n_steps) { if (!issue_sp(u + 1)) { ok = false; break; } }
         const int j = u >> 1, hh = u & 1, st = j & 1, buf = u & 1;
         if (!mbar_wait(&bars->p_full, u & 1, abort_flag)) { ok = false; break; }
+        ATT_TRACE(1, u, 2)
         tc_fence_after_sync();
         const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
 #pragma unroll
@@ -548,6 +551,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     for (int u = 0; u < n_steps && ok; ++u) {
       const int j = u >> 1, hh = u & 1, buf = u & 1;
       if (!mbar_wait(&bars->s_full[buf], (u >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 0) }
       tc_fence_after_sync();
       const bool diag = (j == qt);
       uint32_t pk[16];
@@ -562,9 +566,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 1) }
       if (u >= 2) {  // the dQ product that read this dS buffer two steps ago
         if (!mbar_wait(&bars->acc_done2[buf], ((u >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
       }
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 2) }
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
@@ -574,6 +580,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
+      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 3) }
     }
     if (ok && mbar_wait(&bars->acc_done2[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_flag)) {
       tc_fence_after_sync();
@@ -900,6 +907,7 @@ FSB_API int fsb_attn_bwd(const void* qkv, const void* o, const void* d_o, const 
   p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
   p.o = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(o));
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = static_cast<__nv_bfloat16*>(dqkv); p.status = status;
+  p.trace = g_attn_trace;
   {
     const long long warps = static_cast<long long>(B) * S * H;
     const int threads = 256;
