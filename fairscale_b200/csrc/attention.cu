@@ -822,30 +822,36 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
 }
 
-// delta[b, h, s] = scale * sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head).
+// delta[b, h, s] = scale * sum_d dO[b, s, h, d] * O[b, s, h, d].  D / 8 lanes share one (token, head) pair (16 bytes per
+// lane and tensor), so a warp covers 256 / D pairs per step and keeps several independent loads in flight.
 // Also writes the base-2 log-sum-exp right behind it: delta[B*H*S + i] = lse[i] * log2(e).
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
-                                  float* __restrict__ delta, float scale, int B, int S, int H, int D) {
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                         const float* __restrict__ lse, float* __restrict__ delta, float scale, int B,
+                                                         int S, int H, int D) {
+  const int lanes_per = D >> 3;             // 8 or 16
   const int lane = threadIdx.x & 31;
+  const int sub = lane / lanes_per, sl = lane - sub * lanes_per;
+  const int pairs_per_warp = 32 / lanes_per;
   const long long total = static_cast<long long>(B) * S * H;
-  if (w >= total) return;
-  const long long tok = w / H;
-  const int h = static_cast<int>(w - tok * H);
-  const __nv_bfloat16* po = o + (tok * H + h) * D;
-  const __nv_bfloat16* pd = d_o + (tok * H + h) * D;
-  float acc = 0.f;
-  for (int j = lane * 8; j < D; j += 32 * 8) {
-    const Vec16<__nv_bfloat16> a = ld16(po + j), c = ld16(pd + j);
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long base = warp * pairs_per_warp; base < total; base += n_warps * pairs_per_warp) {
+    const long long pair = base + sub;  // (token, head) index in [B*S, H] order == element offset / D
+    float acc = 0.f;
+    if (pair < total) {
+      const Vec16<__nv_bfloat16> a = ld16(o + pair * D + sl * 8), c = ld16(d_o + pair * D + sl * 8);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc += __bfloat162float(a.v[k]) * __bfloat162float(c.v[k]);
-  }
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    const long long bb = tok / S, s = tok - bb * S;
-    const long long idx = (bb * H + h) * S + s;
-    delta[idx] = acc * scale;
-    delta[total + idx] = lse[idx] * LOG2E;
+      for (int k = 0; k < 8; ++k) acc += __bfloat162float(a.v[k]) * __bfloat162float(c.v[k]);
+    }
+    for (int off = lanes_per >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (sl == 0 && pair < total) {
+      const long long tok = pair / H;
+      const int h = static_cast<int>(pair - tok * H);
+      const long long bb = tok / S, ss = tok - bb * S;
+      const long long idx = (bb * H + h) * S + ss;
+      delta[idx] = acc * scale;
+      delta[total + idx] = lse[idx] * LOG2E;
+    }
   }
 }
 
@@ -909,9 +915,10 @@ FSB_API int fsb_attn_bwd(const void* qkv, const void* o, const void* d_o, const 
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = static_cast<__nv_bfloat16*>(dqkv); p.status = status;
   p.trace = g_attn_trace;
   {
-    const long long warps = static_cast<long long>(B) * S * H;
+    const long long pairs = static_cast<long long>(B) * S * H;
     const int threads = 256;
-    const long long blocks = (warps * 32 + threads - 1) / threads;
+    long long blocks = (pairs * (D / 8) + threads - 1) / threads;  // one step per warp at most ...
+    if (blocks > 148 * 16) blocks = 148 * 16;                       // ... but no more CTAs than keep every SM busy
     attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
                                                                              static_cast<const __nv_bfloat16*>(d_o), lse, delta, scale, B, S, H, D);
   }

@@ -233,28 +233,79 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
 }
 
 // ------------------------------------------------------------------------------------------------ ag_gemm
-__device__ __forceinline__ void ag_copy_cta(const FusedParams& f) {
+// Copy engine of a communication CTA: a ring of COPY_BUFS shared-memory buffers of COPY_PIECE bytes, filled by untiled
+// bulk loads (which may read a peer's memory) and drained by bulk stores or by the CTA's threads.  One thread drives
+// it, so ~190 KB are in flight per CTA whatever the NVLink latency, instead of a few 16-byte loads per thread.
+constexpr int COPY_PIECE = 32 * 1024;
+constexpr int COPY_BUFS = 6;  // 192 KB: the operand ring of the compute CTAs, which a communication CTA does not use
+
+struct CopyJob { int chunk; long long off; uint32_t bytes; };
+
+// n-th piece this CTA moves: chunks are visited in `order` (k = 0 .. n_chunks-1 -> chunk id), pieces strided by n_comm
+__device__ __forceinline__ CopyJob copy_job(int n, int per_cta, long long chunk_bytes, int n_comm, int cta) {
+  CopyJob j;
+  j.chunk = n / per_cta;  // index into the visiting order
+  const long long q = cta + static_cast<long long>(n % per_cta) * n_comm;
+  j.off = q * COPY_PIECE;
+  const long long left = chunk_bytes - j.off;
+  j.bytes = static_cast<uint32_t>(left < COPY_PIECE ? left : COPY_PIECE);
+  return j;
+}
+
+__device__ __forceinline__ void ag_copy_cta(const FusedParams& f, uint8_t* smem) {
   const CommCtx& c = f.c;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + COPY_BUFS * COPY_PIECE);
+  __shared__ int copy_abort;
+  if (threadIdx.x == 0) {
+    copy_abort = 0;
+    for (int i = 0; i < COPY_BUFS; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
   if (blockIdx.x == 0) signal_peers(c, c.channel);  // my shard is ready (stream order) -> peers may read it
   if (!wait_peers(c, c.channel)) return;
-  const long long stride = static_cast<long long>(f.n_comm) * blockDim.x;
-  for (int k = 1; k <= c.world; ++k) {
-    const int pr = (c.rank + k) % c.world;  // remote chunks in ring order, the local copy last (nothing waits for it)
-    const uint4* s = reinterpret_cast<const uint4*>(f.peer.p[pr]);
-    uint4* d = f.gather + static_cast<long long>(pr) * f.chunk16;
-    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (; i + 7 * stride < f.chunk16; i += 8 * stride) {  // 8 loads in flight per thread hide the NVLink latency
-      uint4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = ld_peer16(s + i + u * stride);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) d[i + u * stride] = v[u];
+  const long long chunk_bytes = f.chunk16 * 16;
+  const long long pieces = (chunk_bytes + COPY_PIECE - 1) / COPY_PIECE;
+  const int cta = blockIdx.x;
+  const int per_cta = cta < pieces ? static_cast<int>((pieces - cta + f.n_comm - 1) / f.n_comm) : 0;
+  const int n_jobs = per_cta * c.world;
+  if (threadIdx.x == 0 && per_cta > 0) {
+    volatile int* abort_flag = &copy_abort;
+    // visiting order: remote chunks in ring order, the local copy last (nothing waits for it)
+    auto chunk_id = [&](int k) { return (c.rank + 1 + k) % c.world; };
+    auto issue_load = [&](int n) {
+      const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
+      const int b = n % COPY_BUFS;
+      const uint8_t* src = static_cast<const uint8_t*>(f.peer.p[chunk_id(j.chunk)]) + j.off;
+      mbar_expect_tx(&full[b], j.bytes);
+      bulk_load_1d(smem + b * COPY_PIECE, src, j.bytes, &full[b]);
+    };
+    for (int n = 0; n < COPY_BUFS - 1 && n < n_jobs; ++n) issue_load(n);
+    bool ok = true;
+    for (int n = 0; n < n_jobs && ok; ++n) {
+      const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
+      const int b = n % COPY_BUFS;
+      if (!mbar_wait(&full[b], (n / COPY_BUFS) & 1, abort_flag)) { ok = false; break; }
+      uint8_t* dst = reinterpret_cast<uint8_t*>(f.gather) + static_cast<long long>(chunk_id(j.chunk)) * chunk_bytes + j.off;
+      bulk_store_1d(dst, smem + b * COPY_PIECE, j.bytes);
+      tma_store_commit();
+      if (n + COPY_BUFS - 1 < n_jobs) {
+        tma_store_wait_read<1>();  // the store issued one job ago has drained its buffer: refill it
+        issue_load(n + COPY_BUFS - 1);
+      }
+      if ((n + 1) % per_cta == 0) {  // last piece of a chunk for this CTA: publish it
+        tma_store_wait<0>();
+        fence_proxy_async_all();
+        __threadfence();
+        atomicAdd(f.counts + chunk_id(j.chunk), 1u);
+      }
     }
-    for (; i < f.chunk16; i += stride) d[i] = ld_peer16(s + i);
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd(f.counts + pr, 1u);
+    if (!ok && c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
+    tma_store_wait<0>();
+  } else if (threadIdx.x == 0) {
+    for (int k = 0; k < c.world; ++k) atomicAdd(f.counts + k, 1u);  // nothing to copy: still counted as a publisher
   }
+  __syncthreads();
   exit_barrier_n(c, c.channel + 1, static_cast<unsigned int>(f.n_comm));  // peers are done reading my shard
 }
 
@@ -262,11 +313,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ CUtensorMap tmap_a_gather,
                const __grid_constant__ CUtensorMap tmap_b, GemmParams p, FusedParams f) {
   extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   if (static_cast<int>(blockIdx.x) < f.n_comm) {
-    ag_copy_cta(f);
+    ag_copy_cta(f, smem);
     return;
   }
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   fused_gemm_cta<0>(tmap_a_local, tmap_a_gather, tmap_b, p, f, smem);
 }
 
@@ -277,69 +328,81 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
   for (int i = 0; i < 4; ++i) { o[2 * i] = __low2float(h[i]); o[2 * i + 1] = __high2float(h[i]); }
 }
 
-// Peers' partials of my chunk -> fp32 scratch (first peer writes, the others add).  Returns false after a timeout.
-__device__ __forceinline__ bool rs_reduce_cta(const FusedParams& f) {
+// Peers' partials of my chunk -> fp32 scratch (first peer writes, the others add).  Thread 0 pulls 32 KB pieces of
+// a peer's staging buffer into the shared-memory ring with bulk loads as soon as that peer's flag is up; all threads
+// fold a landed piece into the scratch.  Returns false after a timeout.
+__device__ __forceinline__ bool rs_reduce_cta(const FusedParams& f, uint8_t* smem) {
   const CommCtx& c = f.c;
-  __shared__ int ok_flag;
-  const long long stride = static_cast<long long>(f.n_comm) * blockDim.x;
-  for (int j = 0; j + 1 < c.world; ++j) {
-    const int s = (c.rank - 1 - j + 2 * c.world) % c.world;  // the order in which the peers finish my chunk
-    if (threadIdx.x == 0) {
-      ok_flag = 1;
-      const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + s;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + COPY_BUFS * COPY_PIECE);
+  __shared__ int red_abort;
+  if (threadIdx.x == 0) {
+    red_abort = 0;
+    for (int i = 0; i < COPY_BUFS; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  volatile int* abort_flag = &red_abort;
+  const long long chunk_bytes = f.chunk16 * 16;
+  const long long pieces = (chunk_bytes + COPY_PIECE - 1) / COPY_PIECE;
+  const int cta = blockIdx.x;
+  const int per_cta = cta < pieces ? static_cast<int>((pieces - cta + f.n_comm - 1) / f.n_comm) : 0;
+  const int n_jobs = per_cta * (c.world - 1);
+  auto peer_of = [&](int k) { return (c.rank - 1 - k + 2 * c.world) % c.world; };  // the order in which peers finish my chunk
+  int flag_seen = -1;  // thread 0: peers (in visiting order) whose flag has been observed
+  auto issue_load = [&](int n) -> bool {
+    const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
+    if (j.chunk > flag_seen) {
+      const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + peer_of(j.chunk);
       const uint64_t t0 = globaltimer_ns();
       while (static_cast<int32_t>(ld_acquire_sys(flag) - c.epoch) < 0) {
-        if (globaltimer_ns() - t0 > kCommWaitNs) {
-          ok_flag = 0;
-          if (c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
-          break;
+        if (*abort_flag || globaltimer_ns() - t0 > kCommWaitNs) {
+          *abort_flag = 1;
+          return false;
         }
         __nanosleep(128);
       }
+      flag_seen = j.chunk;
     }
-    __syncthreads();
-    if (!ok_flag) return false;
-    const uint4* src = reinterpret_cast<const uint4*>(f.peer.p[s]) + static_cast<long long>(c.rank) * f.chunk16;
-    float4* acc = reinterpret_cast<float4*>(f.acc);
-    const bool first = (j == 0);
-    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (; i + 7 * stride < f.chunk16; i += 8 * stride) {
-      uint4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = ld_peer16(src + i + u * stride);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        float x[8];
-        unpack8(v[u], x);
-        float4* a = acc + 2 * (i + u * stride);
-        if (!first) {
-          const float4 a0 = a[0], a1 = a[1];
-          x[0] += a0.x; x[1] += a0.y; x[2] += a0.z; x[3] += a0.w;
-          x[4] += a1.x; x[5] += a1.y; x[6] += a1.z; x[7] += a1.w;
-        }
-        a[0] = make_float4(x[0], x[1], x[2], x[3]);
-        a[1] = make_float4(x[4], x[5], x[6], x[7]);
-      }
-    }
-    for (; i < f.chunk16; i += stride) {
+    const int b = n % COPY_BUFS;
+    const uint8_t* src = static_cast<const uint8_t*>(f.peer.p[peer_of(j.chunk)]) + static_cast<long long>(c.rank) * chunk_bytes + j.off;
+    mbar_expect_tx(&full[b], j.bytes);
+    bulk_load_1d(smem + b * COPY_PIECE, src, j.bytes, &full[b]);
+    return true;
+  };
+  if (threadIdx.x == 0) {
+    for (int n = 0; n < COPY_BUFS - 1 && n < n_jobs; ++n)
+      if (!issue_load(n)) break;
+  }
+  for (int n = 0; n < n_jobs; ++n) {
+    if (threadIdx.x == 0 && n + COPY_BUFS - 1 < n_jobs && !*abort_flag) issue_load(n + COPY_BUFS - 1);  // buffer of job n-1: free
+    const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
+    const int b = n % COPY_BUFS;
+    if (!mbar_wait(&full[b], (n / COPY_BUFS) & 1, abort_flag)) break;
+    const uint4* piece = reinterpret_cast<const uint4*>(smem + b * COPY_PIECE);
+    float4* acc = reinterpret_cast<float4*>(f.acc) + 2 * (j.off / 16);
+    const bool first = (j.chunk == 0);
+    const int n16 = static_cast<int>(j.bytes / 16);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) {
       float x[8];
-      unpack8(ld_peer16(src + i), x);
-      float4* a = acc + 2 * i;
+      unpack8(piece[i], x);
       if (!first) {
-        const float4 a0 = a[0], a1 = a[1];
+        const float4 a0 = acc[2 * i], a1 = acc[2 * i + 1];
         x[0] += a0.x; x[1] += a0.y; x[2] += a0.z; x[3] += a0.w;
         x[4] += a1.x; x[5] += a1.y; x[6] += a1.z; x[7] += a1.w;
       }
-      a[0] = make_float4(x[0], x[1], x[2], x[3]);
-      a[1] = make_float4(x[4], x[5], x[6], x[7]);
+      acc[2 * i] = make_float4(x[0], x[1], x[2], x[3]);
+      acc[2 * i + 1] = make_float4(x[4], x[5], x[6], x[7]);
     }
-    __syncthreads();
+    __syncthreads();  // the piece is consumed: its buffer may be refilled
   }
+  __syncthreads();
+  const bool ok = (*abort_flag == 0);
+  if (!ok && threadIdx.x == 0 && c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) atomicAdd(f.counts + kMaxRanks, 1u);
   exit_barrier_n(c, c.channel + 1, static_cast<unsigned int>(f.n_comm));  // peers are done reading my staging buffer
-  return true;
+  return ok;
 }
 
 // out = scratch (the peers' sum) + my own partial chunk + bias, on every CTA of the grid once its other work is done.
@@ -383,10 +446,10 @@ __device__ __forceinline__ void rs_final_pass(const FusedParams& f, int N) {
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p, FusedParams f) {
   extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   if (static_cast<int>(blockIdx.x) < f.n_comm) {
-    if (f.c.world > 1 && !rs_reduce_cta(f)) return;
+    if (f.c.world > 1 && !rs_reduce_cta(f, smem)) return;
   } else {
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     fused_gemm_cta<1>(tmap_a, tmap_a, tmap_b, p, f, smem);
   }
   rs_final_pass(f, p.N);

@@ -56,26 +56,55 @@ class Top2Route(NamedTuple):
     num_experts: int
 
 
+def _route_indices_native(logits: Tensor, noise: Tensor) -> Optional[Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]]:
+    """(idx1, idx2, loc1, loc2, count1) from the three-launch CUDA path, or None when it does not apply."""
+    from ...ops import _bind
+
+    S, E = logits.shape
+    if not (_bind.use_native(logits) and logits.dtype in (torch.float32, torch.bfloat16) and 2 <= E <= 512 and logits.is_contiguous()):
+        return None
+    from ctypes import c_int, c_void_p
+
+    _bind._SIGNATURES.setdefault("fsb_top2_workspace_ints", [c_int, c_int])
+    _bind._SIGNATURES.setdefault("fsb_top2_route", [c_void_p, c_int, c_void_p, c_int, c_int] + [c_void_p] * 7)
+    dev = logits.device
+    out = torch.empty((4, S), dtype=torch.int32, device=dev)
+    ws = torch.empty(_bind.fn("fsb_top2_workspace_ints")(S, E), dtype=torch.int32, device=dev)
+    totals = torch.empty(2 * E, dtype=torch.int32, device=dev)
+    noise = noise.to(torch.float32).contiguous()
+    _bind.call("fsb_top2_route", logits.data_ptr(), _bind.dtype_code(logits.dtype), noise.data_ptr(), S, E, out[0].data_ptr(),
+               out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(), ws.data_ptr(), totals.data_ptr(), _bind.stream_ptr(dev), launches=3)
+    o = out.long()
+    return o[0], o[1], o[2], o[3], totals[:E]
+
+
 def top2_route(logits: torch.Tensor, noise: Optional[Tensor] = None) -> Top2Route:
-    """Index-form top-2 routing; ``noise`` (Gumbel, same shape as ``logits``) can be supplied for reproducibility."""
+    """Index-form top-2 routing; ``noise`` (Gumbel, same shape as ``logits``) can be supplied for reproducibility.
+
+    On CUDA the index part (two arg-maxes, slot assignment in token order, per-expert counts) runs in the kernels of
+    ``csrc/top2gate.cu``; the differentiable part (softmax, gate values, auxiliary loss) is ordinary autograd."""
     gates = F.softmax(logits, dim=1, dtype=torch.float)
     S, E = gates.shape
     capacity = 2 * S // E
     assert S % E == 0
-    idx1 = torch.argmax(gates, dim=1)
     if noise is None:
         noise = gumbel_rsample(logits.shape, device=logits.device)
-    noisy = (logits + noise).scatter(1, idx1.unsqueeze(1), float("-inf"))
-    idx2 = torch.argmax(noisy, dim=1)
-
-    mask1 = one_hot(idx1, E)
-    mask2 = one_hot(idx2, E)
-    # position of each token among the tokens that chose the same expert, in token order
-    loc1 = (torch.cumsum(mask1, dim=0) - 1).gather(1, idx1.unsqueeze(1)).squeeze(1)
-    loc2 = (torch.cumsum(mask2, dim=0) - 1 + mask1.sum(dim=0, keepdim=True)).gather(1, idx2.unsqueeze(1)).squeeze(1)
+    native = _route_indices_native(logits.detach(), noise) if logits.is_cuda else None
+    if native is not None:
+        idx1, idx2, loc1, loc2, count1 = native
+        ce = count1.float() / S
+    else:
+        idx1 = torch.argmax(gates, dim=1)
+        noisy = (logits + noise).scatter(1, idx1.unsqueeze(1), float("-inf"))
+        idx2 = torch.argmax(noisy, dim=1)
+        mask1 = one_hot(idx1, E)
+        mask2 = one_hot(idx2, E)
+        # position of each token among the tokens that chose the same expert, in token order
+        loc1 = (torch.cumsum(mask1, dim=0) - 1).gather(1, idx1.unsqueeze(1)).squeeze(1)
+        loc2 = (torch.cumsum(mask2, dim=0) - 1 + mask1.sum(dim=0, keepdim=True)).gather(1, idx2.unsqueeze(1)).squeeze(1)
+        ce = mask1.float().mean(dim=0)
 
     me = gates.mean(dim=0)
-    ce = mask1.float().mean(dim=0)
     l_aux = torch.mean(me * ce)
 
     keep1, keep2 = loc1 < capacity, loc2 < capacity

@@ -51,15 +51,15 @@ def comm_ctas(remote_bytes: float = 0.0, flops: float = 0.0, world: int = 2) -> 
     """CTAs (SMs) of a fused kernel that move data instead of computing.
 
     Enough of them to move ``remote_bytes`` over NVLink while the remaining SMs spend ``flops`` on the chunks that do
-    not depend on the transfer; one copy CTA sustains roughly 45 GB/s of peer loads.  ``FSB200_FUSED_COMM_CTAS`` overrides."""
+    not depend on the transfer; one copy CTA (bulk copies, 192 KB in flight) sustains roughly 60 GB/s of peer reads.  ``FSB200_FUSED_COMM_CTAS`` overrides."""
     env = os.environ.get("FSB200_FUSED_COMM_CTAS")
     if env:
         return int(env)
     if remote_bytes <= 0 or flops <= 0:
         return 16
     overlap_s = flops / 1.2e15 * max(world - 1, 1) / world
-    need = remote_bytes / max(overlap_s, 1e-6) / 45e9
-    return int(min(32, max(4, -(-need // 1))))
+    need = remote_bytes / max(overlap_s, 1e-6) / 60e9
+    return int(min(24, max(6, -(-need // 1))))
 
 
 class _State:

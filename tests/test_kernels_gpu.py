@@ -325,3 +325,21 @@ def test_flash_attention_fwd_bwd(B, S, H, D):
     g, gr = qkv.grad.view(B, S, 3, H, D), ref_in.grad.view(B, S, 3, H, D)
     for i, name in enumerate("qkv"):
         assert _rel_err(g[:, :, i], gr[:, :, i]) < 3e-2, (name, _rel_err(g[:, :, i], gr[:, :, i]))
+
+
+@pytest.mark.parametrize("S,E,dtype", [(4096, 8, torch.float32), (16384, 64, torch.bfloat16), (1000, 4, torch.float32), (2048, 512, torch.float32)])
+def test_top2_route_kernel_matches_reference(S, E, dtype):
+    """CUDA index path of top-2 gating vs the one-hot / cumsum formulation on the same noise."""
+    from fairscale_b200.nn.moe import top2gate
+
+    torch.manual_seed(3)
+    logits = torch.randn(S, E, device="cuda").to(dtype)
+    noise = top2gate.gumbel_rsample(logits.shape, logits.device).float()
+    got = top2gate.top2_route(logits, noise)
+    cpu_logits = logits.float().cpu() if dtype == torch.float32 else logits.cpu()
+    ref = top2gate.top2_route(cpu_logits, noise.cpu())
+    assert torch.equal(got.expert.cpu(), ref.expert)
+    assert torch.equal(got.slot.cpu(), ref.slot)
+    assert torch.equal(got.keep.cpu(), ref.keep)
+    torch.testing.assert_close(got.gate.cpu(), ref.gate, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(got.l_aux.float().cpu(), ref.l_aux.float(), atol=1e-6, rtol=1e-3)
