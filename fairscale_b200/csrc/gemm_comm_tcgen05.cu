@@ -500,7 +500,7 @@ FSB_API int fsb_ag_gemm_bf16(int rank, int world, unsigned epoch, int channel, v
   GemmParams p{};
   p.C = C; p.bias = static_cast<const __nv_bfloat16*>(bias); p.aux = nullptr; p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ldc; p.a_mn_major = 0; p.b_mn_major = b_mn_major;
-  p.epilogue = epilogue; p.out_f32 = 0; p.accumulate_c = 0; p.status = status;
+  p.epilogue = epilogue; p.out_f32 = 0; p.accumulate_c = 0; p.status = status; p.batch = 1;
   FusedParams f{};
   f.c = fused_ctx(rank, world, epoch, channel, pads, counter, status);
   for (int i = 0; i < world; ++i) f.peer.p[i] = a_peers[i];
@@ -541,7 +541,7 @@ FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, v
   GemmParams p{};
   p.C = const_cast<void*>(stage_peers[rank]);
   p.M = M; p.N = N; p.K = K; p.ldc = N; p.ld_aux = N; p.a_mn_major = 0; p.b_mn_major = b_mn_major;
-  p.epilogue = EPI_NONE; p.out_f32 = 0; p.accumulate_c = 0; p.status = status;
+  p.epilogue = EPI_NONE; p.out_f32 = 0; p.accumulate_c = 0; p.status = status; p.batch = 1;
   FusedParams f{};
   f.c = fused_ctx(rank, world, epoch, channel, pads, counter, status);
   for (int i = 0; i < world; ++i) f.peer.p[i] = stage_peers[i];

@@ -26,7 +26,9 @@
 
 namespace fsb {
 
-template <int BLOCK_N>
+// BATCHED: the tensor maps are 3-D (K / MN, rows, problem) and a tile index also selects the problem; used for the
+// local experts of an MoE layer (equal capacity per expert), where one launch replaces a Python loop of GEMMs.
+template <int BLOCK_N, bool BATCHED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
   using L = SmemLayout<BLOCK_N>;
@@ -45,8 +47,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
   const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const int num_tiles = tiles_m * tiles_n;
+  const int tiles_per_problem = tiles_m * tiles_n;
+  const int num_tiles = tiles_per_problem * (BATCHED ? p.batch : 1);
   const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  auto load_tile = [&](void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    if (BATCHED) tma_load_3d(dst, map, bar, x, y, z);
+    else         tma_load_2d(dst, map, bar, x, y);
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -78,8 +85,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int pb = BATCHED ? tile / tiles_per_problem : 0;
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        tile_coords(tile - pb * tiles_per_problem, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * BLOCK_M, n0 = tn * BLOCK_N;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -88,16 +96,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
           if (!p.a_mn_major) {
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+            load_tile(sa, &tmap_a, &full_bar[stage], k0, m0, pb);
           } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+            for (int j = 0; j < BLOCK_M / 64; ++j) load_tile(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0, pb);
           }
           if (!p.b_mn_major) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            load_tile(sb, &tmap_b, &full_bar[stage], k0, n0, pb);
           } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+            for (int j = 0; j < BLOCK_N / 64; ++j) load_tile(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0, pb);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -147,14 +155,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int pb = BATCHED ? tile / tiles_per_problem : 0;
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(tile - pb * tiles_per_problem, tiles_m, tiles_n, tm, tn);
       const int row = tm * BLOCK_M + quad * 32 + lane;
       const int n0 = tn * BLOCK_N;
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_rows<BLOCK_N>(t_base, row, n0, p);
+      if (BATCHED) epilogue_rows<BLOCK_N>(t_base, row, n0, gemm_params_of_batch(p, pb));
+      else         epilogue_rows<BLOCK_N>(t_base, row, n0, p);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
@@ -404,6 +414,7 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
   p.status = status;
+  p.batch = 1; p.stride_c = p.stride_aux = p.stride_bias = 0;
 
   int dev = 0;
   cudaGetDevice(&dev);
@@ -438,17 +449,71 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   }
   if (block_n == 256) {
     if (!attr_set[di][0]) {
-      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);
       attr_set[di][0] = true;
     }
-    gemm_bf16_tcgen05_kernel<256><<<grid, GEMM_THREADS, SmemLayout<256>::TOTAL, stream>>>(ta, tb, p);
+    gemm_bf16_tcgen05_kernel<256, false><<<grid, GEMM_THREADS, SmemLayout<256>::TOTAL, stream>>>(ta, tb, p);
   } else {
     if (!attr_set[di][1]) {
-      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::TOTAL);
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::TOTAL);
       attr_set[di][1] = true;
     }
-    gemm_bf16_tcgen05_kernel<128><<<grid, GEMM_THREADS, SmemLayout<128>::TOTAL, stream>>>(ta, tb, p);
+    gemm_bf16_tcgen05_kernel<128, false><<<grid, GEMM_THREADS, SmemLayout<128>::TOTAL, stream>>>(ta, tb, p);
   }
   err = cudaGetLastError();
   return static_cast<int>(err);
+}
+
+// `batch` independent products of one shape in a single launch (the local experts of an MoE layer):
+//   C[b] = epilogue( A[b] * B[b]^T ),  b = 0 .. batch-1
+// stride_*: elements between consecutive problems (stride_bias may be 0 for a shared bias).  Layout flags, leading
+// dimensions and epilogues as for fsb_gemm_bf16.  Rows of a problem never leak into the next one: the tensor maps are
+// three-dimensional, so a tile that overhangs M or N reads zeros.
+FSB_API int fsb_gemm_bf16_batched(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out, int batch,
+                                  int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, long long stride_a, long long stride_b,
+                                  long long stride_c, long long stride_aux, long long stride_bias, int a_mn_major, int b_mn_major,
+                                  int epilogue, int out_f32, int accumulate_c, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -1;
+  if (accumulate_c && !out_f32) return -1;
+  const int block_n = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  bool ok = true;
+  if (!a_mn_major) ok &= fsb_host::encode_3d_16bit(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, (uint64_t)lda, (uint64_t)stride_a, BLOCK_K, BLOCK_M, 1);
+  else             ok &= fsb_host::encode_3d_16bit(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)batch, (uint64_t)lda, (uint64_t)stride_a, 64, BLOCK_K, 1);
+  if (!b_mn_major) ok &= fsb_host::encode_3d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint64_t)ldb, (uint64_t)stride_b, BLOCK_K, block_n, 1);
+  else             ok &= fsb_host::encode_3d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, (uint64_t)ldb, (uint64_t)stride_b, 64, BLOCK_K, 1);
+  if (!ok) return -1;
+  GemmParams p;
+  p.C = C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_aux = ld_aux > 0 ? ld_aux : ldc;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
+  p.status = status;
+  p.batch = batch; p.stride_c = stride_c; p.stride_aux = stride_aux > 0 ? stride_aux : stride_c; p.stride_bias = stride_bias;
+  int dev = 0, num_sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = static_cast<long long>(batch) * ((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n);
+  const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
+  static bool attr_set[2] = {false, false};
+  if (block_n == 256) {
+    if (!attr_set[0]) {
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);
+      attr_set[0] = true;
+    }
+    gemm_bf16_tcgen05_kernel<256, true><<<grid, GEMM_THREADS, SmemLayout<256>::TOTAL, stream>>>(ta, tb, p);
+  } else {
+    if (!attr_set[1]) {
+      cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::TOTAL);
+      attr_set[1] = true;
+    }
+    gemm_bf16_tcgen05_kernel<128, true><<<grid, GEMM_THREADS, SmemLayout<128>::TOTAL, stream>>>(ta, tb, p);
+  }
+  return static_cast<int>(cudaGetLastError());
 }

@@ -33,7 +33,21 @@ struct GemmParams {
   int out_f32;       // C is fp32 (else bf16)
   int accumulate_c;  // C += result (fp32 output only)
   int* status;
+  // batched (grouped) products: `batch` independent problems of the same shape; element strides between them
+  int batch;
+  long long stride_c, stride_aux, stride_bias;
 };
+
+// Parameters of problem `b` of a batch (pointers advanced; everything else shared).
+__device__ __forceinline__ GemmParams gemm_params_of_batch(const GemmParams& p, int b) {
+  GemmParams q = p;
+  if (p.out_f32) q.C = reinterpret_cast<float*>(p.C) + b * p.stride_c;
+  else           q.C = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.stride_c;
+  if (p.bias != nullptr) q.bias = p.bias + b * p.stride_bias;
+  if (p.aux != nullptr) q.aux = p.aux + b * p.stride_aux;
+  if (p.aux_out != nullptr) q.aux_out = p.aux_out + b * p.stride_aux;
+  return q;
+}
 
 template <int BLOCK_N>
 struct SmemLayout {

@@ -175,19 +175,20 @@ class MOELayer(Base):
     def __init__(self, gate: Module, experts: Union[Module, ModuleList], group: Optional[Any] = None) -> None:
         super().__init__()
         self.gate = gate
+        self._grouped = bool(getattr(experts, "grouped", False))  # stacked experts: one call for all of them
         self.experts = cast(ModuleList, experts) if type(experts) == ModuleList else ModuleList([experts])
         self.group = group if group is not None else dist.group.WORLD
         for expert in self.experts:
             for p in expert.parameters():
                 p.expert = True  # type: ignore[attr-defined]  # data-parallel reducers must skip these
         self.world_size = dist.get_world_size(self.group)
-        self.num_local_experts = len(self.experts)
+        self.num_local_experts = len(experts) if self._grouped else len(self.experts)  # type: ignore[arg-type]
 
     def forward(self, *input: Tensor, **kwargs: Any) -> Tensor:
         assert len(input) == 1, "only single input Tensor supported"
         x = input[0]
         assert len(x.shape) == 3, "input Tensor must have dimensions: (s)equence, (t)oken, (m)odel"
-        assert x.shape[0] % len(self.experts) == 0, "num tokens must be order of number of local experts"
+        assert x.shape[0] % self.num_local_experts == 0, "num tokens must be order of number of local experts"
         d_model = x.shape[2]
         tokens = x.reshape(-1, d_model)
 
@@ -195,11 +196,14 @@ class MOELayer(Base):
             route: Top2Route = self.gate.route(tokens)
             self.l_aux = route.l_aux
             expert_in = _Dispatch.apply(tokens, route, self.group, self.num_local_experts)  # [n_local, world*C, M]
-            outs = []
-            for e, expert in enumerate(self.experts):
-                chunk = expert_in[e].view(self.world_size, 1, route.capacity, d_model)
-                outs.append(expert(chunk).reshape(self.world_size * route.capacity, d_model))
-            expert_out = torch.stack(outs, dim=0)
+            if self._grouped:
+                expert_out = self.experts[0](expert_in)  # every local expert in one grouped launch
+            else:
+                outs = []
+                for e, expert in enumerate(self.experts):
+                    chunk = expert_in[e].view(self.world_size, 1, route.capacity, d_model)
+                    outs.append(expert(chunk).reshape(self.world_size * route.capacity, d_model))
+                expert_out = torch.stack(outs, dim=0)
             combined = _Combine.apply(expert_out, route.gate, route, self.group, self.num_local_experts)
             return combined.reshape(x.shape)
 
@@ -207,9 +211,13 @@ class MOELayer(Base):
         dispatched = torch.einsum("sec,sm->ecm", dispatch_mask.to(tokens.dtype), tokens)
         dispatched = _AllToAll.apply(self.group, dispatched)
         dispatched = dispatched.reshape(self.world_size, self.num_local_experts, -1, d_model)
-        chunks = dispatched.chunk(self.num_local_experts, dim=1)
-        expert_outputs = [expert(chunk) for chunk, expert in zip(chunks, self.experts)]
-        expert_output = torch.cat(expert_outputs, dim=1)
+        if self._grouped:
+            blk = dispatched.transpose(0, 1).reshape(self.num_local_experts, -1, d_model)
+            expert_output = self.experts[0](blk).reshape(self.num_local_experts, self.world_size, -1, d_model).transpose(0, 1)
+        else:
+            chunks = dispatched.chunk(self.num_local_experts, dim=1)
+            expert_outputs = [expert(chunk) for chunk, expert in zip(chunks, self.experts)]
+            expert_output = torch.cat(expert_outputs, dim=1)
         expert_output = _AllToAll.apply(self.group, expert_output)
         expert_output = expert_output.reshape(self.world_size * self.num_local_experts, -1, d_model)
         combined = torch.einsum("sec,ecm->sm", combine_weights.to(tokens.dtype), expert_output)

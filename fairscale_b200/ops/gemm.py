@@ -182,3 +182,105 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Differentiable fused linear: ``gelu(x w^T + b)`` or ``x w^T + b + residual``."""
     return _LinearFn.apply(x, w, bias, gelu, residual)
+
+
+# ---------------------------------------------------------------------------------------------- grouped (batched) products
+def _launch_batched(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
+                    epilogue: int = EPI_NONE, bias: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None,
+                    aux_out: Optional[torch.Tensor] = None) -> None:
+    """``c[e] = epilogue(a[e] * b[e]^T)`` for 3-D contiguous-last-dim tensors with a common leading (expert) dimension."""
+    from ctypes import c_int, c_longlong, c_void_p
+
+    _bind._SIGNATURES.setdefault("fsb_gemm_bf16_batched", [c_void_p] * 6 + [c_int] * 8 + [c_longlong] * 5 + [c_int] * 5 + [c_void_p, c_void_p])
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 3 and b.dim() == 3 and c.dim() == 3
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and c.stride(-1) == 1
+    ref = aux if aux is not None else aux_out
+    _bind.call(
+        "fsb_gemm_bf16_batched", a.data_ptr(), b.data_ptr(), c.data_ptr(), _bind.ptr(bias), _bind.ptr(aux), _bind.ptr(aux_out),
+        a.shape[0], M, N, K, a.stride(1), b.stride(1), c.stride(1), 0 if ref is None else ref.stride(1),
+        a.stride(0), b.stride(0), c.stride(0), 0 if ref is None else ref.stride(0), 0 if bias is None else bias.stride(0),
+        int(a_mn), int(b_mn), epilogue, int(c.dtype == torch.float32), 0, _bind.status_ptr(a.device), _bind.stream_ptr(a.device),
+    )
+
+
+def _batched_native(*ts: torch.Tensor) -> bool:
+    return _bind.use_native(*ts) and all(t.dtype == torch.bfloat16 for t in ts)
+
+
+def batched_linear_forward(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, gelu: bool = False,
+                           save_pre_activation: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``y[e] = act(x[e] @ w[e]^T + bias[e])`` for ``x [E, C, K]``, ``w [E, N, K]``, ``bias [E, N]``: one launch for all experts."""
+    E, C, K = x.shape
+    N = w.shape[1]
+    if not _batched_native(x, w):
+        pre = torch.baddbmm(bias.float().unsqueeze(1), x.float(), w.float().transpose(1, 2)) if bias is not None else torch.bmm(x.float(), w.float().transpose(1, 2))
+        y = torch.nn.functional.gelu(pre) if gelu else pre
+        return y.to(x.dtype), (pre.to(x.dtype) if gelu and save_pre_activation else None)
+    x, w = x.contiguous(), w.contiguous()
+    y = torch.empty((E, C, N), dtype=torch.bfloat16, device=x.device)
+    pre = torch.empty_like(y) if (gelu and save_pre_activation) else None
+    if gelu:
+        assert bias is not None
+        _launch_batched(x, w, y, C, N, K, False, False, EPI_BIAS_GELU, bias=bias.contiguous(), aux_out=pre)
+    else:
+        _launch_batched(x, w, y, C, N, K, False, False, EPI_BIAS if bias is not None else EPI_NONE, bias=None if bias is None else bias.contiguous())
+    return y, pre
+
+
+def batched_linear_dgrad(dy: torch.Tensor, w: torch.Tensor, *, dgelu_pre: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``dx[e] = dy[e] @ w[e]`` (times ``gelu'(pre[e])`` when given): ``dy [E, C, N]``, ``w [E, N, K]`` -> ``[E, C, K]``."""
+    E, C, N = dy.shape
+    K = w.shape[2]
+    if not _batched_native(dy, w):
+        dx = torch.bmm(dy.float(), w.float())
+        if dgelu_pre is not None:
+            p = dgelu_pre.float()
+            dx = dx * (0.5 * (1 + torch.erf(p * 0.7071067811865476)) + p * torch.exp(-0.5 * p * p) * 0.3989422804014327)
+        return dx.to(dy.dtype)
+    dy, w = dy.contiguous(), w.contiguous()
+    dx = torch.empty((E, C, K), dtype=torch.bfloat16, device=dy.device)
+    if dgelu_pre is not None:
+        _launch_batched(dy, w, dx, C, K, N, False, True, EPI_DGELU, aux=dgelu_pre.contiguous())
+    else:
+        _launch_batched(dy, w, dx, C, K, N, False, True)
+    return dx
+
+
+def batched_linear_wgrad(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """``dw[e] = dy[e]^T @ x[e]``: ``dy [E, C, N]``, ``x [E, C, K]`` -> ``[E, N, K]``."""
+    E, C, N = dy.shape
+    K = x.shape[2]
+    if not _batched_native(dy, x):
+        return torch.bmm(dy.float().transpose(1, 2), x.float()).to(dy.dtype)
+    dy, x = dy.contiguous(), x.contiguous()
+    dw = torch.empty((E, N, K), dtype=torch.bfloat16, device=dy.device)
+    _launch_batched(dy, x, dw, N, K, C, True, True)
+    return dw
+
+
+class _GroupedMLPFn(torch.autograd.Function):
+    """``gelu(x w1^T + b1) w2^T + b2`` for every expert at once; four launches forward + recompute-free backward."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):  # type: ignore[override]
+        h, pre = batched_linear_forward(x, w1, b1, gelu=True, save_pre_activation=True)
+        y, _ = batched_linear_forward(h, w2, b2)
+        ctx.save_for_backward(x, w1, w2, pre, h)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x, w1, w2, pre, h = ctx.saved_tensors
+        dy = dy.contiguous()
+        dw2 = batched_linear_wgrad(dy, h)
+        db2 = dy.float().sum(1).to(dy.dtype)
+        dpre = batched_linear_dgrad(dy, w2, dgelu_pre=pre)
+        dw1 = batched_linear_wgrad(dpre, x)
+        db1 = dpre.float().sum(1).to(dy.dtype)
+        dx = batched_linear_dgrad(dpre, w1)
+        return dx, dw1, db1, dw2, db2
+
+
+def grouped_mlp(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor, b2: torch.Tensor) -> torch.Tensor:
+    """Feed-forward of ``E`` experts on ``x [E, C, M]``: ``w1 [E, F, M]``, ``b1 [E, F]``, ``w2 [E, M, F]``, ``b2 [E, M]``."""
+    return _GroupedMLPFn.apply(x, w1, b1, w2, b2)

@@ -102,3 +102,50 @@ def _moe(rank, world):
 
 def test_moe_index_path_matches_dense_path():
     spawn_ranks(_moe, 2, (), backend="gloo")
+
+
+def test_grouped_experts_match_module_list():
+    spawn_ranks(_grouped_vs_list, 1, (), backend="gloo")
+
+
+def _grouped_vs_list(rank, world):
+    """Stacked experts (one grouped call) give the same layer output and gradients as a ModuleList of FFNs."""
+    import torch
+    from torch import nn
+
+    from fairscale_b200.nn.moe import GroupedExperts, MOELayer, Top2Gate
+
+    torch.manual_seed(0)
+    d, f, n_exp = 8, 16, 4
+    grouped = GroupedExperts(n_exp, d, f)
+
+    class FFN(nn.Module):
+        def __init__(self, e):
+            super().__init__()
+            self.l1, self.l2 = nn.Linear(d, f), nn.Linear(f, d)
+            with torch.no_grad():
+                self.l1.weight.copy_(grouped.w1[e]); self.l1.bias.copy_(grouped.b1[e])
+                self.l2.weight.copy_(grouped.w2[e]); self.l2.bias.copy_(grouped.b2[e])
+
+        def forward(self, x):
+            return self.l2(torch.nn.functional.gelu(self.l1(x)))
+
+    gate = Top2Gate(d, n_exp)
+    a = MOELayer(gate, grouped)
+    b = MOELayer(gate, nn.ModuleList([FFN(e) for e in range(n_exp)]))
+    x = torch.randn(4, 8, d)
+    from fairscale_b200.nn.moe import top2gate as tg
+
+    noise = tg.gumbel_rsample((32, n_exp), x.device)
+    orig = tg.gumbel_rsample
+    tg.gumbel_rsample = lambda shape, device: noise  # same routing for both layers
+    try:
+        ya, yb = a(x), b(x)
+        torch.testing.assert_close(ya, yb, rtol=1e-4, atol=1e-5)
+        ya.pow(2).sum().backward()
+        g_grouped = grouped.w1.grad.clone()
+        gate.zero_grad()
+        yb.pow(2).sum().backward()
+    finally:
+        tg.gumbel_rsample = orig
+    torch.testing.assert_close(g_grouped[1], b.experts[1].l1.weight.grad, rtol=1e-3, atol=1e-5)
