@@ -16,9 +16,9 @@
 //   gemm_rs  rank r computes the chunks in the order r+1, r+2, ..., r (its own last) and writes bf16 partial
 //            tiles to its symmetric staging buffer; the epilogue warp that completes a chunk raises a flag
 //            in the owner's signal pad (st.release.sys).  The owner's reduce CTAs wait for each peer's flag
-//            (bounded), pull that peer's partial chunk (8 loads in flight per thread) and accumulate it in an fp32
-//            scratch while the tensor-core CTAs are still busy.  When a CTA of either kind runs out of work it
-//            joins the final pass, out = scratch + own partial + bias, which therefore runs on every SM.
+//            (bounded) and bulk-copy that peer's partial rows into a local receive buffer while the tensor-core
+//            CTAs are still busy.  When a CTA of either kind runs out of work it joins the final pass,
+//            out = own partial + received partials (fixed order, fp32) + bias, which therefore runs on every SM.
 //
 // Cross-GPU ordering uses the epoch flags of comm_dev.cuh; an exit barrier keeps a rank's buffers alive until
 // every peer is done reading them.  No TMA multicast, no cluster launch.  Replaces all-gather + F.linear and
@@ -40,7 +40,7 @@ struct FusedParams {
   uint32_t target;        // value a chunk counter reaches when the chunk is complete in this call
   uint32_t target_comm;   // rs: value counts[kMaxRanks] reaches when every reduce CTA has folded in all peers
   long long chunk16;      // 16-byte units per chunk (ag: Mc * K * 2 / 16; rs: Mc * N * 2 / 16)
-  float* acc;             // rs: fp32 scratch [Mc * N]
+  float* acc;             // rs: local receive buffers, (world - 1) x [Mc, N] bf16 (one per peer, in arrival order)
   __nv_bfloat16* out;     // rs: result [Mc, N]
   const __nv_bfloat16* out_bias;  // rs: bias added once after the reduction (may be null)
   int n_comm;             // CTAs [0, n_comm) communicate, the rest compute
@@ -199,10 +199,11 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
       epilogue_rows<BLOCK_N>(t_base, row, n0, p);
       tc_fence_before_sync();
       if (MODE == 1) {
-        // publish this warp's share of the tile; the warp that completes the chunk tells its owner
-        __threadfence_system();
+        // publish this warp's share of the tile; the warp that completes the chunk tells its owner.  __syncwarp orders
+        // the lanes' stores before lane 0's system-scope fence, which is cumulative over them.
         __syncwarp();
         if (lane == 0) {
+          __threadfence_system();
           const uint32_t prev = atomicAdd(f.counts + chunk, 1u);
           if (prev + 1u == f.target) {
             __threadfence_system();
@@ -328,10 +329,10 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
   for (int i = 0; i < 4; ++i) { o[2 * i] = __low2float(h[i]); o[2 * i + 1] = __high2float(h[i]); }
 }
 
-// Peers' partials of my chunk -> fp32 scratch (first peer writes, the others add).  Thread 0 pulls 32 KB pieces of
-// a peer's staging buffer into the shared-memory ring with bulk loads as soon as that peer's flag is up; all threads
-// fold a landed piece into the scratch.  Returns false after a timeout.
-__device__ __forceinline__ bool rs_reduce_cta(const FusedParams& f, uint8_t* smem) {
+// Peers' partials of my chunk -> local receive buffers (one per peer, bf16), with the same bulk-copy engine as the
+// all-gather: thread 0 waits for a peer's flag, then streams that peer's rows through the shared-memory ring into
+// recv[k].  Nothing is added here; the final pass sums the buffers in a fixed order.  Returns false after a timeout.
+__device__ __forceinline__ bool rs_pull_cta(const FusedParams& f, uint8_t* smem) {
   const CommCtx& c = f.c;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + COPY_BUFS * COPY_PIECE);
   __shared__ int red_abort;
@@ -347,88 +348,85 @@ __device__ __forceinline__ bool rs_reduce_cta(const FusedParams& f, uint8_t* sme
   const int cta = blockIdx.x;
   const int per_cta = cta < pieces ? static_cast<int>((pieces - cta + f.n_comm - 1) / f.n_comm) : 0;
   const int n_jobs = per_cta * (c.world - 1);
-  auto peer_of = [&](int k) { return (c.rank - 1 - k + 2 * c.world) % c.world; };  // the order in which peers finish my chunk
-  int flag_seen = -1;  // thread 0: peers (in visiting order) whose flag has been observed
-  auto issue_load = [&](int n) -> bool {
-    const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
-    if (j.chunk > flag_seen) {
-      const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + peer_of(j.chunk);
-      const uint64_t t0 = globaltimer_ns();
-      while (static_cast<int32_t>(ld_acquire_sys(flag) - c.epoch) < 0) {
-        if (*abort_flag || globaltimer_ns() - t0 > kCommWaitNs) {
-          *abort_flag = 1;
-          return false;
+  if (threadIdx.x == 0 && per_cta > 0) {
+    auto peer_of = [&](int k) { return (c.rank - 1 - k + 2 * c.world) % c.world; };  // the order in which peers finish my chunk
+    int flag_seen = -1;
+    bool ok = true;
+    auto issue_load = [&](int n) -> bool {
+      const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
+      if (j.chunk > flag_seen) {
+        const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + peer_of(j.chunk);
+        const uint64_t t0 = globaltimer_ns();
+        while (static_cast<int32_t>(ld_acquire_sys(flag) - c.epoch) < 0) {
+          if (globaltimer_ns() - t0 > kCommWaitNs) {
+            *abort_flag = 1;
+            return false;
+          }
+          __nanosleep(128);
         }
-        __nanosleep(128);
+        flag_seen = j.chunk;
       }
-      flag_seen = j.chunk;
-    }
-    const int b = n % COPY_BUFS;
-    const uint8_t* src = static_cast<const uint8_t*>(f.peer.p[peer_of(j.chunk)]) + static_cast<long long>(c.rank) * chunk_bytes + j.off;
-    mbar_expect_tx(&full[b], j.bytes);
-    bulk_load_1d(smem + b * COPY_PIECE, src, j.bytes, &full[b]);
-    return true;
-  };
-  if (threadIdx.x == 0) {
-    for (int n = 0; n < COPY_BUFS - 1 && n < n_jobs; ++n)
-      if (!issue_load(n)) break;
-  }
-  for (int n = 0; n < n_jobs; ++n) {
-    if (threadIdx.x == 0 && n + COPY_BUFS - 1 < n_jobs && !*abort_flag) issue_load(n + COPY_BUFS - 1);  // buffer of job n-1: free
-    const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
-    const int b = n % COPY_BUFS;
-    if (!mbar_wait(&full[b], (n / COPY_BUFS) & 1, abort_flag)) break;
-    const uint4* piece = reinterpret_cast<const uint4*>(smem + b * COPY_PIECE);
-    float4* acc = reinterpret_cast<float4*>(f.acc) + 2 * (j.off / 16);
-    const bool first = (j.chunk == 0);
-    const int n16 = static_cast<int>(j.bytes / 16);
-    for (int i = threadIdx.x; i < n16; i += blockDim.x) {
-      float x[8];
-      unpack8(piece[i], x);
-      if (!first) {
-        const float4 a0 = acc[2 * i], a1 = acc[2 * i + 1];
-        x[0] += a0.x; x[1] += a0.y; x[2] += a0.z; x[3] += a0.w;
-        x[4] += a1.x; x[5] += a1.y; x[6] += a1.z; x[7] += a1.w;
+      const int b = n % COPY_BUFS;
+      const uint8_t* src = static_cast<const uint8_t*>(f.peer.p[peer_of(j.chunk)]) + static_cast<long long>(c.rank) * chunk_bytes + j.off;
+      mbar_expect_tx(&full[b], j.bytes);
+      bulk_load_1d(smem + b * COPY_PIECE, src, j.bytes, &full[b]);
+      return true;
+    };
+    int issued = 0;
+    for (; issued < COPY_BUFS - 1 && issued < n_jobs && ok; ++issued) ok = issue_load(issued);
+    for (int n = 0; n < n_jobs && ok; ++n) {
+      const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
+      const int b = n % COPY_BUFS;
+      if (!mbar_wait(&full[b], (n / COPY_BUFS) & 1, abort_flag)) { ok = false; break; }
+      uint8_t* dst = reinterpret_cast<uint8_t*>(f.acc) + static_cast<long long>(j.chunk) * chunk_bytes + j.off;
+      bulk_store_1d(dst, smem + b * COPY_PIECE, j.bytes);
+      tma_store_commit();
+      if (issued < n_jobs) {
+        tma_store_wait_read<1>();  // the store issued one job ago has drained its buffer: refill it
+        ok = issue_load(issued++);
       }
-      acc[2 * i] = make_float4(x[0], x[1], x[2], x[3]);
-      acc[2 * i + 1] = make_float4(x[4], x[5], x[6], x[7]);
     }
-    __syncthreads();  // the piece is consumed: its buffer may be refilled
+    tma_store_wait<0>();
+    fence_proxy_async_all();
+    if (!ok) {
+      *abort_flag = 1;
+      if (c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
+    }
   }
   __syncthreads();
   const bool ok = (*abort_flag == 0);
-  if (!ok && threadIdx.x == 0 && c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
   __threadfence();
-  __syncthreads();
   if (threadIdx.x == 0) atomicAdd(f.counts + kMaxRanks, 1u);
   exit_barrier_n(c, c.channel + 1, static_cast<unsigned int>(f.n_comm));  // peers are done reading my staging buffer
   return ok;
 }
 
-// out = scratch (the peers' sum) + my own partial chunk + bias, on every CTA of the grid once its other work is done.
+// out = my own partial chunk + the peers' partials (receive buffers, fixed order) + bias, on every CTA of the grid once
+// its other work is done.
 __device__ __forceinline__ void rs_final_pass(const FusedParams& f, int N) {
   __shared__ int final_ok;
   if (threadIdx.x == 0) {
     int dummy_abort = 0;
     bool ok = wait_counter(f.counts + f.c.rank, f.target, &dummy_abort);               // my own chunk is complete
-    if (ok && f.c.world > 1) ok = wait_counter(f.counts + kMaxRanks, f.target_comm, &dummy_abort);  // peers folded in
+    if (ok && f.c.world > 1) ok = wait_counter(f.counts + kMaxRanks, f.target_comm, &dummy_abort);  // peers' rows have landed
     if (!ok && f.c.status != nullptr) atomicExch(f.c.status, FSB_ERR_WAIT_TIMEOUT);
     final_ok = ok ? 1 : 0;
   }
   __syncthreads();
   if (!final_ok) return;
   const uint4* own = reinterpret_cast<const uint4*>(f.peer.p[f.c.rank]) + static_cast<long long>(f.c.rank) * f.chunk16;
-  const float4* acc = reinterpret_cast<const float4*>(f.acc);
+  const uint4* recv = reinterpret_cast<const uint4*>(f.acc);
   const int n16_row = N / 8;
-  const bool have_peers = f.c.world > 1;
+  const int n_peers = f.c.world - 1;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < f.chunk16; i += stride) {
     float v[8];
     unpack8(__ldcg(own + i), v);
-    if (have_peers) {
-      const float4 a0 = __ldcg(acc + 2 * i), a1 = __ldcg(acc + 2 * i + 1);
-      v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
-      v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+    for (int k = 0; k < n_peers; ++k) {
+      float x[8];
+      unpack8(__ldcg(recv + static_cast<long long>(k) * f.chunk16 + i), x);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] += x[u];
     }
     if (f.out_bias != nullptr) {
       float b[8];
@@ -448,7 +446,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   if (static_cast<int>(blockIdx.x) < f.n_comm) {
-    if (f.c.world > 1 && !rs_reduce_cta(f, smem)) return;
+    if (f.c.world > 1 && !rs_pull_cta(f, smem)) return;
   } else {
     fused_gemm_cta<1>(tmap_a, tmap_a, tmap_b, p, f, smem);
   }
@@ -522,7 +520,8 @@ FSB_API int fsb_ag_gemm_bf16(int rank, int world, unsigned epoch, int channel, v
 }
 
 // out[Mc, N] (bf16) = sum over ranks of (A[M, K] * B^T)[my chunk's rows] (+ out_bias).  stage_peers[r]: rank r's
-// staging buffer [M, N] bf16 in the symmetric heap (this rank writes stage_peers[rank]); acc: fp32 scratch [Mc * N];
+// staging buffer [M, N] bf16 in the symmetric heap (this rank writes stage_peers[rank]); acc: local receive buffers,
+// (world - 1) * Mc * N bf16;
 // counts: kMaxRanks + 1 uint32; target as for ag_gemm but counting 4 * tiles-per-chunk arrivals per call;
 // target_comm: cumulative n_comm over the calls (with world > 1) that used `counts`.
 FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,

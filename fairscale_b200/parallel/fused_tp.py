@@ -145,9 +145,10 @@ def gemm_rs(ws: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     dev = x.device
     x = x.contiguous()
     stage = ws.scratch("rs_stage", (M, N), torch.bfloat16)
-    acc = st.acc.get(Mc * N)
+    recv_elems = max(ws.world - 1, 1) * Mc * N  # one bf16 receive buffer per peer
+    acc = st.acc.get(recv_elems)
     if acc is None:
-        acc = st.acc[Mc * N] = torch.empty(Mc * N, dtype=torch.float32, device=dev)
+        acc = st.acc[recv_elems] = torch.empty(recv_elems, dtype=torch.bfloat16, device=dev)
     out = torch.empty((Mc, N), dtype=torch.bfloat16, device=dev)
     n_comm = comm_ctas((ws.world - 1) * Mc * N * 2.0, 2.0 * M * N * K, ws.world)
     arrivals = _bind.fn("fsb_gemm_rs_arrivals")(M, N, ws.world)
