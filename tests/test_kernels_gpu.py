@@ -375,3 +375,51 @@ def test_batched_gemm_matches_fp32(E, C, K, N):
     assert float((out.float() - ref).norm() / ref.norm()) < 2e-2
     for a, r in zip(params, ps):
         assert float((a.grad.float() - r.grad).norm() / r.grad.norm().clamp_min(1e-9)) < 4e-2
+
+
+def test_multi_tensor_norm_and_scale():
+    from fairscale_b200.internal.params import calc_grad_norm
+    from fairscale_b200.ops import multi_tensor
+
+    torch.manual_seed(0)
+    ts = [torch.randn(n, device="cuda") for n in (5, 8192, 100003)] + [torch.randn(4097, device="cuda").bfloat16()]
+    want = torch.sqrt(sum(t.float().pow(2).sum() for t in ts))
+    torch.testing.assert_close(multi_tensor.l2_norm(ts), want, rtol=1e-4, atol=1e-4)
+    params = [torch.nn.Parameter(torch.zeros_like(t)) for t in ts[:3]]
+    for p, t in zip(params, ts):
+        p.grad = t.clone()
+    torch.testing.assert_close(calc_grad_norm(params, 2.0), torch.sqrt(sum(t.pow(2).sum() for t in ts[:3])), rtol=1e-4, atol=1e-4)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    copies = [t.clone() for t in ts]
+    multi_tensor.scale_(copies, torch.tensor([0.5], device="cuda"), flag)
+    for c, t in zip(copies, ts):
+        torch.testing.assert_close(c.float(), t.float() * 0.5, rtol=1e-2, atol=1e-2)
+    assert int(flag) == 0
+    copies[1][7] = float("inf")
+    multi_tensor.scale_(copies, torch.tensor([1.0], device="cuda"), flag)
+    assert int(flag) == 1
+
+
+def test_sharded_grad_scaler_fused_step_with_adam():
+    """No unscale kernel: Adam applies 1/scale itself and skips the step on the device when a gradient is not finite."""
+    from fairscale_b200.optim import Adam, ShardedGradScaler
+
+    torch.manual_seed(0)
+    model = torch.nn.Linear(64, 64).cuda()
+    ref = torch.nn.Linear(64, 64).cuda()
+    ref.load_state_dict(model.state_dict())
+    opt, ropt = Adam(model.parameters(), lr=1e-2), torch.optim.Adam(ref.parameters(), lr=1e-2)
+    scaler = ShardedGradScaler(init_scale=1024.0, growth_interval=1000)
+    x = torch.randn(8, 64, device="cuda")
+    for _ in range(3):
+        opt.zero_grad(); ropt.zero_grad()
+        scaler.scale(model(x).pow(2).sum()).backward()
+        ref(x).pow(2).sum().backward()
+        scaler.step(opt); scaler.update(); ropt.step()
+    torch.testing.assert_close(model.weight, ref.weight, rtol=1e-4, atol=1e-5)
+    before = model.weight.detach().clone()
+    opt.zero_grad()
+    scaler.scale(model(x).pow(2).sum()).backward()
+    model.weight.grad[0, 0] = float("nan")
+    scaler.step(opt); scaler.update()
+    assert torch.equal(before, model.weight) and scaler.get_scale() == 512.0
