@@ -100,11 +100,24 @@ template <typename T> __device__ __forceinline__ void st16(T* p, const Vec16<T>&
   *reinterpret_cast<uint4*>(p) = x.raw;
 }
 
+// erf(x) by Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7, far below bf16 resolution): one reciprocal, one exponential
+// and a degree-5 polynomial instead of the branchy libdevice routine; the GEMM epilogues evaluate it per element.
+__device__ __forceinline__ float fast_erf(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.f, fmaf(0.3275911f, ax, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float e = __expf(-ax * ax);
+  const float r = fmaf(-poly * t, e, 1.f);
+  return copysignf(r, x);
+}
 __device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  return 0.5f * x * (1.f + fast_erf(x * 0.70710678118654752f));
 }
 __device__ __forceinline__ float gelu_erf_grad(float x) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+  const float cdf = 0.5f * (1.f + fast_erf(x * 0.70710678118654752f));
   const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
   return cdf + x * pdf;
 }
