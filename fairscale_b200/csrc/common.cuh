@@ -116,10 +116,19 @@ __device__ __forceinline__ float fast_erf(float x) {
 __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.f + fast_erf(x * 0.70710678118654752f));
 }
+// d/dx gelu(x) = Phi(x) + x phi(x).  erf(x / sqrt 2) and phi(x) need the same exponential exp(-x^2 / 2): one EX2 and
+// one RCP per element.
 __device__ __forceinline__ float gelu_erf_grad(float x) {
-  const float cdf = 0.5f * (1.f + fast_erf(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  const float ax = fabsf(x) * 0.70710678118654752f;
+  const float e = __expf(-0.5f * x * x);
+  const float t = __fdividef(1.f, fmaf(0.3275911f, ax, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.f);
+  const float cdf = fmaf(0.5f, copysignf(erf_abs, x), 0.5f);
+  return fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
 }  // namespace fsb
