@@ -31,6 +31,9 @@
 namespace fsb {
 
 constexpr int FUSED_BLOCK_N = 256;
+// dynamic shared memory of both kernels: operand ring + barriers (SmemLayout) + 4 KB of epilogue staging per epilogue warp
+constexpr int FUSED_EPI_OFFSET = SmemLayout<FUSED_BLOCK_N>::EPI_OFFSET;
+constexpr int FUSED_SMEM = SmemLayout<FUSED_BLOCK_N>::TOTAL;
 
 struct FusedParams {
   CommCtx c;
@@ -183,6 +186,7 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
     }
   } else {
     const int quad = warp & 3;
+    const bool coalesce = epilogue_can_coalesce(p);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -196,7 +200,8 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_rows<BLOCK_N>(t_base, row, n0, p);
+      if (coalesce) epilogue_rows_coalesced(t_base, row - lane, n0, BLOCK_N, p, smem + FUSED_EPI_OFFSET + quad * 4096, lane);
+      else          epilogue_rows<BLOCK_N>(t_base, row, n0, p);
       tc_fence_before_sync();
       if (MODE == 1) {
         // publish this warp's share of the tile; the warp that completes the chunk tells its owner.  __syncwarp orders
@@ -512,10 +517,10 @@ FSB_API int fsb_ag_gemm_bf16(int rank, int world, unsigned epoch, int channel, v
   if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<FUSED_BLOCK_N>::TOTAL);
+    cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM);
     attr_set = true;
   }
-  ag_gemm_kernel<<<grid, GEMM_THREADS, SmemLayout<FUSED_BLOCK_N>::TOTAL, stream>>>(tl, tg, tb, p, f);
+  ag_gemm_kernel<<<grid, GEMM_THREADS, FUSED_SMEM, stream>>>(tl, tg, tb, p, f);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -557,10 +562,10 @@ FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, v
   if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<FUSED_BLOCK_N>::TOTAL);
+    cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM);
     attr_set = true;
   }
-  gemm_rs_kernel<<<grid, GEMM_THREADS, SmemLayout<FUSED_BLOCK_N>::TOTAL, stream>>>(ta, tb, p, f);
+  gemm_rs_kernel<<<grid, GEMM_THREADS, FUSED_SMEM, stream>>>(ta, tb, p, f);
   return static_cast<int>(cudaGetLastError());
 }
 

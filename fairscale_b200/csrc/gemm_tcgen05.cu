@@ -163,8 +163,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
-      if (BATCHED) epilogue_rows<BLOCK_N>(t_base, row, n0, gemm_params_of_batch(p, pb));
-      else         epilogue_rows<BLOCK_N>(t_base, row, n0, p);
+      const GemmParams pt = BATCHED ? gemm_params_of_batch(p, pb) : p;
+      if (epilogue_can_coalesce(pt)) epilogue_rows_coalesced(t_base, row - lane, n0, BLOCK_N, pt, smem + L::EPI_OFFSET + quad * 4096, lane);
+      else                           epilogue_rows<BLOCK_N>(t_base, row, n0, pt);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);

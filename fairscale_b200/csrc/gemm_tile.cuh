@@ -55,7 +55,8 @@ struct SmemLayout {
   static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+  static constexpr int EPI_OFFSET = BAR_OFFSET + 256;     // 4 KB of epilogue staging per epilogue warp (4 warps)
+  static constexpr int TOTAL = EPI_OFFSET + 4 * 4096 + 1024;  // + slack for 1024-byte alignment
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
