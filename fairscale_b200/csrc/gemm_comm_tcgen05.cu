@@ -424,25 +424,47 @@ __device__ __forceinline__ void rs_final_pass(const FusedParams& f, int N) {
   const int n16_row = N / 8;
   const int n_peers = f.c.world - 1;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < f.chunk16; i += stride) {
-    float v[8];
-    unpack8(__ldcg(own + i), v);
+  constexpr int U = 4;  // independent 16-byte loads in flight per thread and source: the pass is latency-bound otherwise
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < f.chunk16; i0 += U * stride) {
+    uint4 raw[U];
+    float v[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      raw[u] = (i < f.chunk16) ? __ldcg(own + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) unpack8(raw[u], v[u]);
     for (int k = 0; k < n_peers; ++k) {
-      float x[8];
-      unpack8(__ldcg(recv + static_cast<long long>(k) * f.chunk16 + i), x);
+      const uint4* rk = recv + static_cast<long long>(k) * f.chunk16;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] += x[u];
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        raw[u] = (i < f.chunk16) ? __ldcg(rk + i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float x[8];
+        unpack8(raw[u], x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[u][e] += x[e];
+      }
     }
-    if (f.out_bias != nullptr) {
-      float b[8];
-      unpack8(*reinterpret_cast<const uint4*>(f.out_bias + static_cast<int>(i % n16_row) * 8), b);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] += b[u];
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= f.chunk16) continue;
+      if (f.out_bias != nullptr) {
+        float b[8];
+        unpack8(*reinterpret_cast<const uint4*>(f.out_bias + static_cast<int>(i % n16_row) * 8), b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[u][e] += b[e];
+      }
+      Vec16<__nv_bfloat16> o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16_rn(v[u][e]);
+      st16(f.out + i * 8, o);
     }
-    Vec16<__nv_bfloat16> o;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) o.v[u] = __float2bfloat16_rn(v[u]);
-    st16(f.out + i * 8, o);
   }
 }
 
