@@ -200,7 +200,8 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
-      if (coalesce) epilogue_rows_coalesced(t_base, row - lane, n0, BLOCK_N, p, smem + FUSED_EPI_OFFSET + quad * 4096, lane);
+      uint4 pre[8];  // the fused kernels' epilogues read no aux operand
+      if (coalesce) epilogue_rows_coalesced(t_base, row - lane, n0, BLOCK_N, p, smem + FUSED_EPI_OFFSET + quad * 4096, lane, pre);
       else          epilogue_rows<BLOCK_N>(t_base, row, n0, p);
       tc_fence_before_sync();
       if (MODE == 1) {

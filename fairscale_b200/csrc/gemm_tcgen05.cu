@@ -164,7 +164,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BLOCK_N) + (static_cast<uint32_t>(quad * 32) << 16);
       const GemmParams pt = BATCHED ? gemm_params_of_batch(p, pb) : p;
-      if (epilogue_can_coalesce(pt)) epilogue_rows_coalesced(t_base, row - lane, n0, BLOCK_N, pt, smem + L::EPI_OFFSET + quad * 4096, lane);
+      uint4 pre[8];
+      if (epilogue_can_coalesce(pt) && epilogue_needs_aux(pt.epilogue)) epi_slab_prefetch(pre, pt.aux, pt.ld_aux, row - lane, n0, pt.M, pt.N, lane);
+      if (epilogue_can_coalesce(pt)) epilogue_rows_coalesced(t_base, row - lane, n0, BLOCK_N, pt, smem + L::EPI_OFFSET + quad * 4096, lane, pre);
       else                           epilogue_rows<BLOCK_N>(t_base, row, n0, pt);
       tc_fence_before_sync();
       __syncwarp();
@@ -351,11 +353,13 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int row0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M + quad * 32;
       const int n0 = tn * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2);
+      uint4 pre[8];
+      if (coalesce && epilogue_needs_aux(p.epilogue) && n0 < p.N) epi_slab_prefetch(pre, p.aux, p.ld_aux, row0, n0, p.M, p.N, lane);
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2)) +
                               (static_cast<uint32_t>(quad * 32) << 16);
-      if (coalesce) epilogue_rows_coalesced(t_base, row0, n0, PAIR_BLOCK_N / 2, p, stage, lane);
+      if (coalesce) epilogue_rows_coalesced(t_base, row0, n0, PAIR_BLOCK_N / 2, p, stage, lane, pre);
       else          epilogue_rows<PAIR_BLOCK_N / 2>(t_base, row0 + lane, n0, p);
       tc_fence_before_sync();
       __syncwarp();

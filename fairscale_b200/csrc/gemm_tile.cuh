@@ -184,6 +184,24 @@ __device__ __forceinline__ void epi_slab_load(uint8_t* stage, const __nv_bfloat1
     *reinterpret_cast<uint4*>(stage + epi_swz(rr, cc)) = v;
   }
 }
+// The same slab in two steps: global -> registers (issued early, e.g. before the accumulator is ready, so the DRAM
+// latency overlaps other work) and registers -> staging.
+__device__ __forceinline__ void epi_slab_prefetch(uint4 (&pre)[8], const __nv_bfloat16* g, int ld, int row0, int col0, int M, int N, int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3);
+    pre[it] = make_uint4(0u, 0u, 0u, 0u);
+    if (row0 + rr < M && col0 + cc * 8 < N) pre[it] = __ldcg(reinterpret_cast<const uint4*>(g + static_cast<size_t>(row0 + rr) * ld + col0 + cc * 8));
+  }
+}
+__device__ __forceinline__ void epi_slab_commit(uint8_t* stage, const uint4 (&pre)[8], int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) *reinterpret_cast<uint4*>(stage + epi_swz(it * 4 + (lane >> 3), cc)) = pre[it];
+}
+__device__ __forceinline__ bool epilogue_needs_aux(int epi) { return epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU; }
+
 // staging -> global [32 rows x 64 cols] bf16 slab (coalesced writes)
 __device__ __forceinline__ void epi_slab_store(const uint8_t* stage, __nv_bfloat16* g, int ld, int row0, int col0, int M, int N, int lane) {
   const int cc = lane & 7;
@@ -205,15 +223,18 @@ __device__ __forceinline__ void epi_row_to_stage(uint8_t* stage, const float (&v
   }
 }
 
-__device__ __forceinline__ void epilogue_rows_coalesced(uint32_t t_base, int row0, int n0, int ncols, const GemmParams& p, uint8_t* stage, int lane) {
+// `pre` holds the aux slab of the first 64 columns when the epilogue reads aux (see epi_slab_prefetch; the caller loads
+// it before it waits for the accumulator); the slabs after the first are prefetched here while the previous one drains.
+__device__ __forceinline__ void epilogue_rows_coalesced(uint32_t t_base, int row0, int n0, int ncols, const GemmParams& p, uint8_t* stage, int lane,
+                                                        uint4 (&pre)[8]) {
   const int epi = p.epilogue;
+  const bool needs_aux = epilogue_needs_aux(epi);
   for (int c0 = 0; c0 < ncols; c0 += 64) {
     const int col0 = n0 + c0;
     uint32_t r0[32], r1[32];
     tmem_ld_32x32(t_base + static_cast<uint32_t>(c0), r0);
     tmem_ld_32x32(t_base + static_cast<uint32_t>(c0 + 32), r1);
-    const bool needs_aux = (epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_DGELU);
-    if (needs_aux && col0 < p.N) epi_slab_load(stage, p.aux, p.ld_aux, row0, col0, p.M, p.N, lane);  // overlaps the TMEM load
+    if (needs_aux && col0 < p.N) epi_slab_commit(stage, pre, lane);  // overlaps the TMEM load
     tmem_ld_wait();
     if (col0 >= p.N) continue;  // warp-uniform
     float v[64];
@@ -250,6 +271,7 @@ __device__ __forceinline__ void epilogue_rows_coalesced(uint32_t t_base, int row
         }
       }
       __syncwarp();
+      if (c0 + 64 < ncols && col0 + 64 < p.N) epi_slab_prefetch(pre, p.aux, p.ld_aux, row0, col0 + 64, p.M, p.N, lane);
     }
     if (epi == EPI_BIAS_GELU) {
       if (p.aux_out != nullptr) {
