@@ -383,6 +383,18 @@ def get_cycles_per_ms() -> float:
     return sum(core) / len(core)
 
 
+def gpu_delay(ms: float, stream: Optional[Any] = None) -> None:
+    """Keep ``stream`` (default: the current one) busy for ``ms`` milliseconds with the library's delay kernel.
+
+    The kernel polls the global nanosecond timer and is capped at one second, so unlike a cycle-count sleep it needs
+    no clock calibration and cannot outlive a test.
+    """
+    from ...ops import _bind
+
+    s = torch.cuda.current_stream() if stream is None else stream
+    _bind.call("fsb_delay", int(ms * 1e6), s.cuda_stream)
+
+
 class DummyProcessGroup:
     """Stands in for a process group in single-process unit tests (no collectives are issued)."""
 
@@ -408,7 +420,7 @@ class SGDWithPausingCompute(torch.optim.SGD):
     def step(self, closure: Optional[Any] = None) -> Any:
         loss = super().step(closure=closure)
         with torch.cuda.stream(torch.cuda.Stream()):
-            torch.cuda._sleep(100000)
+            gpu_delay(0.1)
             for group in self.param_groups:
                 for p in group["params"]:
                     with torch.no_grad():

@@ -32,6 +32,7 @@ from ..nn.model_parallel import (
 from ..ops.activations import swiglu
 from ..ops.attention import causal_attention
 from ..ops.norm import RMSNorm
+from ..ops.rope import rope_qkv
 from ..parallel import comm
 
 
@@ -91,19 +92,6 @@ class _GatherRows(torch.autograd.Function):
         return g[r * n : (r + 1) * n].contiguous(), None
 
 
-def _rope(qkv: torch.Tensor, theta: float) -> torch.Tensor:
-    """Rotary position embedding on the q and k parts of packed ``[B, S, 3, H, Dh]``."""
-    B, S, _, H, Dh = qkv.shape
-    pos = torch.arange(S, device=qkv.device, dtype=torch.float32)
-    inv = theta ** (-torch.arange(0, Dh, 2, device=qkv.device, dtype=torch.float32) / Dh)
-    ang = pos[:, None] * inv[None, :]
-    cos, sin = ang.cos()[None, :, None, None, :], ang.sin()[None, :, None, None, :]
-    qk = qkv[:, :, :2].float()
-    x1, x2 = qk[..., 0::2], qk[..., 1::2]
-    rot = torch.stack([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).flatten(-2)
-    return torch.cat([rot.to(qkv.dtype), qkv[:, :, 2:]], dim=2)
-
-
 class TPBlock(nn.Module):
     def __init__(self, cfg: TPLlamaConfig):
         super().__init__()
@@ -126,7 +114,7 @@ class TPBlock(nn.Module):
         cfg = self.cfg
         qkv = self.qkv(self.norm1(x))  # [T, 3 * D / world]
         S = qkv.shape[0] // batch
-        qkv = _rope(qkv.view(batch, S, 3, self.local_heads, cfg.d_model // cfg.n_heads), cfg.rope_theta)
+        qkv = rope_qkv(qkv.view(batch, S, 3, self.local_heads, cfg.d_model // cfg.n_heads), cfg.rope_theta)
         o = causal_attention(qkv.reshape(batch, S, -1), self.local_heads)
         x = x + self.proj(o.reshape(batch * S, -1))
         return x + self.down(swiglu(self.gate_up(self.norm2(x))))

@@ -20,6 +20,7 @@ from torch import nn
 
 from ..nn.moe import MOELayer, Top2Gate
 from ..ops.attention import causal_attention
+from ..ops.dropout import Dropout
 
 
 class EmbeddingLayer(nn.Embedding):
@@ -35,7 +36,7 @@ class EmbeddingLayer(nn.Embedding):
 class PositionalEncodingLayer(nn.Module):
     def __init__(self, d_model: int, dropout: float = 0.1, max_len: int = 5000):
         super().__init__()
-        self.dropout = nn.Dropout(p=dropout)
+        self.dropout = Dropout(p=dropout)
         pos = torch.arange(max_len, dtype=torch.float32).unsqueeze(1)
         div = torch.exp(torch.arange(0, d_model, 2, dtype=torch.float32) * (-math.log(10000.0) / d_model))
         pe = torch.zeros(max_len, d_model)
@@ -52,9 +53,9 @@ class FeedForwardLayer(nn.Module):
         super().__init__()
         self.linear1 = nn.Linear(d_model, dim_feedforward)
         self.activation = activation
-        self.dropout1 = nn.Dropout(dropout)
+        self.dropout1 = Dropout(dropout)
         self.linear2 = nn.Linear(dim_feedforward, d_model)
-        self.dropout2 = nn.Dropout(dropout)
+        self.dropout2 = Dropout(dropout)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.dropout2(self.linear2(self.dropout1(self.activation(self.linear1(x)))))
@@ -90,7 +91,7 @@ class TransformerDecoderLayer(nn.Module):
         self.norm_first = norm_first
         self.norm1 = nn.LayerNorm(ninp, eps=layer_norm_eps)
         self.norm2 = nn.LayerNorm(ninp, eps=layer_norm_eps)
-        self.dropout = nn.Dropout(dropout)
+        self.dropout = Dropout(dropout)
         self.is_moe = is_moe
         if is_moe:
             world = dist.get_world_size(moe_group) if dist.is_initialized() else 1

@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Any, Optional
 
 import torch
@@ -33,6 +33,9 @@ _SIGNATURES = {
     "fsb_swiglu_fwd": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     "fsb_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     "fsb_add_bf16": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p],
+    "fsb_rope": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "fsb_dropout": [c_void_p, c_void_p, c_longlong, c_float, c_ulonglong, c_ulonglong, c_void_p],
+    "fsb_delay": [c_ulonglong, c_void_p],
     "fsb_softmax": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_int, c_void_p],
 }
 

@@ -423,3 +423,77 @@ def test_sharded_grad_scaler_fused_step_with_adam():
     model.weight.grad[0, 0] = float("nan")
     scaler.step(opt); scaler.update()
     assert torch.equal(before, model.weight) and scaler.get_scale() == 512.0
+
+
+def test_rope_forward_backward():
+    from fairscale_b200.ops.rope import rope_qkv, rope_reference
+
+    torch.manual_seed(11)
+    B, S, H, D = 2, 96, 3, 64
+    qkv = torch.randn(B, S, 3, H, D, device=_dev()).bfloat16().requires_grad_(True)
+    out = rope_qkv(qkv, 10000.0)
+    ref = rope_reference(qkv.detach().float(), 10000.0)
+    assert _rel_err(out, ref) < 1e-2
+    assert torch.equal(out[:, :, 2], qkv[:, :, 2])  # v passes through untouched
+    g = torch.randn_like(out)
+    out.backward(g)
+    gref = rope_reference(g.float(), 10000.0, backward=True)
+    assert _rel_err(qkv.grad, gref) < 1e-2
+    # the backward rotation undoes the forward one
+    back = rope_reference(out.detach().float(), 10000.0, backward=True)
+    assert _rel_err(back, qkv.detach()) < 1e-2
+    _status_ok()
+
+
+def _philox_ref(seed, counters):
+    import numpy as np
+
+    M0, M1, W0, W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
+    c = [(counters & 0xFFFFFFFF).astype(np.uint64), (counters >> 32).astype(np.uint64), np.zeros_like(counters), np.zeros_like(counters)]
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p1 = np.uint64(M0) * c[0], np.uint64(M1) * c[2]
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ np.uint64(k0), lo1, hi0 ^ c[3] ^ np.uint64(k1), lo0]
+        k0, k1 = (k0 + W0) & 0xFFFFFFFF, (k1 + W1) & 0xFFFFFFFF
+    return np.stack(c, axis=1).reshape(-1)
+
+
+@pytest.mark.parametrize("n", [8 * 1000, 4099])
+def test_dropout_matches_philox_reference(n):
+    import numpy as np
+
+    from fairscale_b200.ops.dropout import dropout, dropout_apply
+
+    p, seed, offset = 0.25, 0x1234_5678_9ABC, 40
+    x = torch.randn(n, device=_dev()).bfloat16()
+    y = dropout_apply(x, p, seed, offset)
+    words = _philox_ref(seed, np.arange(offset, offset + (n + 3) // 4, dtype=np.uint64))[:n]
+    keep = torch.from_numpy(words >= np.uint64(int(p * 2**32))).to(_dev())
+    ref = torch.where(keep, x.float() / (1 - p), torch.zeros((), device=_dev())).bfloat16()
+    assert torch.equal(y, ref)
+    assert abs(keep.float().mean().item() - (1 - p)) < 0.03
+    # autograd: the gradient carries the same mask, and a restored generator state reproduces it
+    state = torch.cuda.get_rng_state(_dev())
+    xg = x.clone().requires_grad_(True)
+    y1 = dropout(xg, p)
+    y1.sum().backward()
+    assert torch.equal(xg.grad != 0, y1 != 0) or (x == 0).any()
+    torch.cuda.set_rng_state(state, _dev())
+    assert torch.equal(dropout(x, p), y1.detach())
+    assert not torch.equal(dropout(x, p), y1.detach())  # the offset moved on
+    _status_ok()
+
+
+def test_delay_kernel_occupies_the_stream():
+    from fairscale_b200.fair_dev.testing.testing import gpu_delay
+
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gpu_delay(0.1)
+    torch.cuda.synchronize()
+    t0.record()
+    gpu_delay(5.0)
+    t1.record()
+    torch.cuda.synchronize()
+    assert 4.5 < t0.elapsed_time(t1) < 50.0
