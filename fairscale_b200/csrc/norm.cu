@@ -118,6 +118,98 @@ __global__ void __launch_bounds__(NORM_WARPS * 32) norm_bwd_dx_warp_kernel(const
   }
 }
 
+// dx and the dgamma / dbeta partials in one pass over dy and x (H <= 2048).  Persistent: a warp walks rows
+// blockIdx.x * 4 + warp, + 4 * gridDim.x, ...; a lane owns the same VPL x 8 columns in every row, so it accumulates
+// their dgamma / dbeta contributions in registers.  dy and x stay packed in registers between the statistics pass and
+// the output pass.  At the end the four warps of a CTA are summed through shared memory and the CTA writes one
+// partial row: dgamma_part / dbeta_part are [gridDim.x, H].
+template <bool RMS, int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32, 2) norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                            const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                                            const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                                                            float* __restrict__ dgamma_part, float* __restrict__ dbeta_part,
+                                                                            long long rows, int H) {
+  extern __shared__ float fused_red[];  // [NORM_WARPS][H]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = H / 8;
+  float dg[VPL][8], db[VPL][8];
+#pragma unroll
+  for (int it = 0; it < VPL; ++it) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { dg[it][k] = 0.f; db[it][k] = 0.f; }
+  }
+  for (long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp; row < rows; row += static_cast<long long>(gridDim.x) * NORM_WARPS) {
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    Vec16<__nv_bfloat16> tx[VPL], td[VPL];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < VPL; ++it) {
+      const int j = lane + it * 32;
+      if (j < nvec) {
+        tx[it] = ld16(x + row * H + j * 8);
+        td[it] = ld16(dy + row * H + j * 8);
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < VPL; ++it) {
+      const int j = lane + it * 32;
+      if (j < nvec) {
+        const Vec16<__nv_bfloat16> tg = ld16(gamma + j * 8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float xh = (__bfloat162float(tx[it].v[k]) - mean) * rstd;
+          const float w = __bfloat162float(td[it].v[k]) * __bfloat162float(tg.v[k]);
+          s1 += w;
+          s2 = fmaf(w, xh, s2);
+        }
+      }
+    }
+    s1 = RMS ? 0.f : warp_sum(s1) / H;
+    s2 = warp_sum(s2) / H;
+#pragma unroll
+    for (int it = 0; it < VPL; ++it) {
+      const int j = lane + it * 32;
+      if (j < nvec) {
+        const Vec16<__nv_bfloat16> tg = ld16(gamma + j * 8);
+        Vec16<__nv_bfloat16> o;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float xh = (__bfloat162float(tx[it].v[k]) - mean) * rstd;
+          const float d = __bfloat162float(td[it].v[k]);
+          const float w = d * __bfloat162float(tg.v[k]);
+          o.v[k] = __float2bfloat16_rn(rstd * (w - s1 - xh * s2));
+          dg[it][k] = fmaf(d, xh, dg[it][k]);
+          if (!RMS) db[it][k] += d;
+        }
+        st16(dx + row * H + j * 8, o);
+      }
+    }
+  }
+  // the CTA's partial row: sum of its four warps, dgamma first and dbeta second through the same buffer
+#pragma unroll 1
+  for (int which = 0; which < (RMS ? 1 : 2); ++which) {
+    float* out = which == 0 ? dgamma_part : dbeta_part;
+    if (out == nullptr) break;  // uniform
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < VPL; ++it) {
+      const int j = lane + it * 32;
+      if (j < nvec) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) fused_red[warp * H + j * 8 + k] = which == 0 ? dg[it][k] : db[it][k];
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < H; c += NORM_WARPS * 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < NORM_WARPS; ++w) acc += fused_red[w * H + c];
+      out[static_cast<long long>(blockIdx.x) * H + c] = acc;
+    }
+  }
+}
+
 // Partial column sums of dy * xhat (-> dgamma) and dy (-> dbeta) over a strip of rows.
 // grid = (ceil(H / 256), strips), block = (32, 8): a thread owns 8 consecutive columns.
 template <bool RMS>
@@ -257,14 +349,25 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_dx_kernel(const __nv_bf
   }
 }
 
-// out[c] = sum_r part[r, c]  (fp32 partials -> bf16 or fp32 result)
-__global__ void column_reduce_kernel(const float* __restrict__ part, int rows, int H, __nv_bfloat16* out_bf16, float* out_f32) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+// out[c] = sum_r part[r, c]  (fp32 partials -> bf16 or fp32 result).  block = (32 columns, 8 row groups): a thread
+// adds rows ty, ty + 8, ... of its column in a fixed order, the eight sums are combined through shared memory.
+__global__ void __launch_bounds__(256) column_reduce_kernel(const float* __restrict__ part, int rows, int H, __nv_bfloat16* out_bf16, float* out_f32) {
+  __shared__ float red[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float acc = 0.f;
-  for (int r = 0; r < rows; ++r) acc += part[static_cast<long long>(r) * H + c];
-  if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16_rn(acc);
-  if (out_f32 != nullptr) out_f32[c] = acc;
+  if (c < H) {
+#pragma unroll 4
+    for (int r = threadIdx.y; r < rows; r += 8) acc += part[static_cast<long long>(r) * H + c];
+  }
+  red[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) t += red[y][threadIdx.x];
+    if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16_rn(t);
+    if (out_f32 != nullptr) out_f32[c] = t;
+  }
 }
 
 // Column sums of a bf16 matrix [rows, H] (bias gradient): strip partials then reduce.
@@ -336,9 +439,34 @@ FSB_API int fsb_norm_fwd(const void* x, const void* gamma, const void* beta, voi
   return static_cast<int>(cudaGetLastError());
 }
 
-FSB_API int fsb_norm_bwd_num_strips(long long rows) {
+// Rows of fp32 partials the backward needs room for: the fused kernel (H <= 2048) writes one row per CTA of its
+// persistent grid (two CTAs per SM, never more CTAs than groups of four rows), the two-kernel path at most 48.
+constexpr int NORM_FUSED_MAX_H = 2048;
+constexpr int NORM_FUSED_MAX_CTAS = 2 * 148;
+
+static int norm_bwd_fused_ctas(long long rows) {
+  const long long want = (rows + fsb::NORM_WARPS - 1) / fsb::NORM_WARPS;
+  return static_cast<int>(want < 1 ? 1 : (want > NORM_FUSED_MAX_CTAS ? NORM_FUSED_MAX_CTAS : want));
+}
+static int norm_bwd_split_strips(long long rows) {
   const long long want = (rows + 7) / 8;
   return static_cast<int>(want < 1 ? 1 : (want > 48 ? 48 : want));
+}
+
+FSB_API int fsb_norm_bwd_num_strips(long long rows) {
+  const int a = norm_bwd_fused_ctas(rows), b = norm_bwd_split_strips(rows);
+  return a > b ? a : b;
+}
+
+template <bool RMS>
+static void launch_norm_bwd_fused(const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* g, const float* mean, const float* rstd,
+                                  __nv_bfloat16* dx, float* pg, float* pb, long long rows, int H, int ctas, cudaStream_t stream) {
+  using namespace fsb;
+  const size_t smem = static_cast<size_t>(NORM_WARPS) * H * sizeof(float);  // <= 32 KB
+  const int vpl = (H / 8 + 31) / 32;
+  if (vpl <= 2)      norm_bwd_fused_kernel<RMS, 2><<<ctas, NORM_WARPS * 32, smem, stream>>>(dy, x, g, mean, rstd, dx, pg, pb, rows, H);
+  else if (vpl <= 4) norm_bwd_fused_kernel<RMS, 4><<<ctas, NORM_WARPS * 32, smem, stream>>>(dy, x, g, mean, rstd, dx, pg, pb, rows, H);
+  else               norm_bwd_fused_kernel<RMS, 8><<<ctas, NORM_WARPS * 32, smem, stream>>>(dy, x, g, mean, rstd, dx, pg, pb, rows, H);
 }
 
 // partials: fp32 workspace of 2 * n_strips * H floats (n_strips from fsb_norm_bwd_num_strips).
@@ -348,7 +476,8 @@ FSB_API int fsb_norm_bwd(const void* dy, const void* x, const void* gamma, const
   using namespace fsb;
   if (rows <= 0) return 0;
   if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAX_VEC) return -1;
-  const int strips = fsb_norm_bwd_num_strips(rows);
+  const bool fused = H <= NORM_FUSED_MAX_H;
+  const int strips = fused ? norm_bwd_fused_ctas(rows) : norm_bwd_split_strips(rows);
   float* pg = partials;
   float* pb = partials + static_cast<long long>(strips) * H;
   auto* d = static_cast<const __nv_bfloat16*>(dy);
@@ -356,15 +485,21 @@ FSB_API int fsb_norm_bwd(const void* dy, const void* x, const void* gamma, const
   auto* gg = static_cast<const __nv_bfloat16*>(gamma);
   auto* o = static_cast<__nv_bfloat16*>(dx);
   const bool want_beta = !rms && dbeta != nullptr;
-  dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
-  if (rms) {
-    launch_norm_bwd_dx<true>(d, xx, gg, mean, rstd, o, rows, H, stream);
-    norm_dparam_partial_kernel<true><<<grid, block, 0, stream>>>(d, xx, mean, rstd, pg, nullptr, rows, H);
+  if (fused) {
+    if (rms) launch_norm_bwd_fused<true>(d, xx, gg, mean, rstd, o, pg, nullptr, rows, H, strips, stream);
+    else     launch_norm_bwd_fused<false>(d, xx, gg, mean, rstd, o, pg, want_beta ? pb : nullptr, rows, H, strips, stream);
   } else {
-    launch_norm_bwd_dx<false>(d, xx, gg, mean, rstd, o, rows, H, stream);
-    norm_dparam_partial_kernel<false><<<grid, block, 0, stream>>>(d, xx, mean, rstd, pg, want_beta ? pb : nullptr, rows, H);
+    dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
+    if (rms) {
+      launch_norm_bwd_dx<true>(d, xx, gg, mean, rstd, o, rows, H, stream);
+      norm_dparam_partial_kernel<true><<<grid, block, 0, stream>>>(d, xx, mean, rstd, pg, nullptr, rows, H);
+    } else {
+      launch_norm_bwd_dx<false>(d, xx, gg, mean, rstd, o, rows, H, stream);
+      norm_dparam_partial_kernel<false><<<grid, block, 0, stream>>>(d, xx, mean, rstd, pg, want_beta ? pb : nullptr, rows, H);
+    }
   }
-  const int threads = 128, blocks = (H + threads - 1) / threads;
+  const dim3 threads(32, 8);
+  const int blocks = (H + 31) / 32;
   column_reduce_kernel<<<blocks, threads, 0, stream>>>(pg, strips, H, static_cast<__nv_bfloat16*>(dgamma), nullptr);
   if (want_beta) column_reduce_kernel<<<blocks, threads, 0, stream>>>(pb, strips, H, static_cast<__nv_bfloat16*>(dbeta), nullptr);
   return static_cast<int>(cudaGetLastError());
@@ -383,7 +518,8 @@ FSB_API int fsb_colsum(const void* x, long long rows, int H, float* partials, vo
   const int strips = fsb_colsum_num_strips(rows);
   dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
   colsum_partial_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, H, partials);
-  const int threads = 128, blocks = (H + threads - 1) / threads;
+  const dim3 threads(32, 8);
+  const int blocks = (H + 31) / 32;
   column_reduce_kernel<<<blocks, threads, 0, stream>>>(partials, strips, H, static_cast<__nv_bfloat16*>(out), nullptr);
   return static_cast<int>(cudaGetLastError());
 }
@@ -449,7 +585,8 @@ FSB_API int fsb_colsum_static(const void* x, long long rows, int H, void* out, c
   dim3 block(32, 8), grid((H / 8 + 31) / 32, strips);
   // every (strip, column < H) element read by the reduction below is written here first: no clearing needed
   colsum_partial_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, H, scratch);
-  const int threads = 128, blocks = (H + threads - 1) / threads;
+  const dim3 threads(32, 8);
+  const int blocks = (H + 31) / 32;
   column_reduce_kernel<<<blocks, threads, 0, stream>>>(scratch, strips, H, static_cast<__nv_bfloat16*>(out), nullptr);
   return static_cast<int>(cudaGetLastError());
 }
