@@ -143,17 +143,27 @@ class NvlinkWorkspace:
         return self.lanes[lane % self.N_LANES]
 
     # ------------------------------------------------------------------ capability checks used by comm.py
+    def _fits(self, t: torch.Tensor, nbytes: int) -> bool:
+        """A tensor outside the symmetric heap is copied into a lane's staging window first and has to fit there."""
+        return self.offset_of(t) is not None or nbytes <= self.lanes[0].staging_bytes
+
     def can_all_gather(self, out: torch.Tensor, shard: torch.Tensor) -> bool:
-        return out.is_contiguous() and (shard.numel() * shard.element_size()) % 16 == 0 and out.numel() == shard.numel() * self.world
+        nbytes = shard.numel() * shard.element_size()
+        return out.is_contiguous() and nbytes % 16 == 0 and out.numel() == shard.numel() * self.world and self._fits(shard, nbytes)
 
     def can_reduce_scatter(self, out: torch.Tensor, flat_in: torch.Tensor) -> bool:
-        return flat_in.dtype in _bind._DTYPE_CODE and out.dtype in _bind._DTYPE_CODE and (out.numel() * flat_in.element_size()) % 16 == 0
+        if not (flat_in.dtype in _bind._DTYPE_CODE and out.dtype in _bind._DTYPE_CODE and (out.numel() * flat_in.element_size()) % 16 == 0):
+            return False
+        need = out.numel() * self.world * flat_in.element_size()
+        in_heap = self.offset_of(flat_in) is not None and flat_in.numel() == out.numel() * self.world
+        return in_heap or need <= self.lanes[0].staging_bytes
 
     def can_all_reduce(self, t: torch.Tensor) -> bool:
-        return t.dtype in _bind._DTYPE_CODE and t.is_contiguous() and t.numel() * t.element_size() <= self.lanes[0].staging_bytes
+        return t.dtype in _bind._DTYPE_CODE and t.is_contiguous() and self._fits(t, t.numel() * t.element_size())
 
     def can_all_to_all(self, out: torch.Tensor, inp: torch.Tensor) -> bool:
-        return inp.is_contiguous() and out.is_contiguous() and (inp.numel() * inp.element_size() // self.world) % 16 == 0
+        nbytes = inp.numel() * inp.element_size()
+        return inp.is_contiguous() and out.is_contiguous() and (nbytes // self.world) % 16 == 0 and self._fits(inp, nbytes)
 
     # ------------------------------------------------------------------ collectives
     def barrier(self, lane: int = 0) -> None:
