@@ -38,8 +38,9 @@ def apply_to_type(type_fn: Callable[[Any], bool], fn: Callable, container: Any) 
             out.__dict__.update(x.__dict__)
             return out
         if isinstance(x, PackedSequence):
-            walk(x.data)  # applied for side effects only; PackedSequence is immutable
-            return x
+            # a PackedSequence is an immutable named tuple: rebuild it around the mapped data (the reference calls fn for
+            # its side effects only and returns the input, which loses casts and device moves)
+            return x._replace(data=walk(x.data))
         if isinstance(x, dict):
             return {k: walk(v) for k, v in x.items()}
         if _is_namedtuple(x):
