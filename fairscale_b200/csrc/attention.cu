@@ -23,6 +23,8 @@
 
 #include "sm100.cuh"
 
+#include <cstdlib>
+
 namespace fsb {
 
 constexpr int ATT_THREADS = 320;  // TMA warp + MMA warp + 8 compute warps (two per TMEM lane quadrant, half the columns each)
@@ -869,6 +871,9 @@ static int set_smem(K kernel, int bytes) {
 static constexpr int kMinSmem = 120 * 1024;
 static inline int one_cta_smem(int bytes) { return bytes < kMinSmem ? kMinSmem : bytes; }
 
+FSB_API int fsb_attn_fwd_pingpong(const void* qkv, void* o, float* lse, int B, int S, int H, int D, float scale, int* status,
+                                  cudaStream_t stream);
+
 FSB_API int fsb_last_tensor_map_result() { return fsb_host::last_encode_result(); }
 
 // Debug aid: when set to a device buffer of 4 * 64 * 4 uint64, the forward kernel's CTA (0,0,0) records nanosecond
@@ -883,6 +888,14 @@ FSB_API int fsb_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int
                          cudaStream_t stream) {
   using namespace fsb;
   if (S % ATT_BM != 0 || (D != 64 && D != 128)) return -1;
+  // Two query tiles per CTA in ping-pong (attention_fwd_pingpong.cu) when the sequence allows it; FSB_ATTN_FWD=classic
+  // keeps the one-tile kernel below (also used while a timeline trace is being recorded).
+  static int pingpong = -1;
+  if (pingpong < 0) {
+    const char* e = getenv("FSB_ATTN_FWD");
+    pingpong = (e != nullptr && e[0] == 'p') ? 1 : 0;
+  }
+  if (pingpong == 1 && S % (2 * ATT_BM) == 0 && g_attn_trace == nullptr) return fsb_attn_fwd_pingpong(qkv, o, lse, B, S, H, D, scale, status, stream);
   CUtensorMap tm;
   if (!fsb_host::encode_2d_16bit(&tm, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, ATT_BM)) return -1;
   AttnParams p{};

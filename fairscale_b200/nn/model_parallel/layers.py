@@ -58,8 +58,19 @@ def _initialize_affine_weight(
     if world == 1:
         init_method(weight)
         return weight if return_master_weight else None
-    master = torch.empty(out_features, in_features, dtype=weight.dtype, requires_grad=False)
+    # The full weight is drawn where it is cheapest: on this rank's GPU when there is one (a CPU draw of a 7 B-parameter
+    # model takes minutes per rank), else on the CPU as in the reference.  Every rank uses the same device type and seed,
+    # so the result is still independent of the model-parallel world size.
+    draw_on = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    master = torch.empty(out_features, in_features, dtype=weight.dtype, requires_grad=False, device=draw_on)
     init_method(master)
+    if not return_master_weight and master.device != weight.device:
+        piece = divide_and_check_no_remainder(per_partition_size, stride)
+        mine = torch.split(master, piece, dim=partition_dim)[get_model_parallel_rank()::world]
+        with torch.no_grad():
+            weight.copy_(torch.cat(mine, dim=partition_dim))  # only this rank's slice crosses to the weight's device
+        return None
+    master = master.to(weight.device)
     piece = divide_and_check_no_remainder(per_partition_size, stride)
     pieces = torch.split(master, piece, dim=partition_dim)
     mine = pieces[get_model_parallel_rank()::world]

@@ -1,5 +1,7 @@
 """Numerics of every native kernel against a plain PyTorch fp32 reference of the same op (needs a B200)."""
+import ctypes
 import math
+import os
 
 import pytest
 import torch
@@ -497,3 +499,26 @@ def test_delay_kernel_occupies_the_stream():
     t1.record()
     torch.cuda.synchronize()
     assert 4.5 < t0.elapsed_time(t1) < 50.0
+
+
+@pytest.mark.skipif(os.environ.get("FSB_TEST_PINGPONG", "0") != "1",
+                    reason="opt-in: the two-tile ping-pong forward is enabled with FSB_ATTN_FWD=pingpong and checked with FSB_TEST_PINGPONG=1")
+@pytest.mark.parametrize("B,S,H,D", [(1, 256, 1, 128), (1, 512, 2, 128), (2, 1024, 2, 64)])
+def test_flash_attention_pingpong_forward(B, S, H, D):
+    """The ping-pong forward (called through its own C symbol) against the fp32 reference and the one-tile kernel."""
+    from fairscale_b200.ops import _bind
+
+    torch.manual_seed(5)
+    qkv = (torch.randn(B, S, 3 * H * D, device=_dev()) * 0.7).bfloat16()
+    o = torch.empty(B, S, H * D, device=_dev(), dtype=torch.bfloat16)
+    lse = torch.empty(B, H, S, device=_dev(), dtype=torch.float32)
+    f = _bind.fn("fsb_attn_fwd_pingpong")
+    f.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]
+    assert f(qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), B, S, H, D, 1.0 / math.sqrt(D), _bind.status_ptr(_dev()), _bind.stream_ptr(_dev())) == 0
+    _status_ok()
+    q, k, v = qkv.float().view(B, S, 3, H, D).permute(2, 0, 3, 1, 4)
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(D)
+    s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device=_dev()).triu(1), float("-inf"))
+    ref = (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, H * D)
+    assert _rel_err(o, ref) < 2e-2, _rel_err(o, ref)
+    assert _rel_err(lse, torch.logsumexp(s, -1)) < 1e-3
