@@ -1,0 +1,158 @@
+"""OSS and ShardedDataParallel behaviours on gloo CPU ranks: state-dict consolidation and cross-loading with a plain
+optimizer, gradient clipping, added parameter groups, gradient accumulation under ``no_sync``, frozen parameters and an
+uneven world (3 ranks, fewer large parameters than ranks)."""
+import copy
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from fairscale_b200.fair_dev.testing.testing import spawn_ranks
+from fairscale_b200.nn.data_parallel import ShardedDataParallel
+from fairscale_b200.optim import OSS
+
+
+def _model():
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(6, 11), nn.Tanh(), nn.Linear(11, 5), nn.Tanh(), nn.Linear(5, 3))
+
+
+def _batch(rank, step, n=4):
+    g = torch.Generator().manual_seed(1000 * step + rank)
+    return torch.randn(n, 6, generator=g), torch.randn(n, 3, generator=g)
+
+
+def _step(model, opt, rank, step, clip=None, oss=None):
+    x, y = _batch(rank, step)
+    # gradients of a ShardedDataParallel module are views of its reduce buckets: they are cleared through the module
+    model.zero_grad() if isinstance(model, ShardedDataParallel) else opt.zero_grad()
+    loss = nn.functional.mse_loss(model(x), y)
+    loss.backward()
+    norm = None
+    if clip is not None:
+        norm = oss.clip_grad_norm(clip) if oss is not None else torch.nn.utils.clip_grad_norm_(model.parameters(), clip)
+    opt.step()
+    return loss.item(), norm
+
+
+def _state_and_clip(rank, world):
+    ref = nn.parallel.DistributedDataParallel(_model())
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    base = _model()
+    oss = OSS(base.parameters(), optim=torch.optim.SGD, lr=0.1, momentum=0.9)
+    sdp = ShardedDataParallel(base, oss)
+
+    # every parameter is owned by exactly one rank
+    owned = [sum(len(g["params"]) for g in part) for part in oss.partition_parameters()]
+    assert sum(owned) == len(list(base.parameters())) and len(owned) == world
+
+    for s in range(3):
+        l_ref, n_ref = _step(ref, ref_opt, rank, s, clip=0.5)
+        l_new, n_new = _step(sdp, oss, rank, s, clip=0.5, oss=oss)
+        assert abs(l_ref - l_new) < 1e-6
+        torch.testing.assert_close(torch.as_tensor(n_new).float(), torch.as_tensor(n_ref).float(), atol=1e-5, rtol=1e-5)
+    for a, b in zip(ref.module.parameters(), base.parameters()):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+
+    # consolidated state on rank 0 has the layout of the plain optimizer's state dict and loads into one
+    oss.consolidate_state_dict(recipient_rank=0)
+    if rank == 0:
+        full = oss.state_dict()
+        ref_sd = ref_opt.state_dict()
+        assert len(full["state"]) == len(ref_sd["state"])
+        for pid, st in ref_sd["state"].items():
+            torch.testing.assert_close(full["state"][pid]["momentum_buffer"], st["momentum_buffer"], atol=1e-6, rtol=1e-5)
+        plain = torch.optim.SGD(_model().parameters(), lr=0.1, momentum=0.9)
+        plain.load_state_dict(full)
+        box = [full]
+    else:
+        box = [None]
+    dist.broadcast_object_list(box, src=0)
+
+    # a plain optimizer's state dict loads into a fresh OSS: each rank keeps its shard and training continues in step
+    base2 = copy.deepcopy(base)
+    oss2 = OSS(base2.parameters(), optim=torch.optim.SGD, lr=0.1, momentum=0.9)
+    oss2.load_state_dict(box[0])
+    sdp2 = ShardedDataParallel(base2, oss2)
+    l_ref, _ = _step(ref, ref_opt, rank, 7)
+    l_new, _ = _step(sdp2, oss2, rank, 7)
+    assert abs(l_ref - l_new) < 1e-6
+    for a, b in zip(ref.module.parameters(), base2.parameters()):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+
+    # local (non-consolidated) state dict exists on every rank without communication
+    local = oss.optim.state_dict()
+    assert len(local["state"]) == owned[rank]
+
+
+def test_oss_state_dict_clip_and_cross_loading():
+    spawn_ranks(_state_and_clip, 2, (), backend="gloo")
+
+
+def _accumulate_freeze_add_group(rank, world):
+    ref = nn.parallel.DistributedDataParallel(_model())
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    base = _model()
+    oss = OSS(base.parameters(), optim=torch.optim.SGD, lr=0.05)
+    sdp = ShardedDataParallel(base, oss, reduce_buffer_size=0)
+
+    # two micro-batches without reduction, one with: same update as DDP's no_sync accumulation
+    ref_opt.zero_grad()
+    sdp.zero_grad()
+    for s in range(3):
+        x, y = _batch(rank, s)
+        if s < 2:
+            with ref.no_sync():
+                nn.functional.mse_loss(ref(x), y).backward()
+            with sdp.no_sync():
+                nn.functional.mse_loss(sdp(x), y).backward()
+        else:
+            nn.functional.mse_loss(ref(x), y).backward()
+            nn.functional.mse_loss(sdp(x), y).backward()
+    ref_opt.step()
+    oss.step()
+    for a, b in zip(ref.module.parameters(), base.parameters()):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+
+    # freeze the first layer: refresh_trainable() rebuilds the hooks and the frozen weights stay put
+    for p in base[0].parameters():
+        p.requires_grad = False
+        p.grad = None  # the module's zero_grad only visits trainable parameters, as in the reference
+    sdp.refresh_trainable()
+    frozen = [p.detach().clone() for p in base[0].parameters()]
+    before = base[4].weight.detach().clone()
+    _step(sdp, oss, rank, 5)
+    assert all(torch.equal(a, b) for a, b in zip(frozen, base[0].parameters()))
+    assert not torch.equal(before, base[4].weight)
+    ranks_agree = [torch.zeros_like(base[4].weight) for _ in range(world)]
+    dist.all_gather(ranks_agree, base[4].weight.detach())
+    assert all(torch.equal(ranks_agree[0], t) for t in ranks_agree)  # owners broadcast the update to everyone
+
+    # a parameter group added later is partitioned too
+    extra = nn.Linear(3, 3)
+    oss.add_param_group({"params": list(extra.parameters()), "lr": 0.01})
+    assert len(oss.param_groups) == 2
+    assert sum(len(g["params"]) for part in oss.partition_parameters() for g in part) == len(list(base.parameters())) + 2
+
+
+def test_sdp_accumulation_freezing_and_new_groups():
+    spawn_ranks(_accumulate_freeze_add_group, 2, (), backend="gloo")
+
+
+def _uneven(rank, world):
+    # three ranks, a model with two big tensors and a few tiny ones: some rank owns only small parameters
+    ref = nn.parallel.DistributedDataParallel(_model())
+    ref_opt = torch.optim.Adam(ref.parameters(), lr=1e-2)
+    base = _model()
+    oss = OSS(base.parameters(), optim=torch.optim.Adam, lr=1e-2)
+    sdp = ShardedDataParallel(base, oss)
+    for s in range(3):
+        l_ref, _ = _step(ref, ref_opt, rank, s)
+        l_new, _ = _step(sdp, oss, rank, s)
+        assert abs(l_ref - l_new) < 1e-6
+    for a, b in zip(ref.module.parameters(), base.parameters()):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+
+
+def test_oss_sdp_three_ranks():
+    spawn_ranks(_uneven, 3, (), backend="gloo")
