@@ -1577,14 +1577,23 @@ class FullyShardedDataParallel(nn.Module):
         )
         self.uncollected_opt_state = {}
         assert "uncollected_local_ids" in new_sd
+        if self._step_was_tensor:
+            # torch's own optimizers keep ``step`` as a 0-dim tensor and refuse a plain number after load_state_dict
+            for bufs in new_sd["state"].values():
+                if "step" in bufs and not torch.is_tensor(bufs["step"]):
+                    bufs["step"] = torch.tensor(float(bufs["step"]))
         return new_sd
 
     def _remove_uncollectable_params_from_optim_state_dict(self, osd: Dict) -> Dict:
         """Set aside the state of rank-local (expert) instances; normalise tensor ``step`` to int."""
+        self._step_was_tensor = False
+        # optimizer.state_dict() hands out the live per-parameter dicts: copy them before rewriting ``step``
+        osd["state"] = {k: dict(v) for k, v in osd["state"].items()}
         for bufs in osd["state"].values():
             if "step" in bufs:
                 assert type(bufs["step"]) is int or ou.is_singleton_tensor(bufs["step"])
                 if ou.is_singleton_tensor(bufs["step"]):
+                    self._step_was_tensor = True
                     bufs["step"] = bufs["step"].item()
         local_only = [i for i, m in enumerate(get_fsdp_instances(self)) if m.no_broadcast_optim_state]
         if self.rank == 0:
@@ -1608,7 +1617,9 @@ class FullyShardedDataParallel(nn.Module):
             )
         for pid, per_param in full_optim_state_dict["state"].items():
             for name, v in per_param.items():
-                if torch.is_tensor(v) and pid not in keep_whole:
+                if ou.is_singleton_tensor(v):
+                    piece = v  # e.g. Adam's step counter: the same on every rank
+                elif torch.is_tensor(v) and pid not in keep_whole:
                     piece, _ = self._get_shard(v)
                 elif isinstance(v, list) and ou.is_singleton_tensor(v[0]):
                     piece = v[0] if self.rank >= len(v) else v[self.rank]
