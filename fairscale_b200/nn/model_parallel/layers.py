@@ -39,6 +39,9 @@ def _local_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -
     return F.linear(x, w, b)
 
 
+_GPU_DRAW_MIN_NUMEL = 1 << 24  # full weights of at least this many elements are drawn on the GPU
+
+
 def _initialize_affine_weight(
     weight: torch.Tensor,
     out_features: int,
@@ -58,10 +61,12 @@ def _initialize_affine_weight(
     if world == 1:
         init_method(weight)
         return weight if return_master_weight else None
-    # The full weight is drawn where it is cheapest: on this rank's GPU when there is one (a CPU draw of a 7 B-parameter
-    # model takes minutes per rank), else on the CPU as in the reference.  Every rank uses the same device type and seed,
+    # The full weight is drawn where it is cheapest: large ones on this rank's GPU when there is one (a CPU draw of a
+    # 7 B-parameter model takes minutes per rank), small ones on the CPU as in the reference (same values as a dense layer
+    # initialised with the same seed).  Every rank uses the same device type and seed,
     # so the result is still independent of the model-parallel world size.
-    draw_on = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    big = out_features * in_features >= _GPU_DRAW_MIN_NUMEL
+    draw_on = torch.device("cuda", torch.cuda.current_device()) if (big and torch.cuda.is_available()) else torch.device("cpu")
     master = torch.empty(out_features, in_features, dtype=weight.dtype, requires_grad=False, device=draw_on)
     init_method(master)
     if not return_master_weight and master.device != weight.device:
