@@ -987,7 +987,9 @@ class FullyShardedDataParallel(nn.Module):
         def _pre_backward_hook(*unused: Any) -> None:
             if self._is_root:
                 self._queue_wait_for_post_backward()
-            if self.reshard_after_forward:
+            if self.reshard_after_forward or not self.has_full_params:
+                # also a unit that keeps its parameters after forward has lost them when an earlier backward of the same
+                # step (two forwards, then two backwards) already ran its post-backward and freed them
                 self._rebuild_full_params()
             else:
                 self._use_full_params()

@@ -1,0 +1,206 @@
+"""FSDP behaviours beyond plain training parity (2 gloo ranks, CPU): ``apply`` on sharded weights, frozen sub-modules,
+two forwards before two backwards, a module called several times per step, nesting with ``checkpoint_wrapper``,
+``summon_full_params`` variants, input casting under mixed precision, evaluation without gradients."""
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from fairscale_b200.fair_dev.testing.testing import spawn_ranks
+from fairscale_b200.nn import FullyShardedDataParallel as FSDP
+from fairscale_b200.nn import checkpoint_wrapper
+from fairscale_b200.nn.data_parallel import TrainingState, get_fsdp_instances
+
+CPU = dict(compute_device=torch.device("cpu"))
+
+
+def _mlp(d=8, seed=0):
+    torch.manual_seed(seed)
+    return nn.Sequential(nn.Linear(d, 2 * d + 1), nn.ReLU(), nn.Linear(2 * d + 1, d), nn.ReLU(), nn.Linear(d, 4))
+
+
+def _x(rank, step, d=8):
+    g = torch.Generator().manual_seed(31 * step + rank)
+    return torch.randn(5, d, generator=g)
+
+
+def _wrap(model, **kw):
+    layers = list(model)
+    return FSDP(nn.Sequential(FSDP(nn.Sequential(*layers[:2]), **CPU, **kw), *layers[2:]), **CPU, **kw)
+
+
+def _assert_same_as_ddp(model, ref):
+    full, ref_sd = model.state_dict(), ref.module.state_dict()
+    assert len(full) == len(ref_sd)
+    for v, w in zip(full.values(), ref_sd.values()):  # names differ by the wrapper nesting, the order does not
+        torch.testing.assert_close(v, w, atol=1e-6, rtol=1e-5)
+
+
+def _apply_and_freeze(rank, world):
+    # apply(): the function sees full (unsharded) parameters and its writes survive resharding
+    model = _wrap(_mlp())
+
+    def init(m):
+        if isinstance(m, nn.Linear):
+            with torch.no_grad():
+                m.weight.fill_(0.25)
+                m.bias.zero_()
+
+    model.apply(init)
+    sd = model.state_dict()
+    assert all(torch.all(v == (0.25 if k.endswith("weight") else 0.0)) for k, v in sd.items())
+
+    # frozen inner unit: its shard never changes, the trainable part matches DDP with the same freezing
+    ref_m = _mlp()
+    for p in list(ref_m[0].parameters()):
+        p.requires_grad = False
+    ref = nn.parallel.DistributedDataParallel(ref_m)
+    ref_opt = torch.optim.SGD([p for p in ref.parameters() if p.requires_grad], lr=0.1)
+    base = _mlp()
+    for p in list(base[0].parameters()):
+        p.requires_grad = False
+    model = _wrap(base)
+    opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.1)
+    for s in range(3):
+        for m, o in ((ref, ref_opt), (model, opt)):
+            o.zero_grad()
+            m(_x(rank, s)).pow(2).mean().backward()
+            o.step()
+    _assert_same_as_ddp(model, ref)
+    for inst in get_fsdp_instances(model):
+        assert inst.training_state == TrainingState.IDLE
+
+
+def test_fsdp_apply_and_frozen_unit():
+    spawn_ranks(_apply_and_freeze, 2, (), backend="gloo")
+
+
+class _ManualDP:
+    """Oracle for gradient patterns DDP's reducer does not support (several forwards before the backwards): a bare
+    replica whose accumulated local gradients are averaged by hand before the optimizer step."""
+
+    def __init__(self, model):
+        self.module = model
+
+    def __call__(self, x):
+        return self.module(x)
+
+    def parameters(self):
+        return self.module.parameters()
+
+    def average_grads(self, world):
+        for p in self.module.parameters():
+            dist.all_reduce(p.grad)
+            p.grad /= world
+
+
+def _multi_forward(rank, world):
+    ref = _ManualDP(_mlp())
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    model = _wrap(_mlp())
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    # two forwards, then the two backwards (the first graph outlives the second forward); both backwards reduce
+    for m, o in ((ref, ref_opt), (model, opt)):
+        o.zero_grad()
+        l1 = m(_x(rank, 0)).pow(2).mean()
+        l2 = m(_x(rank, 1)).pow(2).mean()
+        l1.backward()
+        l2.backward()
+        if m is ref:
+            ref.average_grads(world)
+        o.step()
+    _assert_same_as_ddp(model, ref)
+    # the same with only the last backward reducing
+    for m, o in ((ref, ref_opt), (model, opt)):
+        o.zero_grad()
+        l1 = m(_x(rank, 4)).pow(2).mean()
+        l2 = m(_x(rank, 5)).pow(2).mean()
+        if m is ref:
+            l1.backward()
+            l2.backward()
+            ref.average_grads(world)
+        else:
+            with model.no_sync():
+                l1.backward()
+            l2.backward()
+        o.step()
+    _assert_same_as_ddp(model, ref)
+    # one summed loss over two forwards of the same wrapper
+    for m, o in ((ref, ref_opt), (model, opt)):
+        o.zero_grad()
+        (m(_x(rank, 2)).pow(2).mean() + m(_x(rank, 3)).abs().mean()).backward()
+        if m is ref:
+            ref.average_grads(world)
+        o.step()
+    _assert_same_as_ddp(model, ref)
+
+
+def test_fsdp_forward_forward_backward_backward():
+    spawn_ranks(_multi_forward, 2, (), backend="gloo")
+
+
+def _with_checkpoint(rank, world):
+    ref = nn.parallel.DistributedDataParallel(_mlp())
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    layers = list(_mlp())
+    # both nestings: FSDP(checkpoint(m)) and checkpoint(FSDP(m))
+    a = FSDP(checkpoint_wrapper(nn.Sequential(*layers[:2])), **CPU)
+    b = checkpoint_wrapper(FSDP(nn.Sequential(*layers[2:4]), **CPU))
+    model = FSDP(nn.Sequential(a, b, layers[4]), **CPU)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    for s in range(3):
+        losses = []
+        for m, o in ((ref, ref_opt), (model, opt)):
+            o.zero_grad()
+            x = _x(rank, s).requires_grad_()
+            loss = m(x).pow(2).mean()
+            loss.backward()
+            o.step()
+            losses.append(loss.item())
+        assert abs(losses[0] - losses[1]) < 1e-6
+    full = model.state_dict()
+    ref_sd = ref.module.state_dict()
+    assert len(full) == len(ref_sd)
+    for v, w in zip(full.values(), ref_sd.values()):  # names differ by the wrapper nesting, the order does not
+        torch.testing.assert_close(v, w, atol=1e-6, rtol=1e-5)
+
+
+def test_fsdp_with_checkpoint_wrapper_both_nestings():
+    spawn_ranks(_with_checkpoint, 2, (), backend="gloo")
+
+
+def _summon_eval_inputs(rank, world):
+    model = _wrap(_mlp())
+    before = model.state_dict()
+    # volatile: modifications are discarded
+    with model.summon_full_params(volatile=True):
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(1.0)
+    after = model.state_dict()
+    for k in before:
+        torch.testing.assert_close(after[k], before[k])
+    # recurse=False only gathers the outer unit
+    with model.summon_full_params(recurse=False):
+        outer_full = [p.numel() for p in model.params]
+    assert sum(outer_full) == sum(p.numel() for p in list(_mlp())[2:] for p in p.parameters())
+    # evaluation under no_grad leaves every unit idle and resharded
+    model.eval()
+    with torch.no_grad():
+        y1 = model(_x(rank, 0))
+        y2 = model(_x(rank, 0))
+    torch.testing.assert_close(y1, y2)
+    for inst in get_fsdp_instances(model):
+        assert inst.training_state == TrainingState.IDLE
+    # mixed precision: fp32 inputs are cast to the compute dtype at the root, integer inputs pass through
+    mp = FSDP(_mlp(), mixed_precision=True, compute_dtype=torch.bfloat16, **CPU)
+    out = mp(_x(rank, 0))
+    assert out.dtype == torch.bfloat16
+    out.float().sum().backward()
+    assert mp.params[0].grad is not None and mp.params[0].grad.dtype == torch.float32
+    emb = FSDP(nn.Sequential(nn.Embedding(10, 8), nn.Linear(8, 2)), mixed_precision=True, compute_dtype=torch.bfloat16, **CPU)
+    assert emb(torch.randint(0, 10, (3, 4))).dtype == torch.bfloat16
+    dist.barrier()
+
+
+def test_fsdp_summon_eval_and_input_casting():
+    spawn_ranks(_summon_eval_inputs, 2, (), backend="gloo")
