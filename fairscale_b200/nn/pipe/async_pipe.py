@@ -17,8 +17,10 @@ import torch.distributed as dist
 from torch import Tensor, nn
 
 from . import microbatch
+from .async_pipeline import AsyncPipeline
+from .async_schedule import Invocation, Location, ModuleWrapper
 from .batchnorm import DeferredBatchNorm
-from .messages import SendRecvTransport
+from .messages import SendRecvTransport, get_transport
 from .types import LazyModule
 
 Tensors = Tuple[Tensor, ...]
@@ -37,6 +39,32 @@ class _RecvBoundary(torch.autograd.Function):
     def backward(ctx: Any, grad: Tensor):  # type: ignore[override]
         ctx.transport.send(grad, ctx.prev_rank)
         return grad, None, None
+
+
+def plan_invocations(layers: Sequence[Any], balance: Sequence[int]) -> Tuple[List[Location], List[Invocation]]:
+    """Where every entry of the layer list runs, and the chain of invocations.
+
+    Entry ``i`` nominally belongs to the stage given by ``balance``; an entry that is the same object as an earlier one
+    (a shared layer) runs where its first occurrence lives.  Returns one ``Location`` per entry and one ``Invocation``
+    per entry (parity: ``instantiate_partition`` in fairscale/nn/pipe/async_pipe.py:224-319)."""
+    first: dict = {}
+    per_stage_count = [0] * len(balance)
+    locations: List[Location] = []
+    stage, used = 0, 0
+    for layer in layers:
+        while used >= balance[stage]:
+            stage, used = stage + 1, 0
+        used += 1
+        key = id(layer)
+        if key not in first:
+            first[key] = Location(stage, per_stage_count[stage])
+            per_stage_count[stage] += 1
+        locations.append(first[key])
+    n = len(locations)
+    invocations = [
+        Invocation(k, locations[k], locations[k - 1] if k > 0 else None, locations[k + 1] if k + 1 < n else None) for k in range(n)
+    ]
+    return locations, invocations
 
 
 class AsyncPipe(nn.Module):
@@ -73,6 +101,12 @@ class AsyncPipe(nn.Module):
         if sum(self.balance) != n_layers:
             raise ValueError(f"module and sum of balance have different length (module: {n_layers}, sum of balance: {sum(self.balance)})")
         self.final_stage = len(self.balance) - 1
+        self.pipeline: Optional[AsyncPipeline] = None
+        entries = list(module)
+        if len({id(l) for l in entries}) < len(entries):
+            # a layer object that appears more than once: event-loop schedule, data may revisit a stage
+            self._init_event_loop(entries, input_device, deferred_batch_norm)
+            return
         if self.rank >= len(self.balance):
             logging.warning(f"AsyncPipe: rank {self.rank} has no partition and stays idle")
             self.partition: Optional[nn.Sequential] = None
@@ -89,8 +123,54 @@ class AsyncPipe(nn.Module):
         self.input_device = input_device
         if self.partition is not None:
             self.partition.to(self.input_device)
-        self.transport = SendRecvTransport(group, self.input_device)
+        self.transport = get_transport(group, self.input_device)
         self._outputs: List[Tensor] = []
+
+    def _init_event_loop(self, entries: List[Any], input_device: Optional[torch.device], deferred_batch_norm: bool) -> None:
+        locations, invocations = plan_invocations(entries, self.balance)
+        if input_device is None:
+            input_device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(self.group) == "nccl" else torch.device("cpu")
+        self.input_device = input_device
+        self.transport = get_transport(self.group, self.input_device)
+        wrappers: dict = {}
+        for entry, loc, inv in zip(entries, locations, invocations):
+            if loc.stage != self.rank:
+                continue
+            if loc not in wrappers:
+                layer = entry() if isinstance(entry, LazyModule) else entry
+                part = nn.Sequential(layer)
+                if deferred_batch_norm:
+                    part = DeferredBatchNorm.convert_deferred_batch_norm(part, self.chunks)
+                wrappers[loc] = ModuleWrapper(part.to(self.input_device), loc)
+            wrappers[loc].invocations.append(inv)
+        mine = [wrappers[k] for k in sorted(wrappers, key=lambda l: l.index)]
+        self.partition = nn.Sequential(*[w.module for w in mine]) if mine else None  # registers the parameters
+        self._head_stage = invocations[0].this.stage
+        self._tail_stage = invocations[-1].this.stage
+        self._stages_in_use = sorted({loc.stage for loc in locations})
+        self.pipeline = AsyncPipeline(mine, self.group, self.rank, self.transport)
+        self._outputs = []
+
+    def _forward_event_loop(self, input: Optional[TensorOrTensors]) -> Optional[TensorOrTensors]:
+        assert self.pipeline is not None
+        if self.partition is None:
+            return None
+        if self.rank == self._head_stage:
+            assert isinstance(input, Tensor), "the event-loop schedule moves single tensors"
+            batches = [b.tensor for b in microbatch.scatter(input, self.chunks)]
+            n = len(batches)
+            for r in self._stages_in_use:
+                if r != self.rank:
+                    self.transport.send(torch.tensor([n], dtype=torch.int64, device=self.input_device), r)
+        else:
+            batches = None
+            n = int(self.transport.recv(self._head_stage).item())
+        self.pipeline.checkpoint_stop = {"always": n, "except_last": n - 1, "never": 0}[self.checkpoint]
+        outs = self.pipeline.run(self.training, batches, n)
+        if self.rank == self._tail_stage:
+            assert outs is not None
+            return torch.cat(outs)
+        return None
 
     def __len__(self) -> int:
         return 0 if self.partition is None else len(self.partition)
@@ -106,6 +186,8 @@ class AsyncPipe(nn.Module):
     def forward(self, input: Optional[TensorOrTensors] = None) -> Optional[TensorOrTensors]:  # type: ignore[override]
         """Stage 0 consumes ``input``; the final stage returns the gathered output; other stages return the list
         of their micro-batch outputs (pass it to :meth:`back_helper` to run their share of backward)."""
+        if self.pipeline is not None:
+            return self._forward_event_loop(input)
         if self.partition is None:
             return None
         first, last = self.rank == 0, self.rank == self.final_stage
@@ -142,6 +224,11 @@ class AsyncPipe(nn.Module):
     def back_helper(self, output: Optional[List[Tensor]] = None) -> None:
         """Run backward on a non-final stage: receive each micro-batch's output gradient from the next stage
         (reverse order) and back-propagate; gradients for the previous stage leave through the recv boundary."""
+        if self.pipeline is not None:
+            # event-loop schedule: every rank (the last one too, after its loss.backward()) collects the gradients of
+            # the activations it sent away
+            self.pipeline.back()
+            return
         if self.partition is None or self.rank == self.final_stage:
             self.transport.flush()
             return

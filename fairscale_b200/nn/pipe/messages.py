@@ -8,7 +8,10 @@ synchronisation: NCCL orders the transfers on its own stream and the consumer ke
 
 from __future__ import annotations
 
-from typing import Any, List, Optional
+import os
+import queue
+import threading
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -57,3 +60,90 @@ class SendRecvTransport:
             if hasattr(w, "wait"):
                 w.wait()
         self._pending.clear()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# RPC transport: the same send / recv / flush interface carried by torch.distributed.rpc (TensorPipe).  Tensors travel
+# as CPU copies into per-(transport, source) queues of the destination process, as in the reference's RpcTransport
+# (fairscale/nn/pipe/messages.py:55-107).  It needs no process-group p2p support and is meant for control-plane sized
+# traffic and for clusters without NCCL p2p; activations of real models belong on SendRecvTransport.
+# ---------------------------------------------------------------------------------------------------------------------
+_rpc_queues: Dict[Tuple[int, int], "queue.Queue[Any]"] = {}
+_rpc_queues_lock = threading.Lock()
+
+
+def _rpc_queue(channel: int, src: int) -> "queue.Queue[Any]":
+    with _rpc_queues_lock:
+        q = _rpc_queues.get((channel, src))
+        if q is None:
+            q = _rpc_queues[(channel, src)] = queue.Queue()
+        return q
+
+
+def rpc_push_queue(channel: int, src: int, seq: int, payload: Tensor, requires_grad: bool) -> None:
+    """Runs on the destination worker: file message number ``seq`` from group rank ``src`` under ``channel``."""
+    _rpc_queue(channel, src).put((seq, payload, requires_grad))
+
+
+class RpcTransport:
+    """``send`` / ``recv`` / ``flush`` over ``torch.distributed.rpc``.
+
+    Args:
+        rank: this process's rank in the pipeline group.
+        worker_name: maps a group rank to its RPC worker name (default ``"Test<rank>"``, the reference's test naming).
+        device: where received tensors are placed.
+        channel: distinguishes independent transports between the same workers.
+        timeout: seconds a ``recv`` waits before raising ``TimeoutError``.
+    """
+
+    def __init__(self, rank: int, device: torch.device, worker_name: Optional[Callable[[int], str]] = None, channel: int = 0,
+                 timeout: float = 120.0) -> None:
+        from torch.distributed import rpc
+
+        self.rpc = rpc
+        self.rank = rank
+        self.device = device
+        self.worker_name = worker_name or (lambda r: f"Test{r}")
+        self.channel = channel
+        self.timeout = timeout
+        self._pending: List[Any] = []
+        # RPC calls to one worker may run out of order there: messages are numbered per destination and put back in
+        # order by the receiver
+        self._next_send: Dict[int, int] = {}
+        self._next_recv: Dict[int, int] = {}
+        self._early: Dict[Tuple[int, int], Any] = {}
+
+    def send(self, t: Tensor, dst: int) -> None:
+        seq = self._next_send.get(dst, 0)
+        self._next_send[dst] = seq + 1
+        args = (self.channel, self.rank, seq, t.detach().cpu(), bool(t.requires_grad))
+        self._pending.append(self.rpc.rpc_async(self.worker_name(dst), rpc_push_queue, args=args))
+
+    def recv(self, src: int) -> Tensor:
+        want = self._next_recv.get(src, 0)
+        self._next_recv[src] = want + 1
+        q = _rpc_queue(self.channel, src)
+        while (src, want) not in self._early:
+            try:
+                seq, payload, requires_grad = q.get(timeout=self.timeout)
+            except queue.Empty:
+                raise TimeoutError(f"no message from pipeline rank {src} within {self.timeout} s") from None
+            self._early[(src, seq)] = (payload, requires_grad)
+        payload, requires_grad = self._early.pop((src, want))
+        out = payload.to(self.device)
+        if requires_grad and out.is_floating_point():
+            out.requires_grad_()
+        return out
+
+    def flush(self) -> None:
+        for f in self._pending:
+            f.wait()
+        self._pending.clear()
+
+
+def get_transport(group: Any, device: torch.device, **rpc_kwargs: Any) -> Any:
+    """p2p transport unless ``FORCE_RPC`` is set (the reference picks RPC unless it runs under MPI,
+    fairscale/nn/pipe/async_pipeline.py:39-43; here p2p over NCCL / gloo is the default because it always exists)."""
+    if os.environ.get("FORCE_RPC", "").lower() in ("1", "true", "yes"):
+        return RpcTransport(dist.get_rank(group), device, **rpc_kwargs)
+    return SendRecvTransport(group, device)

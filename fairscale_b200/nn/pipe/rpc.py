@@ -36,6 +36,22 @@ def _call(pipe_id: int, fn: Callable[[AsyncPipe], Any]) -> Any:
     return fn(_PIPES[pipe_id])
 
 
+class PipeBackRedirect(torch.autograd.Function):
+    """Identity on the final stage's output as seen by rank 0.  When the loss computed on rank 0 back-propagates, its
+    backward tells every worker to run its share of the pipeline's backward, so the caller needs no explicit
+    ``wrapper.backward()`` (parity: fairscale/nn/pipe/rpc.py:53-71)."""
+
+    @staticmethod
+    def forward(ctx: Any, inputs: Tensor, wrapper: "PipeRPCWrapper") -> Tensor:  # type: ignore[override]
+        ctx.wrapper = wrapper
+        return inputs.view_as(inputs)
+
+    @staticmethod
+    def backward(ctx: Any, *grad: Tensor) -> Any:  # type: ignore[override]
+        ctx.wrapper.backward()
+        return grad[0], None
+
+
 class PipeRPCWrapper(nn.Module):
     """Rank 0 owns the object; workers are addressed by the names in ``worker_map`` (group rank -> rpc name)."""
 
