@@ -15,6 +15,7 @@ from torch import Tensor, nn
 from .async_pipe import AsyncPipe
 
 _PIPES: Dict[int, AsyncPipe] = {}
+_OUTPUTS: Dict[int, Any] = {}  # what the last forward returned on this worker
 _NEXT_ID = 0
 
 
@@ -22,14 +23,24 @@ def _build(pipe_id: int, module_factory: Callable[[], nn.Sequential], args: tupl
     _PIPES[pipe_id] = AsyncPipe(module_factory(), *args, **kwargs)
 
 
-def _forward(pipe_id: int, training: bool) -> None:
+def _forward(pipe_id: int, training: bool, grad_enabled: bool = True) -> None:
     pipe = _PIPES[pipe_id]
     pipe.train(training)
-    pipe(None)
+    with torch.set_grad_enabled(grad_enabled):  # grad mode is per thread: mirror the caller's on this worker
+        out = pipe(None)
+    _OUTPUTS[pipe_id] = out
+    if pipe.rank == pipe.final_stage and pipe.rank != 0 and isinstance(out, Tensor):
+        pipe.transport.send(out, 0)  # rank 0 computes the loss on the pipeline's output
 
 
 def _backward(pipe_id: int) -> None:
-    _PIPES[pipe_id].back_helper()
+    pipe = _PIPES[pipe_id]
+    out = _OUTPUTS.pop(pipe_id, None)
+    if pipe.rank == pipe.final_stage and pipe.rank != 0 and isinstance(out, Tensor) and out.requires_grad:
+        torch.autograd.backward(out, pipe.transport.recv(0))  # d(loss)/d(output) as computed on rank 0
+        pipe.back_helper()
+    else:
+        pipe.back_helper(out if isinstance(out, list) else None)
 
 
 def _call(pipe_id: int, fn: Callable[[AsyncPipe], Any]) -> Any:
@@ -48,8 +59,8 @@ class PipeBackRedirect(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx: Any, *grad: Tensor) -> Any:  # type: ignore[override]
-        ctx.wrapper.backward()
-        return grad[0], None
+        ctx.wrapper.backward(grad[0])
+        return None, None
 
 
 class PipeRPCWrapper(nn.Module):
@@ -76,16 +87,28 @@ class PipeRPCWrapper(nn.Module):
         return out + [f.wait() for f in futs]
 
     def forward(self, tensor: Tensor) -> Any:  # type: ignore[override]
-        futs = [self.rpc.rpc_async(name, _forward, args=(self.pipe_id, self.training)) for r, name in self.worker_map.items() if r != 0]
+        """Feed ``tensor`` to stage 0 (this process) and return the pipeline's output here on rank 0.  When the last
+        stage lives on another worker its output is shipped back, and back-propagating through the returned tensor
+        runs every worker's share of backward (:class:`PipeBackRedirect`)."""
+        futs = [self.rpc.rpc_async(name, _forward, args=(self.pipe_id, self.training, torch.is_grad_enabled())) for r, name in self.worker_map.items() if r != 0]
         out = self.model(tensor)
         self._pending = futs
-        return out
+        self._stage0_outputs = out if isinstance(out, list) else None
+        if self.model.final_stage == 0 or self.model.partition is None:
+            return out
+        remote = self.model.transport.recv(self.model.final_stage)
+        if remote.requires_grad and torch.is_grad_enabled():
+            return PipeBackRedirect.apply(remote, self)
+        return remote.detach()
 
-    def backward(self) -> None:
-        """Run backward on every non-final stage (call after the final stage's ``loss.backward()``)."""
+    def backward(self, output_grad: Optional[Tensor] = None) -> None:
+        """Run backward on every stage.  Called by :class:`PipeBackRedirect` with the gradient of the output; call it
+        directly (no argument) after ``loss.backward()`` when the last stage is this process."""
         for f in getattr(self, "_pending", []):
             f.wait()
+        if output_grad is not None:
+            self.model.transport.send(output_grad, self.model.final_stage)
         futs = [self.rpc.rpc_async(name, _backward, args=(self.pipe_id,)) for r, name in self.worker_map.items() if r != 0]
-        self.model.back_helper()
+        self.model.back_helper(self._stage0_outputs)
         for f in futs:
             f.wait()
