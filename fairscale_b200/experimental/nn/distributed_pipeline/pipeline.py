@@ -26,6 +26,8 @@ class DistributedPipeline(nn.Module):
     worker; train with ``torch.distributed.autograd`` and ``DistributedOptimizer(parameter_rrefs())``.
     """
 
+    DataConsumer = DataConsumer  # the edge record type, reachable from the class as in the reference
+
     @dataclass
     class Partition:
         nodes: List[Node]

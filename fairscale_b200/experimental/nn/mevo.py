@@ -194,6 +194,19 @@ class MemoryEfficientVocabOutput(nn.Module):
         self.scale = scale
         self.trigger = BackwardTrigger(self.proj_weight)
 
+    def get_target_nlprob(self, i: torch.Tensor, w: torch.Tensor, target: torch.Tensor, debase_max: torch.Tensor,
+                          exp_sums: torch.Tensor) -> torch.Tensor:
+        """Summed negative log-probability of the targets from already known softmax statistics: ``debase_max`` is the
+        row maximum of the logits and ``exp_sums`` the row sum of ``exp(logit - max)`` (parity:
+        fairscale/experimental/nn/mevo.py:576-586; the single-pass loss above does not need it)."""
+        score = (i.float() * w.float()[target]).sum(dim=1)
+        if self.scale is not None:
+            score = self.scale * (score - self.margin)
+        prob = (score - debase_max).exp() / exp_sums
+        if self.log_softmax:
+            prob = prob.log()
+        return -prob.sum()
+
     def eval_forward(self, input: torch.Tensor) -> torch.Tensor:
         """Plain logits (no target given at evaluation time)."""
         return torch.matmul(input, self.proj_weight.T)

@@ -151,6 +151,37 @@ class AsyncPipe(nn.Module):
         self.pipeline = AsyncPipeline(mine, self.group, self.rank, self.transport)
         self._outputs = []
 
+    def instantiate_partition(self, module: Union[nn.Sequential, List[LazyModule]], balance: List[int], group: Any = None) -> List[ModuleWrapper]:
+        """This rank's layers as :class:`ModuleWrapper` objects with their invocations (lazy entries are built only if
+        they live here).  ``AsyncPipe`` calls the planner itself when it meets a shared layer; the method is public for
+        code that wants the plan (parity: fairscale/nn/pipe/async_pipe.py:224-319)."""
+        entries = list(module)
+        locations, invocations = plan_invocations(entries, balance)
+        rank = dist.get_rank(group if group is not None else self.group)
+        wrappers: dict = {}
+        for entry, loc, inv in zip(entries, locations, invocations):
+            if loc.stage != rank:
+                continue
+            if loc not in wrappers:
+                layer = entry() if isinstance(entry, LazyModule) else entry
+                wrappers[loc] = ModuleWrapper(nn.Sequential(layer), loc)
+            wrappers[loc].invocations.append(inv)
+        return [wrappers[k] for k in sorted(wrappers, key=lambda l: l.index)]
+
+    def create_pipeline(self) -> AsyncPipeline:
+        """The event-loop driver over this rank's layers (built on demand for a model without shared layers)."""
+        if self.pipeline is None:
+            parts = []
+            if self.partition is not None:
+                lo = sum(self.balance[: self.rank])
+                n_total = sum(self.balance)
+                loc = Location(self.rank, 0)
+                src = Location(self.rank - 1, 0) if self.rank > 0 else None
+                dst = Location(self.rank + 1, 0) if lo + len(self.partition) < n_total else None
+                parts = [ModuleWrapper(self.partition, loc, [Invocation(self.rank, loc, src, dst)])]
+            return AsyncPipeline(parts, self.group, self.rank, self.transport)
+        return self.pipeline
+
     def _forward_event_loop(self, input: Optional[TensorOrTensors]) -> Optional[TensorOrTensors]:
         assert self.pipeline is not None
         if self.partition is None:
