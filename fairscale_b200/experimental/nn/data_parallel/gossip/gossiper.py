@@ -10,11 +10,23 @@ from __future__ import annotations
 import logging
 from typing import Any, Iterator, List, Optional, Tuple
 
+from enum import Enum
+
 import torch
 import torch.distributed as dist
 
 from .graph_manager import GraphManager
 from .mixing_manager import MixingManager, UniformMixing
+
+
+class dist_backend(str, Enum):
+    """Names of the process-group backends the gossip code distinguishes."""
+
+    UNDEFINED = "undefined"
+    TCP = "tcp"
+    MPI = "mpi"
+    GLOO = "gloo"
+    NCCL = "nccl"
 
 
 class Gossiper:

@@ -18,6 +18,13 @@ Device = Union[torch.device, int, str]
 MOVING_DENIED = TypeError("denied to move parameters and buffers, because DistributedPipeline should manage device placement")
 
 
+def check_pytorch_version() -> None:
+    from ....internal.version import torch_version
+
+    if torch_version() < (1, 8, 0):
+        raise Exception("DistributedPipeline requires PyTorch version 1.8 or higher")
+
+
 class DistributedPipeline(nn.Module):
     """GPipe-style synchronous pipeline over modules that live on RPC workers.
 

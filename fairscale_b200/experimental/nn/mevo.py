@@ -146,6 +146,75 @@ class _TiledVocabNll(torch.autograd.Function):
                 torch.zeros(1, dtype=w.dtype, device=w.device) if has_trigger else None, None, None, None, None)
 
 
+def _tile_scores(i: torch.Tensor, w: torch.Tensor, tgt: torch.Tensor, w_idx: int, kernel_obj: Any) -> torch.Tensor:
+    """Logits of one vocab tile: plain ``i @ w.T``, or the LMCL form while the module has a ``scale``."""
+    if kernel_obj.scale is None:
+        return torch.matmul(i, w.T)
+    return lmcl_matmul(i, w, tgt, w_idx, kernel_obj.margin, kernel_obj.scale)
+
+
+def _target_scores(i: torch.Tensor, w: torch.Tensor, target: torch.Tensor, kernel_obj: Any) -> torch.Tensor:
+    if kernel_obj.scale is None:
+        return (i.float() * w.float()[target]).sum(dim=1)
+    cos = (F.normalize(i.float(), dim=1) * F.normalize(w.float(), dim=1)[target]).sum(dim=1)
+    return kernel_obj.scale * (cos - kernel_obj.margin)
+
+
+class GetMaxFunction(torch.autograd.Function):
+    """Row maximum of ``i @ w.T`` (no gradient): the first of the three passes of the reference's formulation
+    (fairscale/experimental/nn/mevo.py:201-263).  ``MemoryEfficientVocabOutput`` here needs a single pass
+    (:class:`_TiledVocabNll`); the three functions remain for code that composes the loss itself."""
+
+    @staticmethod
+    def forward(ctx: Any, i: torch.Tensor, w: torch.Tensor, tgt: torch.Tensor, kernel_obj: Any, w_idx: int = 0) -> torch.Tensor:  # type: ignore[override]
+        return _tile_scores(i, w, tgt, w_idx, kernel_obj).float().max(dim=1).values
+
+    @staticmethod
+    def backward(ctx: Any, *grad: Any) -> Any:  # type: ignore[override]
+        return None, None, None, None, None  # the maximum only stabilises the exponentials: it carries no gradient
+
+
+class GetSumFunction(torch.autograd.Function):
+    """``sum_v exp(logit_v - maxs)`` per token, with the gradient recomputed from ``i`` and ``w`` in backward instead of
+    keeping the ``[tokens, vocab]`` logits (parity: fairscale/experimental/nn/mevo.py:266-354)."""
+
+    @staticmethod
+    def forward(ctx: Any, i: torch.Tensor, w: torch.Tensor, tgt: torch.Tensor, maxs: torch.Tensor, kernel_obj: Any, w_idx: int = 0) -> torch.Tensor:  # type: ignore[override]
+        ctx.save_for_backward(i, w, tgt, maxs)
+        ctx.kernel_obj, ctx.w_idx = kernel_obj, w_idx
+        logits = _tile_scores(i, w, tgt, w_idx, kernel_obj).float()
+        return (logits - maxs.reshape(-1, 1)).exp().sum(dim=1)
+
+    @staticmethod
+    def backward(ctx: Any, *grad: Any) -> Any:  # type: ignore[override]
+        i, w, tgt, maxs = ctx.saved_tensors
+        with torch.enable_grad():
+            i2, w2 = i.detach().requires_grad_(), w.detach().requires_grad_()
+            logits = _tile_scores(i2, w2, tgt, ctx.w_idx, ctx.kernel_obj).float()
+            out = (logits - maxs.reshape(-1, 1)).exp().sum(dim=1)
+            gi, gw = torch.autograd.grad(out, (i2, w2), grad[0])
+        return gi, gw, None, None, None, None
+
+
+class TargetScoreFunction(torch.autograd.Function):
+    """Logit of each token's target class, ``(i * w[target]).sum(1)`` with the LMCL margin / scale applied
+    (parity: fairscale/experimental/nn/mevo.py:357-445)."""
+
+    @staticmethod
+    def forward(ctx: Any, i: torch.Tensor, w: torch.Tensor, target: torch.Tensor, kernel_obj: Any) -> torch.Tensor:  # type: ignore[override]
+        ctx.save_for_backward(i, w, target)
+        ctx.kernel_obj = kernel_obj
+        return _target_scores(i, w, target, kernel_obj)
+
+    @staticmethod
+    def backward(ctx: Any, *grad: Any) -> Any:  # type: ignore[override]
+        i, w, target = ctx.saved_tensors
+        with torch.enable_grad():
+            i2, w2 = i.detach().requires_grad_(), w.detach().requires_grad_()
+            gi, gw = torch.autograd.grad(_target_scores(i2, w2, target, ctx.kernel_obj), (i2, w2), grad[0].float())
+        return gi, gw, None, None
+
+
 class BackwardTriggerFn(torch.autograd.Function):
     """Pass the weight through and tie a tiny trigger parameter into the graph (it receives a zero gradient)."""
 
@@ -199,10 +268,7 @@ class MemoryEfficientVocabOutput(nn.Module):
         """Summed negative log-probability of the targets from already known softmax statistics: ``debase_max`` is the
         row maximum of the logits and ``exp_sums`` the row sum of ``exp(logit - max)`` (parity:
         fairscale/experimental/nn/mevo.py:576-586; the single-pass loss above does not need it)."""
-        score = (i.float() * w.float()[target]).sum(dim=1)
-        if self.scale is not None:
-            score = self.scale * (score - self.margin)
-        prob = (score - debase_max).exp() / exp_sums
+        prob = (_target_scores(i, w, target, self) - debase_max).exp() / exp_sums
         if self.log_softmax:
             prob = prob.log()
         return -prob.sum()

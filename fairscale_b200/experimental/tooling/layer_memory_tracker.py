@@ -18,6 +18,8 @@ from functools import lru_cache
 import json
 from typing import Any, Callable, Dict, List, NamedTuple, Optional, Sequence, Set, Tuple, Union
 
+from contextlib import contextmanager
+
 import torch
 from torch import nn
 
@@ -356,3 +358,20 @@ def compare_memory_traces_in_plot(memory_traces_by_job: Dict[str, List[LayerMemo
     fig.savefig(buf, format="png")
     plt.close(fig)
     return buf.getvalue()
+
+
+@contextmanager
+def null_context() -> Iterator[None]:
+    yield
+
+
+def matplotlib_figure_to_image(fig: Any) -> Any:
+    """Render a matplotlib figure to an RGB ``PIL.Image`` (for saving a plot of the traces)."""
+    import io
+
+    from PIL import Image
+
+    buf = io.BytesIO()
+    fig.savefig(buf)
+    buf.seek(0)
+    return Image.open(buf).convert("RGB")

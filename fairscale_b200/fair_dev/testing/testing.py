@@ -383,6 +383,65 @@ def get_cycles_per_ms() -> float:
     return sum(core) / len(core)
 
 
+def in_circle_ci() -> bool:
+    """True on the reference project's CI machines (kept so ported test code keeps working)."""
+    return os.path.exists("/home/circleci")
+
+
+def skip_a_test_if_in_CI() -> None:
+    if in_circle_ci():
+        import pytest
+
+        pytest.skip("Sometimes a CI test failure is not reproducible locally, we skip them")
+
+
+def torch_cuda_version(compiled: bool = False) -> Tuple[int, ...]:
+    """CUDA version torch was built with (``compiled=True``) or the one the driver reports (needs a GPU)."""
+    if compiled or not torch.cuda.is_available():
+        numbering = (torch.version.cuda or "0.0").split(".")[:2]
+    else:
+        import subprocess
+
+        out = subprocess.check_output(["nvidia-smi"]).decode("utf-8")
+        found = [line.split("CUDA Version:")[1].split()[0] for line in out.splitlines() if "CUDA Version:" in line]
+        numbering = (found[0] if found else "0.0").split(".")[:2]
+    return tuple(int(n) for n in numbering)
+
+
+def test_runner(rank: int, test_func: Callable, deterministic: bool = False, *args: Any, **kwargs: Any) -> None:
+    """Entry of a spawned test process: optionally fix the seeds, then call ``test_func(rank, ...)``."""
+    if deterministic:
+        torch.backends.cudnn.deterministic = True
+        torch.backends.cudnn.benchmark = False
+        torch.manual_seed(1357)
+    test_func(rank, *args, **kwargs)
+
+
+test_runner.__test__ = False  # type: ignore[attr-defined]  # a helper, not a pytest test
+
+
+def worker_process(rank: int, world_size: int, filename: str, filename_rpc: str, func: Callable, args: Any, error_queue: Any) -> None:
+    """Main of a process started by a spawn helper: bring up torch.distributed (and RPC), one model-parallel group of
+    size 1 with ``world_size`` pipeline stages, run ``func(*args)``, tear down; exceptions travel through ``error_queue``."""
+    if not dist_init(rank, world_size, filename, filename_rpc):
+        teardown()
+        return
+    from ...nn.model_parallel import initialize_model_parallel
+
+    initialize_model_parallel(1, world_size)
+    try:
+        func(*args)
+        teardown()
+    except BaseException as e:  # noqa: B902
+        teardown()
+        import pytest
+
+        if isinstance(e, pytest.skip.Exception):
+            error_queue.put(str(e))
+        else:
+            raise
+
+
 def gpu_delay(ms: float, stream: Optional[Any] = None) -> None:
     """Keep ``stream`` (default: the current one) busy for ``ms`` milliseconds with the library's delay kernel.
 

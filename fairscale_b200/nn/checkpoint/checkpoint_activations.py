@@ -163,6 +163,21 @@ class _HostParking:
         return dev
 
 
+def is_autocast_enabled() -> bool:
+    """``torch.is_autocast_enabled()`` (the reference wraps it for very old torch versions)."""
+    return torch.is_autocast_enabled()
+
+
+@contextmanager
+def autocast(enabled: bool) -> Generator:
+    """CUDA autocast when ``enabled``, nothing otherwise (used to replay the forward's autocast state in recomputation)."""
+    if enabled:
+        with torch.autocast("cuda", enabled=True):
+            yield
+    else:
+        yield
+
+
 class CheckpointFunction(torch.autograd.Function):
     """Autograd node that runs ``run_function`` without grad and replays it in backward.
 

@@ -10,6 +10,8 @@ computes micro-batch *i+1* while micro-batch *i* is on the wire.
 from __future__ import annotations
 
 import logging
+from collections import OrderedDict
+from dataclasses import dataclass, field
 from typing import Any, Iterable, List, Optional, Sequence, Tuple, Union
 
 import torch
@@ -39,6 +41,32 @@ class _RecvBoundary(torch.autograd.Function):
     def backward(ctx: Any, grad: Tensor):  # type: ignore[override]
         ctx.transport.send(grad, ctx.prev_rank)
         return grad, None, None
+
+
+def check_balance(module: Union[nn.Sequential, List[LazyModule]], balance: Sequence[int]) -> None:
+    if len(module) != sum(balance):
+        raise ValueError(f"module and sum of balance have different length (module: {len(module)}, sum of balance: {sum(balance)})")
+    if any(x <= 0 for x in balance):
+        raise ValueError(f"all balance numbers must be positive integer (balance: {list(balance)})")
+
+
+def verify_module(module: Union[nn.Sequential, List[LazyModule]]) -> None:
+    """The reference refuses a layer object that occurs twice in a plain :class:`Pipe`; ``AsyncPipe`` here accepts it and
+    switches to the event-loop schedule, so this check only serves callers that want the strict behaviour."""
+    if len(set(map(id, module))) != len(module):
+        raise ValueError("module with duplicate children is not supported")
+
+
+@dataclass
+class PartitionInfo:
+    """Layers of one location (name -> module) and the invocations that run them."""
+
+    location: Location
+    modules: "OrderedDict[str, nn.Module]"
+    invocations: List[Invocation] = field(default_factory=list)
+
+    def __len__(self) -> int:
+        return len(self.modules)
 
 
 def plan_invocations(layers: Sequence[Any], balance: Sequence[int]) -> Tuple[List[Location], List[Invocation]]:

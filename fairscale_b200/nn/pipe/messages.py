@@ -21,7 +21,30 @@ _DTYPES = [torch.float32, torch.float16, torch.bfloat16, torch.int64, torch.int3
 _HEADER = 10  # ndim, dtype, requires_grad, up to 7 dims
 
 
-class SendRecvTransport:
+def to_input_device(tensors: Any, input_device: Optional[torch.device]) -> Any:
+    """Move a tuple of tensors to ``input_device`` (no-op when it is None)."""
+    if input_device is None:
+        return tensors
+    return tuple(t.to(input_device) for t in tensors)
+
+
+class Transport:
+    """Interface of a stage-to-stage tensor transport: ``send(tensor, dst_rank)``, ``recv(src_rank) -> tensor`` (blocking,
+    messages of one pair arrive in the order they were sent) and ``flush()`` (wait for outstanding sends)."""
+
+    device: torch.device
+
+    def send(self, t: Tensor, dst: int) -> None:
+        raise NotImplementedError
+
+    def recv(self, src: int) -> Tensor:
+        raise NotImplementedError
+
+    def flush(self) -> None:
+        raise NotImplementedError
+
+
+class SendRecvTransport(Transport):
     """Blocking-receive / async-send tensor transport for one pipeline group."""
 
     def __init__(self, group: Any, device: torch.device):
@@ -85,7 +108,7 @@ def rpc_push_queue(channel: int, src: int, seq: int, payload: Tensor, requires_g
     _rpc_queue(channel, src).put((seq, payload, requires_grad))
 
 
-class RpcTransport:
+class RpcTransport(Transport):
     """``send`` / ``recv`` / ``flush`` over ``torch.distributed.rpc``.
 
     Args:
@@ -147,3 +170,14 @@ def get_transport(group: Any, device: torch.device, **rpc_kwargs: Any) -> Any:
     if os.environ.get("FORCE_RPC", "").lower() in ("1", "true", "yes"):
         return RpcTransport(dist.get_rank(group), device, **rpc_kwargs)
     return SendRecvTransport(group, device)
+
+
+def MakeTransport(use_rpc: bool, worker_map: Optional[Dict[int, str]], input_device: Optional[torch.device], group: Any = None) -> Transport:
+    """Explicit choice of transport (parity: fairscale/nn/pipe/messages.py:50-58): RPC needs the rank -> worker name map."""
+    device = input_device if input_device is not None else torch.device("cpu")
+    if use_rpc:
+        if worker_map is None:
+            raise ValueError("'RpcTransport' requires 'worker_map' to be set")
+        names = dict(worker_map)
+        return RpcTransport(dist.get_rank(group), device, worker_name=lambda r: names[r])
+    return SendRecvTransport(group if group is not None else dist.group.WORLD, device)

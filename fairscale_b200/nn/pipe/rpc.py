@@ -6,6 +6,7 @@ batch and to run its share of backward; tensors travel between stages over p2p a
 
 from __future__ import annotations
 
+import contextlib
 from typing import Any, Callable, Dict, List, Optional
 
 import torch
@@ -13,6 +14,31 @@ import torch.distributed as dist
 from torch import Tensor, nn
 
 from .async_pipe import AsyncPipe
+
+def set_device_based_on_group(group: Any = None) -> None:
+    """One GPU per rank of the node: global rank modulo the number of visible devices."""
+    torch.cuda.set_device(dist.get_rank() % torch.cuda.device_count())
+
+
+def get_shapes(tensor: Any) -> Any:
+    return tensor.shape if isinstance(tensor, Tensor) else [t.shape for t in tensor]
+
+
+def get_dtype(tensor: Any) -> Any:
+    return tensor.dtype if isinstance(tensor, Tensor) else [t.dtype for t in tensor]
+
+
+def get_global_ranks_from_group(group: Any) -> List[int]:
+    return [dist.get_global_rank(group, r) for r in range(dist.get_world_size(group))]
+
+
+def callback_with_model(callback: Callable[[Any, AsyncPipe], None], ctx: Any, pipe_id: int = 0) -> None:
+    """Run ``callback(ctx, model)`` on this worker's stage with the device of its group selected."""
+    if torch.cuda.is_available():
+        set_device_based_on_group()
+    with _PIPES[pipe_id].lock if hasattr(_PIPES[pipe_id], "lock") else contextlib.nullcontext():
+        callback(ctx, _PIPES[pipe_id])
+
 
 _PIPES: Dict[int, AsyncPipe] = {}
 _OUTPUTS: Dict[int, Any] = {}  # what the last forward returned on this worker

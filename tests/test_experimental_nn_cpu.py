@@ -155,3 +155,25 @@ def test_dynamic_loss_scaler():
     with pytest.raises(FloatingPointError):
         tiny.step(opt)
     assert scaler.state_dict() == {"loss_scale": 4.0}
+
+
+@pytest.mark.parametrize("scale", [None, 8.0])
+def test_mevo_three_pass_functions_compose_to_the_fused_loss(scale):
+    """GetMax / GetSum / TargetScore (the reference's three passes) give the same loss and gradients as the single pass."""
+    from fairscale_b200.experimental.nn.mevo import GetMaxFunction, GetSumFunction, MemoryEfficientVocabOutput, TargetScoreFunction
+
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.randn(40, 8))
+    k = MemoryEfficientVocabOutput(w, tile_factor=2, scale=scale)
+    x = torch.randn(6, 8, requires_grad=True)
+    t = torch.randint(0, 40, (6,))
+    mx = GetMaxFunction.apply(x, w, t, k)
+    sm = GetSumFunction.apply(x, w, t, mx, k)
+    loss = -((TargetScoreFunction.apply(x, w, t, k) - mx) - sm.log()).sum()
+    ref = k(x, t)
+    torch.testing.assert_close(loss, ref, atol=1e-3, rtol=1e-4)
+    torch.testing.assert_close(k.get_target_nlprob(x, w, t, mx, sm), ref, atol=1e-3, rtol=1e-4)
+    gx, gw = torch.autograd.grad(loss, (x, w))
+    rx, rw = torch.autograd.grad(ref, (x, w))
+    torch.testing.assert_close(gx, rx, atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(gw, rw, atol=1e-4, rtol=1e-4)
