@@ -67,6 +67,11 @@ class CudaEventRecorder(EventRecorder):
         return "\n".join(lines) + "\n"
 
     @classmethod
+    def get_all_timings(cls) -> str:
+        """Statistics of every timing recorded since the process started."""
+        return cls.get_common_timings(cls.all_event_recorders, "All timings")
+
+    @classmethod
     def get_timings(cls) -> str:
         """Report since the last ``reset()`` followed by the report over the whole run."""
         out = cls.get_common_timings(cls.event_recorders, "Timings since last reset")

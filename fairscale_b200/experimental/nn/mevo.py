@@ -65,6 +65,12 @@ class BaselineSoftmax(nn.Module):
         logits = logits - self.margin * F.one_hot(target, logits.shape[1]).to(logits.dtype)
         return logits * self.scale
 
+    def lmcl_pre_softmax(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        """Large-margin cosine logits: normalised features times normalised class weights, the margin taken off the
+        target column, times ``scale``."""
+        assert self.scale is not None, "LMCL needs a scale"
+        return self._logits(input, target)
+
     def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
         input, target = _reshape_inputs(input, target)
         x = self._logits(input, target)

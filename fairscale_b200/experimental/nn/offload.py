@@ -83,6 +83,11 @@ class ModelShard(nn.Module):
         self.model_shard.train(mode)
         return self
 
+    def to_device(self) -> None:
+        """Bring the slice onto the compute device and wait for it (the blocking form of :meth:`forward_load`)."""
+        self.forward_load(non_blocking=False)
+        self.use()
+
     @property
     def loaded(self) -> bool:
         return self._dev is not None

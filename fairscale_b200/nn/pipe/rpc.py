@@ -107,6 +107,11 @@ class PipeRPCWrapper(nn.Module):
             f.wait()
         self.model = _PIPES[self.pipe_id]
 
+    @property
+    def final_stage(self) -> int:
+        """Group rank of the stage that produces the pipeline's output."""
+        return self.model.final_stage
+
     def foreach_worker(self, callback: Callable[[AsyncPipe], Any], include_self: bool = False) -> List[Any]:
         futs = [self.rpc.rpc_async(name, _call, args=(self.pipe_id, callback)) for r, name in self.worker_map.items() if r != 0]
         out = [callback(self.model)] if include_self else []

@@ -29,6 +29,13 @@ class SkipLayout:
             if prev_j != next_j:
                 yield prev_j, ns, name
 
+    def copy_policy_by_src(self, prev_j: int) -> Iterable[Tuple[int, Namespace, str]]:
+        """Skip tensors stashed in partition ``prev_j`` that must be copied to a later partition: ``(next_j, ns, name)``,
+        sorted by destination."""
+        out = [(next_j, ns, name) for (ns, name), (src, next_j) in self.by_ns_name.items() if src == prev_j and next_j != prev_j]
+        out.sort(key=lambda e: (e[0], e[2]))
+        return iter(out)
+
     def requires_copy(self, ns: Namespace, name: str) -> bool:
         """False when stash and pop happen in the same partition (or the tensor is unknown)."""
         prev_j, next_j = self.by_ns_name.get((ns, name), (-1, -1))
