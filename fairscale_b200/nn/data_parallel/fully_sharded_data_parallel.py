@@ -835,7 +835,8 @@ class FullyShardedDataParallel(nn.Module):
         if self.move_grads_to_cpu and self.training:
             g = torch.zeros_like(p.data, device="cpu")
             p._cpu_grad = g.pin_memory() if torch.cuda.is_available() else g  # type: ignore[attr-defined]
-        if p.requires_grad and getattr(p, "_shard_bwd_hook", None) is None and not getattr(p, "_is_shared", False):
+        if p.requires_grad and getattr(p, "_shard_bwd_hook", None) is None:
+            # a parameter shared between units carries one hook, owned by whichever unit gets here first
             handle = p.register_post_accumulate_grad_hook(functools.partial(_dispatch_post_backward, p))
             p._shard_bwd_hook = (self, handle)  # type: ignore[attr-defined]
 
@@ -1023,7 +1024,7 @@ class FullyShardedDataParallel(nn.Module):
         if not torch.is_grad_enabled():
             return
         for p in self.params:
-            if p.requires_grad and getattr(p, "_shard_bwd_hook", None) is None and not getattr(p, "_is_shared", False):
+            if p.requires_grad and getattr(p, "_shard_bwd_hook", None) is None:
                 handle = p.register_post_accumulate_grad_hook(functools.partial(_dispatch_post_backward, p))
                 p._shard_bwd_hook = (self, handle)  # type: ignore[attr-defined]
 

@@ -1,6 +1,7 @@
 """FSDP behaviours beyond plain training parity (2 gloo ranks, CPU): ``apply`` on sharded weights, frozen sub-modules,
 two forwards before two backwards, a module called several times per step, nesting with ``checkpoint_wrapper``,
 ``summon_full_params`` variants, input casting under mixed precision, evaluation without gradients."""
+import pytest
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -204,3 +205,73 @@ def _summon_eval_inputs(rank, world):
 
 def test_fsdp_summon_eval_and_input_casting():
     spawn_ranks(_summon_eval_inputs, 2, (), backend="gloo")
+
+
+class _Shared(nn.Module):
+    """Four linears; l1 and l3 share the weight or the bias (each keeps one parameter of its own)."""
+
+    def __init__(self, sharing, with_fsdp=False, inner_flat=False):
+        super().__init__()
+        torch.manual_seed(2)
+        self.l0, self.l1, self.l2, self.l3 = (nn.Linear(4, 4) for _ in range(4))
+        if sharing == "weight":
+            self.l1.weight = self.l3.weight
+        elif sharing == "bias":
+            self.l1.bias = self.l3.bias
+        if with_fsdp:
+            self.l1 = FSDP(self.l1, flatten_parameters=False, **CPU)  # units that share parameters stay unflattened
+            self.l2 = FSDP(self.l2, flatten_parameters=inner_flat, **CPU)
+            self.l3 = FSDP(self.l3, flatten_parameters=False, **CPU)
+            if sharing == "weight":
+                self.l3.append_shared_param(self.l1.module.weight)
+            elif sharing == "bias":
+                self.l3.append_shared_param(self.l1.module.bias)
+
+    def forward(self, x):
+        return self.l3(self.l2(self.l1(self.l0(x))))
+
+
+def _shared_weights(rank, world, sharing, inner_flat):
+    ref = nn.parallel.DistributedDataParallel(_Shared(sharing))
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    model = FSDP(_Shared(sharing, with_fsdp=True, inner_flat=inner_flat), flatten_parameters=False, **CPU)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    for s in range(3):
+        for m, o in ((ref, ref_opt), (model, opt)):
+            o.zero_grad()
+            m(_x(rank, s, d=4)).pow(2).mean().backward()
+            o.step()
+    full, ref_sd = model.state_dict(), ref.module.state_dict()
+    assert set(full) == set(ref_sd)
+    for k in ref_sd:
+        torch.testing.assert_close(full[k], ref_sd[k], atol=1e-6, rtol=1e-5)
+    if sharing == "weight":
+        torch.testing.assert_close(full["l1.weight"], full["l3.weight"])
+
+
+@pytest.mark.parametrize("sharing,inner_flat", [("weight", False), ("bias", True), (None, True)])
+def test_fsdp_units_sharing_a_parameter(sharing, inner_flat):
+    spawn_ranks(_shared_weights, 2, (sharing, inner_flat), backend="gloo")
+
+
+def _rewrap(rank, world):
+    # wrap, train, take the bare module back out, wrap it again with other settings: the weights carry over
+    inner = _mlp()
+    first = FSDP(inner, flatten_parameters=True, **CPU)
+    opt = torch.optim.SGD(first.parameters(), lr=0.1)
+    first(_x(rank, 0)).pow(2).mean().backward()
+    opt.step()
+    trained = first.state_dict()
+    with first.summon_full_params():
+        bare = _mlp()
+        bare.load_state_dict(first.module.state_dict() if not hasattr(first.module, "module") else first.module.module.state_dict())
+    second = FSDP(bare, flatten_parameters=False, reshard_after_forward=False, **CPU)
+    again = second.state_dict()
+    for k in trained:
+        torch.testing.assert_close(again[k], trained[k])
+    second(_x(rank, 1)).pow(2).mean().backward()
+    assert all(p.grad is not None for p in second.params)
+
+
+def test_fsdp_wrap_unwrap_wrap_again():
+    spawn_ranks(_rewrap, 2, (), backend="gloo")
