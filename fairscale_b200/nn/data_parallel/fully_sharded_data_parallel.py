@@ -944,9 +944,15 @@ class FullyShardedDataParallel(nn.Module):
                 and not nxt.has_full_params
                 and nxt._is_root is False
                 and hasattr(nxt.params[0] if nxt.params else None, "_fp32_shard")
+                and not nxt._touches_shared_params()
             ):
                 nxt._rebuild_full_params(wait=False)
                 nxt._use_fp32_param_shard()
+
+    def _touches_shared_params(self) -> bool:
+        """A parameter shared with another unit may be in use there right now: a prefetch must not re-point its
+        ``.data`` (the prefetch ends by switching the unit back to its shards)."""
+        return self._has_shared_params or any(getattr(p, "_is_shared", False) for p in self.params)
 
     def _prefetch_prev_unit(self) -> None:
         """Backward runs the units in reverse forward order: gather the preceding unit's parameters while
@@ -971,6 +977,7 @@ class FullyShardedDataParallel(nn.Module):
             and prev.params
             and hasattr(prev.params[0], "_fp32_shard")
             and any(p.requires_grad for p in prev.params)
+            and not prev._touches_shared_params()
         ):
             prev._rebuild_full_params(wait=False)
             prev._use_fp32_param_shard()

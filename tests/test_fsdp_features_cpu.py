@@ -275,3 +275,52 @@ def _rewrap(rank, world):
 
 def test_fsdp_wrap_unwrap_wrap_again():
     spawn_ranks(_rewrap, 2, (), backend="gloo")
+
+
+class _TiedVocab(nn.Module):
+    """Embedding and a memory-efficient vocabulary output layer that share one weight, each in its own FSDP unit."""
+
+    def __init__(self, with_fsdp):
+        super().__init__()
+        from fairscale_b200.experimental.nn import MEVO
+
+        torch.manual_seed(4)
+        self.l0 = nn.Embedding(12, 8)
+        nn.init.uniform_(self.l0.weight, -0.1, 0.1)
+        self.l1 = MEVO(self.l0.weight, tile_factor=2, reduction="sum")
+        self.middle = nn.Linear(8, 8)
+        self.ln1, self.ln2 = nn.LayerNorm(8), nn.LayerNorm(8)
+        if with_fsdp:
+            self.l0 = FSDP(self.l0, flatten_parameters=False, **CPU)
+            self.l1 = FSDP(self.l1, flatten_parameters=False, **CPU)
+            self.l1.append_shared_param(self.l0.module.weight)
+
+    def forward(self, tokens):
+        target = (tokens + 1) % 12
+        x = self.ln2(self.middle(self.ln1(self.l0(tokens))))
+        return self.l1(x, target)
+
+
+def _tied_vocab(rank, world):
+    ref = nn.parallel.DistributedDataParallel(_TiedVocab(False))
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    model = FSDP(_TiedVocab(True), flatten_parameters=False, **CPU)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(rank)
+    tokens = torch.randint(0, 12, (3, 5), generator=g)
+    for _ in range(3):
+        losses = []
+        for m, o in ((ref, ref_opt), (model, opt)):
+            o.zero_grad()
+            loss = m(tokens)
+            loss.backward()
+            o.step()
+            losses.append(loss.item())
+        assert abs(losses[0] - losses[1]) < 1e-4 * max(1.0, abs(losses[0]))
+    full, ref_sd = model.state_dict(), ref.module.state_dict()
+    torch.testing.assert_close(full["l0.weight"], ref_sd["l0.weight"], atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(full["middle.weight"], ref_sd["middle.weight"], atol=1e-5, rtol=1e-4)
+
+
+def test_fsdp_embedding_and_mevo_output_share_a_weight():
+    spawn_ranks(_tied_vocab, 2, (), backend="gloo")
