@@ -324,3 +324,71 @@ def _tied_vocab(rank, world):
 
 def test_fsdp_embedding_and_mevo_output_share_a_weight():
     spawn_ranks(_tied_vocab, 2, (), backend="gloo")
+
+
+class _TwoHeads(nn.Module):
+    """Returns a tuple that contains one tensor twice plus a second head: the pre-backward work must run once."""
+
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(6)
+        self.body = nn.Linear(8, 8)
+        self.head = nn.Linear(8, 2)
+
+    def forward(self, x):
+        h = torch.tanh(self.body(x))
+        return h, h, self.head(h)
+
+
+def _outputs_and_reuse(rank, world):
+    # (a) several outputs, one of them twice, losses on all of them
+    ref = nn.parallel.DistributedDataParallel(_TwoHeads())
+    model = FSDP(_TwoHeads(), **CPU)
+    calls = []
+    orig = model._prep_grads_for_backward
+    model._prep_grads_for_backward = lambda: (calls.append(1), orig())[1]
+    for m in (ref, model):
+        a, b, c = m(_x(rank, 0))
+        (a.sum() + 2 * b.sum() + c.pow(2).sum()).backward()
+    assert len(calls) == 1  # one preparation of the gradients per backward, however many outputs carry a hook
+    flat_ref = torch.cat([p.grad.reshape(-1) for p in ref.module.parameters()])
+    g = model.params[0].grad
+    parts = [torch.zeros_like(g) for _ in range(world)]
+    dist.all_gather(parts, g)
+    torch.testing.assert_close(torch.cat(parts)[: flat_ref.numel()], flat_ref, atol=1e-6, rtol=1e-5)
+
+    # (b) one checkpointed FSDP unit called twice inside a forward
+    torch.manual_seed(7)
+    blk = nn.Sequential(nn.Linear(8, 8), nn.Tanh())
+    tail = nn.Linear(8, 3)
+    import copy
+
+    ref_blk, ref_tail = copy.deepcopy(blk), copy.deepcopy(tail)
+
+    class Twice(nn.Module):
+        def __init__(self, b, t):
+            super().__init__()
+            self.b, self.t = b, t
+
+        def forward(self, x):
+            return self.t(self.b(self.b(x)))
+
+    ref2 = nn.parallel.DistributedDataParallel(Twice(ref_blk, ref_tail))
+    model2 = FSDP(Twice(FSDP(checkpoint_wrapper(blk), **CPU), tail), **CPU)
+    for m in (ref2, model2):
+        m(_x(rank, 1).requires_grad_()).pow(2).mean().backward()
+    inner = model2.module.b
+    gref = torch.cat([p.grad.reshape(-1) for p in ref_blk.parameters()])
+    g = inner.params[0].grad
+    parts = [torch.zeros_like(g) for _ in range(world)]
+    dist.all_gather(parts, g)
+    torch.testing.assert_close(torch.cat(parts)[: gref.numel()], gref, atol=1e-6, rtol=1e-5)
+
+    # (c) full state dict only on rank 0
+    model3 = FSDP(_mlp(), state_dict_on_rank_0_only=True, **CPU)
+    sd = model3.state_dict()
+    assert (len(sd) > 0) == (rank == 0)
+
+
+def test_fsdp_multiple_outputs_module_reuse_and_rank0_state_dict():
+    spawn_ranks(_outputs_and_reuse, 2, (), backend="gloo")
