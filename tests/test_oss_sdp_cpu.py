@@ -156,3 +156,59 @@ def _uneven(rank, world):
 
 def test_oss_sdp_three_ranks():
     spawn_ranks(_uneven, 3, (), backend="gloo")
+
+
+def _two_optimizers_manual_reduce_buffers(rank, world):
+    # two sharded optimizers over disjoint halves of one module, as one ShardedDataParallel
+    torch.manual_seed(0)
+    base = nn.Sequential(nn.Linear(6, 8), nn.BatchNorm1d(8), nn.Tanh(), nn.Linear(8, 3))
+    ref = nn.parallel.DistributedDataParallel(copy.deepcopy(base), broadcast_buffers=True)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    first = OSS(list(base[0].parameters()) + list(base[1].parameters()), optim=torch.optim.SGD, lr=0.05)
+    second = OSS(base[3].parameters(), optim=torch.optim.SGD, lr=0.05)
+    sdp = ShardedDataParallel(base, [first, second])
+    for s in range(3):
+        x, y = _batch(rank, s)
+        ref_opt.zero_grad()
+        nn.functional.mse_loss(ref(x), y).backward()
+        ref_opt.step()
+        sdp.zero_grad()
+        nn.functional.mse_loss(sdp(x), y).backward()
+        first.step()
+        second.step()
+    for a, b in zip(ref.module.parameters(), base.parameters()):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+
+    # manual reduction after no_sync accumulation
+    sdp.zero_grad()
+    x, y = _batch(rank, 9)
+    with sdp.no_sync():
+        nn.functional.mse_loss(sdp(x), y).backward()
+    local = base[3].weight.grad.clone() if base[3].weight.grad is not None else None
+    sdp.reduce()
+    owner = second._param_to_rank[base[3].weight]
+    # every rank contributes its local gradient; the owner ends up with the mean
+    contrib = local if local is not None else torch.zeros_like(base[3].weight)
+    allg = [torch.zeros_like(contrib) for _ in range(world)]
+    dist.all_gather(allg, contrib)
+    if rank == owner:
+        torch.testing.assert_close(base[3].weight.grad, sum(allg) / world, atol=1e-6, rtol=1e-5)
+
+    # buffers: diverge on one rank, sync_buffers brings rank 0's statistics back everywhere
+    if rank == 1:
+        base[1].running_mean.add_(5.0)
+    sdp.sync_buffers(blocking=True)
+    means = [torch.zeros_like(base[1].running_mean) for _ in range(world)]
+    dist.all_gather(means, base[1].running_mean)
+    assert all(torch.equal(means[0], m) for m in means)
+
+    # evaluation forward does not touch the gradient machinery
+    sdp.eval()
+    with torch.no_grad():
+        out = sdp(x)
+    assert not out.requires_grad
+    sdp.train()
+
+
+def test_sdp_two_optimizers_manual_reduce_and_buffers():
+    spawn_ranks(_two_optimizers_manual_reduce_buffers, 2, (), backend="gloo")
