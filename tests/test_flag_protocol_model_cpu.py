@@ -110,3 +110,85 @@ def test_checker_catches_a_protocol_without_exit_barrier():
     violations, _, _ = explore(2, 2, e0=1, with_exit=False)
     kinds = {v[0] for v in violations}
     assert "overwrite before read" in kinds or "stale or early read" in kinds
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# GEMM -> reduce-scatter (``gemm_rs`` in csrc/gemm_comm_tcgen05.cu): rank r computes the chunks r+1, r+2, ..., r, writes
+# each partial chunk c != r to slot c of its own staging buffer and then raises its flag in owner c's pad; owner c waits
+# for every peer's flag and pulls that peer's slot c; an exit barrier ends the call.  Checked: a slot is only read once
+# its producer has written this call's partial, and never overwritten by the next call while its owner may still read.
+# ---------------------------------------------------------------------------------------------------------------------
+def _rs_program(world: int, rank: int, calls: int, with_exit: bool):
+    steps = []
+    for k in range(calls):
+        for i in range(1, world):
+            c = (rank + i) % world
+            steps.append(("write", k, c))           # my staging slot for chunk c
+            steps.append(("flag", k, c))            # tell owner c
+        for p in range(world):
+            if p != rank:
+                steps.append(("wait_flag", k, p))   # peer p finished my chunk
+                steps.append(("pull", k, p))        # read slot `rank` of peer p's staging buffer
+        if with_exit:
+            steps += [("sig_exit", k, p) for p in range(world)]
+            steps.append(("wait_exit", k, rank))
+    return steps
+
+
+def explore_rs(world: int, calls: int, e0: int, with_exit: bool = True):
+    progs = [_rs_program(world, r, calls, with_exit) for r in range(world)]
+    init = (e0 - 1) & MASK
+    # flags[owner][src], exit pads [dst][src], staging versions [rank][chunk]
+    start = (tuple([0] * world), tuple([init] * (world * world)), tuple([init] * (world * world)), tuple([-1] * (world * world)))
+    seen, queue = {start}, deque([start])
+    violations, deadlocks = [], 0
+    while queue:
+        pcs, flags, exit_, stage = queue.popleft()
+        moved = False
+        for r in range(world):
+            if pcs[r] == len(progs[r]):
+                continue
+            op, k, x = progs[r][pcs[r]]
+            epoch = (e0 + k) & MASK
+            n_flags, n_exit, n_stage = flags, exit_, stage
+            if op == "write":
+                if k > 0:  # owner x must be done pulling slot x of rank r for call k-1
+                    pending = [s for s in progs[x][pcs[x]:] if s == ("pull", k - 1, r)]
+                    if pending:
+                        violations.append(("overwrite before pull", r, x, k))
+                i = r * world + x
+                n_stage = stage[:i] + (k,) + stage[i + 1:]
+            elif op == "flag":
+                i = x * world + r
+                n_flags = flags[:i] + (epoch,) + flags[i + 1:]
+            elif op == "wait_flag":
+                if not _reached(flags[r * world + x], epoch):
+                    continue
+            elif op == "pull":
+                if stage[x * world + r] != k:
+                    violations.append(("pull of a stale or missing partial", r, x, k, stage[x * world + r]))
+            elif op == "sig_exit":
+                i = x * world + r
+                n_exit = exit_[:i] + (epoch,) + exit_[i + 1:]
+            elif op == "wait_exit":
+                if not all(_reached(exit_[r * world + s], epoch) for s in range(world)):
+                    continue
+            moved = True
+            nxt = (pcs[:r] + (pcs[r] + 1,) + pcs[r + 1:], n_flags, n_exit, n_stage)
+            if nxt not in seen:
+                seen.add(nxt)
+                queue.append(nxt)
+        if not moved and not all(pcs[r] == len(progs[r]) for r in range(world)):
+            deadlocks += 1
+    return violations, deadlocks, len(seen)
+
+
+@pytest.mark.parametrize("world,calls,e0", [(2, 3, 9), (3, 2, 0xFFFFFFFF)])
+def test_gemm_rs_flag_protocol(world, calls, e0):
+    violations, deadlocks, states = explore_rs(world, calls, e0)
+    assert states > 50 and violations == [] and deadlocks == 0
+
+
+def test_gemm_rs_checker_needs_the_exit_barrier():
+    violations, _, _ = explore_rs(2, 2, e0=1, with_exit=False)
+    assert any(v[0] == "overwrite before pull" or v[0].startswith("pull of a stale") for v in violations)
