@@ -72,6 +72,58 @@ class EventTimer:
         self._pairs.clear()
 
 
+class device_timer:
+    """Times a block on the device (CUDA events on the current stream; host clock without a GPU) and, in a distributed
+    job, reports the slowest rank: every multi-GPU number is a maximum over ranks, never one rank's wall clock.
+
+        with device_timer(steps=4) as t:
+            for _ in range(4): step()
+        t.ms_per_step      # identical on every rank
+
+    The block is bracketed by a barrier and a device synchronisation on both sides.
+    """
+
+    def __init__(self, steps: int = 1, group: Any = None) -> None:
+        self.steps = steps
+        self.group = group
+        self.ms = 0.0
+        self.ms_per_step = 0.0
+        self._cuda = torch.cuda.is_available()
+
+    def _fence(self) -> None:
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier(group=self.group)
+        if self._cuda:
+            torch.cuda.synchronize()
+
+    def __enter__(self) -> "device_timer":
+        self._fence()
+        if self._cuda:
+            self._a, self._b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._a.record()
+        else:
+            self._t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        import torch.distributed as dist
+
+        if self._cuda:
+            self._b.record()
+            self._b.synchronize()
+            local = float(self._a.elapsed_time(self._b))
+        else:
+            local = (time.perf_counter() - self._t0) * 1e3
+        if exc[0] is None and dist.is_available() and dist.is_initialized():
+            t = torch.tensor([local], dtype=torch.float64, device="cuda" if (self._cuda and dist.get_backend(self.group) == "nccl") else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            local = float(t.item())
+        self.ms = local
+        self.ms_per_step = local / max(self.steps, 1)
+
+
 @contextmanager
 def chrome_trace(path: str, with_cuda: bool = True) -> Iterator[Any]:
     """Profile the block with ``torch.profiler`` and write a Chrome / Perfetto trace to ``path``."""

@@ -34,3 +34,22 @@ def _worker(rank, world):
 
 def test_step_metrics_counts_fsdp_traffic():
     spawn_ranks(_worker, 2, (), backend="gloo")
+
+
+def _timer(rank, world):
+    import time
+
+    from fairscale_b200.utils.profiling import device_timer
+
+    with device_timer(steps=2) as t:
+        time.sleep(0.05 * (rank + 1))  # rank 1 is the slow one
+    assert t.ms >= 95 and abs(t.ms_per_step - t.ms / 2) < 1e-9
+    both = [None, None]
+    import torch.distributed as dist
+
+    dist.all_gather_object(both, t.ms)
+    assert both[0] == both[1]  # every rank reports the maximum
+
+
+def test_device_timer_reports_the_slowest_rank():
+    spawn_ranks(_timer, 2, (), backend="gloo")
