@@ -15,6 +15,7 @@ On CUDA bf16 inputs the local products run on the tcgen05 GEMM; with ``sequence_
 
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional
 
 import torch
@@ -263,6 +264,11 @@ class RowParallelLinear(torch.nn.Module):
             from ...parallel.fused_tp import linear_reduce_scatter
 
             return linear_reduce_scatter(x, self.weight, self.bias, get_model_parallel_group())
+        if os.environ.get("FSB200_FUSED_ROW_ALLREDUCE", "0") == "1":
+            # opt-in: fused GEMM -> reduce-scatter + all-gather of the reduced rows instead of GEMM + all-reduce
+            from ...parallel.fused_tp import linear_all_reduce
+
+            return linear_all_reduce(x, self.weight, self.bias, get_model_parallel_group())
         partial = _local_linear(x, self.weight, None)
         out = reduce_from_model_parallel_region(partial)
         return out if self.bias is None else out + self.bias

@@ -277,3 +277,46 @@ def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
     y = _LinearReduceScatter.apply(x2, weight, bias, group)
     world = comm.group_size(group)
     return y.view((lead[0] // world,) + lead[1:] + (y.shape[-1],)) if lead else y
+
+
+class _LinearAllReduce(torch.autograd.Function):
+    """``y = all_reduce(x @ w^T) + bias`` with the whole result on every rank: the API-exact output of a row-parallel
+    linear (fairscale/nn/model_parallel/layers.py:380-386).  With a workspace the reduction is the fused
+    GEMM -> reduce-scatter kernel followed by an NVLink all-gather of the reduced rows (an all-reduce is a reduce-scatter
+    plus an all-gather anyway; here the first half overlaps the tensor-core work).  Backward is the ``g`` operator's:
+    the incoming gradient is already whole on every rank, so ``dX = dY W`` and ``dW = dY^T X`` are local products."""
+
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], group: Any) -> torch.Tensor:  # type: ignore[override]
+        ws = _workspace(group, x, w)
+        world = comm.group_size(group)
+        if world > 1 and x.shape[0] % world == 0 and gemm_rs_supported(ws, x.shape[0], x.shape[1], w.shape[0]):
+            y = _all_gather_rows(gemm_rs(ws, x, w, bias), group)
+        else:
+            y = F.linear(x, w)
+            if world > 1:
+                comm.all_reduce(y, group=group)
+            if bias is not None:
+                y = y + bias
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, dy: torch.Tensor) -> Any:  # type: ignore[override]
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dy @ w if ctx.needs_input_grad[0] else None
+        dw = gemm_ops.linear_wgrad(dy, x).to(w.dtype) if ctx.needs_input_grad[1] else None
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = column_sum(dy) if _bind.use_native(dy) and dy.dtype == torch.bfloat16 else dy.sum(0)
+        return dx, dw, db, None
+
+
+def linear_all_reduce(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], group: Any = None) -> torch.Tensor:
+    """``x``: ``[tokens, ..., K_local]``; returns the fully reduced ``[tokens, ..., N]`` on every rank (the bias is added
+    once, after the reduction)."""
+    x2, lead = _flatten(x)
+    y = _LinearAllReduce.apply(x2, weight, bias, group)
+    return y.view(lead + (y.shape[-1],)) if lead else y

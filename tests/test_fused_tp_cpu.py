@@ -40,3 +40,31 @@ def _worker(rank, world):
 
 def test_sequence_parallel_linears_match_dense():
     spawn_ranks(_worker, 2, (), backend="gloo")
+
+
+def _all_reduce_worker(rank, world):
+    from fairscale_b200.parallel.fused_tp import linear_all_reduce
+
+    torch.manual_seed(0)
+    T, H, N = 8, 10, 4
+    h_full = torch.randn(T, H)
+    w = torch.randn(N, H)
+    b = torch.randn(N)
+    hs = H // world
+    hl = h_full[:, rank * hs : (rank + 1) * hs].clone().requires_grad_()
+    wl = w[:, rank * hs : (rank + 1) * hs].clone().requires_grad_()
+    bl = b.clone().requires_grad_()
+    out = linear_all_reduce(hl, wl, bl)
+    hr, wr, br = h_full.clone().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    ref = hr @ wr.t() + br
+    torch.testing.assert_close(out, ref.detach(), rtol=1e-4, atol=1e-4)
+    g = torch.randn(T, N)  # the same upstream gradient on every rank (seeded above)
+    out.backward(g)
+    ref.backward(g)
+    torch.testing.assert_close(hl.grad, hr.grad[:, rank * hs : (rank + 1) * hs], rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(wl.grad, wr.grad[:, rank * hs : (rank + 1) * hs], rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(bl.grad, br.grad, rtol=1e-4, atol=1e-4)
+
+
+def test_row_parallel_product_with_fully_reduced_output():
+    spawn_ranks(_all_reduce_worker, 2, (), backend="gloo")
