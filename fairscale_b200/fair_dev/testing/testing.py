@@ -134,7 +134,10 @@ def teardown() -> None:
         pass
 
 
-def _rank_entry(rank: int, fn: Callable, world_size: int, url: str, backend: Optional[str], args: Tuple, err_q: Any) -> None:
+def _rank_entry(rank: int, fn: Callable, world_size: int, url: str, backend: Optional[str], args: Tuple, err_q: Any,
+                env: Optional[Dict[str, str]] = None) -> None:
+    if env:
+        os.environ.update(env)  # a forkserver child starts from the server's environment, not from the caller's
     try:
         ok = dist_init(rank, world_size, url, backend=backend)
         if not ok:
@@ -148,17 +151,29 @@ def _rank_entry(rank: int, fn: Callable, world_size: int, url: str, backend: Opt
             teardown()
 
 
+def _start_context() -> Any:
+    """How rank processes are started.  With a GPU: ``spawn`` (a fresh interpreter per rank).  On CPU-only machines:
+    ``forkserver`` with torch and this package preloaded in the server, so a rank starts in a fraction of a second instead
+    of re-importing torch; the server is forked before any thread pool exists, which a plain ``fork`` of the test process
+    would not guarantee.  ``FSB_TEST_START_METHOD`` overrides the choice."""
+    method = os.environ.get("FSB_TEST_START_METHOD", "spawn" if torch.cuda.is_available() else "forkserver")
+    ctx = mp.get_context(method)
+    if method == "forkserver":
+        ctx.set_forkserver_preload(["torch", "torch.distributed", "torch.distributed.rpc", "numpy", "fairscale_b200", "fairscale_b200.nn", "fairscale_b200.optim"])
+    return ctx
+
+
 def spawn_ranks(fn: Callable, world_size: int, args: Tuple = (), backend: Optional[str] = None, timeout: float = 300.0) -> None:
     """Run ``fn(rank, world_size, *args)`` in ``world_size`` child processes with an initialised default group.
 
     Raises ``RuntimeError`` with the child's traceback if a rank fails or the run exceeds
     ``timeout`` seconds (children are then terminated by pid).
     """
-    ctx = mp.get_context("spawn")
+    ctx = _start_context()
     err_q = ctx.SimpleQueue()
     url = f"tcp://127.0.0.1:{find_free_port()}"
     procs = [
-        ctx.Process(target=_rank_entry, args=(r, fn, world_size, url, backend, args, err_q), daemon=False)
+        ctx.Process(target=_rank_entry, args=(r, fn, world_size, url, backend, args, err_q, dict(os.environ)), daemon=False)
         for r in range(world_size)
     ]
     for p in procs:
