@@ -392,3 +392,40 @@ def _outputs_and_reuse(rank, world):
 
 def test_fsdp_multiple_outputs_module_reuse_and_rank0_state_dict():
     spawn_ranks(_outputs_and_reuse, 2, (), backend="gloo")
+
+
+def _conv_bn(rank, world):
+    """A small conv net whose BatchNorm layers get their own fp32 FSDP wrappers (auto_wrap_bn); the rest trains in one
+    mixed-precision unit.  Every rank sees the same batch, so local BatchNorm statistics equal DDP's."""
+    from fairscale_b200.nn.data_parallel import auto_wrap_bn
+
+    def net():
+        torch.manual_seed(8)
+        return nn.Sequential(nn.Conv2d(2, 4, 3, padding=1), nn.BatchNorm2d(4), nn.ReLU(), nn.Conv2d(4, 4, 3, padding=1), nn.BatchNorm2d(4),
+                             nn.ReLU(), nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(4, 3))
+
+    ref = nn.parallel.DistributedDataParallel(net())
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    wrapped = auto_wrap_bn(net(), single_rank_pg=False, fsdp_config={"mixed_precision": False, "flatten_parameters": False,
+                                                                      "reshard_after_forward": False, "bucket_cap_mb": 0,
+                                                                      "compute_device": torch.device("cpu")})
+    n_bn = sum(isinstance(m, FSDP) for m in wrapped.modules())
+    assert n_bn == 2 and all(isinstance(m.module.module if hasattr(m.module, "module") else m.module, nn.BatchNorm2d)
+                             for m in wrapped.modules() if isinstance(m, FSDP))
+    model = FSDP(wrapped, **CPU)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(6, 2, 5, 5, generator=g)
+    for _ in range(3):
+        for m, o in ((ref, ref_opt), (model, opt)):
+            o.zero_grad()
+            m(x).pow(2).mean().backward()
+            o.step()
+    full, ref_sd = model.state_dict(), ref.module.state_dict()
+    assert set(full) == set(ref_sd)
+    for k in ref_sd:
+        torch.testing.assert_close(full[k].float(), ref_sd[k].float(), atol=1e-5, rtol=1e-4)
+
+
+def test_fsdp_auto_wrap_bn_conv_net():
+    spawn_ranks(_conv_bn, 2, (), backend="gloo")
