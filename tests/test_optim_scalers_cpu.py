@@ -148,3 +148,39 @@ def test_layerwise_gradient_scaler():
     scaler.step(opt)
     assert torch.equal(snap, model[0].weight)
     assert [i.scaling_factor for i in scaler.get_layer_info() if i.scale_layer] == [4096.0, 512.0, 1024.0]  # only the layer that overflowed backs off
+
+
+def _adascale_sequential(rank, world, mode):
+    """Golden gain / mean weight of a 4-layer bias-free linear stack after two steps on orthogonal inputs, for AdaScale
+    alone, AdaScale around OSS, AdaScaleWrapper building an OSS, and OSS around AdaScaleWrapper (values recorded by the
+    reference's tests/optim/test_oss_adascale.py:95-130)."""
+    from statistics import mean
+
+    model = nn.Sequential(nn.Linear(2, 3, bias=False), nn.Linear(3, 4, bias=False), nn.Linear(4, 5, bias=False), nn.Linear(5, 6, bias=False))
+    with torch.no_grad():
+        for layer, n in zip(model, (6, 12, 20, 30)):
+            layer.weight.copy_(torch.arange(n, dtype=torch.float32).reshape(layer.weight.shape) / mean(range(n)))
+    ddp = DDP(model)
+    if mode == "ada-oss":
+        optim = AdaScale(OSS(ddp.parameters(), SGD, lr=0.1))
+    elif mode == "wrapper-oss":
+        optim = AdaScaleWrapper(ddp.parameters(), optim_cls=OSS, optim=SGD, lr=0.1)
+    elif mode == "oss-wrapper":
+        optim = OSS(ddp.parameters(), AdaScaleWrapper, optim_cls=SGD, lr=0.1)
+    else:
+        optim = AdaScale(SGD(ddp.parameters(), lr=0.1))
+    for inputs in ([[1.0, 0], [0, 1.0]], [[0, 1.0], [1.0, 0]]):
+        ddp(torch.tensor(inputs[rank])).sum().backward()
+        optim.step()
+        optim.zero_grad()
+    mean_weight = mean(layer.weight.data.mean().item() for layer in model)
+    if mode == "oss-wrapper":  # every rank scales its own shard: numerically a different algorithm, only the weights are pinned
+        assert np.allclose(mean_weight, 94.93386840820312, rtol=1e-5), mean_weight
+    else:
+        assert np.allclose(optim.gain(), 1.0335265132125744, rtol=1e-6), optim.gain()
+        assert np.allclose(mean_weight, 52.92657661437988, rtol=1e-5), mean_weight
+
+
+@pytest.mark.parametrize("mode", ["none", "ada-oss", "wrapper-oss", "oss-wrapper"])
+def test_adascale_with_oss_sequential_golden(mode):
+    spawn_ranks(_adascale_sequential, 2, (mode,), backend="gloo")
