@@ -83,3 +83,40 @@ def test_repo_add_commit_status_and_get(tmp_path, capsys):
         main(["version"])
     finally:
         os.chdir(cwd)
+
+
+def _golden_cases():
+    """Fixed inputs with the SST / DST / reconstruction recorded by the reference's
+    tests/experimental/wgit/test_signal_sparsity.py:118-200 (FFT, top-k over the flattened tensor and over dim 0)."""
+    t0 = torch.arange(12).sin().reshape(4, 3).float()
+    sst0 = torch.zeros(4, 3, dtype=torch.complex64)
+    sst0[0, 2] = complex(-1.3618, -5.7650)
+    sst0[3, 1] = complex(-1.3618, 5.7650)
+    dst0 = torch.zeros(4, 3)
+    dst0[0, 0], dst0[3, 0] = 0.22696666419506072998, 0.18515183031558990479
+    rt0 = torch.tensor([[0.0, 0.71862268447875976562, 0.94558942317962646484],
+                        [0.22696666419506072998, -0.71862268447875976562, -0.94558942317962646484],
+                        [-0.22696666419506072998, 0.71862268447875976562, 0.94558942317962646484],
+                        [0.41211849451065063477, -0.71862268447875976562, -0.94558942317962646484]])
+    t1 = torch.arange(50, 62).sin().reshape(4, 3) / 100
+    sst1 = torch.zeros(4, 3, dtype=torch.complex64)
+    sst1[2] = torch.tensor([-1.81658901274204254150e-02, 1.96999348700046539307e-02, 3.94537299871444702148e-02], dtype=torch.complex64)
+    dst1 = torch.zeros(4, 3)
+    dst1[0, 0], dst1[3, 1], dst1[3, 2] = 0.00191772403195500374, 0.00187687762081623077, 0.00020225439220666885
+    rt1 = torch.tensor([[-0.00262374849990010262, 0.00492498371750116348, 0.00986343249678611755],
+                        [0.00454147253185510635, -0.00492498371750116348, -0.00986343249678611755],
+                        [-0.00454147253185510635, 0.00492498371750116348, 0.00986343249678611755],
+                        [0.00454147253185510635, -0.00304810609668493271, -0.00966117810457944870]])
+    return [(t0, sst0, dst0, rt0, None, 2), (t1, sst1, dst1, rt1, 0, 1)]
+
+
+@pytest.mark.parametrize("tensor,sst,dst,rt,dim,k", _golden_cases())
+def test_signal_sparsity_reference_golden_values(tensor, sst, dst, rt, dim, k):
+    s = SignalSparsity(sst_top_k_element=k, sst_top_k_dim=dim, dst_top_k_percent=100)
+    torch.testing.assert_close(s.dense_to_sst(tensor), sst, rtol=1e-4, atol=1e-5)
+    s = SignalSparsity(sst_top_k_element=k, sst_top_k_dim=dim, dst_top_k_element=k, dst_top_k_dim=dim)
+    lossy, got_sst, got_dst = s.lossy_compress(tensor)
+    torch.testing.assert_close(got_sst, sst, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(got_dst, dst, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(lossy, rt, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(s.sst_dst_to_dense(sst, dst), rt, rtol=1e-4, atol=1e-5)
