@@ -177,3 +177,39 @@ def test_mevo_three_pass_functions_compose_to_the_fused_loss(scale):
     rx, rw = torch.autograd.grad(ref, (x, w))
     torch.testing.assert_close(gx, rx, atol=1e-4, rtol=1e-4)
     torch.testing.assert_close(gw, rw, atol=1e-4, rtol=1e-4)
+
+
+def test_auto_shard_transformer_reference_split():
+    """A torch TransformerEncoder language model cut in two by parameter count: the reference records 5 998 600 and
+    5 785 383 parameters for the two shards (tests/experimental/nn/test_auto_shard.py:82-99)."""
+    import math
+
+    class PositionalEncoding(nn.Module):
+        def __init__(self, d_model, dropout=0.1, max_len=5000):
+            super().__init__()
+            self.dropout = nn.Dropout(p=dropout)
+            pe = torch.zeros(max_len, d_model)
+            position = torch.arange(0, max_len, dtype=torch.float).unsqueeze(1)
+            div = torch.exp(torch.arange(0, d_model, 2).float() * (-math.log(10000.0) / d_model))
+            pe[:, 0::2], pe[:, 1::2] = torch.sin(position * div), torch.cos(position * div)
+            self.register_buffer("pe", pe.unsqueeze(0).transpose(0, 1))
+
+        def forward(self, x):
+            return self.dropout(x + self.pe[: x.size(0)])
+
+    class TransformerModel(nn.Module):
+        def __init__(self, ntoken, ninp, nhead, nhid, nlayers, dropout):
+            super().__init__()
+            self.pos_encoder = PositionalEncoding(ninp, dropout)
+            self.transformer_encoder = nn.TransformerEncoder(nn.TransformerEncoderLayer(ninp, nhead, nhid, dropout), nlayers)
+            self.encoder = nn.Embedding(ntoken, ninp)
+            self.ninp = ninp
+            self.decoder = nn.Linear(ninp, ntoken)
+
+        def forward(self, *args):
+            src = self.pos_encoder(self.encoder(args[0]) * math.sqrt(self.ninp))
+            return self.decoder(self.transformer_encoder(src, args[1]))
+
+    shards = shard_model(TransformerModel(28783, 200, 2, 200, 1, 0.2))
+    assert len(shards) == 2
+    assert [sum(p.numel() for p in s.parameters()) for s in shards] == [5998600, 5785383]

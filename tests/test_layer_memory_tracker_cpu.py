@@ -46,3 +46,18 @@ def test_tracker_counts_fsdp_all_gathers():
     model(torch.randn(2, 8)).sum().backward()
     tracker.stop()
     assert len(tracker.forward_traces) >= 1
+
+
+def test_find_best_reset_points_reference_values():
+    """Numbers from the reference's tests/experimental/tooling/test_layer_memory_tracker.py:228-254."""
+    activations = [10, 8, 8, 9, 7, 7, 5, 4, 4]
+    memory, _ = find_best_reset_points(activations, num_checkpoints=0)
+    assert memory == sum(activations)
+    memory, _ = find_best_reset_points(activations, num_checkpoints=len(activations))
+    assert memory == max(activations)
+    memory, split_points = find_best_reset_points(activations, num_checkpoints=1)
+    assert memory == 35 and split_points == [4]
+    memory, split_points = find_best_reset_points(activations, num_checkpoints=2)
+    assert memory == 24
+    cuts = [0] + split_points + [len(activations)]
+    assert max(sum(activations[i:j]) for i, j in zip(cuts[:-1], cuts[1:])) == memory
