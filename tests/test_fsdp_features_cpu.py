@@ -429,3 +429,36 @@ def _conv_bn(rank, world):
 
 def test_fsdp_auto_wrap_bn_conv_net():
     spawn_ranks(_conv_bn, 2, (), backend="gloo")
+
+
+def _state_dict_properties(rank, world):
+    torch.manual_seed(9)
+    net = nn.Sequential(nn.Linear(8, 8), nn.BatchNorm1d(8), nn.Linear(8, 3))
+    model = FSDP(net, mixed_precision=True, compute_dtype=torch.bfloat16, state_dict_device=torch.device("cpu"), **CPU)
+    model(_x(rank, 0)).float().sum().backward()
+    sd = model.state_dict()
+    # full precision parameters under the bare module's names, buffers included, on the requested device
+    assert {"0.weight", "1.running_mean", "1.num_batches_tracked", "2.bias"} <= set(sd)
+    assert all(v.dtype == torch.float32 for k, v in sd.items() if v.is_floating_point())
+    assert all(v.device.type == "cpu" for v in sd.values())
+    # strict loading: an unexpected key is refused, the exact dict loads, values survive the round trip
+    bad = dict(sd)
+    bad["nope"] = torch.zeros(1)
+    with pytest.raises(RuntimeError):
+        model.load_state_dict(bad, strict=True)
+    changed = {k: (v + 1 if v.is_floating_point() else v) for k, v in sd.items()}
+    model.load_state_dict(changed)
+    again = model.state_dict()
+    for k, v in changed.items():
+        if "running_" in k:  # buffers live in the compute dtype under mixed precision (buffer_dtype=None), as in the reference
+            torch.testing.assert_close(again[k], v, atol=2e-2, rtol=2e-2)
+        else:
+            torch.testing.assert_close(again[k], v)  # parameters come back from the fp32 master shards unchanged
+    # state dict of a model in eval mode, taken under no_grad, is the same object graph-free
+    model.eval()
+    with torch.no_grad():
+        assert all(not v.requires_grad for v in model.state_dict().values())
+
+
+def test_fsdp_state_dict_dtype_device_and_strictness():
+    spawn_ranks(_state_dict_properties, 2, (), backend="gloo")
