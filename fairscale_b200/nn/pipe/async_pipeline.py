@@ -42,3 +42,7 @@ class AsyncPipeline:
         """This rank's share of backward (after ``loss.backward()`` on the tail)."""
         if self._loop is not None:
             self._loop.run_backward()
+
+    def back_helper(self, output: Optional[List[Tensor]] = None) -> None:
+        """Name used by the reference for the same step; ``output`` is not needed (the loop kept what it sent)."""
+        self.back()
