@@ -6,7 +6,6 @@ batch and to run its share of backward; tensors travel between stages over p2p a
 
 from __future__ import annotations
 
-import contextlib
 from typing import Any, Callable, Dict, List, Optional
 
 import torch
@@ -36,8 +35,7 @@ def callback_with_model(callback: Callable[[Any, AsyncPipe], None], ctx: Any, pi
     """Run ``callback(ctx, model)`` on this worker's stage with the device of its group selected."""
     if torch.cuda.is_available():
         set_device_based_on_group()
-    with _PIPES[pipe_id].lock if hasattr(_PIPES[pipe_id], "lock") else contextlib.nullcontext():
-        callback(ctx, _PIPES[pipe_id])
+    callback(ctx, _PIPES[pipe_id])
 
 
 _PIPES: Dict[int, AsyncPipe] = {}
