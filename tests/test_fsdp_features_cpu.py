@@ -462,3 +462,32 @@ def _state_dict_properties(rank, world):
 
 def test_fsdp_state_dict_dtype_device_and_strictness():
     spawn_ranks(_state_dict_properties, 2, (), backend="gloo")
+
+
+def _collective_counts(rank, world, reshard):
+    """One forward + backward issues an all-gather per unit in forward and, when units are resharded after forward,
+    one more per non-root unit in backward (2 n - 1 in total, as the reference's test_fsdp_grad_acc counts); one
+    reduce-scatter per unit, none under no_sync."""
+    from fairscale_b200.parallel import comm
+
+    kw = dict(reshard_after_forward=reshard, bucket_cap_mb=0, **CPU)
+    layers = list(_mlp())
+    model = FSDP(nn.Sequential(FSDP(nn.Sequential(*layers[:2]), **kw), FSDP(nn.Sequential(*layers[2:4]), **kw), layers[4]), **kw)
+    n = len(get_fsdp_instances(model))
+    assert n == 3
+    model(_x(rank, 0)).sum().backward()  # first pass also records the execution order
+    comm.reset_counters()
+    model(_x(rank, 1)).sum().backward()
+    c = comm.counters()
+    assert c["all_gather"] == (2 * n - 1 if reshard else n), c
+    assert c["reduce_scatter"] == n, c
+    comm.reset_counters()
+    with model.no_sync():
+        model(_x(rank, 2)).sum().backward()
+    c = comm.counters()
+    assert c["reduce_scatter"] == 0 and c["all_gather"] >= n, c
+
+
+@pytest.mark.parametrize("reshard", [True, False])
+def test_fsdp_number_of_collectives_per_step(reshard):
+    spawn_ranks(_collective_counts, 2, (reshard,), backend="gloo")
