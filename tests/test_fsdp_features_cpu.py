@@ -491,3 +491,37 @@ def _collective_counts(rank, world, reshard):
 @pytest.mark.parametrize("reshard", [True, False])
 def test_fsdp_number_of_collectives_per_step(reshard):
     spawn_ranks(_collective_counts, 2, (reshard,), backend="gloo")
+
+
+class _DictIn(nn.Module):
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(3)
+        self.lin = nn.Linear(4, 4)
+
+    def forward(self, batch, scale=None, extra=None):
+        x = batch["x"] if isinstance(batch, dict) else batch[0]
+        y = self.lin(x)
+        if scale is not None:
+            y = y * scale
+        assert extra is None or extra == "tag"
+        return {"out": y, "ids": batch["ids"] if isinstance(batch, dict) else None}
+
+
+def _inputs(rank, world):
+    # containers in, containers out; floating inputs are cast to the compute dtype, integer ones and strings pass through
+    model = FSDP(_DictIn(), mixed_precision=True, compute_dtype=torch.bfloat16, **CPU)
+    ids = torch.arange(3)
+    out = model({"x": torch.randn(3, 4), "ids": ids}, scale=torch.tensor(2.0), extra="tag")
+    assert out["out"].dtype == torch.bfloat16 and out["ids"].dtype == torch.int64 and torch.equal(out["ids"], ids)
+    out["out"].float().sum().backward()
+    assert model.params[0].grad is not None
+    out = model([torch.randn(3, 4)])
+    assert out["out"].shape == (3, 4) and out["ids"] is None
+    # full precision: inputs are left alone
+    fp32 = FSDP(_DictIn(), **CPU)
+    assert fp32({"x": torch.randn(3, 4), "ids": ids})["out"].dtype == torch.float32
+
+
+def test_fsdp_container_inputs_and_casting():
+    spawn_ranks(_inputs, 2, (), backend="gloo")
