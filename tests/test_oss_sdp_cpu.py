@@ -212,3 +212,61 @@ def _two_optimizers_manual_reduce_buffers(rank, world):
 
 def test_sdp_two_optimizers_manual_reduce_and_buffers():
     spawn_ranks(_two_optimizers_manual_reduce_buffers, 2, (), backend="gloo")
+
+
+class _SGDWithKwarg(torch.optim.SGD):
+    def step(self, closure=None, kwarg=None):
+        super().step()
+        kwarg.append(5)
+
+
+def _oss_optimizer_protocol(rank, world):
+    # closure, extra step kwargs, lr schedulers and param-group edits pass through the sharded wrapper
+    x = torch.tensor([float(rank + 1)])
+    m = nn.Linear(1, 1)
+    with torch.no_grad():
+        m.weight.fill_(1.0)
+        m.bias.fill_(2.0)
+    o = OSS(m.parameters(), optim=torch.optim.SGD, lr=0.1)
+
+    def closure():
+        o.zero_grad()
+        loss = (m(x) - 0.0).pow(2).sum()
+        loss.backward()
+        return loss
+
+    loss = o.step(closure=closure)
+    assert loss is not None and float(loss) == (rank + 1 + 2) ** 2
+    # every rank ends with the owners' values (here every rank fed a different input: the owner's update wins)
+    w = [torch.zeros_like(m.weight) for _ in range(world)]
+    dist.all_gather(w, m.weight.detach())
+    assert all(torch.equal(w[0], t) for t in w)
+
+    seen = []
+    o2 = OSS(nn.Linear(1, 1).parameters(), optim=_SGDWithKwarg, lr=0.1)
+    o2.step(kwarg=seen)  # forwarded to the wrapped optimizer
+    assert seen == [5]
+
+    sched = torch.optim.lr_scheduler.StepLR(o, step_size=1, gamma=0.5)
+    o.step()
+    sched.step()
+    assert abs(o.param_groups[0]["lr"] - 0.05) < 1e-12
+    o.step()  # the local optimizer sees the new learning rate
+    assert abs(o.optim.param_groups[0]["lr"] - 0.05) < 1e-12
+
+    # a process group that is not the world: ranks {0, 1} of three shard among themselves
+    sub = dist.new_group(ranks=[0, 1])
+    if rank < 2:
+        m3 = nn.Sequential(nn.Linear(2, 2), nn.Linear(2, 2))
+        o3 = OSS(m3.parameters(), optim=torch.optim.SGD, group=sub, lr=0.1)
+        assert len(o3.partition_parameters()) == 2
+        m3(torch.ones(1, 2)).sum().backward()
+        o3.step()
+        vals = [torch.zeros_like(m3[1].bias) for _ in range(2)]
+        dist.all_gather(vals, m3[1].bias.detach(), group=sub)
+        assert torch.equal(vals[0], vals[1])
+    dist.barrier()
+
+
+def test_oss_closure_kwargs_scheduler_and_subgroup():
+    spawn_ranks(_oss_optimizer_protocol, 3, (), backend="gloo")
