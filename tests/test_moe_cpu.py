@@ -1,4 +1,5 @@
 """Top-2 gating numerics and MOELayer (index path == dense einsum path) on CPU / gloo."""
+import pytest
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -149,3 +150,68 @@ def _grouped_vs_list(rank, world):
     finally:
         tg.gumbel_rsample = orig
     torch.testing.assert_close(g_grouped[1], b.experts[1].l1.weight.grad, rtol=1e-3, atol=1e-5)
+
+
+class _RoundRobinGate(nn.Module):
+    """Deterministic dense gate (any gate returning ``(l_aux, combine_weights, dispatch_mask)`` is accepted): token i goes
+    to expert ``i % E``, slot ``i // E``."""
+
+    def __init__(self, num_experts):
+        super().__init__()
+        self.num_experts = num_experts
+
+    def forward(self, x):
+        s = x.shape[0]
+        capacity = 2 * s // self.num_experts
+        out = torch.zeros(s, self.num_experts, capacity, dtype=x.dtype)
+        for i in range(s):
+            out[i, i % self.num_experts, i // self.num_experts] = 1.0
+        return 0.0, out, out.bool()
+
+
+def _round_robin(rank, world, n_local):
+    d = 8
+    E = world * n_local
+    x = torch.randn(4 * n_local, 16, d)
+    experts = []
+    for i in range(n_local):
+        lin = nn.Linear(d, d, bias=False)
+        lin.weight = nn.Parameter(torch.eye(d) * (rank * n_local + i + 1))  # a scale that names the expert
+        experts.append(lin)
+    moe = MOELayer(_RoundRobinGate(E), experts[0] if n_local == 1 else nn.ModuleList(experts))
+    y = moe(x)
+    assert y.shape == x.shape
+    flat_in, flat_out = x.reshape(-1, d), y.reshape(-1, d)
+    for i in range(flat_in.shape[0]):  # every token came back scaled by the expert it was routed to
+        torch.testing.assert_close(flat_out[i], flat_in[i] * (i % E + 1))
+    # gradients reach the local experts only, and they are tagged for the data-parallel reducers
+    y.sum().backward()
+    assert all(p.grad is not None and p.expert for e in experts for p in e.parameters())
+
+
+@pytest.mark.parametrize("n_local", [1, 2])
+def test_moe_round_robin_gate_routes_to_the_right_expert(n_local):
+    spawn_ranks(_round_robin, 2, (n_local,), backend="gloo")
+
+
+def _identity_experts(rank, world):
+    torch.manual_seed(1)
+    d, n_local = 8, 2
+    x = torch.randn(4 * n_local, 16, d)
+    experts = nn.ModuleList()
+    for _ in range(n_local):
+        lin = nn.Linear(d, d, bias=False)
+        lin.weight = nn.Parameter(torch.eye(d))
+        experts.append(lin)
+    gate = Top2Gate(d, world * n_local)
+    dist.broadcast(gate.wg.weight.data, 0)
+    y = MOELayer(gate, experts)(x)
+    assert y.shape == x.shape
+    kept = y.abs().sum(-1) > 0
+    assert kept.float().mean() > 0.9  # nearly every token found room in one of its two experts
+    # identity experts and gates that sum to one: a routed token comes back unchanged
+    torch.testing.assert_close(y[kept], x[kept], atol=1e-5, rtol=1e-5)
+
+
+def test_moe_identity_experts_reassemble_the_input():
+    spawn_ranks(_identity_experts, 2, (), backend="gloo")
