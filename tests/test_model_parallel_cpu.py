@@ -113,3 +113,42 @@ def _layers(rank, world):
 
 def test_layers_match_dense():
     spawn_ranks(_layers, 2, (), backend="gloo")
+
+
+def test_rng_tracker_single_process():
+    """Named RNG streams: a fork draws from its own stream and leaves the default one untouched, streams continue where
+    they stopped, states can be saved and restored (on CPU the tracker drives the CPU generator)."""
+    import pytest
+
+    from fairscale_b200.nn.model_parallel.random import CudaRNGStatesTracker
+
+    tr = CudaRNGStatesTracker()
+    torch.manual_seed(1)
+    tr.add("a", 100)
+    tr.add("b", 200)
+    with pytest.raises(Exception):
+        tr.add("a", 300)  # the name is taken
+    with pytest.raises(Exception):
+        tr.add("c", 100)  # the seed is taken
+    with pytest.raises(Exception):
+        with tr.fork("missing"):
+            pass
+    torch.manual_seed(1)
+    expected_default = torch.rand(4)
+    torch.manual_seed(1)
+    with tr.fork("a"):
+        a1 = torch.rand(4)
+    assert torch.equal(torch.rand(4), expected_default)  # the fork did not consume the default stream
+    snapshot = tr.get_states()
+    with tr.fork("a"):
+        a2 = torch.rand(4)
+    assert not torch.equal(a1, a2)  # the stream went on
+    tr.set_states(snapshot)
+    with tr.fork("a"):
+        assert torch.equal(torch.rand(4), a2)  # restored: the same continuation
+    torch.manual_seed(100)
+    assert torch.equal(torch.rand(4), a1)  # stream "a" is the generator seeded with 100
+    with tr.fork("b"):
+        assert not torch.equal(torch.rand(4), a1)
+    tr.reset()
+    assert tr.get_states() == {}
