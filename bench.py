@@ -48,6 +48,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--layers", type=int, default=CFG["n_layers"], help="debug only: a run with fewer layers is not a valid benchmark")
     ap.add_argument("--micro-batch", type=int, default=CFG["micro_batch"])
     ap.add_argument("--seq", type=int, default=CFG["seq"])
+    ap.add_argument("--breakdown", action="store_true",
+                    help="also print per-step collective / exposed-wait times (CUDA events on the streams that run them)")
     return ap.parse_args()
 
 
@@ -207,7 +209,7 @@ def main() -> None:
     def run_e2e(i: int) -> float:
         t = host_tokens[i % n_batches].to(device, non_blocking=True)
         loss = step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
-        return float(loss.item())  # device -> host read of the step's result
+        return float(loss.item())  # device -> host read of the step's result, every step, before the next step starts
 
     try:
         for i in range(args.warmup):
@@ -227,22 +229,39 @@ def main() -> None:
         torch.cuda.synchronize()
         launches0 = _bind.launch_count()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0 = time.perf_counter()
         t0.record()
         last = None
         for i in range(args.steps):
             last = fn(i)
         t1.record()
+        host_ms = (time.perf_counter() - h0) * 1e3  # time the host needed to enqueue the steps (it may run ahead of the device)
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        ms = torch.tensor([t0.elapsed_time(t1), host_ms], device=device)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item(), _bind.launch_count() - launches0, last
+        return ms[0].item(), _bind.launch_count() - launches0, last, ms[1].item()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    ms_resident, launches, last_loss = timed(run_resident)
+    ms_resident, launches, last_loss, host_ms = timed(run_resident)
     clocks = sampler.stop() if sampler is not None else {}
-    ms_e2e, _, last_e2e = timed(run_e2e)
+    ms_e2e, _, last_e2e, _ = timed(run_e2e)
+
+    breakdown = None
+    if args.breakdown and args.impl == "ours":
+        from fairscale_b200.utils import profiling
+
+        tr = profiling.enable_comm_trace(True)
+        timed(run_resident)
+        summ = tr.summary()
+        profiling.enable_comm_trace(False)
+        breakdown = {k: {"calls_per_step": v["count"] / args.steps, "ms_per_step": round(v["total_ms"] / args.steps, 3)} for k, v in summ.items()}
+    if args.impl == "ours":
+        # a kernel whose bounded wait ran out leaves a code in the device status word: fail instead of reporting a number
+        from fairscale_b200.utils.failure import check_device_status
+
+        check_device_status(device)
 
     tokens_per_step = B * S * world
     value = tokens_per_step * args.steps / (ms_resident / 1e3)
@@ -269,8 +288,11 @@ def main() -> None:
                 "seq_len": S,
                 "parallelism": f"fsdp{world} full-shard, bf16 compute / fp32 master, checkpoint per block, fused Adam",
                 "l2_policy": "per-step working set (>25 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2",
+            },
+            "results": {
                 "final_loss": float(last_loss.detach()) if last_loss is not None else None,
                 "peak_mem_gb": round(peak_gb, 2),
+                "host_enqueue_ms_per_step": round(host_ms / args.steps, 2),
             },
             "clocks": clocks,
             "e2e": {
@@ -285,9 +307,13 @@ def main() -> None:
         if args.impl == "ours":
             from fairscale_b200.ops import attention
 
-            out["config"]["attention_backend"] = attention.BACKEND
+            out["results"]["attention_backend"] = attention.BACKEND
             if cfg is not None:
-                out["config"]["model_tflops_per_gpu"] = round(cfg.flops_per_token(S) * B * S / (ms_resident / args.steps / 1e3) / 1e12, 1)
+                out["results"]["model_tflops_per_gpu"] = round(cfg.flops_per_token(S) * B * S / (ms_resident / args.steps / 1e3) / 1e12, 1)
+            if clocks.get("sm_mhz"):
+                out["results"]["ms_x_mhz"] = round(ms_resident / args.steps * clocks["sm_mhz"], 0)  # clock-independent work figure
+            if breakdown is not None:
+                out["breakdown"] = breakdown
         print(json.dumps(out))
     dist.barrier()
     dist.destroy_process_group()

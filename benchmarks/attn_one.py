@@ -10,7 +10,6 @@ import sys
 import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-from fairscale_b200.ops.attention import causal_attention  # noqa: E402
 
 ap = argparse.ArgumentParser()
 ap.add_argument("--b", type=int, default=8)
@@ -25,32 +24,56 @@ qkv = (torch.randn(a.b, a.s, 3 * a.h * a.d, device=dev) * 0.5).bfloat16().requir
 do = torch.randn(a.b, a.s, a.h * a.d, device=dev).bfloat16()
 
 
-def run(fn, iters):
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    f = b = 0.0
-    for i in range(iters):
-        qkv.grad = None
-        ev[0].record()
-        o = fn()
-        ev[1].record()
-        o.backward(do)
-        ev[2].record()
-        torch.cuda.synchronize()
-        if i >= iters // 2:
-            f += ev[0].elapsed_time(ev[1])
-            b += ev[1].elapsed_time(ev[2])
-    n = iters - iters // 2
-    return f / n, b / n
+def timed_loop(call, iters):
+    """Mean device time of `iters` back-to-back calls issued behind a spin kernel, so that host launch latency (Python,
+    tensor-map encoding, allocation) stays out of the measurement."""
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(2):
+        call()
+    torch.cuda.synchronize()
+    torch.cuda._sleep(4_000_000)
+    a.record()
+    for _ in range(iters):
+        call()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
 
 
-def sdpa():
-    q, k, v = qkv.view(a.b, a.s, 3, a.h, a.d).permute(2, 0, 3, 1, 4)
-    return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(a.b, a.s, a.h * a.d)
+def ours(iters):
+    """The native kernels called directly (what the autograd function of ops/attention_native.py launches)."""
+    from fairscale_b200.ops import _bind, attention_native
+
+    attention_native._bind_sigs()
+    q = qkv.detach()
+    o = torch.empty(a.b, a.s, a.h * a.d, dtype=q.dtype, device=dev)
+    lse = torch.empty(a.b, a.h, a.s, dtype=torch.float32, device=dev)
+    delta = torch.empty(2, a.b, a.h, a.s, dtype=torch.float32, device=dev)
+    dqkv = torch.empty_like(q)
+    scale = a.d ** -0.5
+    st, stream = _bind.status_ptr(dev), _bind.stream_ptr(dev)
+    f = timed_loop(lambda: _bind.call("fsb_attn_fwd", q.data_ptr(), o.data_ptr(), lse.data_ptr(), a.b, a.s, a.h, a.d, scale, st, stream), iters)
+    g = timed_loop(lambda: _bind.call("fsb_attn_bwd", q.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                                      dqkv.data_ptr(), a.b, a.s, a.h, a.d, scale, st, stream, launches=3), iters)
+    return f, g
+
+
+def sdpa(iters):
+    """cuDNN / flash attention through scaled_dot_product_attention, with the permute it needs on packed QKV."""
+    def fwd():
+        q, k, v = qkv.view(a.b, a.s, 3, a.h, a.d).permute(2, 0, 3, 1, 4)
+        return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(a.b, a.s, a.h * a.d)
+
+    with torch.no_grad():
+        f = timed_loop(fwd, iters)
+    o = fwd()
+    g = timed_loop(lambda: torch.autograd.grad(o, qkv, do, retain_graph=True), iters)
+    return f, g
 
 
 flops_f = 4.0 * a.b * a.h * a.s * a.s * a.d / 2
-f, b = run(lambda: causal_attention(qkv, a.h), a.iters)
+f, b = ours(a.iters)
 print(f"ours  B={a.b} S={a.s} H={a.h} D={a.d}: fwd {f * 1e3:.1f} us ({flops_f / f / 1e9:.0f} TFLOP/s)  bwd {b * 1e3:.1f} us ({2.5 * flops_f / b / 1e9:.0f} TFLOP/s)")
 if not a.no_sdpa:
-    f, b = run(sdpa, a.iters)
+    f, b = sdpa(a.iters)
     print(f"sdpa  (incl. its permute / cat glue): fwd {f * 1e3:.1f} us ({flops_f / f / 1e9:.0f} TFLOP/s)  bwd {b * 1e3:.1f} us ({2.5 * flops_f / b / 1e9:.0f} TFLOP/s)")

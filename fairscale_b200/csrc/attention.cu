@@ -82,6 +82,10 @@ struct AttnBars {
   uint64_t p_full;        // probabilities / dS written to shared memory
   uint64_t acc_done;      // accumulate-type MMAs of the iteration finished (P buffer + accumulators free)
   uint64_t acc_done2[2];  // dQ kernel: the same, alternating with the double-buffered dS tile
+  uint64_t p_full2[2];    // dQ kernel: dS buffer b written.  One barrier per buffer: with a single one the threads could
+                          // complete the phase of step u+1 (other buffer) before the MMA warp had observed step u
+  uint64_t stat_empty;    // backward (persistent): the item's last products that read the stationary tiles have completed
+  uint64_t acc_free;      // backward (persistent): the 8 compute warps have read the item's output accumulators
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -134,6 +138,10 @@ __device__ __forceinline__ void attn_init_bars(AttnBars* b) {
   mbar_init(&b->acc_done, 1);
   mbar_init(&b->acc_done2[0], 1);
   mbar_init(&b->acc_done2[1], 1);
+  mbar_init(&b->p_full2[0], 8);
+  mbar_init(&b->p_full2[1], 8);
+  mbar_init(&b->stat_empty, 1);
+  mbar_init(&b->acc_free, 8);
   b->abort_flag = 0;
   fence_barrier_init();
 }
@@ -143,7 +151,7 @@ __device__ __forceinline__ void attn_teardown(AttnBars* bars, int warp, uint32_t
   tc_fence_before_sync();
   __syncthreads();
   if (bars->abort_flag) {
-    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, FSB_ERR_WAIT_TIMEOUT);
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, FSB_ERR_WAIT_TIMEOUT | (bars->abort_flag << 8));
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
@@ -454,13 +462,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
   AttnBars* bars = reinterpret_cast<AttnBars*>(smem + L::BAR_OFF);
   volatile int* abort_flag = &bars->abort_flag;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // warp-uniform
+  // Persistent: one CTA per SM walks the work items (one 128-row query tile of one head), long rows first, dealt
+  // round-robin; TMEM, barriers and the K / V ring live for the whole kernel (running counters give the phases).
   const int n_qt = p.S / ATT_BM;
-  const int qt = n_qt - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int n_kv = qt + 1;
+  const int HB = p.H * p.B;
+  const int n_items = n_qt * HB;
   const int HD = p.H * D;
-  const int row0 = b * p.S + qt * ATT_BM;
   constexpr uint32_t TMEM_COLS = 512;  // buffer b: S [128 b, +64) dP [128 b + 64, +64); dQ [256, 256+D)
 
   if (threadIdx.x == 0) {
@@ -475,45 +483,55 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, bars->tmem_slot, 0);
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(&bars->stat_full, 2 * L::TILE);
-#pragma unroll
-      for (int c = 0; c < SLABS; ++c) {
-        tma_load_2d(smem + L::Q_OFF + c * SLAB, &tm_qkv, &bars->stat_full, h * D + c * 64, row0);
-        tma_load_2d(smem + L::DO_OFF + c * SLAB, &tm_do, &bars->stat_full, h * D + c * 64, row0);
-      }
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->str_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
-        const int krow = b * p.S + j * ATT_BM;
-        mbar_expect_tx(&bars->str_full[st], 2 * L::TILE);
+      uint32_t jt = 0, it = 0;  // key tiles / items so far
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        const int qt = n_qt - 1 - item / HB;
+        const int hb = item % HB;
+        const int h = hb % p.H, b = hb / p.H;
+        const int n_kv = qt + 1;
+        const int row0 = b * p.S + qt * ATT_BM;
+        if (!mbar_wait(&bars->stat_empty, (it & 1u) ^ 1u, abort_flag, 33)) { ok = false; break; }
+        mbar_expect_tx(&bars->stat_full, 2 * L::TILE);
 #pragma unroll
         for (int c = 0; c < SLABS; ++c) {
-          tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], HD + h * D + c * 64, krow);
-          tma_load_2d(smem + L::V_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], 2 * HD + h * D + c * 64, krow);
+          tma_load_2d(smem + L::Q_OFF + c * SLAB, &tm_qkv, &bars->stat_full, h * D + c * 64, row0);
+          tma_load_2d(smem + L::DO_OFF + c * SLAB, &tm_do, &bars->stat_full, h * D + c * 64, row0);
+        }
+        for (int j = 0; j < n_kv; ++j, ++jt) {
+          const int st = jt & 1;
+          if (!mbar_wait(&bars->str_empty[st], ((jt >> 1) & 1u) ^ 1u, abort_flag, 34)) { ok = false; break; }
+          const int krow = b * p.S + j * ATT_BM;
+          mbar_expect_tx(&bars->str_full[st], 2 * L::TILE);
+#pragma unroll
+          for (int c = 0; c < SLABS; ++c) {
+            tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], HD + h * D + c * 64, krow);
+            tma_load_2d(smem + L::V_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->str_full[st], 2 * HD + h * D + c * 64, krow);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(ATT_BM, 64, true, false, false);
-      const uint32_t idesc_q = make_idesc_f16(ATT_BM, D, true, false, true);  // dS K : K tile read MN-major
-      const uint32_t sq = smem_u32(smem + L::Q_OFF), sdo = smem_u32(smem + L::DO_OFF), sds = smem_u32(smem + L::DS_OFF);
-      const int n_steps = 2 * n_kv;
-      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
-      // step u = key tile u / 2, keys [64 (u & 1), +64) of it; S and dP of step u go to accumulator buffer u & 1
-      auto issue_sp = [&](int u) -> bool {
-        const int j = u >> 1, hh = u & 1, st = j & 1, buf = u & 1;
-        if (hh == 0 && !mbar_wait(&bars->str_full[st], (j >> 1) & 1, abort_flag)) return false;
-        ATT_TRACE(1, u, 0)
-        if (!mbar_wait(&bars->s_empty[buf], ((u >> 1) & 1) ^ 1u, abort_flag)) return false;
-        ATT_TRACE(1, u, 1)
-        tc_fence_after_sync();
-        const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE) + hh * 8192u;  // rows 64 hh .. of every slab
-        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE) + hh * 8192u;
+    // MMA issuer: all lanes run the loop, one elected lane issues each group
+    const uint32_t idesc_s = make_idesc_f16(ATT_BM, 64, true, false, false);
+    const uint32_t idesc_q = make_idesc_f16(ATT_BM, D, true, false, true);  // dS K : K tile read MN-major
+    const uint32_t sq = smem_u32(smem + L::Q_OFF), sdo = smem_u32(smem + L::DO_OFF), sds = smem_u32(smem + L::DS_OFF);
+    uint32_t jt0 = 0, ut0 = 0, it = 0;  // key tiles / steps of earlier items, items so far
+    bool ok = true;
+    // step u = key tile u / 2, keys [64 (u & 1), +64) of it; S and dP of step u go to accumulator buffer u & 1
+    auto issue_sp = [&](int u, int n_steps) -> bool {
+      const uint32_t jt = jt0 + (u >> 1), ut = ut0 + u;
+      const int hh = u & 1, st = jt & 1, buf = u & 1;
+      if (hh == 0 && !mbar_wait_warp(&bars->str_full[st], (jt >> 1) & 1u, abort_flag, 35)) return false;
+      if (!mbar_wait_warp(&bars->s_empty[buf], ((ut >> 1) & 1u) ^ 1u, abort_flag, 36)) return false;
+      tc_fence_after_sync();
+      const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE) + hh * 8192u;  // rows 64 hh .. of every slab
+      const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE) + hh * 8192u;
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
           umma_f16_ss(tmem_base + buf * 128, desc_kmajor(sq, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
@@ -521,22 +539,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
         for (int ks = 0; ks < D / 16; ++ks)
           umma_f16_ss(tmem_base + buf * 128 + 64, desc_kmajor(sdo, ks, SLAB), desc_kmajor(sv, ks, SLAB), idesc_s, ks != 0);
         umma_commit(&bars->s_full[buf]);
-        return true;
-      };
-      if (ok) ok = issue_sp(0);
+        if (u == n_steps - 1) umma_commit(&bars->stat_empty);  // the item's last use of Q and dO
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      const int qt = n_qt - 1 - item / HB;
+      const int n_steps = 2 * (qt + 1);
+      if (!mbar_wait_warp(&bars->stat_full, it & 1u, abort_flag, 37)) { ok = false; break; }
+      ok = issue_sp(0, n_steps);
       for (int u = 0; u < n_steps && ok; ++u) {
-        if (u + 1 < n_steps) { if (!issue_sp(u + 1)) { ok = false; break; } }
-        const int j = u >> 1, hh = u & 1, st = j & 1, buf = u & 1;
-        if (!mbar_wait(&bars->p_full, u & 1, abort_flag)) { ok = false; break; }
-        ATT_TRACE(1, u, 2)
+        if (u + 1 < n_steps) { if (!issue_sp(u + 1, n_steps)) { ok = false; break; } }
+        const uint32_t jt = jt0 + (u >> 1), ut = ut0 + u;
+        const int hh = u & 1, st = jt & 1, buf = u & 1;
+        // the dQ accumulator still belongs to the previous item until its threads have read it
+        if (u == 0 && !mbar_wait_warp(&bars->acc_free, (it & 1u) ^ 1u, abort_flag, 38)) { ok = false; break; }
+        if (!mbar_wait_warp(&bars->p_full2[buf], (ut >> 1) & 1u, abort_flag, 39)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 64 / 16; ++ks)
-          umma_f16_ss(tmem_base + 256, desc_kmajor(sds + buf * 16384u, ks, SLAB), desc_mnmajor(sk, hh * 4 + ks, SLAB), idesc_q, (u | ks) != 0);
-        if (hh == 1) umma_commit(&bars->str_empty[st]);
-        umma_commit(&bars->acc_done2[buf]);
+          for (int ks = 0; ks < 64 / 16; ++ks)
+            umma_f16_ss(tmem_base + 256, desc_kmajor(sds + buf * 16384u, ks, SLAB), desc_mnmajor(sk, hh * 4 + ks, SLAB), idesc_q, (u | ks) != 0);
+          if (hh == 1) umma_commit(&bars->str_empty[st]);
+          umma_commit(&bars->acc_done2[buf]);
+        }
+        __syncwarp();
       }
+      jt0 += static_cast<uint32_t>(n_steps >> 1);
+      ut0 += static_cast<uint32_t>(n_steps);
     }
   } else {
     const int quad = warp & 3;
@@ -544,47 +576,52 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
     const int row = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    const size_t stat_idx = (static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row;
-    const float lse2 = p.delta[static_cast<size_t>(p.B) * p.H * p.S + stat_idx];  // base-2 lse, written by the delta kernel
-    const float delta_s = p.delta[stat_idx];                                       // scale * rowsum(dO * O)
     uint8_t* sds = smem + L::DS_OFF;
-    const int n_steps = 2 * n_kv;
+    uint32_t ut0 = 0;
     bool ok = true;
-    for (int u = 0; u < n_steps && ok; ++u) {
-      const int j = u >> 1, hh = u & 1, buf = u & 1;
-      if (!mbar_wait(&bars->s_full[buf], (u >> 1) & 1, abort_flag)) { ok = false; break; }
-      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 0) }
-      tc_fence_after_sync();
-      const bool diag = (j == qt);
-      uint32_t pk[16];
-      {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + buf * 128 + lane_off + half * 32, rs);
-        tmem_ld_32x32(tmem_base + buf * 128 + 64 + lane_off + half * 32, rp);
-        tmem_ld_wait();
-        if (!diag) dq_cols32<false>(rs, rp, hh * 64 + half * 32, row, sl2, lse2, p.scale, delta_s, pk);
-        else       dq_cols32<true>(rs, rp, hh * 64 + half * 32, row, sl2, lse2, p.scale, delta_s, pk);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
-      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 1) }
-      if (u >= 2) {  // the dQ product that read this dS buffer two steps ago
-        if (!mbar_wait(&bars->acc_done2[buf], ((u >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
-      }
-      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 2) }
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int qt = n_qt - 1 - item / HB;
+      const int hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int n_steps = 2 * (qt + 1);
+      const int row0 = b * p.S + qt * ATT_BM;
+      const size_t stat_idx = (static_cast<size_t>(b) * p.H + h) * p.S + qt * ATT_BM + row;
+      const float lse2 = p.delta[static_cast<size_t>(p.B) * p.H * p.S + stat_idx];  // base-2 lse, written by the delta kernel
+      const float delta_s = p.delta[stat_idx];                                       // scale * rowsum(dO * O)
+      for (int u = 0; u < n_steps && ok; ++u) {
+        const uint32_t ut = ut0 + u;
+        const int j = u >> 1, hh = u & 1, buf = u & 1;
+        if (!mbar_wait(&bars->s_full[buf], (ut >> 1) & 1u, abort_flag, 40)) { ok = false; break; }
+        tc_fence_after_sync();
+        const bool diag = (j == qt);
+        uint32_t pk[16];
+        {
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32(tmem_base + buf * 128 + lane_off + half * 32, rs);
+          tmem_ld_32x32(tmem_base + buf * 128 + 64 + lane_off + half * 32, rp);
+          tmem_ld_wait();
+          if (!diag) dq_cols32<false>(rs, rp, hh * 64 + half * 32, row, sl2, lse2, p.scale, delta_s, pk);
+          else       dq_cols32<true>(rs, rp, hh * 64 + half * 32, row, sl2, lse2, p.scale, delta_s, pk);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
+        if (ut >= 2) {  // the dQ product that read this dS buffer two steps ago
+          if (!mbar_wait(&bars->acc_done2[buf], ((ut >> 1) - 1u) & 1u, abort_flag, 41)) { ok = false; break; }
+        }
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sds + buf * 16384 + swz(row, half * 4 + ch)) = v;
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(sds + buf * 16384 + swz(row, half * 4 + ch)) = v;
+        }
+        fence_proxy_async();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full2[buf]);
       }
-      fence_proxy_async();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full);
-      if (warp == 2 && lane == 0) { ATT_TRACE(2, u, 3) }
-    }
-    if (ok && mbar_wait(&bars->acc_done2[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_flag)) {
+      if (!ok) break;
+      const uint32_t ul = ut0 + static_cast<uint32_t>(n_steps) - 1u;  // the item's last step
+      if (!mbar_wait(&bars->acc_done2[ul & 1u], (ul >> 1) & 1u, abort_flag, 42)) { ok = false; break; }
       tc_fence_after_sync();
       __nv_bfloat16* drow = p.dqkv + static_cast<size_t>(row0 + row) * (3 * HD) + h * D + half * (D / 2);
 #pragma unroll 1
@@ -602,6 +639,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
           *reinterpret_cast<uint4*>(drow + c * 32 + q * 8) = v;
         }
       }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_free);
+      ut0 += static_cast<uint32_t>(n_steps);
     }
   }
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
@@ -664,13 +705,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
   AttnBars* bars = reinterpret_cast<AttnBars*>(smem + L::BAR_OFF);
   volatile int* abort_flag = &bars->abort_flag;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x;  // key tile; small kt = many query sub-tiles = heavy, scheduled first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // warp-uniform
+  // Persistent: one CTA per SM walks the work items (one 128-row key tile of one head); small key tiles see the most
+  // query sub-tiles and come first.  Every item has an even number of sub-tiles, so the accumulator buffer of a
+  // sub-tile is its running index & 1 as well.
+  const int n_kt = p.S / ATT_BM;
+  const int HB = p.H * p.B;
+  const int n_items = n_kt * HB;
   const int HD = p.H * D;
-  const int krow0 = b * p.S + kt * ATT_BM;
-  const int first_sub = kt * (ATT_BM / KV_QSUB);
-  const int n_sub = p.S / KV_QSUB - first_sub;
   // S^T / dP^T are double-buffered so the products of sub-tile t+1 run while the threads work on sub-tile t:
   // buffer 0: S^T [0,64) dP^T [64,128); buffer 1: S^T [384,448) dP^T [448,512); dV [128,128+D); dK [256,256+D)
   constexpr uint32_t TMEM_COLS = 512;
@@ -688,44 +730,58 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, bars->tmem_slot, 0);
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(&bars->stat_full, 2 * L::TILE);
-#pragma unroll
-      for (int c = 0; c < SLABS; ++c) {
-        tma_load_2d(smem + L::K_OFF + c * SLAB, &tm_kv, &bars->stat_full, HD + h * D + c * 64, krow0);
-        tma_load_2d(smem + L::V_OFF + c * SLAB, &tm_kv, &bars->stat_full, 2 * HD + h * D + c * 64, krow0);
-      }
-      for (int t = 0; t < n_sub; ++t) {
-        const int st = t % L::STAGES;
-        if (!mbar_wait(&bars->str_empty[st], ((t / L::STAGES) & 1) ^ 1u, abort_flag)) break;
-        const int qrow = b * p.S + (first_sub + t) * KV_QSUB;
-        mbar_expect_tx(&bars->str_full[st], 2 * L::QTILE);
+      uint32_t tt = 0, it = 0;  // sub-tiles / items so far
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        const int kt = item / HB;
+        const int hb = item % HB;
+        const int h = hb % p.H, b = hb / p.H;
+        const int krow0 = b * p.S + kt * ATT_BM;
+        const int first_sub = kt * (ATT_BM / KV_QSUB);
+        const int n_sub = p.S / KV_QSUB - first_sub;
+        if (!mbar_wait(&bars->stat_empty, (it & 1u) ^ 1u, abort_flag, 65)) { ok = false; break; }
+        mbar_expect_tx(&bars->stat_full, 2 * L::TILE);
 #pragma unroll
         for (int c = 0; c < SLABS; ++c) {
-          tma_load_2d(smem + L::Q_OFF + st * L::QTILE + c * QSLAB, &tm_q, &bars->str_full[st], h * D + c * 64, qrow);
-          tma_load_2d(smem + L::DO_OFF + st * L::QTILE + c * QSLAB, &tm_do, &bars->str_full[st], h * D + c * 64, qrow);
+          tma_load_2d(smem + L::K_OFF + c * SLAB, &tm_kv, &bars->stat_full, HD + h * D + c * 64, krow0);
+          tma_load_2d(smem + L::V_OFF + c * SLAB, &tm_kv, &bars->stat_full, 2 * HD + h * D + c * 64, krow0);
+        }
+        for (int t = 0; t < n_sub; ++t, ++tt) {
+          const int st = tt % L::STAGES;
+          if (!mbar_wait(&bars->str_empty[st], ((tt / L::STAGES) & 1u) ^ 1u, abort_flag, 66)) { ok = false; break; }
+          const int qrow = b * p.S + (first_sub + t) * KV_QSUB;
+          mbar_expect_tx(&bars->str_full[st], 2 * L::QTILE);
+#pragma unroll
+          for (int c = 0; c < SLABS; ++c) {
+            tma_load_2d(smem + L::Q_OFF + st * L::QTILE + c * QSLAB, &tm_q, &bars->str_full[st], h * D + c * 64, qrow);
+            tma_load_2d(smem + L::DO_OFF + st * L::QTILE + c * QSLAB, &tm_do, &bars->str_full[st], h * D + c * 64, qrow);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(ATT_BM, KV_QSUB, true, false, false);  // K Q^T, V dO^T
-      const uint32_t idesc_a = make_idesc_f16(ATT_BM, D, true, false, true);         // P^T dO, dS^T Q (B MN-major)
-      const uint32_t sk = smem_u32(smem + L::K_OFF), sv = smem_u32(smem + L::V_OFF);
-      const uint32_t spt = smem_u32(smem + L::PT_OFF), sdst = smem_u32(smem + L::DST_OFF);
-      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
-      // S^T(t) = K Q_t^T and dP^T(t) = V dO_t^T into accumulator buffer t & 1
-      auto issue_sp = [&](int t) -> bool {
-        const int st = t % L::STAGES, buf = t & 1;
-        if (!mbar_wait(&bars->str_full[st], (t / L::STAGES) & 1, abort_flag)) return false;
-        if (!mbar_wait(&bars->s_empty[buf], ((t >> 1) & 1) ^ 1u, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint32_t sq = smem_u32(smem + L::Q_OFF + st * L::QTILE);
-        const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
-        const uint32_t t_s = tmem_base + (buf ? 384u : 0u), t_p = tmem_base + (buf ? 448u : 64u);
+    // MMA issuer: all lanes run the loop, one elected lane issues each group
+    const uint32_t idesc_s = make_idesc_f16(ATT_BM, KV_QSUB, true, false, false);  // K Q^T, V dO^T
+    const uint32_t idesc_a = make_idesc_f16(ATT_BM, D, true, false, true);         // P^T dO, dS^T Q (B MN-major)
+    const uint32_t sk = smem_u32(smem + L::K_OFF), sv = smem_u32(smem + L::V_OFF);
+    const uint32_t spt = smem_u32(smem + L::PT_OFF), sdst = smem_u32(smem + L::DST_OFF);
+    uint32_t tt0 = 0, it = 0;
+    bool ok = true;
+    // S^T(t) = K Q_t^T and dP^T(t) = V dO_t^T into accumulator buffer t & 1
+    auto issue_sp = [&](int t, int n_sub) -> bool {
+      const uint32_t tt = tt0 + t;
+      const int st = tt % L::STAGES, buf = t & 1;
+      if (!mbar_wait_warp(&bars->str_full[st], (tt / L::STAGES) & 1u, abort_flag, 67)) return false;
+      if (!mbar_wait_warp(&bars->s_empty[buf], ((tt >> 1) & 1u) ^ 1u, abort_flag, 68)) return false;
+      tc_fence_after_sync();
+      const uint32_t sq = smem_u32(smem + L::Q_OFF + st * L::QTILE);
+      const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
+      const uint32_t t_s = tmem_base + (buf ? 384u : 0u), t_p = tmem_base + (buf ? 448u : 64u);
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
           umma_f16_ss(t_s, desc_kmajor(sk, ks, SLAB), desc_kmajor(sq, ks, QSLAB), idesc_s, ks != 0);
@@ -733,25 +789,39 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
         for (int ks = 0; ks < D / 16; ++ks)
           umma_f16_ss(t_p, desc_kmajor(sv, ks, SLAB), desc_kmajor(sdo, ks, QSLAB), idesc_s, ks != 0);
         umma_commit(&bars->s_full[buf]);
-        return true;
-      };
-      if (ok) ok = issue_sp(0);
+        if (t == n_sub - 1) umma_commit(&bars->stat_empty);  // the item's last use of the K and V tiles
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      const int kt = item / HB;
+      const int n_sub = p.S / KV_QSUB - kt * (ATT_BM / KV_QSUB);
+      if (!mbar_wait_warp(&bars->stat_full, it & 1u, abort_flag, 69)) { ok = false; break; }
+      ok = issue_sp(0, n_sub);
       for (int t = 0; t < n_sub && ok; ++t) {
-        if (t + 1 < n_sub) { if (!issue_sp(t + 1)) { ok = false; break; } }
-        const int st = t % L::STAGES;
+        if (t + 1 < n_sub) { if (!issue_sp(t + 1, n_sub)) { ok = false; break; } }
+        const uint32_t tt = tt0 + t;
+        const int st = tt % L::STAGES;
         const uint32_t sq = smem_u32(smem + L::Q_OFF + st * L::QTILE);
         const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
-        if (!mbar_wait(&bars->p_full, t & 1, abort_flag)) { ok = false; break; }
+        // dK / dV still belong to the previous item until its threads have read them
+        if (t == 0 && !mbar_wait_warp(&bars->acc_free, (it & 1u) ^ 1u, abort_flag, 70)) { ok = false; break; }
+        if (!mbar_wait_warp(&bars->p_full, tt & 1u, abort_flag, 71)) { ok = false; break; }
         tc_fence_after_sync();
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < KV_QSUB / 16; ++ks)
-          umma_f16_ss(tmem_base + 128, desc_kmajor(spt, ks, SLAB), desc_mnmajor(sdo, ks, QSLAB), idesc_a, (t | ks) != 0);
+          for (int ks = 0; ks < KV_QSUB / 16; ++ks)
+            umma_f16_ss(tmem_base + 128, desc_kmajor(spt, ks, SLAB), desc_mnmajor(sdo, ks, QSLAB), idesc_a, (t | ks) != 0);
 #pragma unroll
-        for (int ks = 0; ks < KV_QSUB / 16; ++ks)
-          umma_f16_ss(tmem_base + 256, desc_kmajor(sdst, ks, SLAB), desc_mnmajor(sq, ks, QSLAB), idesc_a, (t | ks) != 0);
-        umma_commit(&bars->str_empty[st]);
-        umma_commit(&bars->acc_done);
+          for (int ks = 0; ks < KV_QSUB / 16; ++ks)
+            umma_f16_ss(tmem_base + 256, desc_kmajor(sdst, ks, SLAB), desc_mnmajor(sq, ks, QSLAB), idesc_a, (t | ks) != 0);
+          umma_commit(&bars->str_empty[st]);
+          umma_commit(&bars->acc_done);
+        }
+        __syncwarp();
       }
+      tt0 += static_cast<uint32_t>(n_sub);
     }
   } else {
     const int quad = warp & 3;
@@ -759,44 +829,55 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
     const int row = quad * 32 + lane;  // key row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    const float* delta_bh = p.delta + (static_cast<size_t>(b) * p.H + h) * p.S;   // scale * rowsum(dO * O)
-    const float* lse2_bh = delta_bh + static_cast<size_t>(p.B) * p.H * p.S;        // base-2 lse
     uint8_t* spt = smem + L::PT_OFF;
     uint8_t* sdst = smem + L::DST_OFF;
+    uint32_t tt0 = 0;
     bool ok = true;
-    for (int t = 0; t < n_sub && ok; ++t) {
-      const int buf = t & 1;
-      if (!mbar_wait(&bars->s_full[buf], (t >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      const int qa0 = (first_sub + t) * KV_QSUB + half * 32;  // first query (sequence index) this thread handles
-      const int key = kt * ATT_BM + row;                      // this thread's key (sequence index)
-      const bool diag = qa0 < (kt + 1) * ATT_BM;              // may overlap the diagonal block
-      uint32_t pp[16], pd[16];
-      {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + (buf ? 384u : 0u) + lane_off + half * 32, rs);
-        tmem_ld_32x32(tmem_base + (buf ? 448u : 64u) + lane_off + half * 32, rp);
-        tmem_ld_wait();
-        if (!diag) dkv_row<false>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
-        else       dkv_row<true>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
-      if (t > 0) {
-        if (!mbar_wait(&bars->acc_done, (t - 1) & 1, abort_flag)) { ok = false; break; }
-      }
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int kt = item / HB;
+      const int hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int krow0 = b * p.S + kt * ATT_BM;
+      const int first_sub = kt * (ATT_BM / KV_QSUB);
+      const int n_sub = p.S / KV_QSUB - first_sub;
+      const float* delta_bh = p.delta + (static_cast<size_t>(b) * p.H + h) * p.S;   // scale * rowsum(dO * O)
+      const float* lse2_bh = delta_bh + static_cast<size_t>(p.B) * p.H * p.S;        // base-2 lse
+      for (int t = 0; t < n_sub && ok; ++t) {
+        const uint32_t tt = tt0 + t;
+        const int buf = t & 1;
+        if (!mbar_wait(&bars->s_full[buf], (tt >> 1) & 1u, abort_flag, 72)) { ok = false; break; }
+        tc_fence_after_sync();
+        const int qa0 = (first_sub + t) * KV_QSUB + half * 32;  // first query (sequence index) this thread handles
+        const int key = kt * ATT_BM + row;                      // this thread's key (sequence index)
+        const bool diag = qa0 < (kt + 1) * ATT_BM;              // may overlap the diagonal block
+        uint32_t pp[16], pd[16];
+        {
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32(tmem_base + (buf ? 384u : 0u) + lane_off + half * 32, rs);
+          tmem_ld_32x32(tmem_base + (buf ? 448u : 64u) + lane_off + half * 32, rp);
+          tmem_ld_wait();
+          if (!diag) dkv_row<false>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
+          else       dkv_row<true>(rs, rp, lse2_bh + qa0, delta_bh + qa0, qa0, key, sl2, p.scale, pp, pd);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
+        if (tt > 0) {  // the accumulate products that read the previous P^T / dS^T
+          if (!mbar_wait(&bars->acc_done, (tt - 1u) & 1u, abort_flag, 73)) { ok = false; break; }
+        }
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {  // 32 query columns = 4 chunks of 8 bf16
-        *reinterpret_cast<uint4*>(spt + swz(row, half * 4 + ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sdst + swz(row, half * 4 + ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
+        for (int ch = 0; ch < 4; ++ch) {  // 32 query columns = 4 chunks of 8 bf16
+          *reinterpret_cast<uint4*>(spt + swz(row, half * 4 + ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(sdst + swz(row, half * 4 + ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
+        }
+        fence_proxy_async();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full);
       }
-      fence_proxy_async();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full);
-    }
-    if (ok && mbar_wait(&bars->acc_done, (n_sub - 1) & 1, abort_flag)) {
+      if (!ok) break;
+      const uint32_t tl = tt0 + static_cast<uint32_t>(n_sub) - 1u;  // the item's last sub-tile
+      if (!mbar_wait(&bars->acc_done, tl & 1u, abort_flag, 74)) { ok = false; break; }
       tc_fence_after_sync();
       __nv_bfloat16* base = p.dqkv + static_cast<size_t>(krow0 + row) * (3 * HD) + h * D + half * (D / 2);
 #pragma unroll 1
@@ -819,6 +900,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
           }
         }
       }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_free);
+      tt0 += static_cast<uint32_t>(n_sub);
     }
   }
   attn_teardown(bars, warp, tmem_base, TMEM_COLS, p.status);
@@ -874,6 +959,14 @@ static inline int one_cta_smem(int bytes) { return bytes < kMinSmem ? kMinSmem :
 FSB_API int fsb_attn_fwd_pingpong(const void* qkv, void* o, float* lse, int B, int S, int H, int D, float scale, int* status,
                                   cudaStream_t stream);
 
+// Debug aid: copies (and clears) the bit set of wait sites that were blocked when an attention kernel aborted.
+FSB_API int fsb_attn_wait_sites(unsigned int* out8) {
+  unsigned int zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(out8, fsb::g_blocked_wait_sites, sizeof(zero));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(fsb::g_blocked_wait_sites, zero, sizeof(zero));
+  return static_cast<int>(e);
+}
+
 FSB_API int fsb_last_tensor_map_result() { return fsb_host::last_encode_result(); }
 
 // Debug aid: when set to a device buffer of 4 * 64 * 4 uint64, the forward kernel's CTA (0,0,0) records nanosecond
@@ -888,12 +981,12 @@ FSB_API int fsb_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int
                          cudaStream_t stream) {
   using namespace fsb;
   if (S % ATT_BM != 0 || (D != 64 && D != 128)) return -1;
-  // Two query tiles per CTA in ping-pong (attention_fwd_pingpong.cu) when the sequence allows it; FSB_ATTN_FWD=classic
-  // keeps the one-tile kernel below (also used while a timeline trace is being recorded).
+  // Two query tiles per CTA in ping-pong, persistent (attention_fwd_pingpong.cu), when the sequence is a multiple of
+  // 256; FSB_ATTN_FWD=classic keeps the one-tile kernel below (also used while a timeline trace is being recorded).
   static int pingpong = -1;
   if (pingpong < 0) {
     const char* e = getenv("FSB_ATTN_FWD");
-    pingpong = (e != nullptr && e[0] == 'p') ? 1 : 0;
+    pingpong = (e != nullptr && e[0] == 'c') ? 0 : 1;
   }
   if (pingpong == 1 && S % (2 * ATT_BM) == 0 && g_attn_trace == nullptr) return fsb_attn_fwd_pingpong(qkv, o, lse, B, S, H, D, scale, status, stream);
   CUtensorMap tm;
@@ -935,7 +1028,11 @@ FSB_API int fsb_attn_bwd(const void* qkv, const void* o, const void* d_o, const 
     attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
                                                                              static_cast<const __nv_bfloat16*>(d_o), lse, delta, scale, B, S, H, D);
   }
-  dim3 grid(S / ATT_BM, H, B);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_items = (S / ATT_BM) * H * B;
+  const dim3 grid(n_items < sms ? n_items : sms);  // persistent: one CTA per SM walks the work items
   if (D == 128) {
     set_smem(attn_bwd_dq_kernel<128>, DqSmem<128>::TOTAL);
     set_smem(attn_bwd_dkv_kernel<128>, DkvSmem<128>::TOTAL);

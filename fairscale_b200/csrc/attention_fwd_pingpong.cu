@@ -15,7 +15,13 @@
 // the first 64 columns of their own score tile (two values per 32-bit column) and feed P V as the TMEM A operand of
 // tcgen05.mma, so they never pass through shared memory.  The tensor pipe executes in issue order: S_t(j+1) is issued
 // after PV_t(j) and therefore cannot overwrite P_t(j) early.
-// Tile A skips the last key tile of the CTA (it lies wholly above A's diagonal).  Every mbarrier wait is bounded.
+// Tile A skips the last key tile of the item (it lies wholly above A's diagonal).  Every mbarrier wait is bounded.
+//
+// The kernel is persistent: one CTA per SM walks a list of work items (256 query rows of one head), longest rows first,
+// dealt round-robin.  TMEM, barriers and the K / V ring live for the whole kernel, and the next item's query tiles are
+// loaded as soon as the last Q K^T products of the current item have completed, i.e. during its final softmax and
+// output write.  (With one CTA per item an SM sat idle for 7-10 us between consecutive CTAs - launch, 197 KB of shared
+// memory, TMEM allocation - which was a third of the kernel's run time.)
 //
 // Replaces nn.MultiheadAttention / bmm+softmax in the reference's models
 // (benchmarks/models/transformer_lm.py:107,150-152,169-183).
@@ -37,7 +43,13 @@ struct Params {
   __nv_bfloat16* o;
   float* lse;
   int* status;
+  unsigned long long* trace;  // optional timeline of CTA (0,0,0): [role][step][4] nanosecond stamps
 };
+
+// role 0: MMA issuer, 1: softmax of tile A (warp 2, lane 0), 2: softmax of tile B (warp 6, lane 0)
+#define PP_TRACE(role, j, k)                                                                              \
+  if (p.trace != nullptr && blockIdx.x == 0 && (j) < 32 && (threadIdx.x & 31) == 0)                            \
+    p.trace[((role) * 32 + (j)) * 4 + (k)] = globaltimer_ns();
 
 struct Bars {
   uint64_t q_full;
@@ -46,6 +58,8 @@ struct Bars {
   uint64_t s_full[2];   // per query tile: scores of the current step are in TMEM
   uint64_t p_full[2];   // per query tile: probabilities written (4 warp arrivals)
   uint64_t o_done[2];   // per query tile: P V of the current step has completed
+  uint64_t q_empty;     // the item's last Q K^T products have completed: the query tiles may be replaced
+  uint64_t o_free[2];   // per query tile: the softmax warps have read the item's output accumulator (4 warp arrivals)
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -117,17 +131,17 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tm_qkv, Params p) {
   Bars* bars = reinterpret_cast<Bars*>(smem + L::BAR_OFF);
   volatile int* abort_flag = &bars->abort_flag;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // warp-uniform
+  // Work items (256 query rows of one head) ordered longest first and dealt round-robin to the persistent CTAs: every
+  // role of the CTA walks the same list.  item -> (q2, h, b): all heads of the longest rows come first.
   const int n_q2 = p.S / (2 * BM);
-  const int q2 = n_q2 - 1 - blockIdx.x;  // long rows first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int n_kv = 2 * q2 + 2;           // key tiles seen by tile B; tile A sees one less
-  const int n_a = n_kv - 1;
+  const int HB = p.H * p.B;
+  const int n_items = n_q2 * HB;
   const int HD = p.H * D;
-  const int row0 = b * p.S + q2 * 2 * BM;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->k_empty[i], 1);
@@ -136,6 +150,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tm_qkv, Params p) {
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->p_full[i], 4);
       mbar_init(&bars->o_done[i], 1);
+      mbar_init(&bars->o_free[i], 4);
     }
     bars->abort_flag = 0;
     fence_barrier_init();
@@ -148,78 +163,122 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tm_qkv, Params p) {
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, bars->tmem_slot, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&bars->q_full, 2 * L::TILE);
+      uint32_t kt = 0;  // key tiles loaded so far (selects the K / V stage and its phase)
+      uint32_t it = 0;  // items started so far
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        const int q2 = n_q2 - 1 - item / HB;
+        const int hb = item % HB;
+        const int h = hb % p.H, b = hb / p.H;
+        const int n_kv = 2 * q2 + 2;
+        const int row0 = b * p.S + q2 * 2 * BM;
+        // the query tiles of the previous item are free once its last Q K^T products have completed
+        if (!mbar_wait(&bars->q_empty, (it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(&bars->q_full, 2 * L::TILE);
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
+        for (int t = 0; t < 2; ++t)
 #pragma unroll
-        for (int c = 0; c < SLABS; ++c)
-          tma_load_2d(smem + L::Q_OFF + t * L::TILE + c * SLAB, &tm_qkv, &bars->q_full, h * D + c * 64, row0 + t * BM);
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1u;
-        const int krow = b * p.S + j * BN;
-        if (!mbar_wait(&bars->k_empty[st], par, abort_flag)) break;
-        mbar_expect_tx(&bars->k_full[st], L::TILE);
+          for (int c = 0; c < SLABS; ++c)
+            tma_load_2d(smem + L::Q_OFF + t * L::TILE + c * SLAB, &tm_qkv, &bars->q_full, h * D + c * 64, row0 + t * BM);
+        for (int j = 0; j < n_kv; ++j, ++kt) {
+          const int st = kt & 1;
+          const uint32_t par = ((kt >> 1) & 1u) ^ 1u;
+          const int krow = b * p.S + j * BN;
+          if (!mbar_wait(&bars->k_empty[st], par, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&bars->k_full[st], L::TILE);
 #pragma unroll
-        for (int c = 0; c < SLABS; ++c)
-          tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->k_full[st], HD + h * D + c * 64, krow);
-        if (!mbar_wait(&bars->v_empty[st], par, abort_flag)) break;
-        mbar_expect_tx(&bars->v_full[st], L::TILE);
+          for (int c = 0; c < SLABS; ++c)
+            tma_load_2d(smem + L::K_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->k_full[st], HD + h * D + c * 64, krow);
+          if (!mbar_wait(&bars->v_empty[st], par, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&bars->v_full[st], L::TILE);
 #pragma unroll
-        for (int c = 0; c < SLABS; ++c)
-          tma_load_2d(smem + L::V_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->v_full[st], 2 * HD + h * D + c * 64, krow);
+          for (int c = 0; c < SLABS; ++c)
+            tma_load_2d(smem + L::V_OFF + st * L::TILE + c * SLAB, &tm_qkv, &bars->v_full[st], 2 * HD + h * D + c * 64, krow);
+        }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(BM, BN, true, false, false);  // Q K^T: both K-major
-      const uint32_t idesc_o = make_idesc_f16(BM, D, true, false, true);    // P V: P from TMEM, V MN-major
-      const uint32_t sq = smem_u32(smem + L::Q_OFF);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
-      auto issue_s = [&](int t, int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->k_full[st], (j >> 1) & 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
+    // ------------------------------------------------------------------ MMA issuer (all lanes run the loop, one is elected per group)
+    const uint32_t idesc_s = make_idesc_f16(BM, BN, true, false, false);  // Q K^T: both K-major
+    const uint32_t idesc_o = make_idesc_f16(BM, D, true, false, true);    // P V: P from TMEM, V MN-major
+    const uint32_t sq = smem_u32(smem + L::Q_OFF);
+    uint32_t kt0 = 0;          // key tiles consumed by earlier items
+    uint32_t cs[2] = {0, 0};   // steps issued so far per query tile (phase of p_full)
+    uint32_t it = 0;
+    bool ok = true;
+    auto issue_s = [&](int t, uint32_t kt) -> bool {
+      const int st = kt & 1;
+      if (!mbar_wait_warp(&bars->k_full[st], (kt >> 1) & 1u, abort_flag)) return false;
+      tc_fence_after_sync();
+      const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
           umma_f16_ss(tmem_base + t * 128, desc_kmajor(sq + t * L::TILE, ks, SLAB), desc_kmajor(sk, ks, SLAB), idesc_s, ks != 0);
         umma_commit(&bars->s_full[t]);
-        return true;
-      };
-      auto issue_pv = [&](int t, int j) -> bool {
-        if (!mbar_wait(&bars->p_full[t], j & 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint32_t sv = smem_u32(smem + L::V_OFF + (j & 1) * L::TILE);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_pv = [&](int t, uint32_t kt, bool first) -> bool {
+      if (!mbar_wait_warp(&bars->p_full[t], cs[t] & 1u, abort_flag)) return false;
+      tc_fence_after_sync();
+      const uint32_t sv = smem_u32(smem + L::V_OFF + (kt & 1) * L::TILE);
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)
-          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, desc_mnmajor(sv, ks, SLAB), idesc_o, (j | ks) != 0);
+          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, desc_mnmajor(sv, ks, SLAB), idesc_o, (!first || ks != 0) ? 1u : 0u);
         umma_commit(&bars->o_done[t]);
-        return true;
-      };
-      if (ok) ok = issue_s(0, 0);
-      if (ok) ok = issue_s(1, 0);
-      if (ok) umma_commit(&bars->k_empty[0]);
+      }
+      __syncwarp();
+      ++cs[t];
+      return true;
+    };
+    auto commit = [&](uint64_t* bar) {
+      if (elect_one()) umma_commit(bar);
+      __syncwarp();
+    };
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      const int q2 = n_q2 - 1 - item / HB;
+      const int n_kv = 2 * q2 + 2;  // key tiles seen by tile B; tile A sees one less (its last one is wholly masked)
+      const int n_a = n_kv - 1;
+      if (!mbar_wait_warp(&bars->q_full, it & 1u, abort_flag)) { ok = false; break; }
+      ok = issue_s(0, kt0);
+      if (ok) ok = issue_s(1, kt0);
+      if (ok) commit(&bars->k_empty[kt0 & 1]);
+      if (ok && n_kv == 1) commit(&bars->q_empty);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->v_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
-        if (j < n_a) {
-          if (!issue_pv(0, j)) { ok = false; break; }
-          if (j + 1 < n_a && !issue_s(0, j + 1)) { ok = false; break; }
+        const uint32_t kt = kt0 + j;
+        const int st = kt & 1;
+        if (!mbar_wait_warp(&bars->v_full[st], (kt >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (item == static_cast<int>(blockIdx.x)) { PP_TRACE(0, j, 0); }
+        if (p.trace != nullptr && item == 0 && j < 32 && lane == 0) p.trace[384 + j] = clock64();
+        if (j == 0) {
+          // the output accumulators still belong to the previous item until its softmax warps have read them
+          if (!mbar_wait_warp(&bars->o_free[0], (it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_warp(&bars->o_free[1], (it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         }
-        if (!issue_pv(1, j)) { ok = false; break; }
-        umma_commit(&bars->v_empty[st]);
+        if (j < n_a) {
+          if (!issue_pv(0, kt, j == 0)) { ok = false; break; }
+          if (item == static_cast<int>(blockIdx.x)) { PP_TRACE(0, j, 1); }
+          if (j + 1 < n_a && !issue_s(0, kt + 1)) { ok = false; break; }
+        }
+        if (item == static_cast<int>(blockIdx.x)) { PP_TRACE(0, j, 2); }
+        if (!issue_pv(1, kt, j == 0)) { ok = false; break; }
+        if (item == static_cast<int>(blockIdx.x)) { PP_TRACE(0, j, 3); }
+        commit(&bars->v_empty[st]);
         if (j + 1 < n_kv) {
-          if (!issue_s(1, j + 1)) { ok = false; break; }
-          umma_commit(&bars->k_empty[(j + 1) & 1]);
+          if (!issue_s(1, kt + 1)) { ok = false; break; }
+          commit(&bars->k_empty[(kt + 1) & 1]);
+          if (j + 2 == n_kv) commit(&bars->q_empty);  // that was the item's last use of the query tiles
         }
       }
+      kt0 += n_kv;
     }
   } else {
     // ------------------------------------------------------------------ softmax warps: one thread per query row
@@ -229,76 +288,90 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tm_qkv, Params p) {
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t ts = tmem_base + t * 128 + lane_off;        // scores; probabilities overwrite columns [0, 64)
     const uint32_t to = tmem_base + 256 + t * 128 + lane_off;  // output accumulator
-    const int n_it = t == 0 ? n_a : n_kv;
     const float sl2 = p.scale * LOG2E;
-    float m_run = -INFINITY, l_run = 0.f;
+    uint32_t cs = 0;  // steps of this tile so far, over all items (phase of s_full / o_done)
     bool ok = true;
-    for (int j = 0; j < n_it && ok; ++j) {
-      if (!mbar_wait(&bars->s_full[t], j & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      const bool diag = (j == n_it - 1);
-      uint32_t r0[32], r1[32];
-      // pass 1: row maximum
-      float mx = -INFINITY;
-      tmem_ld_32x32(ts, r0);
-      tmem_ld_32x32(ts + 32, r1);
-      tmem_ld_wait();
-      if (!diag) { mx = chunk_max<false>(r0, 0, row, mx); mx = chunk_max<false>(r1, 32, row, mx); }
-      else       { mx = chunk_max<true>(r0, 0, row, mx);  mx = chunk_max<true>(r1, 32, row, mx); }
-      tmem_ld_32x32(ts + 64, r0);
-      tmem_ld_32x32(ts + 96, r1);
-      tmem_ld_wait();
-      if (!diag) { mx = chunk_max<false>(r0, 64, row, mx); mx = chunk_max<false>(r1, 96, row, mx); }
-      else       { mx = chunk_max<true>(r0, 64, row, mx);  mx = chunk_max<true>(r1, 96, row, mx); }
-      // keep the old maximum while the new one is at most 2^8 above it: no rescaling of O, values stay in range
-      float m_new = fmaxf(m_run, mx);
-      if (m_run != -INFINITY && (m_new - m_run) * sl2 <= 8.f) m_new = m_run;
-      const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - m_new) * sl2);
-      const float mb = m_new * sl2;
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O_t belongs to P V of step j-1 until that has completed (it has: S_t(j) was issued behind it)
-        if (!mbar_wait(&bars->o_done[t], (j - 1) & 1, abort_flag)) { ok = false; break; }
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int q2 = n_q2 - 1 - item / HB;
+      const int hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int n_kv = 2 * q2 + 2;
+      const int n_it = t == 0 ? n_kv - 1 : n_kv;
+      const int row0 = b * p.S + q2 * 2 * BM;
+      const bool traced = (item == static_cast<int>(blockIdx.x)) && quad == 2;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n_it && ok; ++j, ++cs) {
+        if (!mbar_wait(&bars->s_full[t], cs & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
+        if (traced) { PP_TRACE(1 + t, j, 0); }
+        const bool diag = (j == n_it - 1);
+        uint32_t r0[32], r1[32];
+        // pass 1: row maximum
+        float mx = -INFINITY;
+        tmem_ld_32x32(ts, r0);
+        tmem_ld_32x32(ts + 32, r1);
+        tmem_ld_wait();
+        if (!diag) { mx = chunk_max<false>(r0, 0, row, mx); mx = chunk_max<false>(r1, 32, row, mx); }
+        else       { mx = chunk_max<true>(r0, 0, row, mx);  mx = chunk_max<true>(r1, 32, row, mx); }
+        tmem_ld_32x32(ts + 64, r0);
+        tmem_ld_32x32(ts + 96, r1);
+        tmem_ld_wait();
+        if (!diag) { mx = chunk_max<false>(r0, 64, row, mx); mx = chunk_max<false>(r1, 96, row, mx); }
+        else       { mx = chunk_max<true>(r0, 64, row, mx);  mx = chunk_max<true>(r1, 96, row, mx); }
+        // keep the old maximum while the new one is at most 2^8 above it: no rescaling of O, values stay in range
+        float m_new = fmaxf(m_run, mx);
+        if (m_run != -INFINITY && (m_new - m_run) * sl2 <= 8.f) m_new = m_run;
+        const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - m_new) * sl2);
+        const float mb = m_new * sl2;
+        if (traced) { PP_TRACE(1 + t, j, 1); }
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // O_t belongs to P V of step j-1 until that has completed (it has: S_t(j) was issued behind it)
+          if (!mbar_wait(&bars->o_done[t], (cs - 1u) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(to + c * 32, r);
-          tmem_ld_wait();
-          uint32_t lo[16], hi[16];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(to + c * 32, r);
+            tmem_ld_wait();
+            uint32_t lo[16], hi[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            lo[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            hi[i] = __float_as_uint(__uint_as_float(r[16 + i]) * alpha);
+            for (int i = 0; i < 16; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              hi[i] = __float_as_uint(__uint_as_float(r[16 + i]) * alpha);
+            }
+            tmem_st_32x16(to + c * 32, lo);
+            tmem_st_32x16(to + c * 32 + 16, hi);
           }
-          tmem_st_32x16(to + c * 32, lo);
-          tmem_st_32x16(to + c * 32 + 16, hi);
         }
+        if (traced) { PP_TRACE(1 + t, j, 2); }
+        // pass 2: exponentials; chunk c of 32 keys becomes 16 packed columns at [16 c, 16 c + 16), always behind the reads
+        float rs = 0.f;
+        uint32_t pk[16];
+        tmem_ld_32x32(ts, r0);
+        tmem_ld_32x32(ts + 32, r1);
+        tmem_ld_wait();
+        if (!diag) rs += chunk_exp<false>(r0, 0, row, sl2, mb, pk); else rs += chunk_exp<true>(r0, 0, row, sl2, mb, pk);
+        tmem_ld_32x32(ts + 64, r0);  // in flight during the next exponentials
+        tmem_st_32x16(ts, pk);
+        if (!diag) rs += chunk_exp<false>(r1, 32, row, sl2, mb, pk); else rs += chunk_exp<true>(r1, 32, row, sl2, mb, pk);
+        tmem_ld_32x32(ts + 96, r1);
+        tmem_st_32x16(ts + 16, pk);
+        tmem_ld_wait();
+        if (!diag) rs += chunk_exp<false>(r0, 64, row, sl2, mb, pk); else rs += chunk_exp<true>(r0, 64, row, sl2, mb, pk);
+        tmem_st_32x16(ts + 32, pk);
+        if (!diag) rs += chunk_exp<false>(r1, 96, row, sl2, mb, pk); else rs += chunk_exp<true>(r1, 96, row, sl2, mb, pk);
+        tmem_st_32x16(ts + 48, pk);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[t]);
+        if (traced) { PP_TRACE(1 + t, j, 3); }
+        l_run = l_run * alpha + rs;
+        m_run = m_new;
       }
-      // pass 2: exponentials; chunk c of 32 keys becomes 16 packed columns at [16 c, 16 c + 16), always behind the reads
-      float rs = 0.f;
-      uint32_t pk[16];
-      tmem_ld_32x32(ts, r0);
-      tmem_ld_32x32(ts + 32, r1);
-      tmem_ld_wait();
-      if (!diag) rs += chunk_exp<false>(r0, 0, row, sl2, mb, pk); else rs += chunk_exp<true>(r0, 0, row, sl2, mb, pk);
-      tmem_ld_32x32(ts + 64, r0);  // in flight during the next exponentials
-      tmem_st_32x16(ts, pk);
-      if (!diag) rs += chunk_exp<false>(r1, 32, row, sl2, mb, pk); else rs += chunk_exp<true>(r1, 32, row, sl2, mb, pk);
-      tmem_ld_32x32(ts + 96, r1);
-      tmem_st_32x16(ts + 16, pk);
-      tmem_ld_wait();
-      if (!diag) rs += chunk_exp<false>(r0, 64, row, sl2, mb, pk); else rs += chunk_exp<true>(r0, 64, row, sl2, mb, pk);
-      tmem_st_32x16(ts + 32, pk);
-      if (!diag) rs += chunk_exp<false>(r1, 96, row, sl2, mb, pk); else rs += chunk_exp<true>(r1, 96, row, sl2, mb, pk);
-      tmem_st_32x16(ts + 48, pk);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[t]);
-      l_run = l_run * alpha + rs;
-      m_run = m_new;
-    }
-    if (ok && mbar_wait(&bars->o_done[t], (n_it - 1) & 1, abort_flag)) {
+      if (!ok) break;
+      // epilogue of the item: normalise and store this thread's output row, then hand the accumulator back
+      if (!mbar_wait(&bars->o_done[t], (cs - 1u) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const float inv = 1.f / l_run;
       __nv_bfloat16* orow = p.o + static_cast<size_t>(row0 + t * BM + row) * HD + h * D;
@@ -317,6 +390,9 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tm_qkv, Params p) {
           *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
         }
       }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->o_free[t]);
       if (p.lse != nullptr)
         p.lse[(static_cast<size_t>(b) * p.H + h) * p.S + q2 * 2 * BM + t * BM + row] = (m_run * sl2 + log2f(l_run)) * LN2;
     }
@@ -343,6 +419,14 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tm_qkv, Params p) {
 
 // C ABI.  S must be a multiple of 256 and D in {64, 128}; returns -1 otherwise (the caller falls back to the
 // one-tile-per-CTA forward).  Tensors are contiguous and 16-byte aligned.
+// Debug aid: a device buffer of 416 uint64 receives nanosecond stamps [role][step][4] of the first item of CTA 0 and, from
+// entry 384, the issuer's clock64 per step; nullptr switches it off.
+static unsigned long long* g_pp_trace = nullptr;
+FSB_API int fsb_attn_pp_set_trace(void* buf) {
+  g_pp_trace = static_cast<unsigned long long*>(buf);
+  return 0;
+}
+
 FSB_API int fsb_attn_fwd_pingpong(const void* qkv, void* o, float* lse, int B, int S, int H, int D, float scale, int* status,
                                   cudaStream_t stream) {
   using namespace fsb;
@@ -352,8 +436,12 @@ FSB_API int fsb_attn_fwd_pingpong(const void* qkv, void* o, float* lse, int B, i
   if (!fsb_host::encode_2d_16bit(&tm, qkv, (uint64_t)3 * H * D, (uint64_t)B * S, (uint64_t)3 * H * D, 64, BM)) return -1;
   Params p{};
   p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
-  p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = status;
-  dim3 grid(S / (2 * BM), H, B);
+  p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = status; p.trace = g_pp_trace;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_items = (S / (2 * BM)) * H * B;
+  const dim3 grid(n_items < sms ? n_items : sms);  // persistent: one CTA per SM walks the work items
   // each CTA allocates all 512 TMEM columns, so two CTAs must never share an SM: ask for more than half of its shared memory
   constexpr int kMinSmem = 120 * 1024;
   if (D == 128) {

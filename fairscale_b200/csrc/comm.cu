@@ -8,7 +8,7 @@
 //   entry barrier (peers' inputs are ready)  ->  pull / push over NVLink  ->  exit barrier (peers are done
 //   with my buffer), so that in-stream ordering on every GPU is enough for the callers.
 //
-// All polls are bounded: after kCommWaitNs without progress the kernel writes FSB_ERR_WAIT_TIMEOUT to its
+// All polls are bounded: after the wait limit (fsb_comm_set_timeout_ms, default 30 s) without progress the kernel writes FSB_ERR_WAIT_TIMEOUT to its
 // status word and returns; the host raises.  No TMA cluster multicast is used anywhere; remote data is read
 // with ordinary loads (L1-bypassing) by the CTA that needs it.
 //
@@ -20,6 +20,8 @@
 
 #include "comm_dev.cuh"
 
+#include <cstdlib>
+
 namespace fsb {
 
 // ------------------------------------------------------------------------------------------------
@@ -30,29 +32,39 @@ __global__ void __launch_bounds__(COMM_THREADS) barrier_kernel(CommCtx c) {
 
 // out[p * n16 + i] = src_p[i] for every rank p; src pointers address each rank's shard (16-byte units)
 
-__global__ void __launch_bounds__(COMM_THREADS) all_gather_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
+// d[i] = s[i] for i in [0, n16): grid-strided, COMM_UNROLL loads in flight per thread before the first store
+__device__ __forceinline__ void copy_peer16(uint4* __restrict__ d, const uint4* __restrict__ s, long long n16) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + (COMM_UNROLL - 1) * stride < n16; i += COMM_UNROLL * stride) {
+    uint4 v[COMM_UNROLL];
+#pragma unroll
+    for (int u = 0; u < COMM_UNROLL; ++u) v[u] = ld_peer16(s + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < COMM_UNROLL; ++u) d[i + u * stride] = v[u];
+  }
+  for (; i < n16; i += stride) d[i] = ld_peer16(s + i);
+}
+
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
+all_gather_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);
   if (!wait_peers(c, c.channel)) return;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int k = 0; k < c.world; ++k) {
     const int p = (c.rank + k) % c.world;  // start with the local shard, then walk the ring
-    const uint4* s = reinterpret_cast<const uint4*>(src.p[p]);
-    uint4* d = out + static_cast<long long>(p) * n16;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) d[i] = ld_peer16(s + i);
+    copy_peer16(out + static_cast<long long>(p) * n16, reinterpret_cast<const uint4*>(src.p[p]), n16);
   }
   exit_barrier(c, c.channel + 1);
 }
 
 // out[p-th chunk] = src_p[my chunk]: equal-split all-to-all, chunk = n16 16-byte units
-__global__ void __launch_bounds__(COMM_THREADS) all_to_all_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
+all_to_all_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);
   if (!wait_peers(c, c.channel)) return;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int k = 0; k < c.world; ++k) {
     const int p = (c.rank + k) % c.world;
-    const uint4* s = reinterpret_cast<const uint4*>(src.p[p]) + static_cast<long long>(c.rank) * n16;
-    uint4* d = out + static_cast<long long>(p) * n16;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) d[i] = ld_peer16(s + i);
+    copy_peer16(out + static_cast<long long>(p) * n16, reinterpret_cast<const uint4*>(src.p[p]) + static_cast<long long>(c.rank) * n16, n16);
   }
   exit_barrier(c, c.channel + 1);
 }
@@ -87,22 +99,30 @@ template <> struct Acc8<float> {
 //   out[i] = (accumulate ? out[i] : 0) + scale * sum_p src_p[rank * n + i]
 // TI: gradient dtype in the peers' buffers; TO: output dtype (fp32 master-precision shard or TI).
 template <typename TI, typename TO>
-__global__ void __launch_bounds__(COMM_THREADS) reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n, float scale, int accumulate) {
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
+reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n, float scale, int accumulate) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);
   if (!wait_peers(c, c.channel)) return;
   constexpr int E = Acc8<TI>::N;
   const long long nvec = n / E;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long base = static_cast<long long>(c.rank) * n;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    uint4 v[kMaxRanks];
-#pragma unroll
-    for (int q = 0; q < kMaxRanks; ++q)  // all peers' loads in flight together
-      if (q < c.world) v[q] = ld_peer16(reinterpret_cast<const TI*>(src.p[q]) + static_cast<long long>(c.rank) * n + i * E);
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    // fixed summation order (rank 0, 1, ...): the result does not depend on timing
+    // peers in groups of COMM_UNROLL (their loads in flight together); fixed summation order (rank 0, 1, ...), so the
+    // result does not depend on timing
 #pragma unroll
-    for (int q = 0; q < kMaxRanks; ++q)
-      if (q < c.world) Acc8<TI>::add(a, v[q]);
+    for (int g = 0; g < kMaxRanks; g += COMM_UNROLL) {
+      if (g < c.world) {
+        uint4 v[COMM_UNROLL];
+#pragma unroll
+        for (int q = 0; q < COMM_UNROLL; ++q)
+          if (g + q < c.world) v[q] = ld_peer16(reinterpret_cast<const TI*>(src.p[g + q]) + base + i * E);
+#pragma unroll
+        for (int q = 0; q < COMM_UNROLL; ++q)
+          if (g + q < c.world) Acc8<TI>::add(a, v[q]);
+      }
+    }
 #pragma unroll
     for (int e = 0; e < E; ++e) {
       float r = a[e] * scale;
@@ -126,7 +146,7 @@ __global__ void __launch_bounds__(COMM_THREADS) reduce_scatter_kernel(CommCtx c,
 // reduce my chunk from all peers into my buffer, cross-GPU barrier, then pull the other chunks from their owners.
 // The grid must be fully resident (its CTAs wait for one another).
 template <typename T>
-__global__ void __launch_bounds__(COMM_THREADS) all_reduce_kernel(CommCtx c, PtrTable bufs, long long n) {
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM) all_reduce_kernel(CommCtx c, PtrTable bufs, long long n) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);
   if (!wait_peers(c, c.channel)) return;
   constexpr int E = Acc8<T>::N;
@@ -177,7 +197,7 @@ __global__ void __launch_bounds__(COMM_THREADS) all_reduce_kernel(CommCtx c, Ptr
 // gather : out[t] (+)= w[t] * row src_row[t] of rank src_rank[t]'s buffer (remote loads).
 // One warp moves one row; M % 8 == 0 (bf16).
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(COMM_THREADS) moe_scatter_rows_kernel(CommCtx c, PtrTable dst, const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM) moe_scatter_rows_kernel(CommCtx c, PtrTable dst, const __nv_bfloat16* __restrict__ x,
                                                                         const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
                                                                         const float* __restrict__ w, long long T, int rows_per_token, int M) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);  // destinations are zeroed / free
@@ -203,7 +223,7 @@ __global__ void __launch_bounds__(COMM_THREADS) moe_scatter_rows_kernel(CommCtx 
 }
 
 // out[token] = sum over its `rows_per_token` routes of w[t] * peer_row(t); dot[t] (optional) = <peer_row(t), g[token]>
-__global__ void __launch_bounds__(COMM_THREADS) moe_gather_rows_kernel(CommCtx c, PtrTable src, __nv_bfloat16* __restrict__ out,
+__global__ void __launch_bounds__(COMM_THREADS, 8) moe_gather_rows_kernel(CommCtx c, PtrTable src, __nv_bfloat16* __restrict__ out,
                                                                        const int* __restrict__ src_rank, const int* __restrict__ src_row,
                                                                        const float* __restrict__ w, const __nv_bfloat16* __restrict__ g,
                                                                        float* __restrict__ dot, long long tokens, int rows_per_token, int M) {
@@ -261,6 +281,7 @@ static fsb::CommCtx make_ctx(int rank, int world, unsigned epoch, int channel, v
   for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) c.pads[i] = static_cast<uint32_t*>(pads[i]);
   c.counter = static_cast<unsigned int*>(counter);
   c.status = status;
+  c.wait_ns = fsb_host::comm_wait_ns();
   return c;
 }
 static fsb::PtrTable make_table(void* const* ptrs, int world) {
@@ -268,7 +289,14 @@ static fsb::PtrTable make_table(void* const* ptrs, int world) {
   for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) t.p[i] = ptrs[i];
   return t;
 }
+// FSB_COMM_MAX_CTAS overrides the CTA cap of the streaming collectives (default: two 128-thread CTAs per SM).
 static int comm_grid(long long work_items, int max_blocks) {
+  static int cap = -1;
+  if (cap < 0) {
+    const char* e = getenv("FSB_COMM_MAX_CTAS");
+    cap = (e != nullptr && atoi(e) > 0) ? atoi(e) : 0;
+  }
+  if (cap > 0) max_blocks = cap;
   long long b = (work_items + fsb::COMM_THREADS - 1) / fsb::COMM_THREADS;
   if (b < 1) b = 1;
   if (b > max_blocks) b = max_blocks;
@@ -276,6 +304,14 @@ static int comm_grid(long long work_items, int max_blocks) {
 }
 
 FSB_API int fsb_comm_max_ranks() { return fsb::kMaxRanks; }
+
+// Limit of one device-side wait for a peer, for every collective launched from now on (milliseconds; default 30 s).
+FSB_API int fsb_comm_set_timeout_ms(long long ms) {
+  if (ms <= 0) return -1;
+  fsb_host::comm_wait_ns() = static_cast<unsigned long long>(ms) * 1000000ull;
+  return 0;
+}
+FSB_API long long fsb_comm_get_timeout_ms() { return static_cast<long long>(fsb_host::comm_wait_ns() / 1000000ull); }
 
 FSB_API int fsb_comm_barrier(int rank, int world, unsigned epoch, int channel, void* const* pads, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks) return -1;
@@ -333,12 +369,19 @@ FSB_API int fsb_comm_all_reduce(int rank, int world, unsigned epoch, int channel
   if (world > kMaxRanks) return -1;
   const CommCtx c = make_ctx(rank, world, epoch, channel, pads, counter, status);
   const PtrTable t = make_table(bufs, world);
-  const int grid = comm_grid(n / 8 / world + 1, 132);  // fully resident: CTAs wait for one another
-  if (dtype == FSB_BF16) all_reduce_kernel<__nv_bfloat16><<<grid, COMM_THREADS, 0, stream>>>(c, t, n);
-  else if (dtype == FSB_F16) all_reduce_kernel<__half><<<grid, COMM_THREADS, 0, stream>>>(c, t, n);
-  else if (dtype == FSB_F32) all_reduce_kernel<float><<<grid, COMM_THREADS, 0, stream>>>(c, t, n);
+  // The CTAs of this kernel wait for one another, so it is launched cooperatively: the runtime starts it only when
+  // the whole grid can be resident at once, whatever else is running on the device.
+  int grid = comm_grid(n / 8 / world + 1, 132);
+  CommCtx cc = c;
+  PtrTable tt = t;
+  long long nn = n;
+  void* args[] = {&cc, &tt, &nn};
+  const void* fn = nullptr;
+  if (dtype == FSB_BF16) fn = reinterpret_cast<const void*>(all_reduce_kernel<__nv_bfloat16>);
+  else if (dtype == FSB_F16) fn = reinterpret_cast<const void*>(all_reduce_kernel<__half>);
+  else if (dtype == FSB_F32) fn = reinterpret_cast<const void*>(all_reduce_kernel<float>);
   else return -1;
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(COMM_THREADS), args, 0, stream));
 }
 
 FSB_API int fsb_comm_moe_scatter_rows(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,

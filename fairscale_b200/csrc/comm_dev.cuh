@@ -7,8 +7,17 @@
 namespace fsb {
 
 constexpr int kMaxRanks = 8;
-constexpr uint64_t kCommWaitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
-constexpr int COMM_THREADS = 512;
+// Default limit of one wait for a peer.  Ranks drift apart by far more than a kernel's run time in ordinary training
+// (one rank writes a checkpoint, a data loader stalls), so the default is generous; fsb_comm_set_timeout_ms() changes it
+// for the process and every kernel launch carries the value that was current when it was launched.
+constexpr unsigned long long kCommWaitDefaultNs = 30ull * 1000ull * 1000ull * 1000ull;
+// Collective kernels run beside the persistent tensor-core kernels of the compute stream (168 registers x 320 threads
+// and ~225 KB of shared memory per SM), so a communication CTA has to fit into what those leave free: 128 threads,
+// at most 40 registers per thread and no dynamic shared memory.  A larger CTA cannot become resident until a GEMM CTA
+// retires and then keeps the next GEMM off the SM, which serialises communication with compute.
+constexpr int COMM_THREADS = 128;
+constexpr int COMM_MIN_CTAS_PER_SM = 12;  // caps the kernels at 40 registers per thread
+constexpr int COMM_UNROLL = 4;            // independent 16-byte peer loads in flight per thread
 
 struct CommCtx {
   int rank, world;
@@ -17,6 +26,7 @@ struct CommCtx {
   uint32_t* pads[kMaxRanks];  // peer signal pads: pads[p][channel * kMaxRanks + src]
   unsigned int* counter;      // local scratch counter (zero before the call, left at zero)
   int* status;
+  unsigned long long wait_ns; // limit of one wait for a peer
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -48,7 +58,7 @@ __device__ __forceinline__ bool wait_peers(const CommCtx& c, int channel) {
     const uint64_t t0 = globaltimer_ns();
     // epochs wrap: compare as signed distance
     while (static_cast<int32_t>(ld_acquire_sys(mine) - c.epoch) < 0) {
-      if (globaltimer_ns() - t0 > kCommWaitNs) {
+      if (globaltimer_ns() - t0 > c.wait_ns) {
         ok_flag = 0;
         if (c.status != nullptr) atomicExch(c.status, FSB_ERR_WAIT_TIMEOUT);
         break;
@@ -103,3 +113,11 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 }
 
 }  // namespace fsb
+
+// Host side: the process-wide wait limit (one instance per shared object).
+namespace fsb_host {
+inline unsigned long long& comm_wait_ns() {
+  static unsigned long long ns = fsb::kCommWaitDefaultNs;
+  return ns;
+}
+}  // namespace fsb_host

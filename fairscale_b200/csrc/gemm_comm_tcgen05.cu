@@ -50,11 +50,11 @@ struct FusedParams {
   int Mc;                 // rows per chunk
 };
 
-__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, volatile int* abort_flag, unsigned long long wait_ns) {
   const uint64_t t0 = globaltimer_ns();
   while (static_cast<int32_t>(ld_acquire_gpu(ctr) - target) < 0) {
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kCommWaitNs) {
+    if (globaltimer_ns() - t0 > wait_ns) {
       *abort_flag = 1;
       return false;
     }
@@ -128,7 +128,7 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
         const int m0 = local_a ? tm * BLOCK_M : chunk * f.Mc + tm * BLOCK_M;
         if (MODE == 0 && !local_a && ready_chunk != chunk) {
           // the copy CTAs publish a chunk with generic-proxy stores; order them before this thread's TMA reads
-          if (!wait_counter(f.counts + chunk, f.target, abort_flag)) { ok = false; break; }
+          if (!wait_counter(f.counts + chunk, f.target, abort_flag, f.c.wait_ns)) { ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");
           ready_chunk = chunk;
         }
@@ -364,7 +364,7 @@ __device__ __forceinline__ bool rs_pull_cta(const FusedParams& f, uint8_t* smem)
         const uint32_t* flag = c.pads[c.rank] + c.channel * kMaxRanks + peer_of(j.chunk);
         const uint64_t t0 = globaltimer_ns();
         while (static_cast<int32_t>(ld_acquire_sys(flag) - c.epoch) < 0) {
-          if (globaltimer_ns() - t0 > kCommWaitNs) {
+          if (globaltimer_ns() - t0 > c.wait_ns) {
             *abort_flag = 1;
             return false;
           }
@@ -413,8 +413,8 @@ __device__ __forceinline__ void rs_final_pass(const FusedParams& f, int N) {
   __shared__ int final_ok;
   if (threadIdx.x == 0) {
     int dummy_abort = 0;
-    bool ok = wait_counter(f.counts + f.c.rank, f.target, &dummy_abort);               // my own chunk is complete
-    if (ok && f.c.world > 1) ok = wait_counter(f.counts + kMaxRanks, f.target_comm, &dummy_abort);  // peers' rows have landed
+    bool ok = wait_counter(f.counts + f.c.rank, f.target, &dummy_abort, f.c.wait_ns);               // my own chunk is complete
+    if (ok && f.c.world > 1) ok = wait_counter(f.counts + kMaxRanks, f.target_comm, &dummy_abort, f.c.wait_ns);  // peers' rows have landed
     if (!ok && f.c.status != nullptr) atomicExch(f.c.status, FSB_ERR_WAIT_TIMEOUT);
     final_ok = ok ? 1 : 0;
   }
@@ -490,6 +490,7 @@ static fsb::CommCtx fused_ctx(int rank, int world, unsigned epoch, int channel, 
   for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) c.pads[i] = static_cast<uint32_t*>(pads[i]);
   c.counter = static_cast<unsigned int*>(counter);
   c.status = status;
+  c.wait_ns = fsb_host::comm_wait_ns();
   return c;
 }
 

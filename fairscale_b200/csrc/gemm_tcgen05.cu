@@ -42,7 +42,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);  // warp-uniform
   const int lane = threadIdx.x & 31;
 
   const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
@@ -76,7 +76,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -112,8 +112,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (all lanes run the loop, one elected lane issues)
+    {
       const uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, true, p.a_mn_major != 0, p.b_mn_major != 0);
       // K-major: LBO unused, SBO 1024; UMMA_K advance = 32 B inside the swizzle row.
       // MN-major: LBO = 8192 (next 64 MN elements), SBO 1024; UMMA_K advance = 16 k-rows = 2048 B.
@@ -125,25 +125,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024u);
-            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+              const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024u);
+              const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
+              umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[stage]);  // frees the smem slot once these MMAs have read it
           }
-          umma_commit(&empty_bar[stage]);  // frees the smem slot once these MMAs have read it
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(&tmem_full_bar[acc]);
+        if (elect_one()) umma_commit(&tmem_full_bar[acc]);
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -230,7 +234,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);  // warp-uniform
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
@@ -264,7 +268,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   __syncthreads();
   cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -301,8 +305,9 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (leader only)
-    if (lane == 0 && leader) {
+    // ------------------------------------------------------------------ MMA issuer (leader only; all lanes run the loop,
+    // one elected lane issues, so that addresses and descriptors stay warp-uniform)
+    if (leader) {
       const uint32_t idesc = make_idesc_f16(2 * BLOCK_M, PAIR_BLOCK_N, true, p.a_mn_major != 0, p.b_mn_major != 0);
       const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, b_lbo = p.b_mn_major ? 8192u : 16u;
       const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u, b_kstep = p.b_mn_major ? 2048u : 32u;
@@ -312,29 +317,35 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024u);
-            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
-            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
           const uint32_t eb = smem_u32(&empty_bar[stage]);
-          umma_commit_pair(map_to_cta(eb, 0));
-          umma_commit_pair(map_to_cta(eb, 1));
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+              const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024u);
+              const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
+              umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit_pair(map_to_cta(eb, 0));
+            umma_commit_pair(map_to_cta(eb, 1));
+          }
+          __syncwarp();
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
-        umma_commit_pair(map_to_cta(fb, 0));
-        umma_commit_pair(map_to_cta(fb, 1));
+        if (elect_one()) {
+          umma_commit_pair(map_to_cta(fb, 0));
+          umma_commit_pair(map_to_cta(fb, 1));
+        }
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }

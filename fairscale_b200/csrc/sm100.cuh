@@ -44,20 +44,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait on a phase parity. Returns false (and raises *abort_flag) on timeout or when
 // another thread of the CTA already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// Debug aid: every wait that was blocked when a kernel aborted sets bit (site & 31) of word (site >> 5) here (one copy
+// per translation unit; attention.cu exposes its copy through fsb_attn_wait_sites()).
+static __device__ unsigned int g_blocked_wait_sites[8];
+
+// `site` (1..255) identifies the wait in the kernel's source; the first wait that runs out leaves it in the abort flag and
+// the kernel reports it in bits 8..15 of the status word.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site = 1) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (((++spins) & 63u) == 0u) {
-      if (*abort_flag) return false;
+      if (*abort_flag) {
+        atomicOr(&g_blocked_wait_sites[(site >> 5) & 7], 1u << (site & 31));
+        return false;
+      }
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
+        if (*abort_flag == 0) *abort_flag = site;
+        atomicOr(&g_blocked_wait_sites[(site >> 5) & 7], 1u << (site & 31));
         return false;
       }
     }
   }
   return true;
+}
+
+// The warp that issues tcgen05.mma runs its control flow with all 32 lanes and elects one lane per instruction
+// group: loop counters, shared-memory addresses and descriptors then stay warp-uniform values, which keeps the cost
+// of issuing one MMA far below its execution time.  This is the all-lanes wait for that warp; the vote makes the
+// result (and every branch on it) uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site = 1) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, site);
+  return __all_sync(0xffffffffu, ok) != 0;
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -147,8 +147,14 @@ def build_fsdp_gpt(cfg: GPTConfig, device: torch.device, process_group: Any = No
     world = process_group.size()
     if nvlink_heap and world > 1 and device.type == "cuda" and nvlink.available() and symm.workspace_for(process_group) is None:
         # the compute-dtype shards live in the symmetric heap so peers all-gather them without staging
+        # plus three rotating gradient windows (largest unit: the embedding / head matrix or one block), so that the
+        # reduce-scatter kernels read the weight gradients where the GEMMs wrote them
         shard_mb = (2 * cfg.num_params() // world >> 20) + 64
-        ws = nvlink.enable(process_group, device, staging_mb=256, heap_mb=shard_mb)
+        per_block = 4 * cfg.d_model * cfg.d_model + 2 * cfg.d_model * cfg.ffn + 9 * cfg.d_model + cfg.ffn
+        unit = max((cfg.vocab_size + cfg.max_seq + 2) * cfg.d_model, per_block)  # embedding / head / one block
+        window_bytes = 2 * unit + (1 << 20)
+        ws = nvlink.enable(process_group, device, staging_mb=256, heap_mb=shard_mb + 3 * (window_bytes >> 20) + 8)
+        ws.enable_grad_windows(window_bytes, count=3)
         symm.register_workspace(get_process_group_cached(ProcessGroupName.reduce_scatter), ws)
 
     kw = dict(process_group=process_group, mixed_precision=True, compute_dtype=compute_dtype, reshard_after_forward=True,

@@ -70,6 +70,8 @@ from ...internal.reduce_scatter_bucketer import ReduceScatterBucketer
 from ...internal.state_dict import replace_by_prefix_
 from ...ops.cast import cast_into
 from ...parallel import comm, symm
+from ...utils.failure import poll_device_status
+from ...utils.profiling import comm_range
 from ..misc import flatten_params_wrapper as _fpw
 from ..misc.flatten_params_wrapper import FlattenParamsWrapper
 from ..wrap import auto_wrap, config_auto_wrap_policy, enable_wrap
@@ -1002,6 +1004,7 @@ class FullyShardedDataParallel(nn.Module):
             else:
                 self._use_full_params()
             self._prefetch_prev_unit()
+            self._route_grad_buffers()
             if not self._pre_backward_hook_has_run:
                 self._pre_backward_hook_has_run = True
                 self.assert_state([TrainingState.IDLE, TrainingState.BACKWARD_PRE])
@@ -1024,6 +1027,17 @@ class FullyShardedDataParallel(nn.Module):
             return t
 
         return apply_to_tensors(_register, outputs)
+
+    def _route_grad_buffers(self) -> None:
+        """Before a unit's backward: let its flat gradient be produced in a window of the symmetric heap when it is
+        going to be reduce-scattered by the NVLink kernel (no staging copy); ordinary memory otherwise (``no_sync``,
+        NCCL mode, host-resident shards), because such a gradient may outlive the step."""
+        provider = None
+        if self._require_backward_grad_sync and self.compute_device.type == "cuda" and comm.comm_mode() == "fused" and not self.move_params_to_cpu:
+            ws = symm.workspace_for(self.process_group_reduce_scatter)
+            if ws is not None and hasattr(ws, "grad_window"):
+                provider = ws.grad_window
+        _fpw.set_grad_buffer_provider(provider)
 
     def _register_post_backward_hooks(self) -> None:
         """Make sure every trainable, owned parameter carries the post-accumulate hook (parameters may
@@ -1068,35 +1082,40 @@ class FullyShardedDataParallel(nn.Module):
             produced = param.grad.data
             if self.mixed_precision and self.fp32_reduce_scatter:
                 param.grad.data = param.grad.data.to(param.dtype)
-            if self.gradient_predivide_factor > 1:
-                param.grad.data.div_(self.gradient_predivide_factor)
             ws = symm.workspace_for(self.process_group_reduce_scatter) if param._is_sharded else None  # type: ignore[attr-defined]
-            if (
+            saved = getattr(param, "_saved_grad_shard", None)
+            fused = (
                 ws is not None
                 and comm.comm_mode() == "fused"
                 and param.grad.is_cuda
+                and param._fp32_shard.is_cuda  # type: ignore[attr-defined]  # host-resident master shards take the bucketed path
+                and (saved is None or saved.is_cuda)
                 and param.grad.numel() * param.grad.element_size() > (self.bucket_cap_mb << 20) // max(self.world_size, 1)
                 and ws.can_reduce_scatter(param._fp32_shard, param.grad.data)  # type: ignore[attr-defined]
-                and param.grad.numel() * param.grad.element_size() <= ws.lanes[2].staging_bytes
-            ):
-                # one NVLink kernel: pull-reduce this rank's slice from every peer, apply the complete 1/world
-                # averaging, land in the gradient dtype the optimizer sees and accumulate into an earlier shard
+            )
+            if fused:
+                # one NVLink kernel: pull-reduce this rank's slice from every peer, apply the complete averaging
+                # (pre- and post-division in one factor), land in the gradient dtype the optimizer sees and
+                # accumulate into an earlier shard
                 grad = param.grad.data
                 param.grad = None
-                if self.gradient_predivide_factor > 1:
-                    grad.mul_(self.gradient_predivide_factor)  # undo the pre-division applied above
                 out_dtype = grad.dtype if self.keep_low_precision_grads else param.dtype
-                saved = getattr(param, "_saved_grad_shard", None)
                 accumulate = saved is not None and saved.dtype == out_dtype
-                out = saved if accumulate else torch.empty_like(param._fp32_shard, dtype=out_dtype)  # type: ignore[attr-defined]
+                out = saved if accumulate else torch.empty(param._fp32_shard.shape, dtype=out_dtype, device=grad.device)  # type: ignore[attr-defined]
                 comm._COUNTERS["reduce_scatter"] += 1
-                ws.reduce_scatter(out.view(-1), grad.view(-1), scale=1.0 / self.world_size, accumulate=accumulate)
+                scale = 1.0 / (self.gradient_predivide_factor * self.gradient_postdivide_factor)
+                with comm_range("reduce_scatter"):
+                    ws.reduce_scatter(out.view(-1), grad.view(-1), scale=scale, accumulate=accumulate)
                 if saved is not None and not accumulate:
                     out.add_(saved.to(out.dtype))
                 param._saved_grad_shard = out  # type: ignore[attr-defined]
                 if self.move_grads_to_cpu:
                     param._cpu_grad.copy_(out, non_blocking=True)  # type: ignore[attr-defined]
-            elif param._is_sharded:  # type: ignore[attr-defined]
+                _record_stream(produced, rs_stream)
+                return
+            if self.gradient_predivide_factor > 1:
+                param.grad.data.div_(self.gradient_predivide_factor)
+            if param._is_sharded:  # type: ignore[attr-defined]
                 assert self._reducer is not None
                 grad = param.grad.data
                 param.grad = None
@@ -1118,6 +1137,8 @@ class FullyShardedDataParallel(nn.Module):
                     self._post_reduction_hook(param, grad, in_place=True)
             # the gradient was produced on the compute stream and consumed here
             _record_stream(produced, rs_stream)
+            if ws is not None and hasattr(ws, "release_grad_window"):
+                ws.release_grad_window(produced)
 
     def _post_reduction_hook(self, param: Parameter, reduced_grad: torch.Tensor, in_place: bool = False) -> None:
         """Post-divide, cast to the master dtype, accumulate into ``_saved_grad_shard``, optionally copy to host."""
@@ -1168,11 +1189,15 @@ class FullyShardedDataParallel(nn.Module):
                 assert self._reducer is not None
                 self._reducer.flush()
             cur = _current_stream(self.compute_device)
-            cur.wait_stream(self._streams["post_backward"])
+            with comm_range("exposed_wait_reduce_scatter"):
+                cur.wait_stream(self._streams["post_backward"])
             if self.move_grads_to_cpu:
                 cur.synchronize()  # host copies must have landed before the optimizer reads them
         if self._reducer is not None:
             self._reducer.teardown()
+        if self.compute_device.type == "cuda":
+            # once per step, without a device synchronisation: did a kernel give up a bounded wait?
+            poll_device_status(self.compute_device)
 
         def finalize(m: "FullyShardedDataParallel") -> None:
             if not m._is_root and self._require_backward_grad_sync:
@@ -1262,7 +1287,8 @@ class FullyShardedDataParallel(nn.Module):
             for p in self.params:
                 point_at(p)
             if wait:
-                _current_stream(self.compute_device).wait_stream(ag_stream)
+                with comm_range("exposed_wait_all_gather"):
+                    _current_stream(self.compute_device).wait_stream(ag_stream)
             return out
 
         self.has_full_params = True
@@ -1292,14 +1318,16 @@ class FullyShardedDataParallel(nn.Module):
                     if _storage_is_free(p._full_param_padded):  # type: ignore[attr-defined]
                         alloc_storage_(p._full_param_padded, size=full_size)  # type: ignore[attr-defined]
                     landing = p._full_param_padded  # type: ignore[attr-defined]
-                comm.all_gather_into(landing, shard, group=self.process_group)
+                with comm_range("all_gather"):
+                    comm.all_gather_into(landing, shard, group=self.process_group)
                 point_at(p, landing)
                 if low_precision:
                     self._free_fp16_param_shard([p])
                 if self.move_params_to_cpu and self.params[0].dtype == self.compute_dtype:
                     self._free_fp16_param_shard([p])
         if wait:
-            _current_stream(self.compute_device).wait_stream(ag_stream)
+            with comm_range("exposed_wait_all_gather"):
+                _current_stream(self.compute_device).wait_stream(ag_stream)
         return out
 
     @torch.no_grad()

@@ -18,6 +18,7 @@ from itertools import chain
 from typing import (
     TYPE_CHECKING,
     Any,
+    Callable,
     Dict,
     Generator,
     Iterator,
@@ -125,6 +126,25 @@ class FlatParameter(nn.Parameter):
         )
 
 
+# Optional source of gradient buffers: ``fn(numel, dtype, device) -> Tensor | None``.  The data-parallel wrapper points it
+# at the symmetric heap of its NVLink workspace, so that weight-gradient GEMMs write where the peers' reduce-scatter
+# kernels read and no staging copy is needed; None (the default) or a None result means ordinary device memory.
+_GRAD_BUFFER_PROVIDER: Optional[Callable[[int, torch.dtype, torch.device], Optional[Tensor]]] = None
+
+
+def set_grad_buffer_provider(fn: Optional[Callable[[int, torch.dtype, torch.device], Optional[Tensor]]]) -> None:
+    global _GRAD_BUFFER_PROVIDER
+    _GRAD_BUFFER_PROVIDER = fn
+
+
+def _new_grad_buffer(total: int, dtype: torch.dtype, device: torch.device) -> Tensor:
+    if _GRAD_BUFFER_PROVIDER is not None:
+        buf = _GRAD_BUFFER_PROVIDER(total, dtype, device)
+        if buf is not None:
+            return buf
+    return torch.empty(total, dtype=dtype, device=device)
+
+
 class GradArena:
     """Per-flat-parameter landing zone for weight gradients.
 
@@ -146,7 +166,7 @@ class GradArena:
         if offset in self.claimed:
             return None
         if self.buffer is None:
-            self.buffer = torch.empty(self.total, dtype=dtype, device=device)
+            self.buffer = _new_grad_buffer(self.total, dtype, device)
         elif self.buffer.dtype != dtype or self.buffer.device != device:
             return None
         self.claimed.add(offset)
@@ -155,7 +175,7 @@ class GradArena:
     def take(self, dtype: torch.dtype, device: torch.device) -> Tensor:
         buf = self.buffer
         if buf is None or buf.dtype != dtype or buf.device != device:
-            buf = torch.empty(self.total, dtype=dtype, device=device)
+            buf = _new_grad_buffer(self.total, dtype, device)
         self.buffer = None
         self.claimed = set()
         return buf

@@ -14,6 +14,7 @@ all-gather stream and its gradient-reduction stream.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
@@ -34,6 +35,7 @@ def _sigs() -> None:
 
     head = [c_int, c_int, c_uint, c_int, c_void_p]
     S = _bind._SIGNATURES
+    S["fsb_comm_set_timeout_ms"] = [c_longlong]
     S["fsb_comm_barrier"] = head + [c_void_p, c_void_p]
     S["fsb_comm_all_gather"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_all_to_all"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
@@ -66,6 +68,10 @@ class NvlinkWorkspace:
         import torch.distributed._symmetric_memory as symm_mem
 
         _sigs()
+        if os.environ.get("FSB200_COMM_TIMEOUT_S"):
+            set_timeout(float(os.environ["FSB200_COMM_TIMEOUT_S"]))
+        self._peer_cache: Dict[int, Any] = {}
+        self.poisoned = False  # set when a kernel gave up a wait: flags and epochs can no longer be trusted
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -111,6 +117,55 @@ class NvlinkWorkspace:
             n *= s
         return self.alloc(n * torch.empty((), dtype=dtype).element_size()).view(dtype).view(shape)
 
+    # ------------------------------------------------------------------ gradient windows
+    def enable_grad_windows(self, window_bytes: int, count: int = 3) -> None:
+        """Reserve ``count`` equal windows of the heap (collectively: same offsets on every rank) that :meth:`grad_window`
+        hands out in rotation as flat-gradient buffers.  A gradient produced there is reduce-scattered in place: the
+        peers' kernels read it where the weight-gradient GEMMs wrote it."""
+        if getattr(self, "_gw_offsets", None):
+            return
+        window_bytes = (window_bytes + 255) // 256 * 256
+        self._gw_bytes = window_bytes
+        self._gw_offsets = []
+        for _ in range(count):
+            w = self.alloc(window_bytes)
+            self._gw_offsets.append(w.data_ptr() - self.base)
+        self._gw_next = 0
+        self._gw_busy: Dict[int, Any] = {}
+
+    def grad_window(self, numel: int, dtype: torch.dtype, device: torch.device) -> Optional[torch.Tensor]:
+        """Next gradient window as a ``numel``-element tensor (None if windows are off or too small).  The elements up to
+        the next multiple of the world size (the implicit padding of a reduce-scatter) are zeroed.  The current stream
+        first waits until the previous user of the window (a reduce-scatter, hence also every peer's reads) is done."""
+        offs = getattr(self, "_gw_offsets", None)
+        esize = torch.empty((), dtype=dtype).element_size()
+        pad = 2 * self.world + 16
+        if not offs or self.poisoned or device != self.device or (numel + pad) * esize > self._gw_bytes:
+            return None
+        off = offs[self._gw_next]
+        self._gw_next = (self._gw_next + 1) % len(offs)
+        busy = self._gw_busy.pop(off, None)
+        if busy is not None:
+            torch.cuda.current_stream(self.device).wait_event(busy)
+        buf = self.heap[off : off + (numel + pad) * esize].view(dtype)
+        buf[numel:].zero_()
+        return buf[:numel]
+
+    def _window_of(self, t: torch.Tensor) -> Optional[int]:
+        offs = getattr(self, "_gw_offsets", None)
+        if not offs:
+            return None
+        off = t.data_ptr() - self.base
+        return off if off in offs else None
+
+    def release_grad_window(self, t: torch.Tensor) -> None:
+        """Note that the launches enqueued so far on the current stream are the last readers of gradient window ``t``."""
+        off = self._window_of(t)
+        if off is not None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._gw_busy[off] = ev
+
     def offset_of(self, t: torch.Tensor) -> Optional[int]:
         off = t.data_ptr() - self.base
         if 0 <= off and off + t.numel() * t.element_size() <= self.heap_bytes:
@@ -118,7 +173,14 @@ class NvlinkWorkspace:
         return None
 
     def peers(self, offset: int) -> Any:
-        return _ptr_array([b + offset for b in self.peer_base])
+        """ctypes array with the address of heap offset ``offset`` on every rank (cached: the offsets of persistent
+        shards and staging windows repeat every step)."""
+        arr = self._peer_cache.get(offset)
+        if arr is None:
+            if len(self._peer_cache) > 4096:
+                self._peer_cache.clear()
+            arr = self._peer_cache[offset] = _ptr_array([b + offset for b in self.peer_base])
+        return arr
 
     def _stage(self, lane: _Lane, t: torch.Tensor, total_bytes: Optional[int] = None) -> int:
         """Copy ``t`` into the lane's staging window (zero-padding up to ``total_bytes``); returns its heap offset."""
@@ -147,23 +209,33 @@ class NvlinkWorkspace:
         """A tensor outside the symmetric heap is copied into a lane's staging window first and has to fit there."""
         return self.offset_of(t) is not None or nbytes <= self.lanes[0].staging_bytes
 
+    @staticmethod
+    def _aligned(*tensors: torch.Tensor) -> bool:
+        """The kernels move 16-byte vectors: every CUDA pointer they get must sit on a 16-byte boundary."""
+        return all(t.is_cuda and t.data_ptr() % 16 == 0 for t in tensors)
+
     def can_all_gather(self, out: torch.Tensor, shard: torch.Tensor) -> bool:
         nbytes = shard.numel() * shard.element_size()
-        return out.is_contiguous() and nbytes % 16 == 0 and out.numel() == shard.numel() * self.world and self._fits(shard, nbytes)
+        return (out.is_contiguous() and nbytes % 16 == 0 and out.numel() == shard.numel() * self.world and self._fits(shard, nbytes)
+                and self._aligned(out) and (self.offset_of(shard) is None or self._aligned(shard)))
 
     def can_reduce_scatter(self, out: torch.Tensor, flat_in: torch.Tensor) -> bool:
         if not (flat_in.dtype in _bind._DTYPE_CODE and out.dtype in _bind._DTYPE_CODE and (out.numel() * flat_in.element_size()) % 16 == 0):
             return False
+        if not (self._aligned(out) and flat_in.is_cuda and out.is_contiguous()):
+            return False  # e.g. a host-resident master shard (CPU offload): the kernel writes `out` directly
         need = out.numel() * self.world * flat_in.element_size()
-        in_heap = self.offset_of(flat_in) is not None and flat_in.numel() == out.numel() * self.world
-        return in_heap or need <= self.lanes[0].staging_bytes
+        in_heap = self.offset_of(flat_in) is not None and (flat_in.numel() == out.numel() * self.world or self._window_of(flat_in) is not None)
+        return (in_heap and self._aligned(flat_in)) or need <= self.lanes[0].staging_bytes
 
     def can_all_reduce(self, t: torch.Tensor) -> bool:
-        return t.dtype in _bind._DTYPE_CODE and t.is_contiguous() and self._fits(t, t.numel() * t.element_size())
+        return (t.dtype in _bind._DTYPE_CODE and t.is_contiguous() and self._fits(t, t.numel() * t.element_size())
+                and (self.offset_of(t) is None or self._aligned(t)))
 
     def can_all_to_all(self, out: torch.Tensor, inp: torch.Tensor) -> bool:
         nbytes = inp.numel() * inp.element_size()
-        return inp.is_contiguous() and out.is_contiguous() and (nbytes // self.world) % 16 == 0 and self._fits(inp, nbytes)
+        return (inp.is_contiguous() and out.is_contiguous() and (nbytes // self.world) % 16 == 0 and self._fits(inp, nbytes)
+                and self._aligned(out) and (self.offset_of(inp) is None or self._aligned(inp)))
 
     # ------------------------------------------------------------------ collectives
     def barrier(self, lane: int = 0) -> None:
@@ -187,11 +259,14 @@ class NvlinkWorkspace:
         flat_in = flat_in.contiguous()
         need = n * self.world * flat_in.element_size()
         off = self.offset_of(flat_in)
-        if off is None or flat_in.numel() != n * self.world:
-            off = self._stage(ln, flat_in, need)
+        window = self._window_of(flat_in) if off is not None else None
+        if off is None or (flat_in.numel() != n * self.world and (window is None or need > self._gw_bytes)):
+            off = self._stage(ln, flat_in, need)  # local copy into the lane's staging window (zero padded)
         _bind.call("fsb_comm_reduce_scatter", *self._head(ln), self._counter(ln), self.peers(off), _bind.dtype_code(flat_in.dtype),
                    out.data_ptr(), _bind.dtype_code(out.dtype), n, scale, int(accumulate), _bind.status_ptr(self.device),
                    _bind.stream_ptr(self.device))
+        if window is not None:
+            self.release_grad_window(flat_in)  # the kernel's exit barrier covers the peers' reads of this window
 
     def all_reduce(self, t: torch.Tensor, lane: int = 0) -> None:
         ln = self._lane(lane)
@@ -247,6 +322,14 @@ def enable(group: Any = None, device: Optional[torch.device] = None, staging_mb:
     ws = NvlinkWorkspace(group, device, staging_mb=staging_mb, heap_mb=heap_mb)
     symm.register_workspace(group, ws)
     return ws
+
+
+def set_timeout(seconds: float) -> None:
+    """Limit of one device-side wait for a peer in every collective launched from now on (default 30 s, or
+    ``FSB200_COMM_TIMEOUT_S``).  When a wait runs out the kernel records an error in the device status word and returns;
+    the host raises :class:`fairscale_b200.utils.failure.CommTimeoutError` at its next status check."""
+    _sigs()
+    _bind.call("fsb_comm_set_timeout_ms", int(max(1, round(seconds * 1000))))
 
 
 def available() -> bool:

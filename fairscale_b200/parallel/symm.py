@@ -3,17 +3,31 @@
 A workspace owns peer-mapped staging buffers and signal pads for a group and exposes
 the hand-written collectives.  The registry is empty until
 :func:`fairscale_b200.parallel.nvlink.enable` is called on a multi-GPU NVLink box.
+
+Workspaces are keyed by the group's member ranks (not by the Python object's identity, which a later group can
+reuse once the first one has been collected).
 """
 
 from __future__ import annotations
 
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
-_WORKSPACES: Dict[int, Any] = {}
+_WORKSPACES: Dict[Tuple[int, ...], Any] = {}
+
+
+def _key(group: Any) -> Tuple[int, ...]:
+    import torch.distributed as dist
+
+    try:
+        if group is None or group is dist.group.WORLD:
+            return tuple(range(dist.get_world_size()))
+        return tuple(dist.get_process_group_ranks(group))
+    except Exception:
+        return (-1, id(group))
 
 
 def register_workspace(group: Any, ws: Any) -> None:
-    _WORKSPACES[id(group)] = ws
+    _WORKSPACES[_key(group)] = ws
 
 
 def unregister_all() -> None:
@@ -21,6 +35,17 @@ def unregister_all() -> None:
 
 
 def workspace_for(group: Any) -> Optional[Any]:
+    """The usable workspace of ``group``; None if there is none or a kernel of it reported a failed wait."""
     if not _WORKSPACES:
         return None
-    return _WORKSPACES.get(id(group))
+    ws = _WORKSPACES.get(_key(group))
+    if ws is not None and getattr(ws, "poisoned", False):
+        return None
+    return ws
+
+
+def poison_all() -> None:
+    """Mark every workspace unusable: called when a kernel gave up a bounded wait, which leaves the flags, counters
+    and epochs of the in-kernel collectives in an unknown state.  Callers fall back to ``torch.distributed``."""
+    for ws in _WORKSPACES.values():
+        ws.poisoned = True

@@ -23,10 +23,12 @@ class CommTimeoutError(RuntimeError):
     """A native kernel gave up a bounded wait (on an mbarrier, a peer's flag or a barrier) and returned early."""
 
     def __init__(self, code: int, device: Any):
-        self.code = code
+        self.code = code & 0xFF
+        self.site = code >> 8  # which wait gave up (a number from the kernel's source; 0 when the kernel does not say)
         self.device = device
-        what = {1: "a bounded device-side wait ran out", 2: "a kernel rejected its arguments"}.get(code, "unknown status")
-        super().__init__(f"device {device}: status word {code} ({what}); the outputs of the kernels launched since the last check are invalid")
+        what = {1: "a bounded device-side wait ran out", 2: "a kernel rejected its arguments"}.get(self.code, "unknown status")
+        where = f", wait site {self.site}" if self.site else ""
+        super().__init__(f"device {device}: status word {self.code} ({what}{where}); the outputs of the kernels launched since the last check are invalid")
 
 
 class PeerFailureError(RuntimeError):
@@ -45,7 +47,67 @@ def check_device_status(device: Any = None) -> None:
 
     code = _native.read_status(device)
     if code != 0:
+        _poison_workspaces()
         raise CommTimeoutError(code, device if device is not None else "current")
+
+
+class StatusWatch:
+    """Checks the device status word once per step without stalling the device.
+
+    Each :meth:`poll` looks at the value that the previous poll copied to pinned host memory (if that copy has
+    finished) and starts the next copy on the current stream, so an error written by a kernel of step *i* surfaces as
+    :class:`CommTimeoutError` at step *i + 1* at the latest, with no device synchronisation in between.  The data
+    parallel wrappers poll at the end of every backward; after an error the NVLink workspaces of the process are
+    marked unusable (their collectives fall back to ``torch.distributed``), because a kernel that gave up early has
+    left flags, counters and epochs in an unknown state.
+    """
+
+    def __init__(self, device: Any):
+        import torch
+
+        self.device = torch.device(device)
+        self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._event: Optional[Any] = None
+
+    def poll(self) -> None:
+        import torch
+
+        from .. import _native
+
+        if self._event is not None and self._event.query():
+            code = int(self._host[0])
+            self._event = None
+            if code != 0:
+                _native.status_word(self.device).zero_()
+                _poison_workspaces()
+                raise CommTimeoutError(code, self.device)
+        if self._event is None:
+            self._host.copy_(_native.status_word(self.device), non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+
+_WATCHES: Dict[Any, StatusWatch] = {}
+
+
+def poll_device_status(device: Any) -> None:
+    """Per-step, non-blocking status check of ``device`` (see :class:`StatusWatch`); a no-op for CPU devices."""
+    import torch
+
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        return
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    w = _WATCHES.get(key)
+    if w is None:
+        w = _WATCHES[key] = StatusWatch(torch.device("cuda", key))
+    w.poll()
+
+
+def _poison_workspaces() -> None:
+    from ..parallel import symm
+
+    symm.poison_all()
 
 
 class Heartbeat:

@@ -10,6 +10,7 @@ so existing trace tooling keeps working.
 from __future__ import annotations
 
 from contextlib import contextmanager
+import os
 import statistics
 import subprocess
 import threading
@@ -70,6 +71,38 @@ class EventTimer:
 
     def reset(self) -> None:
         self._pairs.clear()
+
+
+# ------------------------------------------------------------------------------------------------
+# Step breakdown of the data-parallel wrappers: time of every collective on its own stream and the time the
+# compute stream spent waiting for one ("exposed").  Off unless ``FSB200_COMM_TRACE=1`` or ``enable_comm_trace()``.
+# ------------------------------------------------------------------------------------------------
+_COMM_TRACE: Optional["EventTimer"] = None
+
+
+def enable_comm_trace(on: bool = True) -> Optional["EventTimer"]:
+    """Switch the collective / exposed-wait timers on (returns the shared :class:`EventTimer`) or off."""
+    global _COMM_TRACE
+    _COMM_TRACE = EventTimer() if on else None
+    return _COMM_TRACE
+
+
+def comm_trace() -> Optional["EventTimer"]:
+    global _COMM_TRACE
+    if _COMM_TRACE is None and os.environ.get("FSB200_COMM_TRACE", "0") == "1":
+        _COMM_TRACE = EventTimer()
+    return _COMM_TRACE
+
+
+@contextmanager
+def comm_range(name: str) -> Iterator[None]:
+    """Time the enclosed launches on the current stream under ``name`` when the breakdown is enabled (no-op otherwise)."""
+    t = comm_trace()
+    if t is None:
+        yield
+        return
+    with t.time(name):
+        yield
 
 
 class device_timer:

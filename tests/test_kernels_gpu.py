@@ -305,7 +305,8 @@ def test_smoke_entry():
     g.smoke()
 
 
-@pytest.mark.parametrize("B,S,H,D", [(1, 128, 1, 128), (2, 384, 3, 128), (2, 256, 4, 64), (1, 1024, 2, 128)])
+# the last two: the flagship benchmark shape (more work items than SMs, so the persistent kernels loop) and a long D=64 case
+@pytest.mark.parametrize("B,S,H,D", [(1, 128, 1, 128), (2, 384, 3, 128), (2, 256, 4, 64), (1, 1024, 2, 128), (8, 2048, 16, 128), (2, 2048, 12, 64)])
 def test_flash_attention_fwd_bwd(B, S, H, D):
     from fairscale_b200.ops import attention
     from fairscale_b200.ops.attention import causal_attention
@@ -501,9 +502,7 @@ def test_delay_kernel_occupies_the_stream():
     assert 4.5 < t0.elapsed_time(t1) < 50.0
 
 
-@pytest.mark.skipif(os.environ.get("FSB_TEST_PINGPONG", "0") != "1",
-                    reason="opt-in: the two-tile ping-pong forward is enabled with FSB_ATTN_FWD=pingpong and checked with FSB_TEST_PINGPONG=1")
-@pytest.mark.parametrize("B,S,H,D", [(1, 256, 1, 128), (1, 512, 2, 128), (2, 1024, 2, 64)])
+@pytest.mark.parametrize("B,S,H,D", [(1, 256, 1, 128), (1, 512, 2, 128), (2, 1024, 2, 64), (4, 2048, 40, 128)])
 def test_flash_attention_pingpong_forward(B, S, H, D):
     """The ping-pong forward (called through its own C symbol) against the fp32 reference and the one-tile kernel."""
     from fairscale_b200.ops import _bind
