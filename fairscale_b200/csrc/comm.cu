@@ -107,7 +107,33 @@ reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n
   const long long nvec = n / E;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long base = static_cast<long long>(c.rank) * n;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // two ranks: two vectors per thread and pass, so that a thread still has four peer loads in flight
+  if (c.world <= 2) {
+    for (; i + stride < nvec; i += 2 * stride) {
+      uint4 v[2][2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          if (q < c.world) v[u][q] = ld_peer16(reinterpret_cast<const TI*>(src.p[q]) + base + (i + u * stride) * E);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          if (q < c.world) Acc8<TI>::add(a, v[u][q]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          float r = a[e] * scale;
+          TO* o = out + (i + u * stride) * E + e;
+          if (accumulate) r += to_f32<TO>(*o);
+          *o = from_f32<TO>(r);
+        }
+      }
+    }
+  }
+  for (; i < nvec; i += stride) {
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     // peers in groups of COMM_UNROLL (their loads in flight together); fixed summation order (rank 0, 1, ...), so the
     // result does not depend on timing
@@ -289,7 +315,8 @@ static fsb::PtrTable make_table(void* const* ptrs, int world) {
   for (int i = 0; i < world && i < fsb::kMaxRanks; ++i) t.p[i] = ptrs[i];
   return t;
 }
-// FSB_COMM_MAX_CTAS overrides the CTA cap of the streaming collectives (default: two 128-thread CTAs per SM).
+// FSB_COMM_MAX_CTAS overrides the CTA cap of the streaming collectives (default: one 128-thread CTA per SM, so that two
+// collectives running on different streams still leave room for a persistent GEMM CTA on every SM).
 static int comm_grid(long long work_items, int max_blocks) {
   static int cap = -1;
   if (cap < 0) {
@@ -324,8 +351,26 @@ FSB_API int fsb_comm_all_gather(int rank, int world, unsigned epoch, int channel
                                 void* out, long long nbytes, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks || nbytes % 16) return -1;
   const long long n16 = nbytes / 16;
-  fsb::all_gather_kernel<<<comm_grid(n16, 148 * 2), fsb::COMM_THREADS, 0, stream>>>(
+  fsb::all_gather_kernel<<<comm_grid(n16, 148), fsb::COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), n16);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The same all-gather with the payload moved by the copy engines: flag barrier (peers' shards are final) -> one
+// cudaMemcpyAsync per peer from its mapped shard -> flag barrier (peers are done reading mine).  No SM takes part in the
+// transfer, so kernels of other streams keep the whole GPU; the price is world + 1 enqueues instead of one.
+// Uses epochs `epoch` (entry) and `epoch + 1` (exit) on `channel`: the caller advances its epoch by two.
+FSB_API int fsb_comm_all_gather_dma(int rank, int world, unsigned epoch, int channel, void* const* pads, void* const* src, void* out,
+                                    long long nbytes, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks) return -1;
+  fsb::barrier_kernel<<<1, fsb::COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch, channel, pads, nullptr, status));
+  for (int k = 0; k < world; ++k) {
+    const int p = (rank + k) % world;  // own shard first, then the ring: the peers' copy engines start on different sources
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(out) + static_cast<long long>(p) * nbytes, src[p], static_cast<size_t>(nbytes),
+                                    cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  fsb::barrier_kernel<<<1, fsb::COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch + 1u, channel, pads, nullptr, status));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -333,7 +378,7 @@ FSB_API int fsb_comm_all_to_all(int rank, int world, unsigned epoch, int channel
                                 void* out, long long chunk_bytes, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks || chunk_bytes % 16) return -1;
   const long long n16 = chunk_bytes / 16;
-  fsb::all_to_all_kernel<<<comm_grid(n16, 148 * 2), fsb::COMM_THREADS, 0, stream>>>(
+  fsb::all_to_all_kernel<<<comm_grid(n16, 148), fsb::COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), n16);
   return static_cast<int>(cudaGetLastError());
 }
@@ -347,7 +392,7 @@ FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int cha
   if ((n * (in_dtype == FSB_F32 ? 4 : 2)) % 16) return -1;  // each rank's chunk must start 16-byte aligned
   const CommCtx c = make_ctx(rank, world, epoch, channel, pads, counter, status);
   const PtrTable t = make_table(src, world);
-  const int grid = comm_grid(n / 8, 148 * 2);
+  const int grid = comm_grid(n / 8, 148);
 #define FSB_RS(IC, IT, OC, OT)                                                                                          \
   if (in_dtype == IC && out_dtype == OC) {                                                                              \
     reduce_scatter_kernel<IT, OT><<<grid, COMM_THREADS, 0, stream>>>(c, t, static_cast<OT*>(out), n, scale, accumulate); \
@@ -389,7 +434,7 @@ FSB_API int fsb_comm_moe_scatter_rows(int rank, int world, unsigned epoch, int c
                                       long long T, int rows_per_token, int M, int* status, cudaStream_t stream) {
   using namespace fsb;
   if (world > kMaxRanks || M % 8) return -1;
-  moe_scatter_rows_kernel<<<comm_grid(T * 32, 148 * 2), COMM_THREADS, 0, stream>>>(
+  moe_scatter_rows_kernel<<<comm_grid(T * 32, 148), COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(dst, world), static_cast<const __nv_bfloat16*>(x),
       dst_rank, dst_row, w, T, rows_per_token, M);
   return static_cast<int>(cudaGetLastError());
@@ -401,7 +446,7 @@ FSB_API int fsb_comm_moe_gather_rows(int rank, int world, unsigned epoch, int ch
                                      cudaStream_t stream) {
   using namespace fsb;
   if (world > kMaxRanks || M % 8 || rows_per_token > 4) return -1;
-  moe_gather_rows_kernel<<<comm_grid(tokens * 32, 148 * 2), COMM_THREADS, 0, stream>>>(
+  moe_gather_rows_kernel<<<comm_grid(tokens * 32, 148), COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<__nv_bfloat16*>(out), src_rank,
       src_row, w, static_cast<const __nv_bfloat16*>(g), dot, tokens, rows_per_token, M);
   return static_cast<int>(cudaGetLastError());

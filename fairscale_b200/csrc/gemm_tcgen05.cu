@@ -23,6 +23,7 @@
 #include "gemm_tile.cuh"
 
 #include <cstdlib>
+#include <mutex>
 
 namespace fsb {
 
@@ -209,6 +210,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 constexpr int PAIR_BLOCK_N = 256;
 constexpr int PAIR_HALF_N = 128;
 constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_SCHED_DEPTH = 4;                      // tile indices in flight between the scheduler and its readers
 constexpr int PAIR_EPI_WARPS = 8;                        // two per TMEM lane quadrant, 128 columns each
 constexpr int PAIR_THREADS = 64 + 32 * PAIR_EPI_WARPS;   // producer warp + MMA warp + epilogue warps
 
@@ -218,27 +220,37 @@ struct PairSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_OFFSET = PAIR_STAGES * STAGE_BYTES;           // 4 KB of staging per epilogue warp
   static constexpr int BAR_OFFSET = EPI_OFFSET + PAIR_EPI_WARPS * 4096;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+  // No slack for re-aligning the base: the kernel has no static shared memory, so its dynamic window starts 1024-byte
+  // aligned (checked at run time).  With the 1 KB the hardware reserves per CTA this leaves 2816 bytes of the SM's
+  // 228 KB, enough for two of the 128-thread communication CTAs (1 KB reserve + 8 bytes each) to stay resident beside
+  // a GEMM CTA; a third would keep the next GEMM CTA off the SM.
+  static constexpr int TOTAL = BAR_OFFSET + 256;
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
   using L = PairSmem;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {  // same for every thread of the pair: nothing has been set up yet
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, FSB_ERR_BAD_ARG);
+    return;
+  }
 
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
   uint64_t* empty_bar = full_bar + PAIR_STAGES;
   uint64_t* tmem_full_bar = empty_bar + PAIR_STAGES;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint64_t* sched_full = tmem_empty_bar + 2;           // [PAIR_SCHED_DEPTH] in every CTA: the slot holds a tile index
+  uint64_t* sched_empty = sched_full + PAIR_SCHED_DEPTH;  // [PAIR_SCHED_DEPTH] in the leader: every reader has taken it
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + PAIR_SCHED_DEPTH);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_cast<int*>(sched_tile) + PAIR_SCHED_DEPTH);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);  // warp-uniform
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
   const int tiles_m = (p.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
@@ -256,6 +268,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       mbar_init(&tmem_full_bar[a], 1);
       mbar_init(&tmem_empty_bar[a], 2 * PAIR_EPI_WARPS);  // the epilogue warps of both CTAs of the pair
     }
+    for (int q = 0; q < PAIR_SCHED_DEPTH; ++q) {
+      mbar_init(&sched_full[q], 1);
+      mbar_init(&sched_empty[q], 2 + 2 * PAIR_EPI_WARPS);  // the peer's producer, the MMA warp, all epilogue warps of the pair
+    }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -270,19 +286,66 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
+  // Tiles are handed out at run time: the leader's producer takes the next index from a counter in global memory and
+  // publishes it (or -1 at the end) to both CTAs through a small ring; every role reads the ring in order.  An SM that
+  // is slowed down or taken by a kernel of another stream (a collective) then simply works off fewer tiles, instead of
+  // holding back the tiles a static schedule would have given it.
+  // Reader side: wait for slot q, take the index, hand the slot back to the leader.
+  auto take_tile = [&](int q, uint32_t qphase, int site) -> int {
+    if (!mbar_wait_cluster(&sched_full[q], qphase, abort_flag, site)) return -2;
+    const int t = sched_tile[q];
+    mbar_arrive_cluster(map_to_cta(smem_u32(&sched_empty[q]), 0));
+    return t;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int q = 0;
+      uint32_t qphase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      // Leader: `cur` is the tile to load now (already published), `nxt` the one after it.  Indices are published one
+      // tile ahead, so the other roles find theirs without waiting, and fetched one more tile ahead, so the atomic's
+      // round trip hides behind a whole tile of loads.
+      auto publish = [&](int t) -> bool {
+        if (!mbar_wait(&sched_empty[q], qphase ^ 1u, abort_flag, 2)) return false;
+        sched_tile[q] = t;
+        st_shared_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(&sched_tile[q])), 1), static_cast<uint32_t>(t));
+        mbar_arrive_cluster(map_to_cta(smem_u32(&sched_full[q]), 0));
+        mbar_arrive_cluster(map_to_cta(smem_u32(&sched_full[q]), 1));
+        if (++q == PAIR_SCHED_DEPTH) { q = 0; qphase ^= 1u; }
+        return true;
+      };
+      int cur = -1, nxt = -1;
+      if (leader) {
+        cur = static_cast<int>(atomicAdd(&p.sched[0], 1u));
+        if (cur >= num_tiles) cur = -1;
+        ok = publish(cur);
+        if (cur >= 0) nxt = static_cast<int>(atomicAdd(&p.sched[0], 1u));
+      }
+      while (ok) {
+        int tile;
+        if (leader) {
+          tile = cur;
+          if (tile >= 0) {
+            const int nt = nxt < num_tiles ? nxt : -1;
+            if (!publish(nt)) break;
+            cur = nt;
+            if (nt >= 0) nxt = static_cast<int>(atomicAdd(&p.sched[0], 1u));  // used one tile from now
+          }
+        } else {
+          tile = take_tile(q, qphase, 3);
+          if (++q == PAIR_SCHED_DEPTH) { q = 0; qphase ^= 1u; }
+        }
+        if (tile < 0) break;
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
         const int n0 = tn * PAIR_BLOCK_N + static_cast<int>(rank) * PAIR_HALF_N;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 4)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * L::STAGE_BYTES);
@@ -303,6 +366,15 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
+      if (leader) {
+        // the last pair to get here has seen every pair's final fetch: put the counters back for the next launch
+        __threadfence();
+        if (atomicAdd(&p.sched[1], 1u) == static_cast<unsigned int>(num_pairs - 1)) {
+          p.sched[0] = 0u;
+          p.sched[1] = 0u;
+          __threadfence();
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only; all lanes run the loop,
@@ -315,13 +387,20 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      int q = 0;
+      uint32_t qphase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        if (!mbar_wait_warp(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+      while (ok) {
+        int tile = 0;
+        if (lane == 0) tile = take_tile(q, qphase, 5);
+        tile = __shfl_sync(0xffffffffu, tile, 0);
+        if (++q == PAIR_SCHED_DEPTH) { q = 0; qphase ^= 1u; }
+        if (tile < 0) break;
+        if (!mbar_wait_warp(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag, 6)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag, 7)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
@@ -358,15 +437,22 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     const bool coalesce = epilogue_can_coalesce(p);
     int acc = 0;
     uint32_t acc_phase = 0;
+    int q = 0;
+    uint32_t qphase = 0;
     bool ok = true;
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+    while (ok) {
+      int tile = 0;
+      if (lane == 0) tile = take_tile(q, qphase, 8);
+      tile = __shfl_sync(0xffffffffu, tile, 0);
+      if (++q == PAIR_SCHED_DEPTH) { q = 0; qphase ^= 1u; }
+      if (tile < 0) break;
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int row0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M + quad * 32;
       const int n0 = tn * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2);
       uint4 pre[8];
       if (coalesce && epilogue_needs_aux(p.epilogue) && n0 < p.N) epi_slab_prefetch(pre, p.aux, p.ld_aux, row0, n0, p.M, p.N, lane);
-      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, 9)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2)) +
                               (static_cast<uint32_t>(quad * 32) << 16);
@@ -385,7 +471,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
-    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, FSB_ERR_WAIT_TIMEOUT);
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, FSB_ERR_WAIT_TIMEOUT | (*abort_flag << 8));
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
@@ -398,6 +484,24 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
 }
 
 }  // namespace fsb
+
+// Counter pairs of the dynamic tile scheduler: a ring of slots per device, one slot per launch, so that GEMMs running
+// at the same time on different streams never share a counter.  A slot is all zero whenever no kernel is using it (the
+// kernel resets it), hence 64 launches would have to be in flight at once on one device before two could collide.
+static unsigned int* next_sched_slot(int di) {
+  constexpr int kSlots = 64;
+  static std::mutex mu;
+  static unsigned int* base[64] = {nullptr};
+  static unsigned int seq[64] = {0};
+  std::lock_guard<std::mutex> lock(mu);
+  if (base[di] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaMalloc(&ptr, kSlots * 2 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    if (cudaMemset(ptr, 0, kSlots * 2 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    base[di] = static_cast<unsigned int*>(ptr);
+  }
+  return base[di] + 2 * ((seq[di]++) % kSlots);
+}
 
 // C ABI ------------------------------------------------------------------------------------------
 // lda / ldb: elements between consecutive rows of the *stored* matrix ([rows,K] when K-major,
@@ -431,6 +535,7 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
   p.status = status;
   p.batch = 1; p.stride_c = p.stride_aux = p.stride_bias = 0;
+  p.sched = nullptr;
 
   int dev = 0;
   cudaGetDevice(&dev);
@@ -460,6 +565,8 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
     const int pair_tiles = ((M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((N + PAIR_BLOCK_N - 1) / PAIR_BLOCK_N);
     const int max_pairs = num_sms / 2;
     const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+    p.sched = next_sched_slot(di);
+    if (p.sched == nullptr) return -1;
     gemm_bf16_tcgen05_pair_kernel<<<2 * pairs, PAIR_THREADS, PairSmem::TOTAL, stream>>>(ta, tb, p);
     return static_cast<int>(cudaGetLastError());
   }
@@ -511,6 +618,7 @@ FSB_API int fsb_gemm_bf16_batched(const void* A, const void* B, void* C, const v
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
   p.status = status;
+  p.sched = nullptr;
   p.batch = batch; p.stride_c = stride_c; p.stride_aux = stride_aux > 0 ? stride_aux : stride_c; p.stride_bias = stride_bias;
   int dev = 0, num_sms = 0;
   cudaGetDevice(&dev);

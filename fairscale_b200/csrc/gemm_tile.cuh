@@ -36,6 +36,9 @@ struct GemmParams {
   // batched (grouped) products: `batch` independent problems of the same shape; element strides between them
   int batch;
   long long stride_c, stride_aux, stride_bias;
+  // dynamic tile scheduler of the CTA-pair kernel: sched[0] = next tile to hand out, sched[1] = pairs that have finished
+  // (both zero before the launch; the last pair to finish resets them)
+  unsigned int* sched;
 };
 
 // Parameters of problem `b` of a batch (pointers advanced; everything else shared).

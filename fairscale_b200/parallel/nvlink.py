@@ -38,6 +38,7 @@ def _sigs() -> None:
     S["fsb_comm_set_timeout_ms"] = [c_longlong]
     S["fsb_comm_barrier"] = head + [c_void_p, c_void_p]
     S["fsb_comm_all_gather"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
+    S["fsb_comm_all_gather_dma"] = head + [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_all_to_all"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_reduce_scatter"] = head + [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
     S["fsb_comm_all_reduce"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p]
@@ -63,6 +64,7 @@ class _Lane:
 
 class NvlinkWorkspace:
     N_LANES = 4
+    DMA_MIN_BYTES = 1 << 20  # below this the extra enqueues of the copy-engine all-gather cost more than they save
 
     def __init__(self, group: Any, device: torch.device, staging_mb: int = 256, heap_mb: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
@@ -71,6 +73,8 @@ class NvlinkWorkspace:
         if os.environ.get("FSB200_COMM_TIMEOUT_S"):
             set_timeout(float(os.environ["FSB200_COMM_TIMEOUT_S"]))
         self._peer_cache: Dict[int, Any] = {}
+        # "kernel": one kernel pulls the shards with SM-issued loads; "dma": copy engines move them between two flag barriers
+        self.all_gather_engine = os.environ.get("FSB200_AG", "dma").lower()
         self.poisoned = False  # set when a kernel gave up a wait: flags and epochs can no longer be trusted
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
@@ -248,8 +252,16 @@ class NvlinkWorkspace:
         off = self.offset_of(shard)
         if off is None:
             off = self._stage(ln, shard)
+        nbytes = shard.numel() * shard.element_size()
+        if self.all_gather_engine == "dma" and nbytes >= self.DMA_MIN_BYTES:
+            # payload on the copy engines (no SM takes part): two flag barriers around one peer copy per rank
+            head = self._head(ln)
+            ln.epoch = (ln.epoch + 1) & 0x7FFFFFFF  # the exit barrier uses the next epoch
+            _bind.call("fsb_comm_all_gather_dma", *head, self.peers(off), out.data_ptr(), nbytes, _bind.status_ptr(self.device),
+                       _bind.stream_ptr(self.device), launches=2)
+            return
         _bind.call("fsb_comm_all_gather", *self._head(ln), self._counter(ln), self.peers(off), out.data_ptr(),
-                   shard.numel() * shard.element_size(), _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
+                   nbytes, _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
 
     def reduce_scatter(self, out: torch.Tensor, flat_in: torch.Tensor, scale: float = 1.0, accumulate: bool = False, lane: int = 2) -> None:
         """``out = (out if accumulate else 0) + scale * sum_ranks flat_in[rank * n : (rank + 1) * n]``, n = out.numel();
