@@ -33,14 +33,14 @@ class _RecvBoundary(torch.autograd.Function):
     """Identity on a received activation whose backward ships the gradient to the previous stage."""
 
     @staticmethod
-    def forward(ctx: Any, x: Tensor, transport: SendRecvTransport, prev_rank: int) -> Tensor:  # type: ignore[override]
-        ctx.transport, ctx.prev_rank = transport, prev_rank
+    def forward(ctx: Any, x: Tensor, transport: SendRecvTransport, prev_rank: int, slot: Optional[int] = None) -> Tensor:  # type: ignore[override]
+        ctx.transport, ctx.prev_rank, ctx.slot = transport, prev_rank, slot
         return x.view_as(x)
 
     @staticmethod
     def backward(ctx: Any, grad: Tensor):  # type: ignore[override]
-        ctx.transport.send(grad, ctx.prev_rank)
-        return grad, None, None
+        ctx.transport.send(grad, ctx.prev_rank, slot=ctx.slot)
+        return grad, None, None, None
 
 
 def check_balance(module: Union[nn.Sequential, List[LazyModule]], balance: Sequence[int]) -> None:
@@ -267,13 +267,13 @@ class AsyncPipe(nn.Module):
             if first:
                 x = batches[i]
             else:
-                x = self.transport.recv(self.rank - 1)
+                x = self.transport.recv(self.rank - 1, slot=i)
                 if x.requires_grad and torch.is_grad_enabled():
-                    x = _RecvBoundary.apply(x, self.transport, self.rank - 1)
+                    x = _RecvBoundary.apply(x, self.transport, self.rank - 1, n + i)  # gradient slots follow the activation slots
             y = self._run_stage(x, i < stop)
             assert isinstance(y, Tensor), "stages of AsyncPipe exchange single tensors"
             if not last:
-                self.transport.send(y, self.rank + 1)
+                self.transport.send(y, self.rank + 1, slot=i)
             outs.append(y)
         self._outputs = outs
         if last:
@@ -292,7 +292,9 @@ class AsyncPipe(nn.Module):
             self.transport.flush()
             return
         outs = self._outputs if output is None else output
-        grads = [self.transport.recv(self.rank + 1) for _ in outs]  # next stage emits them in its backward order
+        n = len(outs)
+        # the next stage emits the gradients in its backward order: last micro-batch first
+        grads = [self.transport.recv(self.rank + 1, slot=n + (n - 1 - k)) for k in range(n)]
         # the final stage back-propagates torch.cat(outs): gradients arrive in autograd's (reverse) order
         for y, g in zip(reversed(outs), grads):
             if y.requires_grad:

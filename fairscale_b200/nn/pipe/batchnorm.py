@@ -1,17 +1,17 @@
-"""BatchNorm whose running statistics follow the mini-batch, not the micro-batch.
+"""BatchNorm whose running statistics see the whole mini-batch although the layer only ever sees micro-batches.
 
-Parity: fairscale/nn/pipe/batchnorm.py:37-172.  Each micro-batch is normalised with its own batch statistics
-(as GPipe requires), while sums and squared sums are accumulated across the ``chunks`` micro-batches and folded
-into ``running_mean`` / ``running_var`` once per mini-batch; recomputation passes are not counted.
+Normalisation itself uses each micro-batch's own statistics (as ``nn.BatchNorm`` in training mode does); the *running*
+mean and variance are updated once per mini-batch from sums accumulated over its ``chunks`` micro-batches, so they
+match what an un-piped model would have tracked.  Contract of fairscale/nn/pipe/batchnorm.py:34-172.
 """
 
 from __future__ import annotations
 
-from typing import Optional, TypeVar, cast
+from typing import List, Optional, TypeVar, cast
 
 import torch
-import torch.nn.functional as F
 from torch import Tensor, nn
+import torch.nn.functional as F
 from torch.nn.modules.batchnorm import _BatchNorm
 
 from .checkpoint import is_recomputing
@@ -27,61 +27,62 @@ class DeferredBatchNorm(_BatchNorm):
 
     def __init__(self, num_features: int, eps: float = 1e-5, momentum: Optional[float] = 0.1, affine: bool = True, chunks: int = 1) -> None:
         super().__init__(num_features, eps, momentum, affine, track_running_stats=True)
-        self.register_buffer("sum", torch.zeros_like(self.running_mean))
-        self.register_buffer("sum_squares", torch.zeros_like(self.running_var))
-        self.counter = 0
-        self.tracked = 0
+        for name in ("sum", "sum_squares"):  # per-channel totals of the current mini-batch (part of the state dict)
+            self.register_buffer(name, torch.zeros(num_features))
         self.chunks = chunks
+        self.counter = 0  # elements per channel behind the totals
+        self.tracked = 0  # micro-batches behind the totals
 
     def _check_input_dim(self, input: Tensor) -> None:
-        if input.dim() <= 2:
+        if input.dim() < 3:
             raise ValueError("expected at least 3D input (got %dD input)" % input.dim())
 
-    def _track(self, input: Tensor) -> bool:
-        """Accumulate this micro-batch; True once all ``chunks`` micro-batches were seen."""
-        reduce_dims = [0] + list(range(2, input.dim()))
-        with torch.no_grad():
-            self.sum += input.sum(reduce_dims)
-            self.sum_squares += (input**2).sum(reduce_dims)
-        self.counter += input.numel() // input.size(1)
+    @torch.no_grad()
+    def _accumulate(self, x: Tensor) -> None:
+        """Add one micro-batch to the totals."""
+        per_channel = x.transpose(0, 1).reshape(x.size(1), -1)
+        self.sum.add_(per_channel.sum(1))
+        self.sum_squares.add_(per_channel.square().sum(1))
+        self.counter += per_channel.size(1)
         self.tracked += 1
-        return self.tracked == self.chunks
 
-    def _commit(self) -> None:
-        """Fold the accumulated mini-batch statistics into the running ones."""
+    @torch.no_grad()
+    def _fold_into_running_stats(self) -> None:
+        """The mini-batch is complete: update the running statistics from the totals and clear them."""
         self.num_batches_tracked += 1
-        factor = 1.0 / float(self.num_batches_tracked) if self.momentum is None else self.momentum
-        mean = self.sum / self.counter
-        var = self.sum_squares / self.counter - mean**2
-        self.running_mean.mul_(1 - factor).add_(mean * factor)
-        self.running_var.mul_(1 - factor).add_(var * factor)
+        # momentum None means a cumulative average over all mini-batches seen so far
+        step = self.momentum if self.momentum is not None else 1.0 / float(self.num_batches_tracked)
+        batch_mean = self.sum / self.counter
+        batch_var = self.sum_squares / self.counter - batch_mean.square()
+        self.running_mean.mul_(1 - step).add_(batch_mean, alpha=step)
+        self.running_var.mul_(1 - step).add_(batch_var, alpha=step)
         self.sum.zero_()
         self.sum_squares.zero_()
-        self.counter = 0
-        self.tracked = 0
+        self.counter = self.tracked = 0
 
     def forward(self, input: Tensor) -> Tensor:  # type: ignore[override]
-        if not self.training:
-            return F.batch_norm(input, self.running_mean, self.running_var, self.weight, self.bias, False, 0.0, self.eps)
-        if not is_recomputing():
-            if self._track(input):
-                self._commit()
-        return F.batch_norm(input, None, None, self.weight, self.bias, True, 0.0, self.eps)
+        use_batch_stats = self.training
+        if use_batch_stats and not is_recomputing():  # a recomputed forward must not count its micro-batch twice
+            self._accumulate(input)
+            if self.tracked == self.chunks:
+                self._fold_into_running_stats()
+        mean, var = (None, None) if use_batch_stats else (self.running_mean, self.running_var)
+        return F.batch_norm(input, mean, var, self.weight, self.bias, use_batch_stats, 0.0, self.eps)
 
     @classmethod
     def convert_deferred_batch_norm(cls, module: TModule, chunks: int = 1) -> TModule:
-        """Recursively replace tracking BatchNorm layers by deferred ones sharing the same parameters and buffers."""
-        if isinstance(module, DeferredBatchNorm) and module.chunks is chunks:
-            return cast(TModule, module)
-        out: nn.Module = module
-        if isinstance(module, _BatchNorm) and module.track_running_stats:
-            out = DeferredBatchNorm(module.num_features, module.eps, module.momentum, module.affine, chunks)
-            if module.affine:
-                out.register_parameter("weight", module.weight)
-                out.register_parameter("bias", module.bias)
-            out.register_buffer("running_mean", module.running_mean)
-            out.register_buffer("running_var", module.running_var)
-            out.register_buffer("num_batches_tracked", module.num_batches_tracked)
-        for name, child in module.named_children():
-            out.add_module(name, cls.convert_deferred_batch_norm(child, chunks))
-        return cast(TModule, out)
+        """``module`` with every ``_BatchNorm`` that tracks running statistics replaced by a deferred one (weights,
+        statistics and counters carried over); other modules are converted in place, child by child."""
+        already = isinstance(module, DeferredBatchNorm) and module.chunks == chunks
+        if already or not isinstance(module, _BatchNorm):
+            if not already:
+                for name, child in list(module.named_children()):
+                    setattr(module, name, cls.convert_deferred_batch_norm(child, chunks))
+            return module
+        if not module.track_running_stats:
+            return module
+        twin = cls(module.num_features, module.eps, module.momentum, module.affine, chunks)
+        carried = ["running_mean", "running_var", "num_batches_tracked"] + (["weight", "bias"] if module.affine else [])
+        for name in carried:
+            setattr(twin, name, getattr(module, name))  # parameters and buffers are shared, not copied
+        return cast(TModule, twin)

@@ -1,13 +1,14 @@
-"""Artificial autograd dependencies between micro-batches (parity: fairscale/nn/pipe/dependency.py:29-67).
+"""Ordering edges for autograd: ``fork`` splits a zero-size token off a tensor, ``join`` ties a token to another tensor.
 
-``fork(a)`` returns ``(a, phony)``; ``join(b, phony)`` returns ``b``.  In backward, ``Join`` hands a gradient
-to the phony, which reaches ``Fork`` — so everything before ``join`` in the graph of ``b`` must run its
-backward before the backward of ``a`` continues.  This serialises micro-batch backward in pipeline order.
+After ``a, token = fork(a)`` and ``b = join(b, token)`` the backward of everything that produced ``b`` runs before the
+backward of what produced ``a`` continues, because ``a``'s producer now also waits for the token's (empty) gradient.
+The pipeline uses this to replay micro-batches in reverse order on every stage and to place recomputation right before
+the backward it serves.  Same contract as fairscale/nn/pipe/dependency.py:29-67.
 """
 
 from __future__ import annotations
 
-from typing import List, Tuple
+from typing import Any, List, Optional, Tuple
 
 import torch
 from torch import Tensor
@@ -17,35 +18,41 @@ from .phony import get_phony
 __all__: List[str] = []
 
 
-def fork(input: Tensor) -> Tuple[Tensor, Tensor]:
-    if torch.is_grad_enabled() and input.requires_grad:
-        input, phony = Fork.apply(input)
-    else:
-        phony = get_phony(input.device, requires_grad=False)
-    return input, phony
+def _tracked(*tensors: Tensor) -> bool:
+    return torch.is_grad_enabled() and any(t.requires_grad for t in tensors)
 
 
 class Fork(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx: "Fork", input: Tensor) -> Tuple[Tensor, Tensor]:  # type: ignore[override]
-        return input.detach(), get_phony(input.device, requires_grad=False).detach()
+    """(x) -> (x, token).  The token's gradient is ignored; what matters is that this node has two consumers."""
 
     @staticmethod
-    def backward(ctx: "Fork", grad_input: Tensor, grad_grad: Tensor) -> Tensor:  # type: ignore[override]
-        return grad_input
+    def forward(ctx: Any, x: Tensor) -> Tuple[Tensor, Tensor]:  # type: ignore[override]
+        ctx.set_materialize_grads(False)  # an unused token contributes None, not a zero tensor
+        token = get_phony(x.device, requires_grad=False)
+        return x.detach(), token.detach()
 
-
-def join(input: Tensor, phony: Tensor) -> Tensor:
-    if torch.is_grad_enabled() and (input.requires_grad or phony.requires_grad):
-        input = Join.apply(input, phony)
-    return input
+    @staticmethod
+    def backward(ctx: Any, grad_x: Optional[Tensor], grad_token: Optional[Tensor]) -> Optional[Tensor]:  # type: ignore[override]
+        return grad_x
 
 
 class Join(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx: "Join", input: Tensor, phony: Tensor) -> Tensor:  # type: ignore[override]
-        return input.detach()
+    """(x, token) -> x.  The token gets no gradient, but its producer is now upstream of x's consumers."""
 
     @staticmethod
-    def backward(ctx: "Join", grad_input: Tensor) -> Tuple[Tensor, None]:  # type: ignore[override]
-        return grad_input, None
+    def forward(ctx: Any, x: Tensor, token: Tensor) -> Tensor:  # type: ignore[override]
+        return x.detach()
+
+    @staticmethod
+    def backward(ctx: Any, grad_x: Tensor) -> Tuple[Tensor, None]:  # type: ignore[override]
+        return grad_x, None
+
+
+def fork(input: Tensor) -> Tuple[Tensor, Tensor]:
+    if _tracked(input):
+        return Fork.apply(input)
+    return input, get_phony(input.device, requires_grad=False)
+
+
+def join(input: Tensor, phony: Tensor) -> Tensor:
+    return Join.apply(input, phony) if _tracked(input, phony) else input

@@ -1,9 +1,12 @@
 """Point-to-point transport between pipeline stages.
 
 The reference pickles a 1 KB header per message and synchronises the CUDA stream around every send / recv
-(fairscale/nn/pipe/messages.py:109-151).  Here a message is a fixed int64 header (ndim, dtype code, dims) plus
-the payload, both sent with ``torch.distributed`` p2p (NCCL over NVLink on GPUs, gloo on CPU) without host
-synchronisation: NCCL orders the transfers on its own stream and the consumer kernel waits on it.
+(fairscale/nn/pipe/messages.py:109-151).  Here a message is a fixed int64 header (ndim, dtype code, dims) plus the
+payload, both sent with ``torch.distributed`` p2p (NCCL over NVLink on GPUs, gloo on CPU).  Reading the header costs
+the receiver one host synchronisation.  With ``static_shapes=True`` and a ``slot`` per message (the micro-batch index)
+the header travels only the first time a (peer, slot) pair is used: from then on both sides rely on the recorded
+shape / dtype contract, the receive is posted straight into a correctly sized buffer and nothing is read on the host.
+A sender whose tensor no longer matches its contract raises instead of sending.
 """
 
 from __future__ import annotations
@@ -34,47 +37,72 @@ class Transport:
 
     device: torch.device
 
-    def send(self, t: Tensor, dst: int) -> None:
+    def send(self, t: Tensor, dst: int, slot: Optional[int] = None) -> None:
         raise NotImplementedError
 
-    def recv(self, src: int) -> Tensor:
+    def recv(self, src: int, slot: Optional[int] = None) -> Tensor:
         raise NotImplementedError
 
     def flush(self) -> None:
         raise NotImplementedError
 
 
+Signature = Tuple[Tuple[int, ...], torch.dtype, bool]  # shape, dtype, requires_grad
+
+
 class SendRecvTransport(Transport):
     """Blocking-receive / async-send tensor transport for one pipeline group."""
 
-    def __init__(self, group: Any, device: torch.device):
+    def __init__(self, group: Any, device: torch.device, static_shapes: bool = False):
         self.group = group
         self.device = device
+        self.static_shapes = static_shapes
         self._pending: List[Any] = []
+        self._sent: Dict[Tuple[int, int], Signature] = {}      # (destination, slot) -> contract
+        self._expected: Dict[Tuple[int, int], Signature] = {}  # (source, slot) -> contract
+        self.headers_sent = 0      # instrumentation: how many messages carried a header ...
+        self.headers_received = 0  # ... and how many receives had to read one on the host
 
     def _global(self, group_rank: int) -> int:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None and self.group is not dist.group.WORLD else group_rank
 
-    def send(self, t: Tensor, dst: int) -> None:
+    def send(self, t: Tensor, dst: int, slot: Optional[int] = None) -> None:
         t = t.contiguous()
         assert t.dim() <= 7
-        head = torch.zeros(_HEADER, dtype=torch.int64)
-        head[0], head[1], head[2] = t.dim(), _DTYPES.index(t.dtype), int(t.requires_grad)
-        for i, s in enumerate(t.shape):
-            head[3 + i] = s
-        head = head.to(self.device)
-        self._pending.append(dist.isend(head, self._global(dst), group=self.group))
+        signature: Signature = (tuple(t.shape), t.dtype, bool(t.requires_grad))
+        contract = self._sent.get((dst, slot)) if (self.static_shapes and slot is not None) else None
+        if contract is not None and contract != signature:
+            raise RuntimeError(f"message for stage {dst}, slot {slot} is {signature} but the static contract says {contract}; "
+                               "create the transport with static_shapes=False for varying shapes")
+        keep: List[Any] = [t]
+        if contract is None:
+            head = torch.zeros(_HEADER, dtype=torch.int64)
+            head[0], head[1], head[2] = t.dim(), _DTYPES.index(t.dtype), int(t.requires_grad)
+            for i, s in enumerate(t.shape):
+                head[3 + i] = s
+            head = head.to(self.device)
+            self._pending.append(dist.isend(head, self._global(dst), group=self.group))
+            self.headers_sent += 1
+            keep.append(head)
+            if self.static_shapes and slot is not None:
+                self._sent[(dst, slot)] = signature
         self._pending.append(dist.isend(t.detach(), self._global(dst), group=self.group))
-        self._pending.append((head, t))  # keep the buffers alive until the sends completed
+        self._pending.append(keep)  # the buffers stay alive until the sends have completed
 
-    def recv(self, src: int) -> Tensor:
-        head = torch.zeros(_HEADER, dtype=torch.int64, device=self.device)
-        dist.recv(head, self._global(src), group=self.group)
-        h = head.tolist()
-        shape = tuple(h[3 : 3 + h[0]])
-        out = torch.empty(shape, dtype=_DTYPES[h[1]], device=self.device)
+    def recv(self, src: int, slot: Optional[int] = None) -> Tensor:
+        contract = self._expected.get((src, slot)) if (self.static_shapes and slot is not None) else None
+        if contract is None:
+            head = torch.zeros(_HEADER, dtype=torch.int64, device=self.device)
+            dist.recv(head, self._global(src), group=self.group)
+            h = head.tolist()  # the one host synchronisation of a message with a header
+            self.headers_received += 1
+            contract = (tuple(h[3 : 3 + h[0]]), _DTYPES[h[1]], bool(h[2]))
+            if self.static_shapes and slot is not None:
+                self._expected[(src, slot)] = contract
+        shape, dtype, requires_grad = contract
+        out = torch.empty(shape, dtype=dtype, device=self.device)
         dist.recv(out, self._global(src), group=self.group)
-        if h[2] and out.is_floating_point():
+        if requires_grad and out.is_floating_point():
             out.requires_grad_()
         return out
 
@@ -136,13 +164,13 @@ class RpcTransport(Transport):
         self._next_recv: Dict[int, int] = {}
         self._early: Dict[Tuple[int, int], Any] = {}
 
-    def send(self, t: Tensor, dst: int) -> None:
+    def send(self, t: Tensor, dst: int, slot: Optional[int] = None) -> None:
         seq = self._next_send.get(dst, 0)
         self._next_send[dst] = seq + 1
         args = (self.channel, self.rank, seq, t.detach().cpu(), bool(t.requires_grad))
         self._pending.append(self.rpc.rpc_async(self.worker_name(dst), rpc_push_queue, args=args))
 
-    def recv(self, src: int) -> Tensor:
+    def recv(self, src: int, slot: Optional[int] = None) -> Tensor:
         want = self._next_recv.get(src, 0)
         self._next_recv[src] = want + 1
         q = _rpc_queue(self.channel, src)
@@ -169,7 +197,8 @@ def get_transport(group: Any, device: torch.device, **rpc_kwargs: Any) -> Any:
     fairscale/nn/pipe/async_pipeline.py:39-43; here p2p over NCCL / gloo is the default because it always exists)."""
     if os.environ.get("FORCE_RPC", "").lower() in ("1", "true", "yes"):
         return RpcTransport(dist.get_rank(group), device, **rpc_kwargs)
-    return SendRecvTransport(group, device)
+    # FSB200_PIPE_STATIC_SHAPES=1: every (peer, micro-batch) message keeps its shape from step to step, headers are sent once
+    return SendRecvTransport(group, device, static_shapes=os.environ.get("FSB200_PIPE_STATIC_SHAPES", "0") == "1")
 
 
 def MakeTransport(use_rpc: bool, worker_map: Optional[Dict[int, str]], input_device: Optional[torch.device], group: Any = None) -> Transport:

@@ -1,12 +1,18 @@
-"""Mini-batch <-> micro-batch conversion (parity: fairscale/nn/pipe/microbatch.py:36-203)."""
+"""Micro-batches: the unit of work that moves through a pipeline.
+
+A :class:`Batch` is either *atomic* (it wraps one tensor, and modules see that tensor) or a tuple of tensors (modules
+see the tuple).  ``scatter`` cuts a mini-batch along dimension 0, ``gather`` concatenates the results again.
+Contract of fairscale/nn/pipe/microbatch.py:36-203.
+"""
 
 from __future__ import annotations
 
-import typing
-from typing import Any, Callable, Iterable, Iterator, List, Tuple, Union, cast
+from typing import Callable, Iterable, Iterator, List, Tuple, Union, cast
 
 import torch
 from torch import Tensor
+
+__all__: List[str] = []
 
 Tensors = Tuple[Tensor, ...]
 TensorOrTensors = Union[Tensor, Tensors]
@@ -14,97 +20,89 @@ Function = Callable[[TensorOrTensors], TensorOrTensors]
 
 
 class Batch:
-    """A micro-batch: one tensor or a tuple of tensors, with uniform access helpers."""
+    """Holds the tensors of one micro-batch plus its position ``index`` in the mini-batch."""
+
+    __slots__ = ("_items", "atomic", "_index")
 
     def __init__(self, value: TensorOrTensors, index: int) -> None:
-        self.value = value
         self.atomic = torch.is_tensor(value)
-        self.__index = index
+        self._items: List[Tensor] = [cast(Tensor, value)] if self.atomic else list(cast(Tensors, value))
+        self._index = index
 
+    # -- views of the payload
     @property
     def index(self) -> int:
-        return self.__index
+        return self._index
 
     @property
     def tensor(self) -> Tensor:
         if not self.atomic:
             raise AttributeError("not atomic batch")
-        return cast(Tensor, self.value)
+        return self._items[0]
 
     @property
     def tensors(self) -> Tensors:
         if self.atomic:
             raise AttributeError("batch is atomic")
-        return cast(Tensors, self.value)
+        return tuple(self._items)
 
     @property
     def tensor_or_tensors(self) -> TensorOrTensors:
-        return self.value
+        return self._items[0] if self.atomic else tuple(self._items)
 
     def call(self, function: Function) -> "Batch":
-        return Batch(function(self.value), self.index)
+        """``function`` applied to the payload, wrapped as a batch with the same index."""
+        return Batch(function(self.tensor_or_tensors), self._index)
 
+    # -- list protocol over the tensors (an atomic batch has length 1)
     def __repr__(self) -> str:
-        return f"Batch[atomic={self.atomic!r}]({self.value!r})"
-
-    def __iter__(self) -> Iterator[Tensor]:
-        if self.atomic:
-            yield self.tensor
-        else:
-            yield from self.tensors
+        return f"Batch[{self._index}, atomic={self.atomic}]({self.tensor_or_tensors!r})"
 
     def __len__(self) -> int:
-        return 1 if self.atomic else len(self.tensors)
+        return len(self._items)
 
-    def __getitem__(self, index: int) -> Tensor:
-        if not self.atomic:
-            return self.tensors[index]
-        if index != 0:
-            raise IndexError("atomic batch allows index 0 only")
-        return self.tensor
+    def __iter__(self) -> Iterator[Tensor]:
+        return iter(self._items)
 
-    def __setitem__(self, index: Union[int, slice], value: Any) -> None:
-        if isinstance(index, int):
-            if self.atomic:
-                if index != 0:
-                    raise IndexError("atomic batch allows index 0 only")
-                self.value = value
-            else:
-                self.value = self.tensors[:index] + (value,) + self.tensors[index + 1:]
-            return
-        if not (index.start is index.stop is index.step is None):
-            raise NotImplementedError("only slice [:] supported")
-        if not self.atomic:
-            self.value = tuple(value)
-            return
-        if len(value) != 1:
-            raise IndexError("atomic batch cannot be replaced with multiple tensors")
-        self.value = value[0]
+    def __getitem__(self, key):  # type: ignore[no-untyped-def]
+        picked = self._items[key]
+        return tuple(picked) if isinstance(key, slice) else picked
+
+    def __setitem__(self, key, value) -> None:  # type: ignore[no-untyped-def]
+        if isinstance(key, slice):
+            new_items = list(self._items)
+            new_items[key] = list(value)
+            if self.atomic and len(new_items) != 1:
+                raise ValueError("an atomic batch holds exactly one tensor")
+            self._items = new_items
+        else:
+            self._items[key] = value
 
 
 def check(input: TensorOrTensors) -> None:
-    """Inputs / outputs of a pipeline must be a tensor or a tuple of tensors."""
-    if isinstance(input, tuple):
-        for x in input:
-            check(x)
+    """``TypeError`` unless ``input`` is a tensor or a tuple of tensors."""
+    if torch.is_tensor(input):
         return
-    if not isinstance(input, Tensor):
-        raise TypeError(f"expected Tensor, but got {input.__class__.__name__}")
+    if not isinstance(input, tuple):
+        raise TypeError(f"expected Tensor or Tensors, but got {type(input).__name__}")
+    for member in input:
+        if not torch.is_tensor(member):
+            raise TypeError(f"expected Tensor, but got {type(member).__name__}")
 
 
 def scatter(input: TensorOrTensors, chunks: int) -> List[Batch]:
-    """Split along dim 0 into at most ``chunks`` micro-batches (``Tensor.chunk`` semantics)."""
-    if isinstance(input, Tensor):
-        pieces: Iterable[TensorOrTensors] = input.chunk(chunks)
+    """Cut ``input`` into at most ``chunks`` micro-batches along dimension 0 (fewer when the batch is small)."""
+    if torch.is_tensor(input):
+        pieces: Iterable[TensorOrTensors] = cast(Tensor, input).chunk(chunks)
     else:
-        per_tensor = [t.chunk(chunks) for t in input]
-        pieces = zip(*per_tensor)
-    return [Batch(x, i) for i, x in enumerate(pieces)]
+        columns = [t.chunk(chunks) for t in cast(Tensors, input)]  # per tensor: its pieces
+        pieces = zip(*columns)                                      # per micro-batch: one piece of every tensor
+    return [Batch(piece, i) for i, piece in enumerate(pieces)]
 
 
 def gather(outputs: List[Batch]) -> TensorOrTensors:
-    """Concatenate micro-batch outputs along dim 0."""
+    """Concatenate the micro-batches back into one mini-batch."""
     if outputs[0].atomic:
-        return torch.cat(tuple(b.tensor for b in outputs))
-    columns = zip(*(b.tensors for b in outputs))
-    return tuple(torch.cat(col) for col in columns)
+        return torch.cat([b.tensor for b in outputs])
+    rows = [b.tensors for b in outputs]
+    return tuple(torch.cat(column) for column in zip(*rows))

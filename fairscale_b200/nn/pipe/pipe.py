@@ -1,18 +1,20 @@
-"""``Pipe``: GPipe for an ``nn.Sequential`` spread over the GPUs of one process.
+"""``Pipe``: GPipe for an ``nn.Sequential`` whose layers are spread over the devices of one process.
 
-API parity with fairscale/nn/pipe/pipe.py:174-418: ``Pipe(module, balance, devices=None, chunks=1,
-checkpoint="except_last", deferred_batch_norm=False)``, the same validation errors, device-move denial,
-``Sequential``-like container protocol.  (The reference's DeprecationWarning is not reproduced.)
+    model = Pipe(nn.Sequential(a, b, c, d), balance=[2, 2], devices=[0, 1], chunks=8)
+    output = model(input)            # input on the first device, output on the last
+
+The constructor validates the arguments, cuts the sequential module into one partition per entry of ``balance`` and
+moves each partition to its device; ``forward`` splits the mini-batch into ``chunks`` micro-batches and hands them to
+the executor in ``pipeline.py``.  Constructor signature, error types and messages, the refusal to move the wrapped
+module and the ``Sequential``-like container protocol follow fairscale/nn/pipe/pipe.py:75-418 (its deprecation warning is
+not reproduced).
 """
 
 from __future__ import annotations
 
-from collections import OrderedDict
-from typing import TYPE_CHECKING, Any, Iterable, Iterator, List, Optional, Tuple, Union, cast
+from typing import Any, Iterable, Iterator, List, Optional, Sequence, Tuple, Union
 
 import torch
-import torch.autograd
-import torch.cuda
 from torch import Tensor, nn
 
 from . import microbatch
@@ -29,15 +31,15 @@ Devices = Union[Iterable[Device], List[Device]]
 Tensors = Tuple[Tensor, ...]
 TensorOrTensors = Union[Tensor, Tensors]
 
-if TYPE_CHECKING:
-    Module = nn.Module[TensorOrTensors]
-    NamedModules = OrderedDict[str, Module]
-else:
-    Module = nn.Module
-    NamedModules = OrderedDict
+_CHECKPOINT_MODES = ("always", "except_last", "never")
+
+
+class BalanceError(ValueError):
+    """The layer counts in ``balance`` do not describe the module."""
 
 
 def recommend_auto_balance(message: str) -> str:
+    """``message`` followed by a pointer to the automatic balancing helpers."""
     return f"""{message}
 
 If your model is still under development, its optimal balance would change
@@ -58,73 +60,60 @@ naive automatic balancing:
 def verify_module(module: nn.Sequential) -> None:
     if not isinstance(module, nn.Sequential):
         raise TypeError("module must be nn.Sequential to be partitioned")
-    if len(list(module.named_children())) != len(module):
+    children = list(module.children())  # children() de-duplicates
+    if len(children) != len(module):
         raise ValueError("module with duplicate children is not supported")
 
 
-def verify_splitting(module: nn.Sequential, partitions: List[nn.Sequential], balance: Iterable[int], devices: List[torch.device]) -> None:
-    """A parameter shared by layers that ended up on different devices cannot be kept consistent."""
-    n_params = len(list(module.parameters()))
-    n_child_params = sum(len(list(child.parameters())) for child in module.children())
-    if n_params == n_child_params:
-        return
-    for i in range(len(partitions)):
-        for j in range(i + 1, len(partitions)):
-            if devices[i] == devices[j]:
-                continue
-            ids_j = {id(q) for q in partitions[j].parameters()}
-            if any(id(p) in ids_j for p in partitions[i].parameters()):
+def verify_splitting(module: nn.Sequential, partitions: Sequence[nn.Sequential], balance: Iterable[int],
+                     devices: Sequence[torch.device]) -> None:
+    """A parameter that two layers share must not end up on two devices: its copies could not be kept equal."""
+    owner: dict = {}  # id(parameter) -> device of the partition that was seen holding it first
+    for partition, device in zip(partitions, devices):
+        for p in partition.parameters():
+            if owner.setdefault(id(p), device) != device:
                 raise ValueError("module with duplicate parameters on distinct devices is not supported")
-
-
-class BalanceError(ValueError):
-    pass
 
 
 def split_module(module: nn.Sequential, balance: Iterable[int], devices: List[torch.device]
                  ) -> Tuple[List[nn.Sequential], List[int], List[torch.device]]:
-    """Cut ``module`` into consecutive partitions of ``balance`` layers and move each to its device."""
+    """Partitions of ``balance[k]`` consecutive layers each, every one moved to ``devices[k]``.  Returns the partitions
+    (registered in a ``ModuleList``), the balance as a list and the devices actually used."""
     balance = list(balance)
-    if len(module) != sum(balance):
-        raise BalanceError(
-            f"module and sum of balance have different length (module: {len(module)}, sum of balance: {sum(balance)})"
-        )
-    if any(x <= 0 for x in balance):
+    if sum(balance) != len(module):
+        raise BalanceError(f"module and sum of balance have different length (module: {len(module)}, sum of balance: {sum(balance)})")
+    if min(balance, default=1) <= 0:
         raise BalanceError(f"all balance numbers must be positive integer (balance: {balance})")
-    if len(balance) > len(devices):
+    if len(devices) < len(balance):
         raise IndexError(f"too few devices to hold given partitions (devices: {len(devices)}, partitions: {len(balance)})")
 
-    partitions = []
-    layers: NamedModules = OrderedDict()
-    j = 0
-    for name, layer in module.named_children():
-        layers[name] = layer
-        if len(layers) == balance[j]:
-            partition = nn.Sequential(layers)
-            partition.to(devices[j])
-            partitions.append(partition)
-            layers.clear()
-            j += 1
-    del devices[j:]
-    return cast(List[nn.Sequential], nn.ModuleList(partitions)), balance, devices
+    named = list(module.named_children())
+    partitions: List[nn.Sequential] = []
+    start = 0
+    for count, device in zip(balance, devices):
+        part = nn.Sequential()
+        for name, layer in named[start:start + count]:
+            part.add_module(name, layer)  # layers keep their names, so state-dict keys only gain the partition index
+        partitions.append(part.to(device))
+        start += count
+    return nn.ModuleList(partitions), balance, list(devices[: len(balance)])  # type: ignore[return-value]
 
 
-MOVING_DENIED = TypeError("denied to move parameters and buffers, because Pipe should manage device placement")
+def _moving_denied() -> TypeError:
+    return TypeError("denied to move parameters and buffers, because Pipe should manage device placement")
 
 
-class Pipe(Module):
-    """Wrap a sequential model for GPipe training::
-
-        model = Pipe(nn.Sequential(a, b, c, d), balance=[1, 1, 1, 1], chunks=8)
-        output = model(input)      # input on the first device, output on the last
+class Pipe(nn.Module):
+    """See the module docstring.
 
     Args:
-        module: ``nn.Sequential`` to split.
-        balance: layers per partition (``sum(balance) == len(module)``).
-        devices: devices to use (default: all CUDA devices, or CPU when there is none).
-        chunks: number of micro-batches.
-        checkpoint: ``"always"``, ``"except_last"`` (default) or ``"never"``.
-        deferred_batch_norm: accumulate BatchNorm statistics over the whole mini-batch.
+        module: the ``nn.Sequential`` to pipeline.
+        balance: number of layers per partition; its sum must be ``len(module)``.
+        devices: one device per partition (default: the CUDA devices in order, or CPU if there is none).
+        chunks: number of micro-batches a mini-batch is cut into.
+        checkpoint: which micro-batches recompute their forward in backward - ``"always"``, ``"except_last"``
+            (all but the last micro-batch, whose backward starts right after its forward) or ``"never"``.
+        deferred_batch_norm: let BatchNorm layers track running statistics per mini-batch (``batchnorm.py``).
     """
 
     balance: List[int] = []
@@ -135,85 +124,72 @@ class Pipe(Module):
     def __init__(self, module: nn.Sequential, balance: Optional[Iterable[int]] = None, *, devices: Optional[Devices] = None,
                  chunks: int = chunks, checkpoint: str = checkpoint, deferred_batch_norm: bool = False) -> None:
         super().__init__()
-        chunks = int(chunks)
-        checkpoint = str(checkpoint)
+        chunks, checkpoint = int(chunks), str(checkpoint)
         if balance is None:
             raise ValueError(recommend_auto_balance("balance is required"))
         if chunks <= 0:
             raise ValueError("number of chunks must be positive integer")
-        if checkpoint not in ["always", "except_last", "never"]:
+        if checkpoint not in _CHECKPOINT_MODES:
             raise ValueError("checkpoint is not one of 'always', 'except_last', or 'never'")
-
         verify_module(module)
-        verify_skippables(module)  # TypeError for unmatched stash / pop pairs
+        verify_skippables(module)  # TypeError when stash / pop declarations do not pair up
 
-        self.chunks = chunks
-        self.checkpoint = checkpoint
+        self.chunks, self.checkpoint = chunks, checkpoint
         if deferred_batch_norm:
             module = DeferredBatchNorm.convert_deferred_batch_norm(module, chunks)
 
+        balance = list(balance)
         if devices is None:
-            devices = range(torch.cuda.device_count()) if torch.cuda.is_available() else ["cpu"] * len(list(balance))
-        devices = [torch.device(d) for d in devices]
-        devices = cast(List[torch.device], devices)
+            devices = range(torch.cuda.device_count()) if torch.cuda.is_available() else ["cpu"] * len(balance)
         try:
-            self.partitions, self.balance, self.devices = split_module(module, balance, devices)
+            self.partitions, self.balance, self.devices = split_module(module, balance, [torch.device(d) for d in devices])
         except BalanceError as exc:
-            raise ValueError(recommend_auto_balance(str(exc)))
+            raise ValueError(recommend_auto_balance(str(exc))) from None
         verify_splitting(module, self.partitions, self.balance, self.devices)
 
-        self._copy_streams: List[List[AbstractStream]] = []
+        # one copy stream per (partition, micro-batch): transfers of different micro-batches overlap each other and compute
+        self._copy_streams: List[List[AbstractStream]] = [[new_stream(d) for _ in range(chunks)] for d in self.devices]
         self._skip_layout = inspect_skip_layout(self.partitions)
-        checkpoint_stop = {"always": self.chunks, "except_last": self.chunks - 1, "never": 0}[self.checkpoint]
-        self.pipeline = Pipeline(self.partitions, self.devices, self._ensure_copy_streams(), self._skip_layout, checkpoint_stop)
+        recomputed = {"always": chunks, "except_last": chunks - 1, "never": 0}[checkpoint]  # micro-batches [0, recomputed)
+        self.pipeline = Pipeline(self.partitions, self.devices, self._copy_streams, self._skip_layout, recomputed)
 
-    # ------------------------------------------------------------------ Sequential-like protocol
+    # ------------------------------------------------------------------ the layers, as nn.Sequential exposes them
+    def _layers(self) -> List[nn.Module]:
+        return [layer for partition in self.partitions for layer in partition]
+
     def __len__(self) -> int:
-        return sum(len(p) for p in self.partitions)
+        return len(self._layers())
+
+    def __iter__(self) -> Iterator[nn.Module]:
+        return iter(self._layers())
 
     def __getitem__(self, index: int) -> nn.Module:
-        partitions = self.partitions
-        if index < 0:
-            partitions = partitions[::-1]
-        for partition in partitions:
-            try:
-                return partition[index]
-            except IndexError:
-                pass
-            shift = len(partition)
-            index = index + shift if index < 0 else index - shift
-        raise IndexError
+        layers = self._layers()
+        if not -len(layers) <= index < len(layers):
+            raise IndexError
+        return layers[index]
 
-    def __iter__(self) -> Iterable[nn.Module]:
-        for partition in self.partitions:
-            yield from partition
-
-    # ------------------------------------------------------------------ device placement is Pipe's business
+    # ------------------------------------------------------------------ devices are fixed at construction
     def cuda(self, device: Optional[Device] = None) -> "Pipe":
-        raise MOVING_DENIED
+        raise _moving_denied()
 
     def cpu(self) -> "Pipe":
-        raise MOVING_DENIED
+        raise _moving_denied()
 
     def to(self, *args: Any, **kwargs: Any) -> "Pipe":
-        """Only dtype conversions are allowed."""
-        if "device" in kwargs or "tensor" in kwargs:
-            raise MOVING_DENIED
-        if args and isinstance(args[0], (torch.device, int, str, torch.Tensor)):
-            raise MOVING_DENIED
+        """dtype conversions pass through; anything that names a device or a tensor to follow is refused."""
+        names_device = bool(args) and isinstance(args[0], (torch.device, int, str, torch.Tensor))
+        if names_device or "device" in kwargs or "tensor" in kwargs:
+            raise _moving_denied()
         return super().to(*args, **kwargs)
 
-    def _ensure_copy_streams(self) -> List[List[AbstractStream]]:
-        """One copy stream per (partition, micro-batch) so copies of different micro-batches overlap."""
-        if not self._copy_streams:
-            for device in self.devices:
-                self._copy_streams.append([new_stream(device) for _ in range(self.chunks)])
-        return self._copy_streams
-
+    # ------------------------------------------------------------------ running
     def forward(self, input: TensorOrTensors) -> TensorOrTensors:  # type: ignore[override]
+        """``input`` (a tensor or tuple of tensors on the first device) through all partitions; the result lives on
+        the last device.  Batches smaller than ``chunks`` simply give fewer micro-batches."""
         microbatch.check(input)
         if not self.devices:
-            return input  # an empty sequential module
+            return input  # nothing to run: an empty sequential module
         batches = microbatch.scatter(input, self.chunks)
         self.pipeline.run(batches)
         return microbatch.gather(batches)

@@ -1,39 +1,35 @@
-"""Namespaces isolate skip-tensor names between module instances (parity: fairscale/nn/pipe/skip/namespace.py:29-63)."""
+"""Namespaces keep equal skip names apart: ``stash("x")`` isolated in one namespace only meets the ``pop("x")`` isolated
+in the same one.  A namespace is an opaque identity; two of them are equal only if they are the same object.
+(fairscale/nn/pipe/skip/namespace.py:16-50 orders and hashes them through a uuid; identity gives the same behaviour.)
+"""
 
 from __future__ import annotations
 
-import abc
-import uuid
-from functools import total_ordering
+import itertools
 from typing import Any
 
 __all__ = ["Namespace"]
 
+_serial = itertools.count()
 
-@total_ordering
-class Namespace(metaclass=abc.ABCMeta):
-    """A unique, hashable, orderable token; ``None`` is accepted wherever a namespace is (default namespace)."""
 
+class Namespace:
     __slots__ = ("id",)
 
     def __init__(self) -> None:
-        self.id = uuid.uuid4()
+        self.id = next(_serial)
 
     def __repr__(self) -> str:
-        return f"<Namespace '{self.id}'>"
+        return f"<Namespace #{self.id}>"
 
     def __hash__(self) -> int:
-        return hash(self.id)
-
-    def __lt__(self, other: Any) -> bool:  # ordering only serves deterministic sorting of layouts
-        if isinstance(other, Namespace):
-            return self.id < other.id
-        return False
+        return hash(("fsb-skip-namespace", self.id))
 
     def __eq__(self, other: Any) -> bool:
-        if isinstance(other, Namespace):
-            return self.id == other.id
-        return False
+        return isinstance(other, Namespace) and other.id == self.id
 
-
-Namespace.register(type(None))
+    # sortable, so that error messages and port orders are deterministic
+    def __lt__(self, other: Any) -> bool:
+        if not isinstance(other, Namespace):
+            return NotImplemented
+        return self.id < other.id

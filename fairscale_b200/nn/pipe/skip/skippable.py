@@ -1,34 +1,31 @@
-"""The ``@skippable`` decorator and its ``stash`` / ``pop`` commands.
+"""``@skippable`` modules: layers that hand a tensor to a later layer around the sequential data flow.
 
-API parity with fairscale/nn/pipe/skip/skippable.py:52-453.  A skippable module's ``forward`` is a generator:
-``yield stash(name, tensor)`` parks a tensor, ``tensor = yield pop(name)`` retrieves one parked by an earlier
-layer; the tensor travels outside the sequential data flow (and, under ``Pipe``, outside the autograd graph
-through portals) to the partition that pops it.
+    @skippable(stash=["residual"])
+    class Save(nn.Module):
+        def forward(self, x):
+            yield stash("residual", x)
+            return self.conv(x)
+
+    @skippable(pop=["residual"])
+    class Add(nn.Module):
+        def forward(self, x):
+            residual = yield pop("residual")
+            return x + residual
+
+The wrapped ``forward`` is a generator that yields :class:`stash` / :class:`pop` commands; the wrapper executes them
+against the current skip tracker (``skip/tracker.py``).  User-facing behaviour and error messages follow
+fairscale/nn/pipe/skip/skippable.py:52-453.
 """
 
 from __future__ import annotations
 
-from typing import (
-    Any,
-    Callable,
-    ClassVar,
-    Dict,
-    FrozenSet,
-    Generator,
-    Iterable,
-    List,
-    Optional,
-    Set,
-    Tuple,
-    Type,
-    TypeVar,
-    Union,
-    cast,
-)
+import inspect
+from typing import Any, Callable, ClassVar, Dict, FrozenSet, Iterable, Iterator, List, Optional, Tuple, Type, TypeVar, Union
 
 from torch import Tensor, nn
 
 from ..microbatch import Batch
+from .layout import SkipKey
 from .namespace import Namespace
 from .tracker import current_skip_tracker
 
@@ -36,11 +33,33 @@ __all__ = ["skippable", "stash", "pop", "verify_skippables"]
 
 Tensors = Tuple[Tensor, ...]
 TensorOrTensors = Union[Tensor, Tensors]
-T = TypeVar("T", bound="Skippable")
+S = TypeVar("S", bound="Skippable")
+
+
+class stash:
+    """Command: ``yield stash(name, tensor)`` files ``tensor`` (or None) under ``name``."""
+
+    __slots__ = ("name", "tensor")
+
+    def __init__(self, name: str, tensor: Optional[Tensor]) -> None:
+        self.name, self.tensor = name, tensor
+
+
+class pop:
+    """Command: ``tensor = yield pop(name)`` fetches what an earlier layer stashed under ``name``."""
+
+    __slots__ = ("name",)
+
+    def __init__(self, name: str) -> None:
+        self.name = name
+
+
+def _quoted(names: Iterable[str]) -> str:
+    return ", ".join(f"'{n}'" for n in sorted(names))
 
 
 class Skippable(nn.Module):
-    """Base of the classes produced by :func:`skippable`; do not subclass directly."""
+    """What :func:`skippable` makes of a module class.  Holds an instance of the original class as ``self.module``."""
 
     module_cls: ClassVar[Type[nn.Module]]
     stashable_names: ClassVar[FrozenSet[str]]
@@ -54,155 +73,120 @@ class Skippable(nn.Module):
     def __repr__(self) -> str:
         return f"@skippable({self.module})"
 
-    def namespaced(self, name: str) -> Tuple[Namespace, str]:
-        return (cast(Namespace, self.namespaces.get(name)), name)
+    # -- names and namespaces
+    def namespaced(self, name: str) -> SkipKey:
+        return (self.namespaces.get(name), name)
 
-    def stashable(self) -> Iterable[Tuple[Namespace, str]]:
-        for name in self.stashable_names:
-            yield self.namespaced(name)
+    def stashable(self) -> Iterator[SkipKey]:
+        return (self.namespaced(n) for n in self.stashable_names)
 
-    def poppable(self) -> Iterable[Tuple[Namespace, str]]:
-        for name in self.poppable_names:
-            yield self.namespaced(name)
+    def poppable(self) -> Iterator[SkipKey]:
+        return (self.namespaced(n) for n in self.poppable_names)
 
-    def isolate(self: T, ns: Namespace, *, only: Optional[Iterable[str]] = None) -> T:
-        """Put all (or ``only`` the listed) skip names of this layer into namespace ``ns`` so the same
-        names can be reused by another stash/pop pair in the same sequential model."""
-        names: Iterable[str] = self.stashable_names | self.poppable_names if only is None else set(only)
-        for name in names:
+    def isolate(self: S, ns: Namespace, *, only: Optional[Iterable[str]] = None) -> S:
+        """Move this layer's skip names (all of them, or ``only`` the given ones) into namespace ``ns``; returns self."""
+        for name in (self.stashable_names | self.poppable_names) if only is None else only:
             self.namespaces[name] = ns
         return self
 
-    def dispatch(self, input: Any, handle_stash: Callable[[str, Optional[Tensor]], None], handle_pop: Callable[[str], Optional[Tensor]]) -> Any:
-        """Drive the generator returned by the wrapped module's ``forward``."""
-        gen = self.module(input)
-        if not isinstance(gen, Generator):
-            return gen  # an ordinary forward
-        try:
-            op = next(gen)
-            while True:
-                if isinstance(op, stash):
-                    handle_stash(op.name, op.tensor)
-                    op = next(gen)
-                elif isinstance(op, pop):
-                    op = gen.send(handle_pop(op.name))
-                else:
-                    raise TypeError(f"{op!r} is not a command from @skippable")
-        except StopIteration as stop:
-            return stop.args[0]
+    # -- running the generator
+    def dispatch(self, input: Any, handle_stash: Callable[[str, Optional[Tensor]], None],
+                 handle_pop: Callable[[str], Optional[Tensor]]) -> Any:
+        """Call the wrapped module; if its forward is a generator, serve its commands until it returns."""
+        running = self.module(input)
+        if not inspect.isgenerator(running):
+            return running
+        reply: Optional[Tensor] = None
+        while True:
+            try:
+                command = running.send(reply)
+            except StopIteration as finished:
+                return finished.value
+            if isinstance(command, stash):
+                handle_stash(command.name, command.tensor)
+                reply = None
+            elif isinstance(command, pop):
+                reply = handle_pop(command.name)
+            else:
+                raise TypeError(f"{command!r} is not a command from @skippable")
 
     def forward(self, input: TensorOrTensors) -> TensorOrTensors:  # type: ignore[override]
-        """Skip tensors to pop are fetched *before* the wrapped module runs (the fetch forks the graph from the
-        input) and stashed tensors are filed *after* it (the filing joins into the output); that ordering is
-        what lets portals keep backward correct under ``Pipe``."""
         tracker = current_skip_tracker()
-        stashed: Dict[str, Optional[Tensor]] = {}
-        poppable: Dict[str, Optional[Tensor]] = {}
+        carrier = Batch(input, tracker.index)
 
-        batch = Batch(input, tracker.index)
+        # everything this layer may pop is fetched up front, everything it stashes is filed after it has run
+        fetched: Dict[str, Optional[Tensor]] = {}
         for ns, name in self.poppable():
             try:
-                poppable[name] = tracker.load(batch, ns, name)
+                fetched[name] = tracker.load(carrier, ns, name)
             except KeyError:
-                raise RuntimeError(f"'{name}' has not been stashed")
-        input = batch.tensor_or_tensors
+                raise RuntimeError(f"'{name}' has not been stashed") from None
+        filed: Dict[str, Optional[Tensor]] = {}
 
         def on_stash(name: str, tensor: Optional[Tensor]) -> None:
             if name not in self.stashable_names:
                 raise RuntimeError(f"'{name}' has not been declared as stashable")
-            stashed[name] = tensor
+            filed[name] = tensor
 
         def on_pop(name: str) -> Optional[Tensor]:
             if name not in self.poppable_names:
                 raise RuntimeError(f"'{name}' has not been declared as poppable")
-            return poppable.pop(name)
+            return fetched.pop(name)
 
-        output = self.dispatch(input, on_stash, on_pop)
+        output = self.dispatch(carrier.tensor_or_tensors, on_stash, on_pop)
 
-        missing_stash = self.stashable_names - stashed.keys()
-        if missing_stash:
-            raise RuntimeError(f"{', '.join(repr(n) for n in sorted(missing_stash))} must be stashed but have not")
-        if poppable:
-            raise RuntimeError(f"{', '.join(repr(n) for n in sorted(poppable))} must be popped but have not")
+        unstashed = self.stashable_names - filed.keys()
+        if unstashed:
+            raise RuntimeError(f"{_quoted(unstashed)} must be stashed but have not")
+        if fetched:
+            raise RuntimeError(f"{_quoted(fetched)} must be popped but have not")
 
-        batch = Batch(output, tracker.index)
+        carrier = Batch(output, tracker.index)
         for ns, name in self.stashable():
-            tracker.save(batch, ns, name, stashed[name])
-        return batch.tensor_or_tensors
+            tracker.save(carrier, ns, name, filed[name])
+        return carrier.tensor_or_tensors
 
 
 def skippable(stash: Iterable[str] = (), pop: Iterable[str] = ()) -> Callable[[Type[nn.Module]], Type[Skippable]]:
-    """Class decorator declaring which skip names a module stashes and pops::
+    """Class decorator: declares the names the module may stash and pop and wraps it into a :class:`Skippable`."""
+    declared = {"stashable_names": frozenset(stash), "poppable_names": frozenset(pop)}
 
-        @skippable(stash=["skip"])
-        class Stash(nn.Module):
-            def forward(self, x):
-                yield stash("skip", x)
-                return x
-    """
-    stashable_names = frozenset(stash)
-    poppable_names = frozenset(pop)
+    def wrap(module_cls: Type[nn.Module]) -> Type[Skippable]:
+        return type(module_cls.__name__, (Skippable,), dict(declared, module_cls=module_cls))
 
-    def extend(module_cls: Type[nn.Module]) -> Type[Skippable]:
-        name = module_cls.__name__
-        bases = (Skippable,)
-        attrs = {"module_cls": module_cls, "stashable_names": stashable_names, "poppable_names": poppable_names}
-        return type(name, bases, attrs)
-
-    return extend
-
-
-class stash:
-    """``yield stash(name, tensor)`` inside a skippable forward."""
-
-    __slots__ = ("name", "tensor")
-
-    def __init__(self, name: str, tensor: Optional[Tensor]) -> None:
-        self.name = name
-        self.tensor = tensor
-
-
-class pop:
-    """``tensor = yield pop(name)`` inside a skippable forward."""
-
-    __slots__ = ("name",)
-
-    def __init__(self, name: str) -> None:
-        self.name = name
+    return wrap
 
 
 def verify_skippables(module: nn.Sequential) -> None:
-    """Check that every stash has exactly one later pop in the same namespace (and vice versa).
-
-    Raises ``TypeError`` listing every violation: pop before stash, stash never popped, a name declared
-    twice by different layers, or one layer that both stashes and pops the same name.
-    """
-    stashed: Set[Tuple[Namespace, str]] = set()
-    popped: Set[Tuple[Namespace, str]] = set()
-    msgs: List[str] = []
+    """``TypeError`` listing every stash / pop mismatch of ``module``: a pop without an earlier stash, a stash nobody
+    pops, a name two layers declare in the same namespace, a layer that declares one name both ways."""
+    open_stashes: Dict[SkipKey, str] = {}  # stashed and not yet popped -> layer that stashed
+    closed: set = set()
+    problems: List[str] = []
     for layer_name, layer in module.named_children():
         if not isinstance(layer, Skippable):
             continue
-        for name in layer.stashable_names & layer.poppable_names:
-            msgs.append(f"'{layer_name}' declared '{name}' both as stashable and as poppable")
-        for ns, name in layer.stashable():
-            if name in layer.poppable_names:
+        both = layer.stashable_names & layer.poppable_names
+        for name in sorted(both):
+            problems.append(f"'{layer_name}' declared '{name}' both as stashable and as poppable")
+        for key in layer.stashable():
+            if key[1] in both:
                 continue
-            if (ns, name) in stashed:
-                msgs.append(f"'{layer_name}' redeclared '{name}' as stashable but not isolated by namespace")
+            if key in open_stashes or key in closed:
+                problems.append(f"'{layer_name}' redeclared '{key[1]}' as stashable but not isolated by namespace")
+            else:
+                open_stashes[key] = layer_name
+        for key in layer.poppable():
+            if key[1] in both:
                 continue
-            stashed.add((ns, name))
-        for ns, name in layer.poppable():
-            if name in layer.stashable_names:
-                continue
-            if (ns, name) in popped:
-                msgs.append(f"'{layer_name}' redeclared '{name}' as poppable but not isolated by namespace")
-                continue
-            if (ns, name) not in stashed:
-                msgs.append(f"'{layer_name}' declared '{name}' as poppable but it was not stashed")
-                continue
-            popped.add((ns, name))
-    for _, name in stashed - popped:
-        msgs.append(f"no module declared '{name}' as poppable but stashed")
-    if msgs:
-        raise TypeError("one or more pairs of stash and pop do not match:\n\n%s" % "\n".join("* %s" % x for x in msgs))
+            if key in closed:
+                problems.append(f"'{layer_name}' redeclared '{key[1]}' as poppable but not isolated by namespace")
+            elif key not in open_stashes:
+                problems.append(f"'{layer_name}' declared '{key[1]}' as poppable but it was not stashed")
+            else:
+                del open_stashes[key]
+                closed.add(key)
+    for (_, name) in open_stashes:
+        problems.append(f"no module declared '{name}' as poppable but stashed")
+    if problems:
+        raise TypeError("one or more pairs of stash and pop do not match:\n\n" + "\n".join(f"* {p}" for p in problems))

@@ -1,4 +1,11 @@
-"""Per-micro-batch registry of live skip tensors (parity: fairscale/nn/pipe/skip/tracker.py:38-211)."""
+"""Where skippable modules put and find their skip tensors while a model runs.
+
+Outside a pipeline the tracker is a dictionary.  Inside one, every micro-batch has a :class:`StageSkipTracker`: skip
+tensors that stay within the running partition still go through the dictionary, while routed ones (see
+``skip/layout.py``) are taken from the stage's *inbox* (filled by the pipeline from the stage's extra inputs) and put into
+its *outbox* (returned by the pipeline as the stage's extra outputs).  Between stages the pipeline keeps a routed
+tensor in ``in_transit`` on the device that produced it.  Interface of fairscale/nn/pipe/skip/tracker.py:38-211.
+"""
 
 from __future__ import annotations
 
@@ -8,101 +15,110 @@ from typing import Dict, Generator, List, Optional, Tuple
 
 from torch import Tensor
 
-from ..checkpoint import is_checkpointing
-from ..dependency import fork, join
+from ..copy import Copy, Wait
 from ..microbatch import Batch
 from ..stream import AbstractStream
-from .layout import SkipLayout
+from .layout import SkipKey, SkipLayout
 from .namespace import Namespace
-from .portal import Portal
 
 __all__: List[str] = []
 
 
 class SkipTracker:
-    """Plain dictionary tracker used outside ``Pipe`` (skippable modules then behave like ordinary modules)."""
+    """Dictionary tracker: what a skippable module sees when no pipeline is driving it."""
 
     def __init__(self) -> None:
-        self.tensors: Dict[Tuple[Namespace, str], Optional[Tensor]] = {}
-
-    def save(self, batch: Batch, ns: Namespace, name: str, tensor: Optional[Tensor]) -> None:
-        self.tensors[(ns, name)] = tensor
-
-    def load(self, batch: Batch, ns: Namespace, name: str) -> Optional[Tensor]:
-        return self.tensors.pop((ns, name))
-
-    def copy(self, batch: Batch, prev_stream: AbstractStream, next_stream: AbstractStream, ns: Namespace, name: str) -> None:
-        raise TypeError("copy is not supported for non-portal skip tensors")
+        self.tensors: Dict[SkipKey, Optional[Tensor]] = {}
 
     @property
     def index(self) -> int:
         return 0
 
+    def save(self, batch: Batch, ns: Optional[Namespace], name: str, tensor: Optional[Tensor]) -> None:
+        self.tensors[(ns, name)] = tensor
 
-class SkipTrackerThroughPotals(SkipTracker):
-    """Tracker used by ``Pipe``: tensors that cross partitions travel through :class:`Portal` objects."""
+    def load(self, batch: Batch, ns: Optional[Namespace], name: str) -> Optional[Tensor]:
+        return self.tensors.pop((ns, name))  # KeyError: popped before stashed
+
+    def copy(self, batch: Batch, prev_stream: AbstractStream, next_stream: AbstractStream, ns: Optional[Namespace], name: str) -> None:
+        raise TypeError("copy is not supported for non-portal skip tensors")
+
+
+class StageSkipTracker(SkipTracker):
+    """Tracker of one micro-batch inside a pipeline."""
 
     def __init__(self, skip_layout: SkipLayout, index: int = 0) -> None:
         super().__init__()
         self.skip_layout = skip_layout
-        self.portals: Dict[Tuple[Namespace, str], Portal] = {}
-        self.__index = index
+        self._index = index
+        self.inbox: Dict[SkipKey, Optional[Tensor]] = {}       # routed tensors delivered to the running stage
+        self.outbox: Dict[SkipKey, Optional[Tensor]] = {}      # routed tensors stashed by the running stage
+        self.in_transit: Dict[SkipKey, Optional[Tensor]] = {}  # routed tensors between their two stages
 
     @property
     def index(self) -> int:
-        return self.__index
+        return self._index
 
-    def save(self, batch: Batch, ns: Namespace, name: str, tensor: Optional[Tensor]) -> None:
-        if not self.skip_layout.requires_copy(ns, name):
-            super().save(batch, ns, name, tensor)
-            return
-        if (ns, name) not in self.portals:
-            # requested once by the copy + once by the pop, plus once more by the recomputed pop when checkpointing
-            life = 3 if is_checkpointing() else 2
-            portal = Portal(tensor, life, batch.index)
-            portal.ns_name = (ns, name)
-            self.portals[(ns, name)] = portal
+    def save(self, batch: Batch, ns: Optional[Namespace], name: str, tensor: Optional[Tensor]) -> None:
+        if self.skip_layout.requires_copy(ns, name):
+            self.outbox[(ns, name)] = tensor
         else:
-            # the stash re-executes during recomputation: only blue() below will take the tensor
-            portal = self.portals[(ns, name)]
-            portal.put_tensor(tensor, 1)
-        phony = portal.blue()
-        batch[0] = join(batch[0], phony)
+            super().save(batch, ns, name, tensor)
 
-    def load(self, batch: Batch, ns: Namespace, name: str) -> Optional[Tensor]:
-        if not self.skip_layout.requires_copy(ns, name):
-            return super().load(batch, ns, name)
-        portal = self.portals[(ns, name)]
-        batch[0], phony = fork(batch[0])
-        return portal.orange(phony)
+    def load(self, batch: Batch, ns: Optional[Namespace], name: str) -> Optional[Tensor]:
+        if self.skip_layout.requires_copy(ns, name):
+            return self.inbox.pop((ns, name))
+        return super().load(batch, ns, name)
 
-    def copy(self, batch: Batch, prev_stream: AbstractStream, next_stream: AbstractStream, ns: Namespace, name: str) -> None:
-        assert self.skip_layout.requires_copy(ns, name)
-        batch[0], phony = fork(batch[0])
-        portal = self.portals[(ns, name)]
-        phony = portal.copy(prev_stream, next_stream, phony)
-        batch[0] = join(batch[0], phony)
+    def copy(self, batch: Batch, prev_stream: AbstractStream, next_stream: AbstractStream, ns: Optional[Namespace], name: str) -> None:
+        """Bring the routed tensor ``(ns, name)`` from the device of ``prev_stream`` to the device of ``next_stream``
+        (asynchronously, on those copy streams); it stays in ``in_transit`` until its stage starts."""
+        key = (ns, name)
+        tensor = self.in_transit.get(key)
+        if tensor is None:
+            return  # stashed as None: nothing to move
+        (moved,) = Copy.apply(prev_stream, next_stream, tensor)
+        self.in_transit[key] = moved if moved.is_floating_point() else moved.detach()
+
+    def deliver(self, keys: List[SkipKey], copy_stream: AbstractStream, compute_stream: AbstractStream) -> Tuple[List[SkipKey], List[Tensor]]:
+        """Take the tensors for input ports ``keys`` out of ``in_transit`` after making ``compute_stream`` wait for
+        their copies on ``copy_stream``.  Returns the keys that carry a tensor and those tensors; a key whose value was
+        stashed as ``None`` goes to the inbox directly and needs no port."""
+        carried: List[SkipKey] = []
+        for key in keys:
+            if self.in_transit.get(key) is None:
+                self.in_transit.pop(key, None)
+                self.inbox[key] = None
+            else:
+                carried.append(key)
+        if not carried:
+            return [], []
+        waited = Wait.apply(copy_stream, compute_stream, *[self.in_transit.pop(k) for k in carried])
+        return carried, [t if t.is_floating_point() else t.detach() for t in waited]
 
 
-class _Local(threading.local):
-    def __init__(self) -> None:
-        self.skip_tracker: Optional[SkipTracker] = None
+# the reference's (misspelt) name for the pipeline tracker
+SkipTrackerThroughPotals = StageSkipTracker
 
 
-thread_local = _Local()
+class _Current(threading.local):
+    tracker: Optional[SkipTracker] = None
+
+
+_current = _Current()
 
 
 @contextmanager
 def use_skip_tracker(skip_tracker: SkipTracker) -> Generator[None, None, None]:
-    prev = thread_local.skip_tracker
-    thread_local.skip_tracker = skip_tracker
+    """Make ``skip_tracker`` the one skippable modules of this thread talk to."""
+    saved, _current.tracker = _current.tracker, skip_tracker
     try:
         yield
     finally:
-        thread_local.skip_tracker = prev
+        _current.tracker = saved
 
 
 def current_skip_tracker() -> SkipTracker:
-    if thread_local.skip_tracker is None:
-        thread_local.skip_tracker = SkipTracker()
-    return thread_local.skip_tracker
+    if _current.tracker is None:
+        _current.tracker = SkipTracker()
+    return _current.tracker

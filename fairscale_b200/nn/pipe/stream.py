@@ -1,9 +1,13 @@
-"""Uniform handling of CUDA streams and the CPU "stream" placeholder (parity: fairscale/nn/pipe/stream.py:31-134)."""
+"""One vocabulary for CUDA streams and "the CPU stream", so that the pipeline code has no device-type branches.
+
+Function names and meanings follow fairscale/nn/pipe/stream.py:24-123.  A CPU "stream" is the singleton
+:data:`CPUStream`; every operation on it is a no-op (CPU work is synchronous).
+"""
 
 from __future__ import annotations
 
 from contextlib import contextmanager
-from typing import Generator, List, Union, cast
+from typing import Generator, List, Union
 
 import torch
 
@@ -11,68 +15,73 @@ __all__: List[str] = []
 
 
 class CPUStreamType:
-    pass
+    def __repr__(self) -> str:
+        return "CPUStream"
 
 
 CPUStream = CPUStreamType()
 AbstractStream = Union[torch.cuda.Stream, CPUStreamType]
 
 
+def is_cuda(stream: AbstractStream) -> bool:
+    return not isinstance(stream, CPUStreamType)
+
+
+def as_cuda(stream: AbstractStream) -> torch.cuda.Stream:
+    assert is_cuda(stream), "a CUDA stream is required here"
+    return stream  # type: ignore[return-value]
+
+
+def _pick(device: torch.device, cuda_factory) -> AbstractStream:  # type: ignore[no-untyped-def]
+    return cuda_factory(device) if torch.device(device).type == "cuda" else CPUStream
+
+
 def new_stream(device: torch.device) -> AbstractStream:
-    return CPUStream if device.type != "cuda" else torch.cuda.Stream(device)
+    return _pick(device, torch.cuda.Stream)
 
 
 def current_stream(device: torch.device) -> AbstractStream:
-    return CPUStream if device.type != "cuda" else torch.cuda.current_stream(device)
+    return _pick(device, torch.cuda.current_stream)
 
 
 def default_stream(device: torch.device) -> AbstractStream:
-    return CPUStream if device.type != "cuda" else torch.cuda.default_stream(device)
-
-
-@contextmanager
-def use_device(device: torch.device) -> Generator[None, None, None]:
-    if device.type != "cuda":
-        yield
-        return
-    with torch.cuda.device(device):
-        yield
-
-
-@contextmanager
-def use_stream(stream: AbstractStream) -> Generator[None, None, None]:
-    if not is_cuda(stream):
-        yield
-        return
-    with torch.cuda.stream(as_cuda(stream)):
-        yield
+    return _pick(device, torch.cuda.default_stream)
 
 
 def get_device(stream: AbstractStream) -> torch.device:
     return as_cuda(stream).device if is_cuda(stream) else torch.device("cpu")
 
 
+@contextmanager
+def use_device(device: torch.device) -> Generator[None, None, None]:
+    if torch.device(device).type == "cuda":
+        with torch.cuda.device(device):
+            yield
+    else:
+        yield
+
+
+@contextmanager
+def use_stream(stream: AbstractStream) -> Generator[None, None, None]:
+    if is_cuda(stream):
+        with torch.cuda.stream(as_cuda(stream)):
+            yield
+    else:
+        yield
+
+
 def wait_stream(source: AbstractStream, target: AbstractStream) -> None:
-    """``source`` waits for the work currently queued on ``target``."""
-    if is_cuda(target):
-        if is_cuda(source):
-            as_cuda(source).wait_stream(as_cuda(target))
-        else:
-            as_cuda(target).synchronize()  # the CPU waits for the device
-    # a CUDA stream never needs to wait for the (synchronous) CPU
+    """Work queued on ``source`` after this call starts only when what is queued on ``target`` now has finished."""
+    if not is_cuda(target):
+        return
+    if is_cuda(source):
+        as_cuda(source).wait_stream(as_cuda(target))
+    else:
+        as_cuda(target).synchronize()  # the host itself is the waiter
 
 
 def record_stream(tensor: torch.Tensor, stream: AbstractStream) -> None:
-    """Tell the caching allocator that ``tensor`` is in use on ``stream``."""
-    if is_cuda(stream) and tensor.is_cuda:
-        # record on a view of the whole storage so that shifted views are covered too
-        tensor = tensor.new_empty([0]).set_(tensor.untyped_storage())
-        tensor.record_stream(as_cuda(stream))
-
-
-def is_cuda(stream: AbstractStream) -> bool:
-    return stream is not CPUStream
-
-
-def as_cuda(stream: AbstractStream) -> torch.cuda.Stream:
-    return cast(torch.cuda.Stream, stream)
+    """Tell the caching allocator that ``tensor`` is in use on ``stream`` (its block is not recycled before)."""
+    if not is_cuda(stream):
+        return
+    tensor.record_stream(as_cuda(stream))

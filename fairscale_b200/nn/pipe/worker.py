@@ -1,17 +1,21 @@
-"""One worker thread per pipeline device (parity: fairscale/nn/pipe/worker.py:48-176).
+"""Optional helper threads for the single-process pipeline: one per device, fed through queues.
 
-Kernel launches for different stages are issued from different host threads so that a slow Python section of
-one stage does not delay the launches of the others.  Exceptions travel back to the caller as ``exc_info``.
+The pipeline issues all stages from one thread by default (kernel launches are asynchronous, so a second Python thread
+adds nothing under the GIL unless a stage spends its time in host code that releases it).  With ``Pipeline(...,
+threads=True)`` every stage's ``Task`` is handed to the thread of its device instead and the results come back in
+order; exceptions travel back as ``sys.exc_info()`` triples.  Names and queue protocol as in
+fairscale/nn/pipe/worker.py:48-176: an in-queue takes ``Task`` objects (``None`` stops the thread), the out-queue
+yields ``(True, (task, batch))``, ``(False, exc_info)`` or, once after ``None``, ``(False, None)``.
 """
 
 from __future__ import annotations
 
 import sys
+import threading
 from contextlib import contextmanager
 from queue import Empty, Queue
-from threading import Thread
 from types import TracebackType
-from typing import TYPE_CHECKING, Callable, Dict, Generator, List, Optional, Tuple, Type, Union, cast
+from typing import Callable, Dict, Generator, Hashable, List, Optional, Tuple, Type
 
 import torch
 
@@ -21,97 +25,84 @@ from .stream import AbstractStream, use_device, use_stream
 __all__: List[str] = []
 
 ExcInfo = Tuple[Type[BaseException], BaseException, TracebackType]
-
-if TYPE_CHECKING:
-    InQueue = Queue[Optional["Task"]]
-    OutQueue = Queue[Tuple[bool, Union[Tuple["Task", Batch], ExcInfo, None]]]
-else:
-    InQueue = Queue
-    OutQueue = Queue
+InQueue = Queue
+OutQueue = Queue
 
 
 class Task:
-    """A unit of stage work: ``compute`` runs in the worker thread on ``stream``; ``finalize`` (optional) runs
-    in the main thread afterwards and is where early recomputation is wired into the graph."""
+    """Work of one stage on one micro-batch.  ``compute`` produces the stage's output on ``stream`` (possibly in a
+    helper thread); ``finalize`` runs afterwards in the dispatching thread, on the same stream, and is where an early
+    recomputation gets attached.  Both run under the autograd mode that was active when the task was made."""
 
     def __init__(self, stream: AbstractStream, *, compute: Callable[[], Batch], finalize: Optional[Callable[[Batch], None]]) -> None:
         self.stream = stream
-        self._compute = compute
-        self._finalize = finalize
-        self._grad_enabled = torch.is_grad_enabled()
+        self._body = compute
+        self._epilogue = finalize
+        self._grad_mode = torch.is_grad_enabled()
+
+    @contextmanager
+    def _scope(self) -> Generator[None, None, None]:
+        with use_stream(self.stream), torch.set_grad_enabled(self._grad_mode):
+            yield
 
     def compute(self) -> Batch:
-        with use_stream(self.stream), torch.set_grad_enabled(self._grad_enabled):
-            return self._compute()
+        with self._scope():
+            return self._body()
 
     def finalize(self, batch: Batch) -> None:
-        if self._finalize is None:
-            return
-        with use_stream(self.stream), torch.set_grad_enabled(self._grad_enabled):
-            self._finalize(batch)
+        if self._epilogue is not None:
+            with self._scope():
+                self._epilogue(batch)
 
 
 def worker(in_queue: InQueue, out_queue: OutQueue, device: torch.device) -> None:
+    """Thread body: run tasks until ``None`` arrives, then post the termination marker."""
     with use_device(device):
-        while True:
-            task = in_queue.get()
-            if task is None:
-                break
+        for task in iter(in_queue.get, None):
             try:
-                batch = task.compute()
+                out_queue.put((True, (task, task.compute())))
             except Exception:
-                out_queue.put((False, cast(ExcInfo, sys.exc_info())))
-                continue
-            out_queue.put((True, (task, batch)))
+                out_queue.put((False, sys.exc_info()))
     out_queue.put((False, None))
 
 
+def _device_key(device: torch.device) -> Hashable:
+    device = torch.device(device)
+    if device.type == "cuda":
+        return ("cuda", torch.cuda.current_device() if device.index is None else device.index)
+    return (device.type, 0)
+
+
 def create_workers(devices: List[torch.device]) -> Tuple[List[InQueue], List[OutQueue]]:
-    """Start one daemon thread per distinct device; stages on the same device share a thread."""
-    in_queues: List[InQueue] = []
-    out_queues: List[OutQueue] = []
-    by_device: Dict[torch.device, Tuple[InQueue, OutQueue]] = {}
-
-    def normalize(device: torch.device) -> torch.device:
-        if device.type == "cuda" and device.index is None:
-            return torch.device("cuda", index=torch.cuda.current_device())
-        if device.type == "cpu" and device.index is not None:
-            return torch.device("cpu")
-        return device
-
+    """Queues per entry of ``devices``; entries naming the same device share one thread and one queue pair."""
+    pairs: Dict[Hashable, Tuple[InQueue, OutQueue]] = {}
     for device in devices:
-        device = normalize(device)
-        if device not in by_device:
-            in_q: InQueue = Queue()
-            out_q: OutQueue = Queue()
-            by_device[device] = (in_q, out_q)
-            Thread(target=worker, args=(in_q, out_q, device), daemon=True).start()
-        in_q, out_q = by_device[device]
-        in_queues.append(in_q)
-        out_queues.append(out_q)
-    return in_queues, out_queues
+        key = _device_key(device)
+        if key not in pairs:
+            pairs[key] = (Queue(), Queue())
+            threading.Thread(target=worker, args=(*pairs[key], torch.device(device)), daemon=True).start()
+    chosen = [pairs[_device_key(d)] for d in devices]
+    return [p[0] for p in chosen], [p[1] for p in chosen]
 
 
 def join_workers(in_queues: List[InQueue], out_queues: List[OutQueue]) -> None:
-    """Ask every worker thread to stop and wait for its termination marker."""
+    """Stop the threads behind the queues and wait for their termination markers."""
     if sys.is_finalizing():
-        return  # daemon threads are already gone at interpreter shutdown
-    for q in set(in_queues):
+        return  # daemon threads do not survive interpreter shutdown; nothing to wait for
+    for q in {id(q): q for q in in_queues}.values():
         q.put(None)
-    for q in set(out_queues):
-        while True:
-            try:
-                ok, payload = q.get(timeout=2.0)
-            except Empty:
-                break  # the thread died with the interpreter or never started
-            if not ok and payload is None:
-                break  # termination marker; anything else is a stale result or exception record
+    for q in {id(q): q for q in out_queues}.values():
+        try:
+            while q.get(timeout=2.0) != (False, None):
+                pass  # a stale result or exception record
+        except Empty:
+            pass  # the thread is gone already
 
 
 @contextmanager
 def spawn_workers(devices: List[torch.device]) -> Generator[Tuple[List[InQueue], List[OutQueue]], None, None]:
+    queues = create_workers(devices)
     try:
-        in_queues, out_queues = create_workers(devices)
-        yield in_queues, out_queues
+        yield queues
     finally:
-        join_workers(in_queues, out_queues)
+        join_workers(*queues)

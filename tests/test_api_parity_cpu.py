@@ -18,6 +18,8 @@ pytestmark = pytest.mark.skipif(not os.path.isdir(REF), reason="reference instal
 ALLOWED_MISSING = {
     "nn.pipe.checkpoint": {"ThreadLocal", "Context"},
     "nn.pipe.skip.tracker": {"ThreadLocal"},
+    # skip tensors that cross partitions are extra input / output ports of their stages here: there are no portal objects
+    "nn.pipe.skip.portal": {"Portal", "Context", "PortalBlue", "PortalOrange", "PortalCopy"},
     "nn.pipe.async_schedule": {"create_task", "TailBackwardContext", "AsyncMessageType", "AsyncMessageBody"},
     "nn.checkpoint.checkpoint_activations": {"ThreadLocalCheckpointingState"},
     "experimental.nn.distributed_pipeline.trace": {"GraphCreator"},

@@ -46,3 +46,37 @@ def _worker(rank, world, checkpoint, lazy):
 @pytest.mark.parametrize("checkpoint,lazy", [("never", False), ("always", True), ("except_last", False)])
 def test_async_pipe_matches_sequential(checkpoint, lazy):
     spawn_ranks(_worker, 4, (checkpoint, lazy), backend="gloo")
+
+
+def _static_worker(rank, world):
+    """Three steps with fixed shapes: with the static contract only the first step's messages carry a header."""
+    pipe = AsyncPipe(nn.Sequential(*_layers()), balance=[2, 2, 1], chunks=3, checkpoint="never")
+    pipe.transport.static_shapes = True
+    torch.manual_seed(5)
+    x = torch.randn(6, 6)
+    counts = []
+    for _ in range(3):
+        out = pipe(x if rank == 0 else None)
+        if rank == 2:
+            out.sum().backward()
+            pipe.back_helper()
+        elif rank < 2:
+            pipe.back_helper(out)
+        counts.append((pipe.transport.headers_sent, pipe.transport.headers_received))
+        dist.barrier()
+    if rank < 3:
+        assert counts[1] != counts[0] or rank == 3  # the chunk-count message has no slot and keeps its header
+        per_step_after_first = (counts[2][0] - counts[1][0], counts[2][1] - counts[1][1])
+        first_step = counts[0]
+        assert per_step_after_first[0] < first_step[0] or first_step[0] == 0
+        assert per_step_after_first[1] < first_step[1] or first_step[1] == 0
+        assert per_step_after_first[0] <= 1 and per_step_after_first[1] <= 1  # only the chunk-count message
+    if rank == 1:
+        # a tensor that breaks the contract is refused by the sender
+        with pytest.raises(RuntimeError, match="static contract"):
+            pipe.transport.send(torch.zeros(5, 5), 2, slot=0)
+    dist.barrier()
+
+
+def test_static_shape_contract_skips_headers_after_the_first_step():
+    spawn_ranks(_static_worker, 4, (), backend="gloo")

@@ -13,7 +13,7 @@ from fairscale_b200.nn.pipe.dependency import fork, join
 from fairscale_b200.nn.pipe.phony import get_phony
 from fairscale_b200.nn.pipe.skip import Namespace, pop, skippable, stash, verify_skippables
 from fairscale_b200.nn.pipe.skip.layout import inspect_skip_layout
-from fairscale_b200.nn.pipe.skip.portal import Portal
+from fairscale_b200.nn.pipe.skip.tracker import StageSkipTracker
 from fairscale_b200.nn.pipe.stream import CPUStream, current_stream, default_stream, get_device, is_cuda, new_stream, use_stream, wait_stream
 from fairscale_b200.nn.pipe.worker import Task, spawn_workers
 
@@ -101,23 +101,31 @@ def test_worker_threads_run_tasks_and_forward_exceptions():
         assert not ok and payload[0] is ValueError
 
 
-def test_portal_tensor_life_and_gradient_passage():
-    t = torch.ones(3, requires_grad=True)
-    portal = Portal(t * 2, tensor_life=2)
-    assert portal.use_tensor() is not None  # first use
-    assert portal.use_tensor() is not None  # second use exhausts the life
-    assert portal.tensor is None
-    with pytest.raises(RuntimeError):
-        portal.check_tensor_life()
-    # blue hides the tensor behind a phony, orange brings it back on the other side of the graph
+def test_routed_skip_tensors_travel_as_stage_ports():
+    """A skip tensor that crosses partitions is stashed into the stage's outbox, waits in transit, is moved by ``copy``
+    and comes back through ``deliver`` as an extra stage input; its gradient flows through those nodes."""
+    Stash, Pop = _skip_model()
+    parts = [nn.Sequential(Stash()), nn.Sequential(nn.Identity()), nn.Sequential(Pop())]
+    layout = inspect_skip_layout(parts)
+    (key,) = layout.exports(0)
+    assert layout.imports(2) == [key] and layout.imports(1) == [] and layout.exports(2) == []
+    tracker = StageSkipTracker(layout, index=3)
+    assert tracker.index == 3
     src = torch.ones(3, requires_grad=True)
-    portal = Portal(src * 3, tensor_life=2)  # one life for blue, one for orange
-    phony = portal.blue()
-    assert phony.numel() == 0
-    back = portal.orange(phony)
-    assert torch.equal(back, torch.full((3,), 3.0))
+    carrier = microbatch.Batch(torch.zeros(1), 3)
+    tracker.save(carrier, key[0], key[1], src * 3)      # routed: goes to the outbox, not into the dictionary
+    assert key in tracker.outbox and not tracker.tensors
+    tracker.in_transit[key] = tracker.outbox.pop(key)   # what the pipeline does after the stage has run
+    tracker.copy(carrier, CPUStream, CPUStream, key[0], key[1])
+    carried, tensors = tracker.deliver([key], CPUStream, CPUStream)
+    assert carried == [key] and torch.equal(tensors[0], torch.full((3,), 3.0)) and not tracker.in_transit
+    tracker.inbox[key] = tensors[0]
+    back = tracker.load(carrier, key[0], key[1])
     back.sum().backward()
     assert torch.equal(src.grad, torch.full((3,), 3.0))
+    # a value stashed as None needs no port: it goes straight to the inbox
+    tracker.in_transit[key] = None
+    assert tracker.deliver([key], CPUStream, CPUStream) == ([], []) and tracker.load(carrier, key[0], key[1]) is None
 
 
 def _skip_model():
