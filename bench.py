@@ -133,7 +133,10 @@ def build_ours(args: argparse.Namespace, device: torch.device):
     torch.manual_seed(0)
     model = build_fsdp_gpt(cfg, device)
     opt = FusedAdam(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8)
-    model.attach_optimizer(opt)  # the Adam kernel also writes the bf16 compute shards
+    # The Adam kernel also writes the bf16 compute shards.  FSB200_FUSED_RS_ADAM=1 runs the step of every block inside the
+    # NVLink reduce-scatter of its gradient (one kernel per FSDP unit); measured slower than reduce-scatter + one full-width
+    # Adam launch at 2 GPUs (206.4 vs 200.7 ms per step), so it is off unless asked for.
+    model.attach_optimizer(opt, fuse_step_into_reduce_scatter=os.environ.get("FSB200_FUSED_RS_ADAM", "0") == "1")
 
     def step(tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         loss = model(tokens, targets)

@@ -1,7 +1,7 @@
 """Run the tcgen05 causal attention (forward + backward) a few times on one shape and print CUDA-event timings next to
 cuDNN / flash SDPA through PyTorch (small driver for `ncu` captures and quick comparisons).
 
-    python benchmarks/attn_one.py --b 8 --s 2048 --h 16 --d 128 --iters 5
+    python benchmarks/attn_bench.py --b 8 --s 2048 --h 16 --d 128 --iters 5
 """
 import argparse
 import os

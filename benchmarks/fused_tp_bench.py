@@ -1,6 +1,7 @@
 """Time the fused tensor-parallel kernels against the unfused baseline (NCCL collective + the same tcgen05 GEMM).
 
-Launch: ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/fused_tp_bench.py``.
+Launch: ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/fused_tp_bench.py``
+(or ``python benchmarks/fused_tp_bench.py --tokens 8192 --hidden 2048 --ffn 4096 --iters 2`` for a one-rank run on GPU 0).
 CUDA-event timing after warm-up, max over ranks; a buffer larger than L2 is rewritten between iterations.
 Roofline per op: the slower of FLOPs / measured bf16 GEMM peak and NVLink bytes / 770 GB/s (measured peer copy).
 """
@@ -55,7 +56,17 @@ def main():
     args = ap.parse_args()
     rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    if "RANK" in os.environ:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    else:
+        # started plainly (no launcher): a one-rank group on GPU 0.  The kernels then show their structure (copy CTAs and
+        # tcgen05 CTAs in one launch) without any peer, which is what a single-GPU profiler capture needs.
+        import socket
+
+        with socket.socket() as sock:
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
+        dist.init_process_group("nccl", rank=0, world_size=1, init_method=f"tcp://127.0.0.1:{port}", device_id=torch.device("cuda", 0))
     world = dist.get_world_size()
     dev = torch.device("cuda", rank)
     T, H, F = args.tokens, args.hidden, args.ffn // world

@@ -1,6 +1,7 @@
 """Time the tcgen05 GEMM against torch.matmul (cuBLAS) on the linear-layer shapes of the flagship models.
 
     python benchmarks/gemm_bench.py [--json out.json]
+    python benchmarks/gemm_bench.py --shape 8192 8192 2048 --mode fwd --iters 4     # one product, a few launches (profiler captures)
 
 Each product is timed with CUDA events over `iters` back-to-back launches after warm-up; operands are
 rotated through enough distinct buffers to exceed the 126 MB L2.
@@ -35,11 +36,42 @@ def timeit(fn, sets, iters=20, warmup=5):
     return t0.elapsed_time(t1) / iters
 
 
+def run_one(m: int, n: int, k: int, mode: str, iters: int) -> None:
+    """A few launches of one product (with its fused epilogue variants); prints the time of the last launch."""
+    dev = torch.device("cuda", 0)
+    x = torch.randn(m, k, device=dev).bfloat16()
+    w = torch.randn(n, k, device=dev).bfloat16()
+    dy = torch.randn(m, n, device=dev).bfloat16()
+    bias = torch.randn(n, device=dev).bfloat16()
+    pre = torch.randn(m, k, device=dev).bfloat16()
+    calls = {
+        "fwd": lambda: linear_forward(x, w),
+        "fwd_gelu": lambda: linear_forward(x, w, bias, gelu=True, save_pre_activation=True),
+        "dgrad": lambda: linear_dgrad(dy, w),
+        "dgrad_dgelu": lambda: linear_dgrad(dy, w, dgelu_pre=pre),
+        "wgrad": lambda: linear_wgrad(dy, x),
+    }
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(iters):
+        if i == iters - 1:
+            t0.record()
+        calls[mode]()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1)
+    print(f"{mode} M={m} N={n} K={k}: {ms * 1e3:.1f} us, {2.0 * m * n * k / ms / 1e9:.0f} TFLOP/s")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None, help="run only this product")
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "fwd_gelu", "dgrad", "dgrad_dgelu", "wgrad"])
     args = ap.parse_args()
+    if args.shape is not None:
+        run_one(*args.shape, args.mode, args.iters)
+        return
     dev = torch.device("cuda", 0)
     rows = []
     for M, N, K in SHAPES:

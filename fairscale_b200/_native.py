@@ -120,8 +120,8 @@ def lib() -> ctypes.CDLL:
             if _lib is None:
                 if not os.path.exists(LIB_PATH):
                     raise RuntimeError(
-                        f"native library {LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
-                        "(or fairscale_b200._native.build()) before using CUDA ops"
+                        f"native library {LIB_PATH} is missing: run `python -m fairscale_b200._native` "
+                        "(or call fairscale_b200._native.build()) before using CUDA ops"
                     )
                 _lib = ctypes.CDLL(LIB_PATH)
     return _lib

@@ -57,6 +57,38 @@ all_gather_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n1
   exit_barrier(c, c.channel + 1);
 }
 
+// Column-interleaved all-gather: every rank holds src_p [rows, cols16] (16-byte units); out is [rows, world * cols16] and
+// receives rank p's rows in columns [p * cols16, (p + 1) * cols16): the layout of a gather along the last dimension,
+// written directly (no all-gather into a leading axis followed by a transposing copy).
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
+all_gather_cols_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long rows, int cols16) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);
+  if (!wait_peers(c, c.channel)) return;
+  const long long per_rank = rows * cols16;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long out_ld = static_cast<long long>(c.world) * cols16;
+  for (int k = 0; k < c.world; ++k) {
+    const int p = (c.rank + k) % c.world;
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[p]);
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + (COMM_UNROLL - 1) * stride < per_rank; i += COMM_UNROLL * stride) {
+      uint4 v[COMM_UNROLL];
+#pragma unroll
+      for (int u = 0; u < COMM_UNROLL; ++u) v[u] = ld_peer16(s + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < COMM_UNROLL; ++u) {
+        const long long e = i + u * stride, r = e / cols16;
+        out[r * out_ld + static_cast<long long>(p) * cols16 + (e - r * cols16)] = v[u];
+      }
+    }
+    for (; i < per_rank; i += stride) {
+      const long long r = i / cols16;
+      out[r * out_ld + static_cast<long long>(p) * cols16 + (i - r * cols16)] = ld_peer16(s + i);
+    }
+  }
+  exit_barrier(c, c.channel + 1);
+}
+
 // out[p-th chunk] = src_p[my chunk]: equal-split all-to-all, chunk = n16 16-byte units
 __global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
 all_to_all_kernel(CommCtx c, PtrTable src, uint4* __restrict__ out, long long n16) {
@@ -165,6 +197,96 @@ reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n
     if (accumulate) r += to_f32<TO>(out[i]);
     out[i] = from_f32<TO>(r);
   }
+  exit_barrier(c, c.channel + 1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Reduce-scatter fused with the sharded Adam update (the gradient shard never exists in memory):
+//   g[i]  = scale * sum_p src_p[rank * n + i]                      (fp32, fixed summation order)
+//   m, v, p updated as in the multi-tensor Adam kernel (adam.cu) on this rank's fp32 master shard,
+//   p_copy[i] = bf16 / fp16 (p[i])   written into the symmetric heap, where the next all-gather reads it.
+// Side outputs: *gnorm_sq += sum g^2 (for logging / a later clip of the *next* step), *found_inf = 1 on a non-finite g.
+// The exit barrier also covers p_copy: no peer reads the new shard before every rank has left the kernel.
+// ------------------------------------------------------------------------------------------------
+struct AdamHyper {
+  float step_size, lr, beta1, beta2, eps, decay;
+  int eps_inside_sqrt, adamw;
+};
+
+__device__ __forceinline__ void adam_update(float& p, float g, float& m, float& v, const AdamHyper& h) {
+  m = h.beta1 * m + (1.f - h.beta1) * g;
+  v = h.beta2 * v + (1.f - h.beta2) * g * g;
+  const float denom = h.eps_inside_sqrt ? sqrtf(v + h.eps) : sqrtf(v) + h.eps;
+  if (h.adamw) p = p * (1.f - h.lr * h.decay) - h.step_size * (m / denom);
+  else         p = p - h.step_size * (m / denom + h.decay * p);
+}
+
+template <typename TI, typename TC>
+__global__ void __launch_bounds__(COMM_THREADS, 8)
+reduce_scatter_adam_kernel(CommCtx c, PtrTable src, long long n, float scale, float* __restrict__ p, float* __restrict__ m,
+                           float* __restrict__ v, TC* __restrict__ p_copy, AdamHyper h, float* gnorm_sq, int* found_inf) {
+  if (blockIdx.x == 0) signal_peers(c, c.channel);
+  if (!wait_peers(c, c.channel)) return;
+  constexpr int E = Acc8<TI>::N;
+  const long long nvec = n / E;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long base = static_cast<long long>(c.rank) * n;
+  float sq = 0.f;
+  bool bad = false;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int grp = 0; grp < kMaxRanks; grp += COMM_UNROLL) {
+      if (grp < c.world) {
+        uint4 ld[COMM_UNROLL];
+#pragma unroll
+        for (int q = 0; q < COMM_UNROLL; ++q)
+          if (grp + q < c.world) ld[q] = ld_peer16(reinterpret_cast<const TI*>(src.p[grp + q]) + base + i * E);
+#pragma unroll
+        for (int q = 0; q < COMM_UNROLL; ++q)
+          if (grp + q < c.world) Acc8<TI>::add(g, ld[q]);
+      }
+    }
+#pragma unroll
+    for (int half = 0; half < E / 4; ++half) {
+      const long long o = i * E + half * 4;
+      float4 pp = *reinterpret_cast<const float4*>(p + o), mm = *reinterpret_cast<const float4*>(m + o),
+             vv = *reinterpret_cast<const float4*>(v + o);
+      float pa[4] = {pp.x, pp.y, pp.z, pp.w}, ma[4] = {mm.x, mm.y, mm.z, mm.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gk = g[half * 4 + k] * scale;
+        sq += gk * gk;
+        bad |= !isfinite(gk);
+        adam_update(pa[k], gk, ma[k], va[k], h);
+      }
+      *reinterpret_cast<float4*>(p + o) = make_float4(pa[0], pa[1], pa[2], pa[3]);
+      *reinterpret_cast<float4*>(m + o) = make_float4(ma[0], ma[1], ma[2], ma[3]);
+      *reinterpret_cast<float4*>(v + o) = make_float4(va[0], va[1], va[2], va[3]);
+      if (p_copy != nullptr) {
+        TC lo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) lo[k] = from_f32<TC>(pa[k]);
+        *reinterpret_cast<uint2*>(p_copy + o) = *reinterpret_cast<const uint2*>(lo);  // 8-byte store (o is a multiple of 4)
+      }
+    }
+  }
+  for (long long i = nvec * E + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float gk = 0.f;
+    for (int q = 0; q < c.world; ++q) gk += to_f32<TI>(reinterpret_cast<const TI*>(src.p[q])[base + i]);
+    gk *= scale;
+    sq += gk * gk;
+    bad |= !isfinite(gk);
+    float pk = p[i], mk = m[i], vk = v[i];
+    adam_update(pk, gk, mk, vk, h);
+    p[i] = pk; m[i] = mk; v[i] = vk;
+    if (p_copy != nullptr) p_copy[i] = from_f32<TC>(pk);
+  }
+  if (gnorm_sq != nullptr) {
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) atomicAdd(gnorm_sq, sq);
+  }
+  if (bad && found_inf != nullptr) *found_inf = 1;
   exit_barrier(c, c.channel + 1);
 }
 
@@ -374,6 +496,16 @@ FSB_API int fsb_comm_all_gather_dma(int rank, int world, unsigned epoch, int cha
   return static_cast<int>(cudaGetLastError());
 }
 
+// out[rows, world * row_bytes] <- every rank's [rows, row_bytes] tensor, rank p in byte columns [p * row_bytes, ...)
+FSB_API int fsb_comm_all_gather_cols(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                                     void* const* src, void* out, long long rows, long long row_bytes, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || row_bytes % 16 || row_bytes / 16 > 0x7fffffff) return -1;
+  const int cols16 = static_cast<int>(row_bytes / 16);
+  fsb::all_gather_cols_kernel<<<comm_grid(rows * cols16, 148), fsb::COMM_THREADS, 0, stream>>>(
+      make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), rows, cols16);
+  return static_cast<int>(cudaGetLastError());
+}
+
 FSB_API int fsb_comm_all_to_all(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* src,
                                 void* out, long long chunk_bytes, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks || chunk_bytes % 16) return -1;
@@ -404,6 +536,36 @@ FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int cha
   FSB_RS(FSB_F16, __half, FSB_F16, __half)
   FSB_RS(FSB_F32, float, FSB_F32, float)
 #undef FSB_RS
+  return -1;
+}
+
+// Fused reduce-scatter + Adam on this rank's shard.  src: every rank's flat gradient (in_dtype, world * n elements, in the
+// symmetric heap); p / m / v: fp32 shards of n elements; p_copy (copy_dtype bf16 / fp16, may be null): the compute-dtype
+// shard.  n * sizeof(in_dtype) must be a multiple of 16 and p / m / v 16-byte aligned.
+FSB_API int fsb_comm_reduce_scatter_adam(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                                         void* const* src, int in_dtype, long long n, float scale, float* p, float* m, float* v,
+                                         void* p_copy, int copy_dtype, float step_size, float lr, float beta1, float beta2, float eps,
+                                         float decay, int eps_inside_sqrt, int adamw, float* gnorm_sq, int* found_inf, int* status,
+                                         cudaStream_t stream) {
+  using namespace fsb;
+  if (world > kMaxRanks) return -1;
+  if ((n * (in_dtype == FSB_F32 ? 4 : 2)) % 16) return -1;
+  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15u) return -1;
+  const CommCtx c = make_ctx(rank, world, epoch, channel, pads, counter, status);
+  const PtrTable t = make_table(src, world);
+  const AdamHyper h{step_size, lr, beta1, beta2, eps, decay, eps_inside_sqrt, adamw};
+  const int grid = comm_grid(n / 8, 148);
+#define FSB_RSA(IC, IT, CC, CT)                                                                                               \
+  if (in_dtype == IC && (p_copy == nullptr || copy_dtype == CC)) {                                                            \
+    reduce_scatter_adam_kernel<IT, CT><<<grid, COMM_THREADS, 0, stream>>>(c, t, n, scale, p, m, v, static_cast<CT*>(p_copy), h, \
+                                                                          gnorm_sq, found_inf);                               \
+    return static_cast<int>(cudaGetLastError());                                                                             \
+  }
+  FSB_RSA(FSB_BF16, __nv_bfloat16, FSB_BF16, __nv_bfloat16)
+  FSB_RSA(FSB_F16, __half, FSB_F16, __half)
+  FSB_RSA(FSB_F32, float, FSB_BF16, __nv_bfloat16)
+  FSB_RSA(FSB_F32, float, FSB_F16, __half)
+#undef FSB_RSA
   return -1;
 }
 

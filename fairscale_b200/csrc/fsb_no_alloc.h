@@ -1,10 +1,11 @@
 // Entry points of libfsb200 that never allocate memory.
 //
 // These have no counterpart in the reference library; they exist for callers that must not allocate while
-// they run: code between cudaStreamBeginCapture and cudaStreamEndCapture, a callback on a CUDA stream, a
-// process whose allocator is owned by another runtime and must not be re-entered, or a tight loop that
-// cannot afford an allocator's synchronisation.  Such callers cannot hand the kernel a workspace from
-// torch or cudaMalloc, so the workspace lives inside the library as a fixed device array.
+// they run: code between cudaStreamBeginCapture and cudaStreamEndCapture, a process whose allocator is
+// owned by another runtime and must not be re-entered, or a tight loop that cannot afford an allocator's
+// synchronisation.  Such callers cannot hand the kernel a workspace from torch or cudaMalloc, so the
+// workspace lives inside the library as a fixed device array.  (They still launch kernels: do not call them
+// from a host function enqueued on a stream, where CUDA forbids runtime calls altogether.)
 #pragma once
 
 #include <cuda_runtime.h>

@@ -1093,6 +1093,28 @@ class FullyShardedDataParallel(nn.Module):
                 and param.grad.numel() * param.grad.element_size() > (self.bucket_cap_mb << 20) // max(self.world_size, 1)
                 and ws.can_reduce_scatter(param._fp32_shard, param.grad.data)  # type: ignore[attr-defined]
             )
+            fused_optim = getattr(self, "_fused_optim", None)
+            if (
+                fused
+                and fused_optim is not None
+                and saved is None
+                and not self.move_grads_to_cpu
+                and fused_optim.can_fuse_reduce_scatter(param)
+                and ws.can_reduce_scatter_adam(param.grad.data.view(-1), param.data.view(-1), param.data.view(-1), param.data.view(-1),
+                                               fused_optim.param_copies.get(param))
+            ):
+                # reduce-scatter and optimizer step in ONE kernel: the peers' slices are summed in registers, Adam updates
+                # the fp32 master shard and its moments, and the compute-dtype shard the next all-gather reads is written in
+                # the same pass; the gradient shard is never materialised and ``optim.step()`` finds nothing left to do here
+                grad = param.grad.data
+                param.grad = None
+                comm._COUNTERS["reduce_scatter"] += 1
+                scale = 1.0 / (self.gradient_predivide_factor * self.gradient_postdivide_factor)
+                with comm_range("reduce_scatter_adam"):
+                    fused_optim.reduce_scatter_step(param, ws, grad.view(-1), scale)
+                param._fp16_shard_current = True  # type: ignore[attr-defined]
+                _record_stream(produced, rs_stream)
+                return
             if fused:
                 # one NVLink kernel: pull-reduce this rank's slice from every peer, apply the complete averaging
                 # (pre- and post-division in one factor), land in the gradient dtype the optimizer sees and
@@ -1497,14 +1519,26 @@ class FullyShardedDataParallel(nn.Module):
             for p in m.params:
                 p._fp16_shard_current = False  # type: ignore[attr-defined]
 
-    def attach_optimizer(self, optim: torch.optim.Optimizer) -> None:
+    def attach_optimizer(self, optim: torch.optim.Optimizer, fuse_step_into_reduce_scatter: bool = False) -> None:
         """Let a fused optimizer refresh the resident compute-dtype shards in its update pass.
 
         Requires ``persistent_compute_shards`` and an optimizer exposing ``param_copies`` (this library's
         :class:`~fairscale_b200.optim.Adam`): after every ``optim.step()`` the compute shards are current and
         the master->compute cast before the next all-gather is skipped.
+
+        ``fuse_step_into_reduce_scatter``: additionally run the optimizer step of every large sharded parameter inside
+        the NVLink reduce-scatter of its gradient (one kernel per FSDP unit, launched from the post-backward hook, while
+        the backward of earlier layers is still running).  ``optim.step()`` then only updates what is left (small
+        parameters that travel in buckets).  Only valid when nothing has to inspect all gradients before any update:
+        no gradient accumulation over several backwards, no ``clip_grad_norm_``, no loss scaler.  Under ``no_sync()``
+        and for parameters with an already reduced gradient shard the unfused route is taken automatically.
         """
         self._lazy_init()
+        if fuse_step_into_reduce_scatter:
+            if not hasattr(optim, "reduce_scatter_step"):
+                raise TypeError("optimizer cannot step inside the reduce-scatter; use fairscale_b200.optim.Adam")
+            for m in get_fsdp_instances(self):
+                m._fused_optim = optim
         copies = getattr(optim, "param_copies", None)
         if copies is None:
             raise TypeError("optimizer has no `param_copies`; use fairscale_b200.optim.Adam")

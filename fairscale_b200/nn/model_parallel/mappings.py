@@ -3,8 +3,9 @@
 Parity: fairscale/nn/model_parallel/mappings.py:30-156 (the Megatron f / g operators and the
 scatter / gather pair).  Collectives go through :mod:`fairscale_b200.parallel.comm`, i.e. the NVLink
 kernels when a symmetric workspace exists for the model-parallel group and NCCL / gloo otherwise.
-The gather writes every rank's slice straight into its column window of the output (strided all-gather)
-instead of ``all_gather`` + ``torch.cat``.
+The gather along the last dimension is :func:`fairscale_b200.parallel.comm.all_gather_last_dim`: over NVLink the pulling
+kernel writes every rank's slice straight into its column window of the output; over NCCL / gloo it is one all-gather
+along a leading axis plus one transposing copy (the reference uses ``all_gather`` into a list + ``torch.cat``).
 """
 
 from __future__ import annotations
@@ -45,13 +46,7 @@ def _gather(input_: torch.Tensor) -> torch.Tensor:
     world = dist.get_world_size(group=group)
     if world == 1:
         return input_
-    rank = dist.get_rank(group=group)
-    last = input_.size(-1)
-    # all-gather along a leading axis, then one transposing copy into the interleaved layout
-    stacked = torch.empty((world,) + tuple(input_.shape), dtype=input_.dtype, device=input_.device)
-    comm.all_gather_into(stacked.view(-1), input_.contiguous().view(-1), group=group)
-    out = stacked.movedim(0, -2).reshape(*input_.shape[:-1], world * last)
-    return out.contiguous()
+    return comm.all_gather_last_dim(input_, group=group)
 
 
 class _CopyToModelParallelRegion(torch.autograd.Function):

@@ -254,6 +254,44 @@ class Adam(Optimizer):
             self._update_optim_scale(any_overflow)
         return loss
 
+    # ------------------------------------------------------------------ step fused into the gradient reduction
+    def group_of(self, p: torch.Tensor) -> Optional[Dict[str, Any]]:
+        for group in self.param_groups:
+            if any(q is p for q in group["params"]):
+                return group
+        return None
+
+    def can_fuse_reduce_scatter(self, p: torch.Tensor) -> bool:
+        """Whether :meth:`reduce_scatter_step` may update ``p``: plain fp32 Adam state, nothing that has to look at all
+        gradients first (a loss scaler's skip flag, a clip coefficient) and the parameter known to this optimizer."""
+        return (self.precision is Precision.FULL_PRECISION and p.dtype == torch.float32 and self.inv_scale is None
+                and self.noop_flag is None and self.group_of(p) is not None)
+
+    @torch.no_grad()
+    def reduce_scatter_step(self, p: torch.Tensor, workspace: Any, flat_grad: torch.Tensor, scale: float,
+                            gnorm_sq: Optional[torch.Tensor] = None) -> None:
+        """This optimizer's step for the single (sharded, fp32) parameter ``p``, executed inside the reduce-scatter of its
+        unreduced flat gradient ``flat_grad``: one NVLink kernel sums the peers' slices, applies Adam to ``p`` and its
+        moments and writes the compute-dtype copy registered in ``param_copies``.  The caller leaves ``p.grad`` unset, so
+        the regular :meth:`step` of the same iteration skips ``p``."""
+        group = self.group_of(p)
+        assert group is not None
+        state = self.state[p]
+        if len(state) == 0:
+            state["step"] = 0
+            state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+            state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+        state["step"] += 1
+        t = state["step"]
+        beta1, beta2 = group["betas"]
+        step_size = group["lr"] * (1 - beta2**t) ** 0.5 / (1 - beta1**t) if group["bias_correction"] else group["lr"]
+        found = self._found_inf.get(p.device)
+        if found is None:
+            found = self._found_inf[p.device] = torch.zeros(1, dtype=torch.int32, device=p.device)
+        workspace.reduce_scatter_adam(flat_grad, p.data.view(-1), state["exp_avg"].view(-1), state["exp_avg_sq"].view(-1),
+                                      self.param_copies.get(p), scale, step_size, group["lr"], beta1, beta2, group["eps"],
+                                      group["weight_decay"], self.eps_mode == 0, self.adamw, gnorm_sq=gnorm_sq, found_inf=found)
+
     def _launch(self, gi: int, device: torch.device, items: List[Any], group: Dict[str, Any], step_size: float) -> None:
         chunk = _bind.fn("fsb_adam_chunk_size")()
         # one launch per distinct dtype signature (normally exactly one)

@@ -111,6 +111,28 @@ def all_gather_into(out: torch.Tensor, shard: torch.Tensor, group: Any = None, a
     return dist.all_gather_into_tensor(out, shard.contiguous(), group=group, async_op=async_op)
 
 
+def all_gather_last_dim(part: torch.Tensor, group: Any = None) -> torch.Tensor:
+    """Every rank's ``part [..., L]`` side by side along the last dimension: ``[..., world * L]``.
+
+    With an NVLink workspace the pulling kernel writes each rank's rows straight into their column window of the result;
+    otherwise the parts are gathered along a leading axis (one collective) and moved into place by one transposing copy.
+    """
+    _COUNTERS["all_gather"] += 1
+    world = group_size(group)
+    if world == 1 or not _is_real_group(group):
+        return part
+    part = part.contiguous()
+    out = torch.empty(*part.shape[:-1], world * part.shape[-1], dtype=part.dtype, device=part.device)
+    ws = _symm_for(group, part)
+    if ws is not None and ws.can_all_gather_cols(out, part):
+        ws.all_gather_cols(out, part)
+        return out
+    stacked = torch.empty((world,) + tuple(part.shape), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(stacked.view(-1), part.view(-1), group=group)
+    out.view(*part.shape[:-1], world, part.shape[-1]).copy_(stacked.movedim(0, -2))
+    return out
+
+
 def reduce_scatter_into(out: torch.Tensor, flat_in: torch.Tensor, group: Any = None, async_op: bool = False):
     """Sum ``flat_in`` (``world*n`` elements) over ranks; rank r keeps elements ``[r*n,(r+1)*n)``."""
     _COUNTERS["reduce_scatter"] += 1

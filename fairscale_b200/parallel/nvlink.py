@@ -38,9 +38,13 @@ def _sigs() -> None:
     S["fsb_comm_set_timeout_ms"] = [c_longlong]
     S["fsb_comm_barrier"] = head + [c_void_p, c_void_p]
     S["fsb_comm_all_gather"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
+    S["fsb_comm_all_gather_cols"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_all_gather_dma"] = head + [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_all_to_all"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_reduce_scatter"] = head + [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
+    S["fsb_comm_reduce_scatter_adam"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_float, c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p]
     S["fsb_comm_all_reduce"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_moe_scatter_rows"] = head + [c_void_p] * 6 + [c_longlong, c_int, c_int, c_void_p, c_void_p]
     S["fsb_comm_moe_gather_rows"] = head + [c_void_p] * 8 + [c_longlong, c_int, c_int, c_void_p, c_void_p]
@@ -263,6 +267,23 @@ class NvlinkWorkspace:
         _bind.call("fsb_comm_all_gather", *self._head(ln), self._counter(ln), self.peers(off), out.data_ptr(),
                    nbytes, _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
 
+    def can_all_gather_cols(self, out: torch.Tensor, part: torch.Tensor) -> bool:
+        row_bytes = part.shape[-1] * part.element_size()
+        return (part.dim() >= 1 and part.is_contiguous() and out.is_contiguous() and row_bytes % 16 == 0 and self._aligned(out)
+                and out.numel() == part.numel() * self.world and self._fits(part, part.numel() * part.element_size())
+                and (self.offset_of(part) is None or self._aligned(part)))
+
+    def all_gather_cols(self, out: torch.Tensor, part: torch.Tensor, lane: int = 0) -> None:
+        """``out[..., r * L:(r + 1) * L] = part of rank r`` (L = ``part.shape[-1]``): a gather along the last dimension
+        written straight into its interleaved layout by the pulling kernel."""
+        ln = self._lane(lane)
+        off = self.offset_of(part)
+        if off is None:
+            off = self._stage(ln, part)
+        rows = part.numel() // part.shape[-1]
+        _bind.call("fsb_comm_all_gather_cols", *self._head(ln), self._counter(ln), self.peers(off), out.data_ptr(), rows,
+                   part.shape[-1] * part.element_size(), _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
+
     def reduce_scatter(self, out: torch.Tensor, flat_in: torch.Tensor, scale: float = 1.0, accumulate: bool = False, lane: int = 2) -> None:
         """``out = (out if accumulate else 0) + scale * sum_ranks flat_in[rank * n : (rank + 1) * n]``, n = out.numel();
         ``flat_in`` may be shorter than ``world * n`` (implicit zero padding)."""
@@ -279,6 +300,32 @@ class NvlinkWorkspace:
                    _bind.stream_ptr(self.device))
         if window is not None:
             self.release_grad_window(flat_in)  # the kernel's exit barrier covers the peers' reads of this window
+
+    def can_reduce_scatter_adam(self, flat_in: torch.Tensor, p: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
+                                p_copy: Optional[torch.Tensor]) -> bool:
+        """The fused reduce-scatter + Adam kernel reads the flat gradient where it lies, so that has to be a gradient
+        window of the heap; master parameter and moments are fp32 shards on this device."""
+        n = p.numel()
+        return (self._window_of(flat_in) is not None and flat_in.dtype in (torch.bfloat16, torch.float16, torch.float32)
+                and (n * flat_in.element_size()) % 16 == 0 and n * self.world * flat_in.element_size() <= self._gw_bytes
+                and all(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n for t in (p, m, v)) and self._aligned(p, m, v)
+                and (p_copy is None or (p_copy.dtype in (torch.bfloat16, torch.float16) and p_copy.numel() == n and p_copy.data_ptr() % 8 == 0)))
+
+    def reduce_scatter_adam(self, flat_in: torch.Tensor, p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, p_copy: Optional[torch.Tensor],
+                            scale: float, step_size: float, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
+                            eps_inside_sqrt: bool, adamw: bool, gnorm_sq: Optional[torch.Tensor] = None,
+                            found_inf: Optional[torch.Tensor] = None, lane: int = 2) -> None:
+        """One kernel: ``g = scale * sum_ranks flat_in[rank slice]`` and the Adam update of ``p, m, v`` with it; the updated
+        value also goes to ``p_copy`` (the compute-dtype shard the next all-gather reads)."""
+        ln = self._lane(lane)
+        off = self.offset_of(flat_in)
+        assert off is not None and self._window_of(flat_in) is not None
+        _bind.call("fsb_comm_reduce_scatter_adam", *self._head(ln), self._counter(ln), self.peers(off), _bind.dtype_code(flat_in.dtype),
+                   p.numel(), scale, p.data_ptr(), m.data_ptr(), v.data_ptr(), _bind.ptr(p_copy),
+                   _bind.dtype_code(p_copy.dtype) if p_copy is not None else 0, step_size, lr, beta1, beta2, eps, weight_decay,
+                   int(eps_inside_sqrt), int(adamw), _bind.ptr(gnorm_sq), _bind.ptr(found_inf), _bind.status_ptr(self.device),
+                   _bind.stream_ptr(self.device))
+        self.release_grad_window(flat_in)
 
     def all_reduce(self, t: torch.Tensor, lane: int = 0) -> None:
         ln = self._lane(lane)

@@ -300,9 +300,9 @@ def test_gpt_forward_backward_matches_torch():
 
 
 def test_smoke_entry():
-    import __graft_entry__ as g
+    from fairscale_b200.utils.smoke import smoke
 
-    g.smoke()
+    smoke()
 
 
 # the last two: the flagship benchmark shape (more work items than SMs, so the persistent kernels loop) and a long D=64 case
