@@ -82,7 +82,7 @@ struct AttnBars {
   uint64_t p_full;        // probabilities / dS written to shared memory
   uint64_t acc_done;      // accumulate-type MMAs of the iteration finished (P buffer + accumulators free)
   uint64_t acc_done2[2];  // dQ kernel: the same, alternating with the double-buffered dS tile
-  uint64_t p_full2[2];    // dQ kernel: dS buffer b written.  One barrier per buffer: with a single one the threads could
+  uint64_t p_full2[2];    // backward kernels: dS (dQ kernel) / P^T and dS^T (dK/dV kernel) buffer b written.  One barrier per buffer: with a single one the threads could
                           // complete the phase of step u+1 (other buffer) before the MMA warp had observed step u
   uint64_t stat_empty;    // backward (persistent): the item's last products that read the stationary tiles have completed
   uint64_t acc_free;      // backward (persistent): the 8 compute warps have read the item's output accumulators
@@ -686,9 +686,10 @@ struct DkvSmem {
   static constexpr int STAGES = 3;                             // Q / dO sub-tiles in flight
   static constexpr int Q_OFF = 2 * TILE;
   static constexpr int DO_OFF = 2 * TILE + STAGES * QTILE;
-  static constexpr int PT_OFF = 2 * TILE + 2 * STAGES * QTILE;  // [128 keys x 64 q] bf16
-  static constexpr int DST_OFF = PT_OFF + ATT_BM * KV_QSUB * 2;
-  static constexpr int BAR_OFF = DST_OFF + ATT_BM * KV_QSUB * 2;
+  static constexpr int PT_BYTES = ATT_BM * KV_QSUB * 2;          // [128 keys x 64 q] bf16
+  static constexpr int PT_OFF = 2 * TILE + 2 * STAGES * QTILE;  // P^T, two buffers: the threads fill one while the
+  static constexpr int DST_OFF = PT_OFF + 2 * PT_BYTES;         // tensor cores still read the other; dS^T likewise
+  static constexpr int BAR_OFF = DST_OFF + 2 * PT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -807,17 +808,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
         const uint32_t sdo = smem_u32(smem + L::DO_OFF + st * L::QTILE);
         // dK / dV still belong to the previous item until its threads have read them
         if (t == 0 && !mbar_wait_warp(&bars->acc_free, (it & 1u) ^ 1u, abort_flag, 70)) { ok = false; break; }
-        if (!mbar_wait_warp(&bars->p_full, tt & 1u, abort_flag, 71)) { ok = false; break; }
+        const int buf = t & 1;
+        if (!mbar_wait_warp(&bars->p_full2[buf], (tt >> 1) & 1u, abort_flag, 71)) { ok = false; break; }
         tc_fence_after_sync();
+        const uint32_t pbuf = static_cast<uint32_t>(buf) * L::PT_BYTES;
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < KV_QSUB / 16; ++ks)
-            umma_f16_ss(tmem_base + 128, desc_kmajor(spt, ks, SLAB), desc_mnmajor(sdo, ks, QSLAB), idesc_a, (t | ks) != 0);
+            umma_f16_ss(tmem_base + 128, desc_kmajor(spt + pbuf, ks, SLAB), desc_mnmajor(sdo, ks, QSLAB), idesc_a, (t | ks) != 0);
 #pragma unroll
           for (int ks = 0; ks < KV_QSUB / 16; ++ks)
-            umma_f16_ss(tmem_base + 256, desc_kmajor(sdst, ks, SLAB), desc_mnmajor(sq, ks, QSLAB), idesc_a, (t | ks) != 0);
+            umma_f16_ss(tmem_base + 256, desc_kmajor(sdst + pbuf, ks, SLAB), desc_mnmajor(sq, ks, QSLAB), idesc_a, (t | ks) != 0);
           umma_commit(&bars->str_empty[st]);
-          umma_commit(&bars->acc_done);
+          umma_commit(&bars->acc_done2[buf]);
         }
         __syncwarp();
       }
@@ -862,22 +865,24 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_cons
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
-        if (tt > 0) {  // the accumulate products that read the previous P^T / dS^T
-          if (!mbar_wait(&bars->acc_done, (tt - 1u) & 1u, abort_flag, 73)) { ok = false; break; }
+        if (tt >= 2) {  // the accumulate products that read this P^T / dS^T buffer two sub-tiles ago
+          if (!mbar_wait(&bars->acc_done2[buf], ((tt >> 1) - 1u) & 1u, abort_flag, 73)) { ok = false; break; }
         }
+        uint8_t* pt = spt + buf * L::PT_BYTES;
+        uint8_t* dst = sdst + buf * L::PT_BYTES;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {  // 32 query columns = 4 chunks of 8 bf16
-          *reinterpret_cast<uint4*>(spt + swz(row, half * 4 + ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
-          *reinterpret_cast<uint4*>(sdst + swz(row, half * 4 + ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(pt + swz(row, half * 4 + ch)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(dst + swz(row, half * 4 + ch)) = make_uint4(pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
         }
         fence_proxy_async();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_full);
+        if (lane == 0) mbar_arrive(&bars->p_full2[buf]);
       }
       if (!ok) break;
       const uint32_t tl = tt0 + static_cast<uint32_t>(n_sub) - 1u;  // the item's last sub-tile
-      if (!mbar_wait(&bars->acc_done, tl & 1u, abort_flag, 74)) { ok = false; break; }
+      if (!mbar_wait(&bars->acc_done2[tl & 1u], (tl >> 1) & 1u, abort_flag, 74)) { ok = false; break; }
       tc_fence_after_sync();
       __nv_bfloat16* base = p.dqkv + static_cast<size_t>(krow0 + row) * (3 * HD) + h * D + half * (D / 2);
 #pragma unroll 1

@@ -506,6 +506,96 @@ FSB_API int fsb_comm_all_gather_cols(int rank, int world, unsigned epoch, int ch
   return static_cast<int>(cudaGetLastError());
 }
 
+// Partial all-gather on the copy engines: byte ranges [lo[i], hi[i]) of the gathered buffer (`world` shards of
+// `shard_bytes`) are fetched from the shards that hold them, behind one flag barrier (peers' shards are final).  There is
+// no exit barrier: the caller must run a full collective on the same shards (which has one) before any shard changes.
+FSB_API int fsb_comm_gather_ranges_dma(int rank, int world, unsigned epoch, int channel, void* const* pads, void* const* src, void* out,
+                                       long long shard_bytes, int n_ranges, const long long* lo, const long long* hi, int* status,
+                                       cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || shard_bytes <= 0) return -1;
+  fsb::barrier_kernel<<<1, fsb::COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch, channel, pads, nullptr, status));
+  for (int i = 0; i < n_ranges; ++i) {
+    long long a = lo[i];
+    while (a < hi[i]) {
+      const long long p = a / shard_bytes;
+      if (p >= world) return -1;
+      const long long end = (p + 1) * shard_bytes < hi[i] ? (p + 1) * shard_bytes : hi[i];
+      cudaError_t e = cudaMemcpyAsync(static_cast<char*>(out) + a, static_cast<const char*>(src[p]) + (a - p * shard_bytes),
+                                      static_cast<size_t>(end - a), cudaMemcpyDeviceToDevice, stream);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      a = end;
+    }
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Stream-ordered 32-bit store by the driver (no kernel, no SM): cuStreamWriteValue32, looked up once.
+using stream_write_fn = int (*)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
+static stream_write_fn stream_write_entry() {
+  static stream_write_fn fn = []() -> stream_write_fn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<stream_write_fn>(f);
+  }();
+  return fn;
+}
+
+FSB_API int fsb_comm_stream_memops_available() { return stream_write_entry() != nullptr ? 1 : 0; }
+
+// The copies of an all-gather, reporting their progress to a consumer that runs concurrently.  Bytes [prio_lo, prio_hi) of
+// the gathered buffer go first, in pieces of `piece_bytes`; after piece i is in place flags[i] = flag_value is stored in
+// stream order by the driver.  The rest of the buffer follows.
+//
+// Two phases, because only copies from a PEER are certain to run on a copy engine: a copy within this GPU's own memory
+// made no progress while a persistent kernel that fills every SM was waiting for it.
+//   phase 0 - the part of [prio_lo, prio_hi) that lies in this rank's own shard.  Enqueue it on the consumer's stream,
+//             before the consumer.
+//   phase 1 - on a side stream that waits for phase 0: the peers' parts of [prio_lo, prio_hi) with one flag store per
+//             piece, then the peers' parts of the rest, then the rest of the own shard (which may have to wait for the
+//             consumer to leave the SMs).  Nothing the consumer waits for needs an SM.
+// The caller brackets the two calls with barriers (peers' shards final before / peers done reading after) on the
+// consumer's stream.  Returns -2 without stream memory operations.
+FSB_API int fsb_comm_gather_flagged_copies(int rank, int world, int phase, void* const* src, void* out, long long shard_bytes,
+                                           long long prio_lo, long long prio_hi, long long piece_bytes, unsigned int* flags,
+                                           unsigned int flag_value, cudaStream_t stream) {
+  const long long total = shard_bytes * world;
+  if (world > fsb::kMaxRanks || rank < 0 || rank >= world || shard_bytes <= 0 || piece_bytes <= 0 || prio_lo < 0 || prio_hi > total ||
+      prio_lo > prio_hi)
+    return -1;
+  const stream_write_fn write_u32 = stream_write_entry();
+  if (write_u32 == nullptr) return -2;
+  // copies the part of [a, b) held by the peers (own == false) or by this rank (own == true)
+  auto copy_range = [&](long long a, long long b, bool own) -> cudaError_t {
+    while (a < b) {
+      const long long p = a / shard_bytes;
+      const long long end = (p + 1) * shard_bytes < b ? (p + 1) * shard_bytes : b;
+      if ((p == rank) == own) {
+        cudaError_t e = cudaMemcpyAsync(static_cast<char*>(out) + a, static_cast<const char*>(src[p]) + (a - p * shard_bytes),
+                                        static_cast<size_t>(end - a), cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) return e;
+      }
+      a = end;
+    }
+    return cudaSuccess;
+  };
+  if (phase == 0) return static_cast<int>(copy_range(prio_lo, prio_hi, true));
+  int piece = 0;
+  for (long long a = prio_lo; a < prio_hi; a += piece_bytes, ++piece) {
+    cudaError_t e = copy_range(a, a + piece_bytes < prio_hi ? a + piece_bytes : prio_hi, false);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (write_u32(stream, reinterpret_cast<unsigned long long>(flags + piece), flag_value, 0u) != 0) return -3;
+  }
+  cudaError_t e = copy_range(0, prio_lo, false);
+  if (e == cudaSuccess) e = copy_range(prio_hi, total, false);
+  if (e == cudaSuccess) e = copy_range(0, prio_lo, true);
+  if (e == cudaSuccess) e = copy_range(prio_hi, total, true);
+  return static_cast<int>(e);
+}
+
 FSB_API int fsb_comm_all_to_all(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* src,
                                 void* out, long long chunk_bytes, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks || chunk_bytes % 16) return -1;

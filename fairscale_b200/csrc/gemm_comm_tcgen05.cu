@@ -35,6 +35,8 @@ constexpr int FUSED_BLOCK_N = 256;
 constexpr int FUSED_EPI_OFFSET = SmemLayout<FUSED_BLOCK_N>::EPI_OFFSET;
 constexpr int FUSED_SMEM = SmemLayout<FUSED_BLOCK_N>::TOTAL;
 
+constexpr int kMaxNTiles = 64;  // N tiles of the weight-gather GEMM (N <= 16384)
+
 struct FusedParams {
   CommCtx c;
   PtrTable peer;          // ag: every rank's A shard; rs: every rank's staging buffer [M, N]
@@ -48,6 +50,10 @@ struct FusedParams {
   const __nv_bfloat16* out_bias;  // rs: bias added once after the reduction (may be null)
   int n_comm;             // CTAs [0, n_comm) communicate, the rest compute
   int Mc;                 // rows per chunk
+  // weight-gather GEMM (MODE 2): the B operand is a row range of a flat buffer that arrives shard by shard.
+  // N-tile visited o-th: order[o]; it may start once chunks need_lo[tn] .. need_hi[tn] (rank ids) have landed.
+  int local_first;        // copy CTAs move the local shard first (its tiles start almost at once)
+  uint8_t order[kMaxNTiles], need_lo[kMaxNTiles], need_hi[kMaxNTiles];
 };
 
 __device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, volatile int* abort_flag, unsigned long long wait_ns) {
@@ -76,15 +82,15 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);  // warp-uniform
   const int lane = threadIdx.x & 31;
   const int g = blockIdx.x - f.n_comm, G = gridDim.x - f.n_comm;
   const int world = f.c.world, rank = f.c.rank;
 
-  const int tiles_mc = f.Mc / BLOCK_M;
+  const int tiles_mc = (MODE == 2) ? (p.M + BLOCK_M - 1) / BLOCK_M : f.Mc / BLOCK_M;  // MODE 2: all M tiles
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int tiles_per_chunk = tiles_mc * tiles_n;
-  const int num_tiles = tiles_per_chunk * world;
+  const int num_tiles = (MODE == 2) ? tiles_per_chunk : tiles_per_chunk * world;
   const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
   // chunk visited k-th: ag starts at home, rs ends at home
   auto chunk_of = [&](int k) { return (rank + k + (MODE == 1 ? 1 : 0)) % world; };
@@ -110,7 +116,7 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -119,20 +125,33 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
       bool ok = true;
       int ready_chunk = -1;
       for (int tile = g; tile < num_tiles && ok; tile += G) {
-        const int k = tile / tiles_per_chunk;
-        const int chunk = chunk_of(k);
+        const int k = (MODE == 2) ? 0 : tile / tiles_per_chunk;
+        const int chunk = (MODE == 2) ? rank : chunk_of(k);
         int tm, tn;
-        tile_coords(tile - k * tiles_per_chunk, tiles_mc, tiles_n, tm, tn);
+        if (MODE == 2) {
+          // all M tiles of one N tile run back to back (its weight rows stay in L2), N tiles in arrival order
+          tn = f.order[tile / tiles_mc];
+          tm = tile % tiles_mc;
+          if (ready_chunk != tn) {
+            for (int cnk = f.need_lo[tn]; cnk <= f.need_hi[tn] && ok; ++cnk)
+              if (!wait_counter(f.counts + cnk, f.target, abort_flag, f.c.wait_ns)) ok = false;
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");  // the copy CTAs' stores before this thread's TMA reads
+            ready_chunk = tn;
+          }
+        } else {
+          tile_coords(tile - k * tiles_per_chunk, tiles_mc, tiles_n, tm, tn);
+        }
         const int n0 = tn * BLOCK_N;
         const bool local_a = (MODE == 0) && (chunk == rank);
-        const int m0 = local_a ? tm * BLOCK_M : chunk * f.Mc + tm * BLOCK_M;
+        const int m0 = (MODE == 2) ? tm * BLOCK_M : (local_a ? tm * BLOCK_M : chunk * f.Mc + tm * BLOCK_M);
         if (MODE == 0 && !local_a && ready_chunk != chunk) {
           // the copy CTAs publish a chunk with generic-proxy stores; order them before this thread's TMA reads
           if (!wait_counter(f.counts + chunk, f.target, abort_flag, f.c.wait_ns)) { ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");
           ready_chunk = chunk;
         }
-        const CUtensorMap* ta = local_a ? &tmap_a_local : &tmap_a;
+        const CUtensorMap* ta = (local_a || MODE == 2) ? &tmap_a_local : &tmap_a;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -151,7 +170,8 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // MMA issuer: all lanes run the loop (warp-uniform addresses and descriptors), one elected lane issues
+    {
       const uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, true, false, p.b_mn_major != 0);
       const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
       const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
@@ -161,25 +181,29 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = g; tile < num_tiles && ok; tile += G) {
-        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            const uint64_t adesc = make_smem_desc(sa + k * 32u, 16u, 1024u);
-            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+              const uint64_t adesc = make_smem_desc(sa + k * 32u, 16u, 1024u);
+              const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024u);
+              umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[stage]);
           }
-          umma_commit(&empty_bar[stage]);
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(&tmem_full_bar[acc]);
+        if (elect_one()) umma_commit(&tmem_full_bar[acc]);
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -191,11 +215,12 @@ __device__ __forceinline__ void fused_gemm_cta(const CUtensorMap& tmap_a_local, 
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = g; tile < num_tiles && ok; tile += G) {
-      const int k = tile / tiles_per_chunk;
-      const int chunk = chunk_of(k);
+      const int k = (MODE == 2) ? 0 : tile / tiles_per_chunk;
+      const int chunk = (MODE == 2) ? 0 : chunk_of(k);
       int tm, tn;
-      tile_coords(tile - k * tiles_per_chunk, tiles_mc, tiles_n, tm, tn);
-      const int row = chunk * f.Mc + tm * BLOCK_M + quad * 32 + lane;
+      if (MODE == 2) { tn = f.order[tile / tiles_mc]; tm = tile % tiles_mc; }
+      else           { tile_coords(tile - k * tiles_per_chunk, tiles_mc, tiles_n, tm, tn); }
+      const int row = (MODE == 2 ? 0 : chunk * f.Mc) + tm * BLOCK_M + quad * 32 + lane;
       const int n0 = tn * BLOCK_N;
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
@@ -278,8 +303,9 @@ __device__ __forceinline__ void ag_copy_cta(const FusedParams& f, uint8_t* smem)
   const int n_jobs = per_cta * c.world;
   if (threadIdx.x == 0 && per_cta > 0) {
     volatile int* abort_flag = &copy_abort;
-    // visiting order: remote chunks in ring order, the local copy last (nothing waits for it)
-    auto chunk_id = [&](int k) { return (c.rank + 1 + k) % c.world; };
+    // visiting order: remote chunks in ring order, the local copy last (nothing waits for it) - or first, when the
+    // consumers also read the local chunk from the gather buffer (weight-gather GEMM)
+    auto chunk_id = [&](int k) { return (c.rank + (f.local_first ? 0 : 1) + k) % c.world; };
     auto issue_load = [&](int n) {
       const CopyJob j = copy_job(n, per_cta, chunk_bytes, f.n_comm, cta);
       const int b = n % COPY_BUFS;
@@ -326,6 +352,22 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
     return;
   }
   fused_gemm_cta<0>(tmap_a_local, tmap_a_gather, tmap_b, p, f, smem);
+}
+
+// ------------------------------------------------------------------------------------------------ weight-gather GEMM
+// C[M, N] = epilogue( A[M, K] * W^T ) where W [N, K] is a row range of a flat parameter whose shards are being
+// all-gathered by the SAME kernel: the copy CTAs pull every rank's shard into the local full-parameter buffer (kept for
+// the unit's other products and for backward) and publish one counter per shard; a compute CTA starts an N tile as soon
+// as the shards holding its weight rows have landed.  N tiles are visited in arrival order, the local shard first.
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+wag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, GemmParams p, FusedParams f) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (static_cast<int>(blockIdx.x) < f.n_comm) {
+    ag_copy_cta(f, smem);
+    return;
+  }
+  fused_gemm_cta<2>(tmap_a, tmap_a, tmap_w, p, f, smem);
 }
 
 // ------------------------------------------------------------------------------------------------ gemm_rs
@@ -539,12 +581,80 @@ FSB_API int fsb_ag_gemm_bf16(int rank, int world, unsigned epoch, int channel, v
   int grid = 0;
   const int tiles = (M / BLOCK_M) * ((N + FUSED_BLOCK_N - 1) / FUSED_BLOCK_N);
   if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
-  static bool attr_set = false;
-  if (!attr_set) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_set[64] = {false};  // the attribute is per device
+  if (!attr_set[dev & 63]) {
     cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM);
-    attr_set = true;
+    attr_set[dev & 63] = true;
   }
   ag_gemm_kernel<<<grid, GEMM_THREADS, FUSED_SMEM, stream>>>(tl, tg, tb, p, f);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Weight-gather GEMM (FSDP: the all-gather of a unit's flat parameter fused with the first product that consumes it).
+//   shard_peers[r]: rank r's shard of the flat parameter (shard_elems bf16, in the symmetric heap)
+//   full: local buffer of world * shard_elems bf16 that receives every shard (the gathered flat parameter)
+//   W = full + w_offset, [N, K] row-major (w_offset and K multiples of 8);  C[M, N] = epilogue(A[M, K] W^T + bias)
+// bias (optional) must already be valid (it is NOT awaited).  counts / target as for fsb_ag_gemm_bf16.
+FSB_API int fsb_wag_gemm_bf16(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                              void* const* shard_peers, long long shard_elems, void* full, long long w_offset, const void* A,
+                              void* C, const void* bias, void* aux_out, int M, int N, int K, int lda, int ldc, int epilogue,
+                              void* counts, unsigned target, int n_comm, int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world < 1 || world > kMaxRanks || K % 8 || lda % 8 || ldc % 8 || w_offset % 8 || (shard_elems * 2) % 16) return -1;
+  if (epilogue != EPI_NONE && epilogue != EPI_BIAS && epilogue != EPI_BIAS_GELU) return -1;
+  const int tiles_n = (N + FUSED_BLOCK_N - 1) / FUSED_BLOCK_N;
+  if (tiles_n > kMaxNTiles || w_offset + static_cast<long long>(N) * K > shard_elems * world) return -1;
+  const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(full) + w_offset;
+  CUtensorMap ta, tw;
+  bool ok = fsb_host::encode_2d_16bit(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M);
+  ok &= fsb_host::encode_2d_16bit(&tw, W, (uint64_t)K, (uint64_t)N, (uint64_t)K, BLOCK_K, FUSED_BLOCK_N);
+  if (!ok) return -1;
+  GemmParams p{};
+  p.C = C; p.bias = static_cast<const __nv_bfloat16*>(bias); p.aux = nullptr; p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ldc; p.a_mn_major = 0; p.b_mn_major = 0;
+  p.epilogue = epilogue; p.out_f32 = 0; p.accumulate_c = 0; p.status = status; p.batch = 1;
+  FusedParams f{};
+  f.c = fused_ctx(rank, world, epoch, channel, pads, counter, status);
+  for (int i = 0; i < world; ++i) f.peer.p[i] = shard_peers[i];
+  f.gather = static_cast<uint4*>(full);
+  f.counts = static_cast<uint32_t*>(counts);
+  f.target = target;
+  f.chunk16 = shard_elems * 2 / 16;
+  f.n_comm = n_comm; f.Mc = 0; f.local_first = 1;
+  // plan: which shards an N tile needs and in which order the tiles become runnable (shard r arrives (r - rank) mod
+  // world-th; a tile is runnable when its last shard is)
+  int ready_pos[kMaxNTiles];
+  for (int tn = 0; tn < tiles_n; ++tn) {
+    const long long first = w_offset + static_cast<long long>(tn) * FUSED_BLOCK_N * K;
+    const int rows = (tn + 1) * FUSED_BLOCK_N <= N ? FUSED_BLOCK_N : N - tn * FUSED_BLOCK_N;
+    const long long last = first + static_cast<long long>(rows) * K - 1;
+    const int lo = static_cast<int>(first / shard_elems), hi = static_cast<int>(last / shard_elems);
+    f.need_lo[tn] = static_cast<uint8_t>(lo);
+    f.need_hi[tn] = static_cast<uint8_t>(hi);
+    int pos = 0;
+    for (int c = lo; c <= hi; ++c) {
+      const int q = (c - rank + world) % world;
+      if (q > pos) pos = q;
+    }
+    ready_pos[tn] = pos;
+  }
+  int filled = 0;
+  for (int pos = 0; pos < world; ++pos)
+    for (int tn = 0; tn < tiles_n; ++tn)
+      if (ready_pos[tn] == pos) f.order[filled++] = static_cast<uint8_t>(tn);
+  int grid = 0;
+  const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * tiles_n;
+  if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev & 63]) {
+    cudaFuncSetAttribute(wag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM);
+    attr_set[dev & 63] = true;
+  }
+  wag_gemm_kernel<<<grid, GEMM_THREADS, FUSED_SMEM, stream>>>(ta, tw, p, f);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -584,10 +694,12 @@ FSB_API int fsb_gemm_rs_bf16(int rank, int world, unsigned epoch, int channel, v
   int grid = 0;
   const int tiles = (M / BLOCK_M) * ((N + FUSED_BLOCK_N - 1) / FUSED_BLOCK_N);
   if (fused_grid(n_comm, tiles, &grid) != 0) return -1;
-  static bool attr_set = false;
-  if (!attr_set) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_set[64] = {false};  // the attribute is per device
+  if (!attr_set[dev & 63]) {
     cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM);
-    attr_set = true;
+    attr_set[dev & 63] = true;
   }
   gemm_rs_kernel<<<grid, GEMM_THREADS, FUSED_SMEM, stream>>>(ta, tb, p, f);
   return static_cast<int>(cudaGetLastError());

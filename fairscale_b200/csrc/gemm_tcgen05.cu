@@ -227,6 +227,40 @@ struct PairSmem {
   static constexpr int TOTAL = BAR_OFFSET + 256;
 };
 
+__device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  if (p.b_ready != nullptr) {  // N-major: every M tile of the lowest outstanding weight rows first
+    tn = tile / tiles_m;
+    tm = tile - tn * tiles_m;
+  } else {
+    tile_coords(tile, tiles_m, tiles_n, tm, tn);
+  }
+}
+
+// Wait until bytes [lo, hi) of the B operand have arrived (see GemmParams::b_ready).  `upto` caches the highest piece
+// already seen.  Returns false when the wait limit ran out.
+__device__ __forceinline__ bool wait_b_pieces(const GemmParams& p, long long lo, long long hi, int& upto, volatile int* abort_flag) {
+  const int first = static_cast<int>(lo / p.b_piece_bytes), last = static_cast<int>((hi - 1) / p.b_piece_bytes);
+  bool waited = false;
+  for (int i = (first > upto + 1 ? first : upto + 1); i <= last; ++i) {
+    const uint64_t t0 = globaltimer_ns();
+    unsigned int v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.b_ready + i) : "memory");
+      if (static_cast<int>(v - p.b_ready_epoch) >= 0) break;
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > p.b_wait_ns) {
+        if (*abort_flag == 0) *abort_flag = 10;
+        return false;
+      }
+      __nanosleep(200);
+    }
+    waited = true;
+  }
+  if (last > upto) upto = last;
+  if (waited) asm volatile("fence.proxy.async;" ::: "memory");  // the arrived bytes before this thread's TMA reads of them
+  return true;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
   using L = PairSmem;
@@ -275,6 +309,12 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.b_ready != nullptr) {
+      // The first piece of B arrives only after every peer has entered the gather, which can be long after this kernel
+      // started (rank skew).  Wait for it here, under the long limit, before any of the pipeline's short waits counts.
+      int upto = -1;
+      wait_b_pieces(p, 0, 1, upto, abort_flag);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 2 * PAIR_BLOCK_N);
@@ -319,6 +359,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         return true;
       };
       int cur = -1, nxt = -1;
+      int b_upto = -1;  // highest B piece known to have arrived
       if (leader) {
         cur = static_cast<int>(atomicAdd(&p.sched[0], 1u));
         if (cur >= num_tiles) cur = -1;
@@ -341,9 +382,14 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         }
         if (tile < 0) break;
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        pair_tile_coords(p, tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
         const int n0 = tn * PAIR_BLOCK_N + static_cast<int>(rank) * PAIR_HALF_N;
+        if (p.b_ready != nullptr && n0 < p.N) {
+          const long long row_bytes = static_cast<long long>(p.K) * 2;
+          const int n1 = n0 + PAIR_HALF_N < p.N ? n0 + PAIR_HALF_N : p.N;
+          if (!wait_b_pieces(p, n0 * row_bytes, n1 * row_bytes, b_upto, abort_flag)) break;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 4)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -447,7 +493,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       if (++q == PAIR_SCHED_DEPTH) { q = 0; qphase ^= 1u; }
       if (tile < 0) break;
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      pair_tile_coords(p, tile, tiles_m, tiles_n, tm, tn);
       const int row0 = tm * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M + quad * 32;
       const int n0 = tn * PAIR_BLOCK_N + half * (PAIR_BLOCK_N / 2);
       uint4 pre[8];
@@ -507,9 +553,34 @@ static unsigned int* next_sched_slot(int di) {
 // lda / ldb: elements between consecutive rows of the *stored* matrix ([rows,K] when K-major,
 // [K,rows] when MN-major). All leading dimensions must be multiples of 8; pointers 16-byte aligned.
 // Returns 0 on success, a cudaError_t value, or -1 for an argument / tensor-map problem.
+static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
+                          int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
+                          int epilogue, int out_f32, int accumulate_c, int max_ctas, int* status, cudaStream_t stream,
+                          const unsigned int* b_ready, unsigned int b_ready_epoch, long long b_piece_bytes, unsigned long long b_wait_ns);
+
 FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
                           int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
                           int epilogue, int out_f32, int accumulate_c, int max_ctas, int* status, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, bias, aux, aux_out, M, N, K, lda, ldb, ldc, ld_aux, a_mn_major, b_mn_major, epilogue, out_f32,
+                        accumulate_c, max_ctas, status, stream, nullptr, 0u, 0, 0ull);
+}
+
+// C[M, N] = epilogue(A[M, K] * B^T + bias) with B ([N, K], rows contiguous: ldb == K) arriving while the kernel runs:
+// ready[i] >= ready_epoch means bytes [i * piece_bytes, (i + 1) * piece_bytes) of B are in place (see GemmParams::b_ready).
+// Needs the CTA-pair kernel (M, N >= 256); returns -1 otherwise.  wait_ms bounds every wait for a piece.
+FSB_API int fsb_gemm_bf16_streamed_b(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
+                                     int epilogue, const unsigned int* ready, unsigned int ready_epoch, long long piece_bytes,
+                                     long long wait_ms, int* status, cudaStream_t stream) {
+  if (M < 256 || N < 256 || ready == nullptr || piece_bytes <= 0) return -1;
+  if (epilogue != fsb::EPI_NONE && epilogue != fsb::EPI_BIAS) return -1;
+  return gemm_bf16_impl(A, B, C, bias, nullptr, nullptr, M, N, K, lda, K, ldc, ldc, 0, 0, epilogue, 0, 0, 0, status, stream, ready,
+                        ready_epoch, piece_bytes, static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 30000) * 1000000ull);
+}
+
+static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
+                          int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
+                          int epilogue, int out_f32, int accumulate_c, int max_ctas, int* status, cudaStream_t stream,
+                          const unsigned int* b_ready, unsigned int b_ready_epoch, long long b_piece_bytes, unsigned long long b_wait_ns) {
   using namespace fsb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -1;
@@ -536,6 +607,7 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   p.status = status;
   p.batch = 1; p.stride_c = p.stride_aux = p.stride_bias = 0;
   p.sched = nullptr;
+  p.b_ready = b_ready; p.b_ready_epoch = b_ready_epoch; p.b_piece_bytes = b_piece_bytes; p.b_wait_ns = b_wait_ns;
 
   int dev = 0;
   cudaGetDevice(&dev);
@@ -554,6 +626,7 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
     const char* e = getenv("FSB_GEMM_PAIR");
     pair_mode = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
+  if (b_ready != nullptr && !(pair_mode == 1 && M >= 256 && N >= 256 && max_ctas == 0)) return -1;
   if (pair_mode == 1 && M >= 256 && N >= 256 && max_ctas == 0) {
     // the B map's box is this CTA's 128 columns (K-major) / 64 (MN-major, unchanged)
     if (!b_mn_major && !fsb_host::encode_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, PAIR_HALF_N)) return -1;
@@ -619,13 +692,15 @@ FSB_API int fsb_gemm_bf16_batched(const void* A, const void* B, void* C, const v
   p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
   p.status = status;
   p.sched = nullptr;
+  p.b_ready = nullptr; p.b_ready_epoch = 0; p.b_piece_bytes = 0; p.b_wait_ns = 0;
   p.batch = batch; p.stride_c = stride_c; p.stride_aux = stride_aux > 0 ? stride_aux : stride_c; p.stride_bias = stride_bias;
   int dev = 0, num_sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = static_cast<long long>(batch) * ((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n);
   const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
-  static bool attr_set[2] = {false, false};
+  static bool attr_set_dev[64][2] = {{false}};  // the attribute is per device
+  bool* attr_set = attr_set_dev[dev & 63];
   if (block_n == 256) {
     if (!attr_set[0]) {
       cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);

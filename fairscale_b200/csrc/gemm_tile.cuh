@@ -39,6 +39,14 @@ struct GemmParams {
   // dynamic tile scheduler of the CTA-pair kernel: sched[0] = next tile to hand out, sched[1] = pairs that have finished
   // (both zero before the launch; the last pair to finish resets them)
   unsigned int* sched;
+  // Optional arrival flags of the B operand (CTA-pair kernel, B K-major with contiguous rows): the operand is being
+  // written by somebody else (copy engines gathering a sharded weight) while the kernel runs.  Bytes
+  // [i * b_piece_bytes, (i + 1) * b_piece_bytes) of B are valid once b_ready[i] >= b_ready_epoch (epochs only grow).
+  // Tiles are then visited N-major, rows ascending - the order in which the pieces are sent.
+  const unsigned int* b_ready;
+  unsigned int b_ready_epoch;
+  long long b_piece_bytes;
+  unsigned long long b_wait_ns;
 };
 
 // Parameters of problem `b` of a batch (pointers advanced; everything else shared).

@@ -70,6 +70,10 @@ class Embedding(nn.Module):
 
 
 class Block(nn.Module):
+    # The first use of this block's matrices is the QKV ``linear`` (the LayerNorm before it only reads small parameters),
+    # so an FSDP unit wrapping one block may fuse its parameter all-gather into that product (FSB200_FSDP_AG_GEMM=1).
+    fsb_fused_first_gemm = True
+
     def __init__(self, cfg: GPTConfig):
         super().__init__()
         d, f = cfg.d_model, cfg.ffn

@@ -78,6 +78,7 @@ def checkpoint_wrapper(module: nn.Module, offload_to_cpu: bool = False) -> nn.Mo
     :func:`disable_checkpointing`.
     """
     patch_batchnorm(module)
+    module._fsb_checkpointed = True  # type: ignore[assignment]  # wrappers may rely on the forward being replayed in backward
     # a weak reference avoids the module ↔ bound-partial cycle that would keep it alive forever
     module.forward = functools.partial(  # type: ignore[method-assign]
         _checkpointed_forward, type(module).forward, weakref.ref(module), offload_to_cpu

@@ -296,6 +296,13 @@ class FullyShardedDataParallel(nn.Module):
         self.persistent_compute_shards = persistent_compute_shards and mixed_precision and not self.move_params_to_cpu
         self.numel_padded_per_param: List[int] = []
         self._tstart = time.time()
+        # Opt-in fusion of this unit's parameter all-gather with its first product (FSB200_FSDP_AG_GEMM=1 and a wrapped
+        # module that declares ``fsb_fused_first_gemm = True``: its forward must reach a ``linear`` on one of the unit's
+        # matrices before any other use of them).  A unit whose forward is replayed in backward (activation
+        # checkpointing) can take the same route there.
+        opted = [m for m in module.modules() if getattr(m, "fsb_fused_first_gemm", False)]
+        self._fused_first_gemm = bool(opted) and os.environ.get("FSB200_FSDP_AG_GEMM", "0") == "1" and self.persistent_compute_shards
+        self._fused_first_gemm_replays = self._fused_first_gemm and all(getattr(m, "_fsb_checkpointed", False) for m in opted)
 
         if self.fp32_reduce_scatter and not self.mixed_precision:
             raise ValueError("fp32_reduce_scatter requires mixed_precision=True")
@@ -906,10 +913,15 @@ class FullyShardedDataParallel(nn.Module):
         if self.force_input_to_fp32 and not self.mixed_precision:
             args, kwargs = cast_floats_to_right_precision(False, False, *args, **kwargs)
 
-        self._rebuild_full_params()
+        self._allow_deferred_gather = True  # the module's first product may carry the all-gather (opt-in units only)
+        try:
+            self._rebuild_full_params()
+        finally:
+            self._allow_deferred_gather = False
         self._register_post_backward_hooks()
         self._prefetch_next_unit()
         outputs = self.module(*args, **kwargs)
+        self._finish_deferred_gathers()
 
         if self.reshard_after_forward:
             self._free_full_params()
@@ -947,6 +959,7 @@ class FullyShardedDataParallel(nn.Module):
                 and nxt._is_root is False
                 and hasattr(nxt.params[0] if nxt.params else None, "_fp32_shard")
                 and not nxt._touches_shared_params()
+                and not getattr(nxt, "_fused_first_gemm", False)  # its gather rides on its own first product
             ):
                 nxt._rebuild_full_params(wait=False)
                 nxt._use_fp32_param_shard()
@@ -980,6 +993,7 @@ class FullyShardedDataParallel(nn.Module):
             and hasattr(prev.params[0], "_fp32_shard")
             and any(p.requires_grad for p in prev.params)
             and not prev._touches_shared_params()
+            and not getattr(prev, "_fused_first_gemm_replays", False)
         ):
             prev._rebuild_full_params(wait=False)
             prev._use_fp32_param_shard()
@@ -1000,7 +1014,12 @@ class FullyShardedDataParallel(nn.Module):
             if self.reshard_after_forward or not self.has_full_params:
                 # also a unit that keeps its parameters after forward has lost them when an earlier backward of the same
                 # step (two forwards, then two backwards) already ran its post-backward and freed them
-                self._rebuild_full_params()
+                # (a checkpointed unit replays its forward first, so its first product can again carry the gather)
+                self._allow_deferred_gather = getattr(self, "_fused_first_gemm_replays", False)
+                try:
+                    self._rebuild_full_params()
+                finally:
+                    self._allow_deferred_gather = False
             else:
                 self._use_full_params()
             self._prefetch_prev_unit()
@@ -1340,8 +1359,11 @@ class FullyShardedDataParallel(nn.Module):
                     if _storage_is_free(p._full_param_padded):  # type: ignore[attr-defined]
                         alloc_storage_(p._full_param_padded, size=full_size)  # type: ignore[attr-defined]
                     landing = p._full_param_padded  # type: ignore[attr-defined]
-                with comm_range("all_gather"):
-                    comm.all_gather_into(landing, shard, group=self.process_group)
+                if self._defer_gather_to_first_gemm(p, shard, landing, low_precision):
+                    pass  # small parameters fetched; the matrices arrive inside the unit's first product
+                else:
+                    with comm_range("all_gather"):
+                        comm.all_gather_into(landing, shard, group=self.process_group)
                 point_at(p, landing)
                 if low_precision:
                     self._free_fp16_param_shard([p])
@@ -1351,6 +1373,44 @@ class FullyShardedDataParallel(nn.Module):
             with comm_range("exposed_wait_all_gather"):
                 _current_stream(self.compute_device).wait_stream(ag_stream)
         return out
+
+    def _finish_deferred_gathers(self) -> None:
+        pending = getattr(self, "_pending_gathers", None)
+        if pending:
+            from ...ops import gemm as gemm_ops
+
+            for pg in pending:
+                gemm_ops.complete_deferred_gather(pg)
+            pending.clear()
+
+    def _defer_gather_to_first_gemm(self, p: Parameter, shard: torch.Tensor, landing: torch.Tensor, low_precision: bool) -> bool:
+        """Fused path for units that opt in (a wrapped module with ``fsb_fused_first_gemm = True`` and
+        ``FSB200_FSDP_AG_GEMM=1``): fetch only the unit's small parameters now (copy engines, all-gather stream) and leave
+        the rest of the flat parameter to the kernel of the first ``linear`` that reads one of its matrices
+        (``ops.gemm.PendingGather``; on the compute stream, overlapping the transfer with that product's tiles)."""
+        if not (getattr(self, "_fused_first_gemm", False) and getattr(self, "_allow_deferred_gather", False)):
+            return False
+        if not low_precision or not p._is_sharded:  # type: ignore[attr-defined]
+            return False
+        ws = symm.workspace_for(self.process_group)
+        if ws is None or comm.comm_mode() != "fused" or shard.dtype != torch.bfloat16 or ws.offset_of(shard) is None:
+            return False
+        if landing.numel() != shard.numel() * self.world_size or not hasattr(p, "_param_numels"):
+            return False
+        from ...ops import gemm as gemm_ops
+
+        small, off = [], 0
+        for n in p._param_numels:  # type: ignore[attr-defined]
+            if n <= 65536:
+                small.append((off, off + n))
+            off += n
+        if small:
+            with comm_range("all_gather_small"):
+                ws.gather_ranges(landing, shard, small)
+        if not hasattr(self, "_pending_gathers"):
+            self._pending_gathers = []
+        self._pending_gathers.append(gemm_ops.defer_gather(gemm_ops.PendingGather(ws, shard, landing, self._streams["all_gather"])))
+        return True
 
     @torch.no_grad()
     def _use_full_params(self) -> None:

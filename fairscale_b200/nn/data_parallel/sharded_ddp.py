@@ -64,6 +64,7 @@ class _ReduceHook:
 
         if self.bucketed:
             bucket = sdp._buckets[param.device][self.dst_rank]
+            bucket.readopt_grad(param)  # a gradient dropped by zero_grad(set_to_none=True) comes back as a private tensor
             bucket.params_checked_in += 1
             if bucket.all_checked_in:
                 sdp._send_bucket(bucket)

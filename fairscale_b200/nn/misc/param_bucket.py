@@ -14,7 +14,7 @@ buffer somewhere special - the symmetric heap of an NVLink workspace, so that pe
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Iterable, List, Optional, Union
+from typing import Any, Callable, Dict, Iterable, List, Optional, Union
 
 import torch
 
@@ -39,6 +39,7 @@ class Bucket:
         self._align = max(int(align), 1)
         self._allocator = allocator
         self._slots: List[_Slot] = []
+        self._by_id: Dict[int, _Slot] = {}
         self._cursor = 0  # first free element
         self.buffer: torch.Tensor = self._allocate(size, dtype, torch.device(device))
 
@@ -59,7 +60,7 @@ class Bucket:
         return [s.tensor for s in self._slots]
 
     def _holds(self, tensor: torch.Tensor) -> bool:
-        return any(s.tensor is tensor for s in self._slots)
+        return id(tensor) in self._by_id
 
     def _reserve(self, tensor: torch.Tensor) -> _Slot:
         end = self._cursor + tensor.numel()
@@ -67,6 +68,7 @@ class Bucket:
         slot = _Slot(tensor, self._cursor, tensor.numel())
         self._cursor = _aligned(end, self._align)
         self._slots.append(slot)
+        self._by_id[id(tensor)] = slot
         return slot
 
     def _window(self, slot: _Slot) -> torch.Tensor:
@@ -172,6 +174,19 @@ class GradBucket(Bucket):
         if carry_value:
             window.copy_(param.grad)
         param.grad.data = window
+
+    @torch.no_grad()
+    def readopt_grad(self, param: torch.Tensor) -> None:
+        """If ``param.grad`` was replaced since it joined (an optimizer's ``zero_grad(set_to_none=True)`` drops it and
+        autograd then allocates a fresh one), move the new gradient into its window and point ``param.grad`` back."""
+        slot = self._by_id[id(param)]
+        grad = param.grad
+        if grad is None or self._is_collapsed:
+            return
+        if grad.data_ptr() != self.buffer.data_ptr() + slot.offset * self.buffer.element_size():
+            window = self._window(slot)
+            window.copy_(grad)
+            param.grad = window
 
     # -- buffer life cycle
     def to(  # type: ignore[no-untyped-def,override]

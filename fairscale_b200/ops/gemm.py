@@ -22,6 +22,55 @@ from . import _bind
 EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_DGELU, EPI_RESIDUAL = range(6)
 
 
+class PendingGather:
+    """A flat parameter whose all-gather has been deferred to the first product that reads one of its matrices
+    (registered by FullyShardedDataParallel for units that opt in).  ``full`` is the gathered buffer (the parameter
+    views point into it), ``shard`` this rank's heap-resident slice; small parameters are already in place."""
+
+    def __init__(self, workspace, shard: torch.Tensor, full: torch.Tensor, stream=None) -> None:  # type: ignore[no-untyped-def]
+        self.workspace, self.shard, self.full = workspace, shard, full
+        self.stream = stream  # the stream that owns the workspace's all-gather lane (None: a private one)
+        self.lo = full.data_ptr()
+        self.hi = self.lo + full.numel() * full.element_size()
+
+    def owns(self, t: torch.Tensor) -> bool:
+        return self.lo <= t.data_ptr() < self.hi
+
+    def finish_unfused(self) -> None:
+        """Complete the gather with the ordinary collective (the consumer cannot use the fused kernel)."""
+        if self.stream is None:
+            self.workspace.all_gather(self.full, self.shard)
+            return
+        cur = torch.cuda.current_stream(self.full.device)
+        self.stream.wait_stream(cur)
+        with torch.cuda.stream(self.stream):
+            self.workspace.all_gather(self.full, self.shard)
+        cur.wait_stream(self.stream)
+
+
+_PENDING_GATHERS: list = []
+
+
+def defer_gather(pending: PendingGather) -> PendingGather:
+    _PENDING_GATHERS.append(pending)
+    return pending
+
+
+def complete_deferred_gather(pending: PendingGather) -> None:
+    """Gather now if ``pending`` is still waiting (its unit finished without a product that could take the fused route)."""
+    for i, pg in enumerate(_PENDING_GATHERS):
+        if pg is pending:
+            _PENDING_GATHERS.pop(i).finish_unfused()
+            return
+
+
+def _take_pending(w: torch.Tensor) -> Optional[PendingGather]:
+    for i, pg in enumerate(_PENDING_GATHERS):
+        if pg.owns(w):
+            return _PENDING_GATHERS.pop(i)
+    return None
+
+
 def _as_2d(t: torch.Tensor) -> torch.Tensor:
     t2 = t.reshape(-1, t.shape[-1])
     return t2 if t2.is_contiguous() else t2.contiguous()
@@ -67,6 +116,18 @@ def linear_forward(
             y = y + _as_2d(residual).float()
         pre_out = pre.to(x.dtype) if (gelu and save_pre_activation) else None
         return y.to(out_dtype if x.dtype == torch.bfloat16 else x.dtype).view(*x.shape[:-1], N), pre_out
+    if _PENDING_GATHERS:
+        pending = _take_pending(w)
+        if pending is not None:
+            from ..parallel import fused_tp
+
+            w_offset = (w.data_ptr() - pending.lo) // 2
+            plain = not gelu and residual is None and out_dtype == torch.bfloat16 and w.is_contiguous()
+            if plain and fused_tp.weight_gather_gemm_supported(pending.workspace, pending.shard, pending.full, w_offset, N, K):
+                # the unit's parameter all-gather runs inside this product's kernel
+                y = fused_tp.weight_gather_gemm(pending.workspace, x2, pending.shard, pending.full, w_offset, N, K, bias)
+                return y.view(*x.shape[:-1], N), None
+            pending.finish_unfused()
     y = torch.empty((M, N), dtype=out_dtype, device=x.device)
     pre_out = None
     w = w if w.is_contiguous() else w.contiguous()

@@ -27,9 +27,9 @@ import torch.nn.functional as F
 from ..ops import _bind
 from ..ops import gemm as gemm_ops
 from ..ops.reduce import column_sum
-from . import comm, symm
+from . import comm, nvlink, symm
 
-_AG_CHANNEL, _RS_CHANNEL = 16, 18  # signal-pad channels (entry / flags, exit) outside the collective lanes
+_AG_CHANNEL, _RS_CHANNEL, _WAG_CHANNEL, _WAG_DMA_CHANNEL = 16, 18, 20, 22  # signal-pad channels (entry / flags, exit) outside the collective lanes
 _SIGS_DONE = False
 
 
@@ -44,6 +44,10 @@ def _sigs() -> None:
     S["fsb_ag_gemm_bf16"] = head + [c_void_p] * 7 + [c_int] * 7 + [c_void_p, c_uint, c_int, c_void_p, c_void_p]
     S["fsb_gemm_rs_bf16"] = head + [c_void_p] * 6 + [c_int] * 6 + [c_void_p, c_uint, c_uint, c_int, c_void_p, c_void_p]
     S["fsb_gemm_rs_arrivals"] = [c_int, c_int, c_int]
+    from ctypes import c_longlong
+
+    S["fsb_wag_gemm_bf16"] = head + [c_void_p, c_longlong, c_void_p, c_longlong] + [c_void_p] * 4 + [c_int] * 6 + [c_void_p, c_uint, c_int,
+                                                                                                                     c_void_p, c_void_p]
     _SIGS_DONE = True
 
 
@@ -75,6 +79,12 @@ class _State:
         self.rs_target_comm = 0
         self.ag_epoch = 0
         self.rs_epoch = 0
+        self.wag_counts = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.wag_target = 0
+        self.wag_epoch = 0
+        self.wag_flags = torch.zeros(256, dtype=torch.int32, device=dev)  # piece arrivals of the copy-engine variant
+        self.wag_flag_epoch = 0
+        self.wag_stream: Optional[torch.cuda.Stream] = None
         self.acc: Dict[int, torch.Tensor] = {}
 
 
@@ -134,6 +144,78 @@ def ag_gemm(ws: Any, x_shard: torch.Tensor, w: torch.Tensor, bias: Optional[torc
         _bind.status_ptr(dev), _bind.stream_ptr(dev),
     )
     return y, gathered
+
+
+def weight_gather_gemm_supported(ws: Any, shard: torch.Tensor, full: torch.Tensor, w_offset: int, N: int, K: int) -> bool:
+    """The fused all-gather + first GEMM of an FSDP unit needs: the shard in the symmetric heap, bf16, 16-byte friendly
+    sizes and offsets, the weight rows inside the gathered buffer and at most 64 N tiles."""
+    return (ws is not None and shard.dtype == torch.bfloat16 and full.dtype == torch.bfloat16 and ws.offset_of(shard) is not None
+            and shard.is_contiguous() and full.is_contiguous() and full.numel() == shard.numel() * ws.world
+            and (shard.numel() * 2) % 16 == 0 and shard.data_ptr() % 16 == 0 and full.data_ptr() % 16 == 0
+            and w_offset % 8 == 0 and K % 8 == 0 and w_offset + N * K <= full.numel() and (N + 255) // 256 <= 64)
+
+
+WAG_PIECE_BYTES = 4 << 20  # granularity of the arrival flags of the copy-engine variant
+
+
+def weight_gather_engine() -> str:
+    """``"dma"`` (default): copy engines move the shards while the CTA-pair GEMM waits on per-piece arrival flags;
+    ``"sm"``: copy CTAs inside the GEMM's own launch pull the shards.  ``FSB200_WAG_ENGINE`` selects."""
+    return os.environ.get("FSB200_WAG_ENGINE", "dma")
+
+
+def weight_gather_gemm(ws: Any, x: torch.Tensor, shard: torch.Tensor, full: torch.Tensor, w_offset: int, N: int, K: int,
+                       bias: Optional[torch.Tensor] = None, *, gelu: bool = False, n_comm: Optional[int] = None,
+                       engine: Optional[str] = None) -> torch.Tensor:
+    """``y[M, N] = x[M, K] @ W^T (+ bias)`` where ``W = full[w_offset : w_offset + N * K].view(N, K)`` and ``full`` - the
+    gathered flat parameter of an FSDP unit - is filled from every rank's ``shard`` (heap resident) while the product
+    runs.  On return (in stream order) ``full`` is complete.  ``bias`` must already hold valid data.
+
+    Engine ``"dma"``: behind a flag barrier on the current stream, the copy engines of a side stream move the shards,
+    weight rows first, and the driver stores a flag per 4 MB piece; the GEMM on the current stream visits its tiles in
+    row order of W and waits for the pieces under each tile; a second barrier follows the GEMM.  Engine ``"sm"``: one
+    launch whose copy CTAs pull the shards and whose GEMM CTAs wait on their chunk counters."""
+    st = _state(ws)
+    x = x.contiguous()
+    M = x.shape[0]
+    dev = x.device
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    engine = engine or weight_gather_engine()
+    if (engine == "dma" and not gelu and M >= 256 and N >= 256 and -(-N * K * 2 // WAG_PIECE_BYTES) <= st.wag_flags.numel()
+            and nvlink.stream_memops_available()):
+        # Only copies from peers (copy engines) and driver-side flag stores run beside the GEMM.  Both barriers and the
+        # copy of this rank's own rows of W are enqueued on the GEMM's stream, before / after it: nothing the GEMM waits
+        # for depends on finding room on an SM next to it.
+        cur = torch.cuda.current_stream(dev)
+        if st.wag_stream is None:
+            st.wag_stream = torch.cuda.Stream(device=dev)
+        side = st.wag_stream
+        st.wag_flag_epoch = (st.wag_flag_epoch + 1) & 0x3FFFFFFF
+        ws.barrier_on(_WAG_DMA_CHANNEL, 2 * st.wag_flag_epoch)  # every peer's shard is final
+        rng = (w_offset, w_offset + N * K)
+        ws.gather_flagged_copies(full, shard, rng, WAG_PIECE_BYTES, st.wag_flags, st.wag_flag_epoch, phase=0)  # own rows of W
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            ws.gather_flagged_copies(full, shard, rng, WAG_PIECE_BYTES, st.wag_flags, st.wag_flag_epoch, phase=1)
+        _bind.call("fsb_gemm_bf16_streamed_b", x.data_ptr(), full.data_ptr() + 2 * w_offset, y.data_ptr(), _bind.ptr(bias), M, N, K,
+                   x.stride(0), N, 0 if bias is None else 1, st.wag_flags.data_ptr(), st.wag_flag_epoch, WAG_PIECE_BYTES,
+                   nvlink.timeout_ms(), _bind.status_ptr(dev), _bind.stream_ptr(dev))
+        cur.wait_stream(side)  # the rest of the flat parameter
+        ws.barrier_on(_WAG_DMA_CHANNEL, 2 * st.wag_flag_epoch + 1)  # every peer is done reading this rank's shard
+        for t in (full, shard, st.wag_flags):
+            t.record_stream(side)
+        return y
+    remote = (ws.world - 1) * shard.numel() * 2.0
+    n_comm = n_comm if n_comm is not None else comm_ctas(remote, 2.0 * M * N * K, ws.world)
+    st.wag_epoch = (st.wag_epoch + 1) & 0x7FFFFFFF
+    st.wag_target = (st.wag_target + n_comm) & 0xFFFFFFFF
+    epi = 0 if bias is None else (2 if gelu else 1)
+    _bind.call(
+        "fsb_wag_gemm_bf16", ws.rank, ws.world, st.wag_epoch, _WAG_CHANNEL, ws.pad_ptrs, ws.counters.data_ptr() + 4 * 20,
+        ws.peers(ws.offset_of(shard)), shard.numel(), full.data_ptr(), w_offset, x.data_ptr(), y.data_ptr(), _bind.ptr(bias), None,
+        M, N, K, x.stride(0), N, epi, st.wag_counts.data_ptr(), st.wag_target, n_comm, _bind.status_ptr(dev), _bind.stream_ptr(dev),
+    )
+    return y
 
 
 def gemm_rs(ws: Any, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], *, w_is_kn: bool = False) -> torch.Tensor:

@@ -38,8 +38,11 @@ def _sigs() -> None:
     S["fsb_comm_set_timeout_ms"] = [c_longlong]
     S["fsb_comm_barrier"] = head + [c_void_p, c_void_p]
     S["fsb_comm_all_gather"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
+    S["fsb_comm_gather_ranges_dma"] = head + [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     S["fsb_comm_all_gather_cols"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_all_gather_dma"] = head + [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
+    S["fsb_comm_gather_flagged_copies"] = [c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_uint,
+                                           c_void_p]
     S["fsb_comm_all_to_all"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_reduce_scatter"] = head + [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
     S["fsb_comm_reduce_scatter_adam"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -267,6 +270,41 @@ class NvlinkWorkspace:
         _bind.call("fsb_comm_all_gather", *self._head(ln), self._counter(ln), self.peers(off), out.data_ptr(),
                    nbytes, _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
 
+    def barrier_on(self, channel: int, epoch: int) -> None:
+        """Flag barrier on an explicit signal-pad channel (callers outside the collective lanes keep their own epochs)."""
+        _bind.call("fsb_comm_barrier", self.rank, self.world, epoch, channel, self.pad_ptrs, _bind.status_ptr(self.device),
+                   _bind.stream_ptr(self.device))
+
+    def gather_flagged_copies(self, out: torch.Tensor, shard: torch.Tensor, first: Tuple[int, int], piece_bytes: int,
+                              flags: torch.Tensor, flag_value: int, phase: int) -> None:
+        """The copies of an all-gather of heap-resident ``shard`` into ``out``, reporting progress: elements
+        ``first = [lo, hi)`` of ``out`` go first, in pieces of ``piece_bytes``, and ``flags[i] = flag_value`` is stored by
+        the driver (in stream order) once piece ``i`` is in place; the rest follows.  ``phase=0`` (on the consumer's
+        stream, before the consumer) copies this rank's own part of ``first``; ``phase=1`` (on a side stream that waits
+        for phase 0) moves the peers' parts on the copy engines and stores the flags, then the remainder.  No kernel is
+        launched, and nothing a persistent consumer waits for needs an SM.  The caller provides the barriers around the
+        two calls (:func:`fairscale_b200.parallel.fused_tp.weight_gather_gemm`)."""
+        off = self.offset_of(shard)
+        assert off is not None, "the shard must live in the symmetric heap"
+        es = shard.element_size()
+        n_pieces = -(-(first[1] - first[0]) * es // piece_bytes)
+        assert flags.dtype == torch.int32 and flags.numel() >= n_pieces
+        _bind.call("fsb_comm_gather_flagged_copies", self.rank, self.world, phase, self.peers(off), out.data_ptr(), shard.numel() * es, first[0] * es,
+                   first[1] * es, piece_bytes, flags.data_ptr(), flag_value, _bind.stream_ptr(self.device), launches=0)
+
+    def gather_ranges(self, out: torch.Tensor, shard: torch.Tensor, ranges: List[Tuple[int, int]], lane: int = 1) -> None:
+        """Fetch only the element ranges ``[lo, hi)`` of the gathered flat buffer ``out`` (the shards' concatenation) from
+        the shards that hold them, on the copy engines.  Used for the small parameters a unit needs before the kernel
+        that gathers the rest; that kernel's exit barrier also covers these reads."""
+        ln = self._lane(lane)
+        off = self.offset_of(shard)
+        assert off is not None, "the shard must live in the symmetric heap"
+        es = shard.element_size()
+        lo = (ctypes.c_longlong * len(ranges))(*[a * es for a, _ in ranges])
+        hi = (ctypes.c_longlong * len(ranges))(*[b * es for _, b in ranges])
+        _bind.call("fsb_comm_gather_ranges_dma", *self._head(ln), self.peers(off), out.data_ptr(), shard.numel() * es, len(ranges),
+                   lo, hi, _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
+
     def can_all_gather_cols(self, out: torch.Tensor, part: torch.Tensor) -> bool:
         row_bytes = part.shape[-1] * part.element_size()
         return (part.dim() >= 1 and part.is_contiguous() and out.is_contiguous() and row_bytes % 16 == 0 and self._aligned(out)
@@ -389,6 +427,18 @@ def set_timeout(seconds: float) -> None:
     the host raises :class:`fairscale_b200.utils.failure.CommTimeoutError` at its next status check."""
     _sigs()
     _bind.call("fsb_comm_set_timeout_ms", int(max(1, round(seconds * 1000))))
+
+
+def stream_memops_available() -> bool:
+    """True when the driver exports stream-ordered memory writes (needed by the copy-engine weight-gather GEMM)."""
+    return bool(_bind.fn("fsb_comm_stream_memops_available")())
+
+
+def timeout_ms() -> int:
+    """The current limit of one device-side wait for a peer, in milliseconds."""
+    fn = _bind.fn("fsb_comm_get_timeout_ms")
+    fn.restype = ctypes.c_longlong
+    return int(fn())
 
 
 def available() -> bool:

@@ -270,3 +270,30 @@ def _oss_optimizer_protocol(rank, world):
 
 def test_oss_closure_kwargs_scheduler_and_subgroup():
     spawn_ranks(_oss_optimizer_protocol, 3, (), backend="gloo")
+
+
+def _bucketed_with_optimizer_zero_grad(rank, world):
+    # the optimizer's zero_grad drops the gradients (set_to_none): autograd then produces private tensors, which the
+    # wrapper moves back into the reduce bucket before the bucket is sent
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    ref = DDP(_model())
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    base = _model()
+    oss = OSS(base.parameters(), optim=torch.optim.SGD, lr=0.1, momentum=0.9)
+    sdp = ShardedDataParallel(base, oss, reduce_buffer_size=2**20)
+    for step in range(4):
+        x, y = _batch(rank, step)
+        ref_opt.zero_grad()
+        nn.functional.mse_loss(ref(x), y).backward()
+        ref_opt.step()
+        oss.zero_grad()
+        nn.functional.mse_loss(sdp(x), y).backward()
+        oss.step()
+    assert any(sdp._should_bucket_grad)
+    for a, b in zip(ref.module.parameters(), base.parameters()):
+        torch.testing.assert_close(b, a, atol=1e-6, rtol=1e-5)
+
+
+def test_sdp_buckets_survive_optimizer_zero_grad():
+    spawn_ranks(_bucketed_with_optimizer_zero_grad, 2, (), backend="gloo")

@@ -93,8 +93,8 @@ def _fsdp_offload_worker(rank, world):
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     ref = _mlp(4).to(dev)
-    fsdp = FSDP(copy.deepcopy(ref), mixed_precision=True, compute_dtype=torch.bfloat16, move_params_to_cpu=True, compute_device=dev)
-    assert all(p.device.type == "cpu" for p in fsdp.parameters())
+    # host-resident shards start from a module on the host (the wrapper asserts it, like the reference)
+    fsdp = FSDP(copy.deepcopy(ref).cpu(), mixed_precision=True, compute_dtype=torch.bfloat16, move_params_to_cpu=True, compute_device=dev)
     opt = torch.optim.SGD(fsdp.parameters(), lr=0.05)
     opt_ref = torch.optim.SGD(ref.parameters(), lr=0.05)
     torch.manual_seed(7)  # the same data on both ranks: the averaged gradient equals the local one
@@ -106,6 +106,7 @@ def _fsdp_offload_worker(rank, world):
         opt.zero_grad()
         fsdp(x).float().pow(2).mean().backward()
         opt.step()
+    assert all(p.device.type == "cpu" for p in fsdp.parameters()), "between steps the shards rest on the host"
     sd = fsdp.state_dict()
     for (k, a), b in zip(ref.state_dict().items(), sd.values()):
         torch.testing.assert_close(b.float().cpu(), a.float().cpu(), atol=3e-2, rtol=3e-2)
