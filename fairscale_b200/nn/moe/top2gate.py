@@ -136,6 +136,49 @@ def top2gating(logits: torch.Tensor) -> Tuple[Tensor, Tensor, Tensor]:
     return route.l_aux, combine, mask
 
 
+class _GateProjection(torch.autograd.Function):
+    """``logits[T, E] = x[T, d] @ wg[E, d]^T`` in fp32 for bf16 activations on the GPU: the product runs on the tcgen05 GEMM
+    (bf16 operands, fp32 accumulation and fp32 output) with the expert dimension zero-padded to one 128-row tile."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, w: Tensor) -> Tensor:  # type: ignore[override]
+        from ...ops import gemm as gemm_ops
+
+        E, d = w.shape
+        x2 = x.reshape(-1, d)
+        w_pad = torch.zeros((-(-E // 128) * 128, d), dtype=torch.bfloat16, device=x.device)
+        w_pad[:E].copy_(w)
+        logits, _ = gemm_ops.linear_forward(x2, w_pad, None, out_dtype=torch.float32)
+        ctx.save_for_backward(x2, w_pad)
+        ctx.meta = (E, x.shape, w.dtype)
+        return logits[:, :E].reshape(*x.shape[:-1], E)
+
+    @staticmethod
+    def backward(ctx, d_logits: Tensor):  # type: ignore[override]
+        from ...ops import gemm as gemm_ops
+
+        x2, w_pad = ctx.saved_tensors
+        E, x_shape, w_dtype = ctx.meta
+        dl = torch.zeros((x2.shape[0], w_pad.shape[0]), dtype=torch.bfloat16, device=x2.device)
+        dl[:, :E].copy_(d_logits.reshape(-1, E))
+        dx = gemm_ops.linear_dgrad(dl, w_pad).view(x_shape) if ctx.needs_input_grad[0] else None
+        dw = gemm_ops.linear_wgrad(dl, x2)[:E].to(w_dtype) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def gate_logits(x: Tensor, wg: torch.nn.Linear) -> Tensor:
+    """Router logits in fp32 (the softmax over experts is taken in fp32 whatever the activations' dtype)."""
+    w = wg.weight
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.shape[1] % 8 == 0:
+        from ...ops import _bind
+
+        if _bind.use_native(x):
+            return _GateProjection.apply(x, w)
+    if x.dtype != w.dtype:
+        return torch.nn.functional.linear(x.float(), w.float())
+    return wg(x)
+
+
 class Top2Gate(torch.nn.Module):
     """Gate network ``wg: model_dim -> num_experts`` followed by top-2 routing.
 
@@ -150,7 +193,7 @@ class Top2Gate(torch.nn.Module):
         self.wg = torch.nn.Linear(model_dim, num_experts, bias=False)
 
     def route(self, input: torch.Tensor) -> Top2Route:
-        return top2_route(self.wg(input))
+        return top2_route(gate_logits(input, self.wg))
 
     def forward(self, input: torch.Tensor) -> Tuple[Tensor, Tensor, Tensor]:  # type: ignore[override]
-        return top2gating(self.wg(input))
+        return top2gating(gate_logits(input, self.wg))

@@ -215,3 +215,19 @@ def _identity_experts(rank, world):
 
 def test_moe_identity_experts_reassemble_the_input():
     spawn_ranks(_identity_experts, 2, (), backend="gloo")
+
+
+def test_gate_takes_low_precision_activations_and_routes_in_fp32():
+    """A bf16 activation against the fp32 gate weight: logits (and so the softmax over experts) come out in fp32."""
+    from fairscale_b200.nn.moe.top2gate import Top2Gate, gate_logits
+
+    torch.manual_seed(0)
+    gate = Top2Gate(16, 4)
+    x = torch.randn(12, 16).bfloat16().requires_grad_()
+    logits = gate_logits(x, gate.wg)
+    assert logits.dtype == torch.float32
+    torch.testing.assert_close(logits, torch.nn.functional.linear(x.float(), gate.wg.weight))
+    l_aux, combine, mask = gate(x)
+    assert combine.dtype == torch.float32 and mask.dtype == torch.bool
+    (l_aux + combine.sum()).backward()
+    assert x.grad is not None and gate.wg.weight.grad is not None

@@ -167,11 +167,37 @@ def test_moe_layer_on_one_gpu_index_path_matches_dense_einsum():
     _status_ok()
 
 
+@pytest.mark.parametrize("experts", [4, 64, 136])
+def test_gate_projection_on_tensor_cores_matches_fp32(experts):
+    """Router logits of bf16 activations: tcgen05 GEMM with fp32 output (expert dimension padded to a tile) and its
+    backward against a plain fp32 linear."""
+    from fairscale_b200.nn.moe.top2gate import Top2Gate, gate_logits
+
+    torch.manual_seed(3)
+    gate = Top2Gate(256, experts).to(_dev())
+    x = torch.randn(4, 200, 256, device=_dev()).bfloat16().requires_grad_()
+    logits = gate_logits(x, gate.wg)
+    assert logits.dtype == torch.float32 and logits.shape == (4, 200, experts)
+    xr = x.detach().float().requires_grad_()
+    wr = gate.wg.weight.detach().bfloat16().float().requires_grad_()
+    ref = torch.nn.functional.linear(xr, wr)
+    torch.testing.assert_close(logits, ref, atol=2e-3, rtol=2e-3)
+    g = torch.randn_like(ref)
+    logits.backward(g)
+    ref.backward(g.bfloat16().float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(gate.wg.weight.grad, wr.grad, atol=6e-2, rtol=3e-2)
+    _status_ok()
+
+
 def _fsdp_pair(**kw):
     from fairscale_b200.nn.data_parallel import FullyShardedDataParallel as FSDP
 
     ref = _mlp(9).to(_dev())
-    wrapped = FSDP(copy.deepcopy(ref), **kw)
+    inner = copy.deepcopy(ref)
+    if kw.get("move_params_to_cpu"):
+        inner = inner.cpu()  # host-resident shards start from a module on the host (the wrapper asserts it, like the reference)
+    wrapped = FSDP(inner, **kw)
     return ref, wrapped
 
 
