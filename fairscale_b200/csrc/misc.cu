@@ -105,6 +105,14 @@ __global__ void delay_kernel(unsigned long long ns) {
   while (globaltimer_ns() - t0 < ns) __nanosleep(500);
 }
 
+// The same with a dynamic shared-memory footprint, so that each of its CTAs keeps a whole SM from anybody else.
+__global__ void delay_wide_kernel(unsigned long long ns) {
+  extern __shared__ unsigned char delay_smem[];
+  if (threadIdx.x == 0) delay_smem[0] = 0;
+  const uint64_t t0 = globaltimer_ns();
+  while (globaltimer_ns() - t0 < ns) __nanosleep(500);
+}
+
 }  // namespace fsb
 
 // qkv_in / qkv_out: packed [B, S, 3, H, D] bf16 (may be the same pointer); D a multiple of 8.  backward != 0 applies
@@ -141,5 +149,17 @@ FSB_API int fsb_dropout(const void* x, void* y, long long n, float p, unsigned l
 FSB_API int fsb_delay(unsigned long long ns, cudaStream_t stream) {
   if (ns > 1000000000ull) ns = 1000000000ull;
   fsb::delay_kernel<<<1, 1, 0, stream>>>(ns);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Takes `ctas` whole SMs (200 KB of shared memory per CTA) for `ns` nanoseconds (at most one second): a stand-in for a
+// foreign kernel that leaves a persistent kernel of another stream fewer SMs than its grid has CTAs.
+FSB_API int fsb_delay_wide(unsigned long long ns, int ctas, cudaStream_t stream) {
+  if (ns > 1000000000ull) ns = 1000000000ull;
+  if (ctas < 1 || ctas > 1024) return -1;
+  constexpr int kSmem = 200 * 1024;
+  cudaError_t e = cudaFuncSetAttribute(fsb::delay_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  fsb::delay_wide_kernel<<<ctas, 32, kSmem, stream>>>(ns);
   return static_cast<int>(cudaGetLastError());
 }

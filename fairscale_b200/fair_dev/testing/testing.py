@@ -469,6 +469,19 @@ def gpu_delay(ms: float, stream: Optional[Any] = None) -> None:
     _bind.call("fsb_delay", int(ms * 1e6), s.cuda_stream)
 
 
+def gpu_occupy_sms(ms: float, sms: int, stream: Optional[Any] = None) -> None:
+    """Take ``sms`` whole SMs of the current device for ``ms`` milliseconds on ``stream`` (each CTA of the kernel claims
+    200 KB of shared memory): a stand-in for a foreign kernel that leaves a persistent kernel of another stream fewer SMs
+    than its grid has CTAs.  Capped at one second like :func:`gpu_delay`."""
+    from ctypes import c_int, c_ulonglong, c_void_p
+
+    from ...ops import _bind
+
+    _bind._SIGNATURES.setdefault("fsb_delay_wide", [c_ulonglong, c_int, c_void_p])
+    s = torch.cuda.current_stream() if stream is None else stream
+    _bind.call("fsb_delay_wide", int(ms * 1e6), int(sms), s.cuda_stream)
+
+
 class DummyProcessGroup:
     """Stands in for a process group in single-process unit tests (no collectives are issued)."""
 

@@ -24,7 +24,8 @@ def _rel_err(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 128), (384, 256, 320), (200, 136, 72), (1024, 2048, 512), (4096, 50304 // 8, 256)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 128), (384, 256, 320), (200, 136, 72), (1024, 2048, 512), (4096, 50304 // 8, 256),
+                                   (512, 384, 8192), (1000, 264, 8192)])
 def test_gemm_forward_shapes(M, N, K):
     from fairscale_b200.ops.gemm import linear_forward
 
@@ -62,7 +63,8 @@ def test_gemm_epilogues():
     _status_ok()
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 192), (200, 136, 72), (2048, 1024, 512)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 192), (200, 136, 72), (2048, 1024, 512), (8192, 256, 384), (1000, 264, 136),
+                                   (8200, 520, 264)])
 def test_gemm_dgrad_wgrad(M, N, K):
     from fairscale_b200.ops.gemm import linear_dgrad, linear_wgrad
 

