@@ -132,13 +132,16 @@ template <> struct Acc8<float> {
 // TI: gradient dtype in the peers' buffers; TO: output dtype (fp32 master-precision shard or TI).
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
-reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n, float scale, int accumulate) {
+reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n, float scale, int accumulate, long long base,
+                      int active) {
+  // `base`: first element of the slice this rank sums (rank * n for a reduce-scatter, 0 for a reduction of the whole
+  // buffer to one owner); `active` == 0: this rank only takes part in the two barriers (it is not the owner).
   if (blockIdx.x == 0) signal_peers(c, c.channel);
   if (!wait_peers(c, c.channel)) return;
   constexpr int E = Acc8<TI>::N;
-  const long long nvec = n / E;
+  const long long nvec = active ? n / E : 0;
+  if (!active) n = 0;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  const long long base = static_cast<long long>(c.rank) * n;
   long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   // two ranks: two vectors per thread and pass, so that a thread still has four peer loads in flight
   if (c.world <= 2) {
@@ -192,7 +195,7 @@ reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n
   // ragged tail (n not a multiple of the vector width)
   for (long long i = nvec * E + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
     float a = 0.f;
-    for (int q = 0; q < c.world; ++q) a += to_f32<TI>(reinterpret_cast<const TI*>(src.p[q])[static_cast<long long>(c.rank) * n + i]);
+    for (int q = 0; q < c.world; ++q) a += to_f32<TI>(reinterpret_cast<const TI*>(src.p[q])[base + i]);
     float r = a * scale;
     if (accumulate) r += to_f32<TO>(out[i]);
     out[i] = from_f32<TO>(r);
@@ -439,13 +442,16 @@ static fsb::PtrTable make_table(void* const* ptrs, int world) {
 }
 // FSB_COMM_MAX_CTAS overrides the CTA cap of the streaming collectives (default: one 128-thread CTA per SM, so that two
 // collectives running on different streams still leave room for a persistent GEMM CTA on every SM).
+// Collectives that sit on the critical path of their layer (MoE dispatch / combine, all-to-all, the column gather of a
+// tensor-parallel output) have nothing to share the SMs with: eight CTAs per SM instead of one.
+constexpr int kWideGrid = 148 * 8;
 static int comm_grid(long long work_items, int max_blocks) {
   static int cap = -1;
   if (cap < 0) {
     const char* e = getenv("FSB_COMM_MAX_CTAS");
     cap = (e != nullptr && atoi(e) > 0) ? atoi(e) : 0;
   }
-  if (cap > 0) max_blocks = cap;
+  if (cap > 0 && max_blocks != kWideGrid) max_blocks = cap;
   long long b = (work_items + fsb::COMM_THREADS - 1) / fsb::COMM_THREADS;
   if (b < 1) b = 1;
   if (b > max_blocks) b = max_blocks;
@@ -501,7 +507,7 @@ FSB_API int fsb_comm_all_gather_cols(int rank, int world, unsigned epoch, int ch
                                      void* const* src, void* out, long long rows, long long row_bytes, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks || row_bytes % 16 || row_bytes / 16 > 0x7fffffff) return -1;
   const int cols16 = static_cast<int>(row_bytes / 16);
-  fsb::all_gather_cols_kernel<<<comm_grid(rows * cols16, 148), fsb::COMM_THREADS, 0, stream>>>(
+  fsb::all_gather_cols_kernel<<<comm_grid(rows * cols16, kWideGrid), fsb::COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), rows, cols16);
   return static_cast<int>(cudaGetLastError());
 }
@@ -600,24 +606,22 @@ FSB_API int fsb_comm_all_to_all(int rank, int world, unsigned epoch, int channel
                                 void* out, long long chunk_bytes, int* status, cudaStream_t stream) {
   if (world > fsb::kMaxRanks || chunk_bytes % 16) return -1;
   const long long n16 = chunk_bytes / 16;
-  fsb::all_to_all_kernel<<<comm_grid(n16, 148), fsb::COMM_THREADS, 0, stream>>>(
+  fsb::all_to_all_kernel<<<comm_grid(n16, kWideGrid), fsb::COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<uint4*>(out), n16);
   return static_cast<int>(cudaGetLastError());
 }
 
 // out[n] (out_dtype) = (accumulate ? out : 0) + scale * sum_p src[p][rank * n + i]   (src in in_dtype)
-FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
-                                    void* const* src, int in_dtype, void* out, int out_dtype, long long n, float scale, int accumulate,
-                                    int* status, cudaStream_t stream) {
+static int launch_reduce(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* src,
+                         int in_dtype, void* out, int out_dtype, long long n, float scale, int accumulate, long long base, int active,
+                         int* status, cudaStream_t stream) {
   using namespace fsb;
-  if (world > kMaxRanks) return -1;
-  if ((n * (in_dtype == FSB_F32 ? 4 : 2)) % 16) return -1;  // each rank's chunk must start 16-byte aligned
   const CommCtx c = make_ctx(rank, world, epoch, channel, pads, counter, status);
   const PtrTable t = make_table(src, world);
-  const int grid = comm_grid(n / 8, 148);
+  const int grid = active ? comm_grid(n / 8, 148) : 1;
 #define FSB_RS(IC, IT, OC, OT)                                                                                          \
   if (in_dtype == IC && out_dtype == OC) {                                                                              \
-    reduce_scatter_kernel<IT, OT><<<grid, COMM_THREADS, 0, stream>>>(c, t, static_cast<OT*>(out), n, scale, accumulate); \
+    reduce_scatter_kernel<IT, OT><<<grid, COMM_THREADS, 0, stream>>>(c, t, static_cast<OT*>(out), n, scale, accumulate, base, active); \
     return static_cast<int>(cudaGetLastError());                                                                        \
   }
   FSB_RS(FSB_BF16, __nv_bfloat16, FSB_F32, float)
@@ -627,6 +631,40 @@ FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int cha
   FSB_RS(FSB_F32, float, FSB_F32, float)
 #undef FSB_RS
   return -1;
+}
+
+FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
+                                    void* const* src, int in_dtype, void* out, int out_dtype, long long n, float scale, int accumulate,
+                                    int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks) return -1;
+  if ((n * (in_dtype == FSB_F32 ? 4 : 2)) % 16) return -1;  // each rank's chunk must start 16-byte aligned
+  return launch_reduce(rank, world, epoch, channel, pads, counter, src, in_dtype, out, out_dtype, n, scale, accumulate,
+                       static_cast<long long>(rank) * n, 1, status, stream);
+}
+
+// Sum of every rank's symmetric buffer bufs[p] (n elements of `dtype`) into rank `owner`'s buffer, in place and scaled; the
+// other ranks' buffers are left as they are.  The owner pulls; the others only take part in the two barriers (peers'
+// buffers final before, owner done reading after).  ZeRO-2's reduction of a gradient bucket to the rank that owns it.
+FSB_API int fsb_comm_reduce_to(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* bufs,
+                               int dtype, long long n, float scale, int owner, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || owner < 0 || owner >= world) return -1;
+  return launch_reduce(rank, world, epoch, channel, pads, counter, bufs, dtype, bufs[rank], dtype, n, scale, 0, 0, rank == owner ? 1 : 0,
+                       status, stream);
+}
+
+// Every rank but `owner` copies the owner's symmetric buffer into `out` (nbytes) on the copy engines, between two flag
+// barriers (owner's buffer final before, everybody done reading after).  ZeRO-1's publication of the updated parameters
+// of one owner.  Uses epochs `epoch` and `epoch + 1` on `channel`.
+FSB_API int fsb_comm_broadcast_dma(int rank, int world, unsigned epoch, int channel, void* const* pads, void* const* src, void* out,
+                                   long long nbytes, int owner, int* status, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || owner < 0 || owner >= world) return -1;
+  fsb::barrier_kernel<<<1, fsb::COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch, channel, pads, nullptr, status));
+  if (rank != owner && out != src[owner]) {
+    cudaError_t e = cudaMemcpyAsync(out, src[owner], static_cast<size_t>(nbytes), cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  fsb::barrier_kernel<<<1, fsb::COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch + 1u, channel, pads, nullptr, status));
+  return static_cast<int>(cudaGetLastError());
 }
 
 // Fused reduce-scatter + Adam on this rank's shard.  src: every rank's flat gradient (in_dtype, world * n elements, in the
@@ -686,7 +724,7 @@ FSB_API int fsb_comm_moe_scatter_rows(int rank, int world, unsigned epoch, int c
                                       long long T, int rows_per_token, int M, int* status, cudaStream_t stream) {
   using namespace fsb;
   if (world > kMaxRanks || M % 8) return -1;
-  moe_scatter_rows_kernel<<<comm_grid(T * 32, 148), COMM_THREADS, 0, stream>>>(
+  moe_scatter_rows_kernel<<<comm_grid(T * 32, kWideGrid), COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(dst, world), static_cast<const __nv_bfloat16*>(x),
       dst_rank, dst_row, w, T, rows_per_token, M);
   return static_cast<int>(cudaGetLastError());
@@ -698,7 +736,7 @@ FSB_API int fsb_comm_moe_gather_rows(int rank, int world, unsigned epoch, int ch
                                      cudaStream_t stream) {
   using namespace fsb;
   if (world > kMaxRanks || M % 8 || rows_per_token > 4) return -1;
-  moe_gather_rows_kernel<<<comm_grid(tokens * 32, 148), COMM_THREADS, 0, stream>>>(
+  moe_gather_rows_kernel<<<comm_grid(tokens * 32, kWideGrid), COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(src, world), static_cast<__nv_bfloat16*>(out), src_rank,
       src_row, w, static_cast<const __nv_bfloat16*>(g), dot, tokens, rows_per_token, M);
   return static_cast<int>(cudaGetLastError());

@@ -29,7 +29,7 @@ from torch import nn
 from torch.autograd import Variable, profiler
 
 from ...internal.params import Workhandle, get_global_rank
-from ...parallel import comm
+from ...parallel import comm, symm
 from ..misc.param_bucket import GradBucket
 
 
@@ -88,6 +88,7 @@ class _ReduceHook:
 
 
 class ShardedDataParallel(nn.Module):
+    _instances = 0  # construction order is the same on every rank: names the heap windows of this wrapper's buckets
     """Wrap ``module`` so its gradients are reduced to the owning rank of ``sharded_optimizer``.
 
     Args:
@@ -116,6 +117,8 @@ class ShardedDataParallel(nn.Module):
         warn_on_trainable_params_changed: bool = True,
     ):
         super().__init__()
+        self._instance = ShardedDataParallel._instances
+        ShardedDataParallel._instances += 1
         self.module = module
         self._sharded_optimizers = sharded_optimizer if isinstance(sharded_optimizer, list) else [sharded_optimizer]
         self._enable_broadcast_buffers = broadcast_buffers
@@ -360,11 +363,14 @@ class ShardedDataParallel(nn.Module):
                 dst = self._trainable_param_to_rank[p]
                 per_dev = self._buckets.setdefault(p.device, {})
                 if dst not in per_dev:
+                    # with an NVLink workspace the bucket lives in the symmetric heap: its owner pulls the peers' copies
                     per_dev[dst] = GradBucket(
                         self._buffer_max_size,
                         dtype=p.dtype,
                         device=p.device,
                         destination=self._local_to_global_rank[dst],
+                        align=max(1, 16 // p.element_size()),
+                        allocator=symm.heap_allocator(self._process_group, f"sdp{self._instance}-grad{dst}") if p.is_cuda else None,
                     )
                 bucket = per_dev[dst]
                 if bucket.buffer.dtype == p.dtype and bucket.can_add_grad_view(p):

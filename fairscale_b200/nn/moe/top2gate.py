@@ -74,35 +74,82 @@ def _route_indices_native(logits: Tensor, noise: Tensor) -> Optional[Tuple[Tenso
     noise = noise.to(torch.float32).contiguous()
     _bind.call("fsb_top2_route", logits.data_ptr(), _bind.dtype_code(logits.dtype), noise.data_ptr(), S, E, out[0].data_ptr(),
                out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(), ws.data_ptr(), totals.data_ptr(), _bind.stream_ptr(dev), launches=3)
-    o = out.long()
-    return o[0], o[1], o[2], o[3], totals[:E]
+    return out, totals[:E]
+
+
+class _GateValues(torch.autograd.Function):
+    """Softmax, the two kept gate values (renormalised) and the auxiliary loss in one kernel, with a one-kernel backward
+    (``csrc/top2gate.cu``).  ``route`` is the int32 ``[4, S]`` output of the index kernels (idx1, idx2, loc1, loc2)."""
+
+    @staticmethod
+    def forward(ctx, logits: Tensor, route: Tensor, count1: Tensor, capacity: int):  # type: ignore[override]
+        from ctypes import c_float, c_int, c_void_p
+
+        from ...ops import _bind
+
+        _bind._SIGNATURES.setdefault("fsb_top2_gate_fwd", [c_void_p, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_float] + [c_void_p] * 6)
+        S, E = logits.shape
+        dev = logits.device
+        gate = torch.empty((S, 2), dtype=torch.float32, device=dev)
+        scratch = torch.zeros(E + 2, dtype=torch.float32, device=dev)  # column sums | l_aux | ticket
+        eps = float(torch.finfo(torch.float32).eps)
+        _bind.call("fsb_top2_gate_fwd", logits.data_ptr(), _bind.dtype_code(logits.dtype), S, E, route[0].data_ptr(), route[1].data_ptr(),
+                   route[2].data_ptr(), route[3].data_ptr(), capacity, eps, count1.data_ptr(), gate.data_ptr(), scratch.data_ptr(),
+                   scratch[E:].data_ptr(), scratch[E + 1:].data_ptr(), _bind.stream_ptr(dev))
+        ctx.save_for_backward(logits, route, count1)
+        ctx.capacity, ctx.eps = capacity, eps
+        return gate, scratch[E]
+
+    @staticmethod
+    def backward(ctx, d_gate: Tensor, d_l_aux: Tensor):  # type: ignore[override]
+        from ctypes import c_float, c_int, c_void_p
+
+        from ...ops import _bind
+
+        _bind._SIGNATURES.setdefault("fsb_top2_gate_bwd", [c_void_p, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_float] + [c_void_p] * 5)
+        logits, route, count1 = ctx.saved_tensors
+        S, E = logits.shape
+        d_logits = torch.empty_like(logits)
+        d_gate = d_gate.to(torch.float32).contiguous()
+        d_aux = d_l_aux.to(torch.float32).reshape(1).contiguous()
+        _bind.call("fsb_top2_gate_bwd", logits.data_ptr(), _bind.dtype_code(logits.dtype), S, E, route[0].data_ptr(), route[1].data_ptr(),
+                   route[2].data_ptr(), route[3].data_ptr(), ctx.capacity, ctx.eps, d_gate.data_ptr(), d_aux.data_ptr(), count1.data_ptr(),
+                   d_logits.data_ptr(), _bind.stream_ptr(logits.device))
+        return d_logits, None, None, None
 
 
 def top2_route(logits: torch.Tensor, noise: Optional[Tensor] = None) -> Top2Route:
     """Index-form top-2 routing; ``noise`` (Gumbel, same shape as ``logits``) can be supplied for reproducibility.
 
-    On CUDA the index part (two arg-maxes, slot assignment in token order, per-expert counts) runs in the kernels of
-    ``csrc/top2gate.cu``; the differentiable part (softmax, gate values, auxiliary loss) is ordinary autograd."""
-    gates = F.softmax(logits, dim=1, dtype=torch.float)
-    S, E = gates.shape
+    On CUDA everything runs in the kernels of ``csrc/top2gate.cu``: three launches for the index part (two arg-maxes, slot
+    assignment in token order, per-expert counts) and one for the differentiable part (fp32 softmax, renormalised gate
+    values, auxiliary loss), whose backward is one more kernel.  The eager formulation below is the CPU path and the
+    oracle of the kernels' tests."""
+    S, E = logits.shape
     capacity = 2 * S // E
     assert S % E == 0
     if noise is None:
         noise = gumbel_rsample(logits.shape, device=logits.device)
     native = _route_indices_native(logits.detach(), noise) if logits.is_cuda else None
     if native is not None:
-        idx1, idx2, loc1, loc2, count1 = native
-        ce = count1.float() / S
-    else:
-        idx1 = torch.argmax(gates, dim=1)
-        noisy = (logits + noise).scatter(1, idx1.unsqueeze(1), float("-inf"))
-        idx2 = torch.argmax(noisy, dim=1)
-        mask1 = one_hot(idx1, E)
-        mask2 = one_hot(idx2, E)
-        # position of each token among the tokens that chose the same expert, in token order
-        loc1 = (torch.cumsum(mask1, dim=0) - 1).gather(1, idx1.unsqueeze(1)).squeeze(1)
-        loc2 = (torch.cumsum(mask2, dim=0) - 1 + mask1.sum(dim=0, keepdim=True)).gather(1, idx2.unsqueeze(1)).squeeze(1)
-        ce = mask1.float().mean(dim=0)
+        # five launches in all: three for the indices, one for softmax + gate values + auxiliary loss, one memset
+        route, count1 = native
+        gate, l_aux = _GateValues.apply(logits, route, count1, capacity)
+        r = route.long()
+        keep = torch.stack([r[2] < capacity, r[3] < capacity], dim=1)
+        expert = torch.stack([r[0], r[1]], dim=1)
+        slot = torch.stack([r[2], r[3]], dim=1) * keep
+        return Top2Route(l_aux.to(logits.dtype), expert, slot, keep, gate, capacity, E)
+    gates = F.softmax(logits, dim=1, dtype=torch.float)
+    idx1 = torch.argmax(gates, dim=1)
+    noisy = (logits + noise).scatter(1, idx1.unsqueeze(1), float("-inf"))
+    idx2 = torch.argmax(noisy, dim=1)
+    mask1 = one_hot(idx1, E)
+    mask2 = one_hot(idx2, E)
+    # position of each token among the tokens that chose the same expert, in token order
+    loc1 = (torch.cumsum(mask1, dim=0) - 1).gather(1, idx1.unsqueeze(1)).squeeze(1)
+    loc2 = (torch.cumsum(mask2, dim=0) - 1 + mask1.sum(dim=0, keepdim=True)).gather(1, idx2.unsqueeze(1)).squeeze(1)
+    ce = mask1.float().mean(dim=0)
 
     me = gates.mean(dim=0)
     l_aux = torch.mean(me * ce)

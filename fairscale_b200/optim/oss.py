@@ -30,7 +30,7 @@ from torch.optim import SGD, Optimizer
 
 from ..internal.params import calc_grad_norm, get_global_rank, recursive_copy_to_device
 from ..nn.misc.param_bucket import ParamBucket
-from ..parallel import comm
+from ..parallel import comm, symm
 
 __all__ = ["OSS"]
 
@@ -75,6 +75,8 @@ class OSS(Optimizer):
         **default: forwarded to ``optim``.
     """
 
+    _instances = 0
+
     #: the wrapped optimizer, built on this rank's shard
     optim: Optimizer
     in_super_constructor: bool
@@ -92,6 +94,8 @@ class OSS(Optimizer):
         self.in_super_constructor = True
         super().__init__(params, default)
         self.in_super_constructor = False
+        self._instance = OSS._instances  # construction order is the same on every rank: names this optimizer's heap windows
+        OSS._instances += 1
 
         # lazily (re)built partition caches; cleared by _clear_cache()
         self._cache_per_device: Dict[torch.device, List[List[Parameter]]] = OrderedDict()
@@ -410,8 +414,10 @@ class OSS(Optimizer):
                 members = [p for p in trainable if p.dtype == dtype]
                 dev_loose[owner] = [p for p in trainable if p.dtype != dtype]
                 align = max(1, 16 // members[0].element_size())
+                # with an NVLink workspace the bucket lives in the symmetric heap: peers copy the owner's values out of it
                 bucket = ParamBucket(
-                    size=ParamBucket.required_size(members, align), dtype=dtype, device=device, align=align
+                    size=ParamBucket.required_size(members, align), dtype=dtype, device=device, align=align,
+                    allocator=symm.heap_allocator(self.group, f"oss{self._instance}-param{owner}-{device}") if device.type == "cuda" else None,
                 )
                 for p in members:
                     bucket.add_param(p)

@@ -18,7 +18,7 @@ fairscale/nn/moe/moe_layer.py:29, fairscale/nn/model_parallel/mappings.py:42,76-
 from __future__ import annotations
 
 import os
-from typing import Any, List, Optional
+from typing import Callable, Any, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -197,17 +197,62 @@ def all_to_all_single(out: torch.Tensor, inp: torch.Tensor, group: Any = None):
     return dist.all_to_all_single(out, inp.contiguous(), group=group)
 
 
+class StreamWork:
+    """Handle of a collective that runs on a side stream of an NVLink workspace: the interface of a
+    ``torch.distributed`` work object that the callers here use (``wait`` / ``is_completed``)."""
+
+    def __init__(self, event: "torch.cuda.Event", device: torch.device) -> None:
+        self.event, self.device = event, device
+
+    def wait(self) -> bool:
+        torch.cuda.current_stream(self.device).wait_event(self.event)  # stream-ordered, like a NCCL work object
+        return True
+
+    def is_completed(self) -> bool:
+        return bool(self.event.query())
+
+
+def _on_side_stream(ws: Any, t: torch.Tensor, fn: Callable[[], None], async_op: bool, lane: int = 3) -> Optional[StreamWork]:
+    cur = torch.cuda.current_stream(t.device)
+    side = ws.side_stream(lane)
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        fn()
+        ev = torch.cuda.Event()
+        ev.record(side)
+    t.record_stream(side)
+    work = StreamWork(ev, t.device)
+    if async_op:
+        return work
+    work.wait()
+    return None
+
+
+def _local_rank_of(group: Any, global_rank: int) -> int:
+    return global_rank if group is None or group is dist.group.WORLD else dist.get_group_rank(group, global_rank)
+
+
 def broadcast(t: torch.Tensor, src: int, group: Any = None, async_op: bool = False):
-    """``src`` is a *global* rank, as in ``torch.distributed.broadcast``."""
+    """``src`` is a *global* rank, as in ``torch.distributed.broadcast``.  With an NVLink workspace the other ranks copy the
+    tensor out of the owner's symmetric heap on their copy engines (OSS publishing an owner's updated parameters)."""
     _COUNTERS["broadcast"] += 1
     if group_size(group) == 1 or not _is_real_group(group):
         return None
+    ws = _symm_for(group, t)
+    if ws is not None and ws.can_broadcast(t):
+        owner = _local_rank_of(group, src)
+        return _on_side_stream(ws, t, lambda: ws.broadcast(t, owner), async_op)
     return dist.broadcast(t, src=src, group=group, async_op=async_op)
 
 
 def reduce(t: torch.Tensor, dst: int, group: Any = None, async_op: bool = False):
-    """Sum-reduce to the *global* rank ``dst``."""
+    """Sum-reduce to the *global* rank ``dst``.  With an NVLink workspace the owner's kernel pulls the peers' buffers
+    (ShardedDataParallel reducing a gradient or a gradient bucket to the rank that owns it)."""
     _COUNTERS["reduce"] += 1
     if group_size(group) == 1 or not _is_real_group(group):
         return None
+    ws = _symm_for(group, t)
+    if ws is not None and ws.can_reduce_to(t):
+        owner = _local_rank_of(group, dst)
+        return _on_side_stream(ws, t, lambda: ws.reduce_to(t, owner), async_op)
     return dist.reduce(t, dst=dst, group=group, async_op=async_op)

@@ -48,6 +48,8 @@ def _sigs() -> None:
     S["fsb_comm_reduce_scatter_adam"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                  c_float, c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p, c_void_p,
                                                  c_void_p, c_void_p]
+    S["fsb_comm_reduce_to"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
+    S["fsb_comm_broadcast_dma"] = head + [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p]
     S["fsb_comm_all_reduce"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_moe_scatter_rows"] = head + [c_void_p] * 6 + [c_longlong, c_int, c_int, c_void_p, c_void_p]
     S["fsb_comm_moe_gather_rows"] = head + [c_void_p] * 8 + [c_longlong, c_int, c_int, c_void_p, c_void_p]
@@ -364,6 +366,46 @@ class NvlinkWorkspace:
                    int(eps_inside_sqrt), int(adamw), _bind.ptr(gnorm_sq), _bind.ptr(found_inf), _bind.status_ptr(self.device),
                    _bind.stream_ptr(self.device))
         self.release_grad_window(flat_in)
+
+    # ------------------------------------------------------------------ one-owner collectives (ZeRO-1 / ZeRO-2)
+    def side_stream(self, lane: int) -> "torch.cuda.Stream":
+        """The stream on which the collectives of ``lane`` run when they are to overlap with the caller's stream."""
+        streams = self.__dict__.setdefault("_side_streams", {})
+        if lane not in streams:
+            streams[lane] = torch.cuda.Stream(device=self.device)
+        return streams[lane]
+
+    def can_reduce_to(self, t: torch.Tensor) -> bool:
+        return (t.is_cuda and t.dtype in _bind._DTYPE_CODE and t.is_contiguous() and not self.poisoned
+                and self._fits(t, t.numel() * t.element_size()) and (self.offset_of(t) is None or self._aligned(t)))
+
+    def reduce_to(self, t: torch.Tensor, owner: int, scale: float = 1.0, lane: int = 3) -> None:
+        """Sum of every rank's ``t`` into rank ``owner``'s ``t`` (in place, times ``scale``); the other ranks keep theirs.
+        The owner's kernel pulls from the peers' heap (a tensor outside the heap is staged first, on every rank alike)."""
+        ln = self._lane(lane)
+        off = self.offset_of(t)
+        staged = off is None
+        if staged:
+            off = self._stage(ln, t)
+        _bind.call("fsb_comm_reduce_to", *self._head(ln), self._counter(ln), self.peers(off), _bind.dtype_code(t.dtype), t.numel(), scale,
+                   owner, _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
+        if staged and owner == self.rank:
+            t.view(-1).copy_(self.heap[off : off + t.numel() * t.element_size()].view(t.dtype))
+
+    def can_broadcast(self, t: torch.Tensor) -> bool:
+        return t.is_cuda and t.is_contiguous() and not self.poisoned and self._fits(t, t.numel() * t.element_size())
+
+    def broadcast(self, t: torch.Tensor, owner: int, lane: int = 3) -> None:
+        """Every rank's ``t`` becomes rank ``owner``'s: the others copy it out of the owner's heap on their copy engines
+        (no SM takes part).  Whether ``t`` lives in the heap must be the same on every rank."""
+        ln = self._lane(lane)
+        off = self.offset_of(t)
+        if off is None:
+            off = self._stage(ln, t) if owner == self.rank else ln.staging_off
+        head = self._head(ln)
+        ln.epoch = (ln.epoch + 1) & 0x7FFFFFFF  # the exit barrier uses the next epoch
+        _bind.call("fsb_comm_broadcast_dma", *head, self.peers(off), t.data_ptr(), t.numel() * t.element_size(), owner,
+                   _bind.status_ptr(self.device), _bind.stream_ptr(self.device), launches=2)
 
     def all_reduce(self, t: torch.Tensor, lane: int = 0) -> None:
         ln = self._lane(lane)

@@ -49,3 +49,25 @@ def poison_all() -> None:
     and epochs of the in-kernel collectives in an unknown state.  Callers fall back to ``torch.distributed``."""
     for ws in _WORKSPACES.values():
         ws.poisoned = True
+
+
+def heap_allocator(group: Any, tag: str) -> Optional[Any]:
+    """An ``allocator(numel, dtype, device)`` for flat buckets that places them in the symmetric heap of ``group``'s
+    workspace (so that peers can pull them directly), or None without a workspace.  Buffers are named by ``tag``, size and
+    dtype and reused: rebuilding the same bucket does not grow the heap.  Every rank must allocate the same buckets in the
+    same order (the heap hands out the same offsets on every rank); when the heap is full the bucket silently goes to
+    ordinary device memory on every rank alike (sizes are the same everywhere)."""
+    ws = workspace_for(group)
+    if ws is None:
+        return None
+    import torch
+
+    def allocate(numel: int, dtype: "torch.dtype", device: "torch.device") -> "torch.Tensor":
+        if torch.device(device) != ws.device or numel == 0:
+            return torch.empty(numel, dtype=dtype, device=device)
+        try:
+            return ws.scratch(f"{tag}:{numel}", (numel,), dtype)
+        except MemoryError:
+            return torch.empty(numel, dtype=dtype, device=device)
+
+    return allocate

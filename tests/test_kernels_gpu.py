@@ -523,3 +523,26 @@ def test_flash_attention_pingpong_forward(B, S, H, D):
     ref = (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, H * D)
     assert _rel_err(o, ref) < 2e-2, _rel_err(o, ref)
     assert _rel_err(lse, torch.logsumexp(s, -1)) < 1e-3
+
+
+@pytest.mark.parametrize("S,E,dtype", [(2048, 64, torch.float32), (512, 8, torch.float32), (1024, 136, torch.float32), (1024, 16, torch.bfloat16)])
+def test_top2_gate_values_kernel_matches_eager(S, E, dtype):
+    """Softmax + kept gate values + auxiliary loss (one kernel) and their backward (one kernel) against the eager
+    formulation evaluated on the host with the same Gumbel noise."""
+    from fairscale_b200.nn.moe.top2gate import top2_route
+
+    torch.manual_seed(S + E)
+    logits = (torch.randn(S, E, device=_dev()) * 2).to(dtype).requires_grad_()
+    noise = -torch.log(-torch.log(torch.rand(S, E, device=_dev()).clamp_(1e-9, 1 - 1e-7)))
+    route = top2_route(logits, noise)
+    ref_logits = logits.detach().float().cpu().requires_grad_()
+    ref = top2_route(ref_logits, noise.cpu())
+    assert torch.equal(route.expert.cpu(), ref.expert) and torch.equal(route.slot.cpu(), ref.slot) and torch.equal(route.keep.cpu(), ref.keep)
+    torch.testing.assert_close(route.gate.cpu(), ref.gate, atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(route.l_aux.float().cpu(), ref.l_aux, atol=1e-6, rtol=2e-3 if dtype == torch.bfloat16 else 1e-4)
+    w = torch.randn(S, 2)
+    (route.gate * w.to(_dev())).sum().add(3.0 * route.l_aux.float()).backward()
+    (ref.gate * w).sum().add(3.0 * ref.l_aux).backward()
+    tol = dict(atol=2e-3, rtol=2e-2) if dtype == torch.bfloat16 else dict(atol=2e-5, rtol=1e-3)
+    torch.testing.assert_close(logits.grad.float().cpu(), ref_logits.grad, **tol)
+    _status_ok()

@@ -21,13 +21,19 @@ def _mlp(seed=0, d=64):
     return nn.Sequential(nn.Linear(d, 2 * d), nn.GELU(), nn.Linear(2 * d, 2 * d), nn.Tanh(), nn.Linear(2 * d, d))
 
 
-def _oss_sdp_worker(rank, world, reduce_fp16, buffer_size):
+def _oss_sdp_worker(rank, world, reduce_fp16, buffer_size, over_nvlink=False):
     from torch.nn.parallel import DistributedDataParallel as DDP
 
     from fairscale_b200.nn.data_parallel import ShardedDataParallel
     from fairscale_b200.optim import OSS
 
     dev = torch.device("cuda", rank)
+    ws = None
+    if over_nvlink:
+        # gradient (buckets) reduced by the owner's pull kernel, updated parameters copied out of the owner's heap
+        from fairscale_b200.parallel import nvlink
+
+        ws = nvlink.enable(None, dev, staging_mb=8, heap_mb=64)
     ref = DDP(_mlp().to(dev), device_ids=[rank])
     model = _mlp().to(dev)
     ref_opt = torch.optim.Adam(ref.parameters(), lr=1e-3)
@@ -45,12 +51,24 @@ def _oss_sdp_worker(rank, world, reduce_fp16, buffer_size):
     tol = dict(atol=3e-3, rtol=3e-2) if reduce_fp16 else dict(atol=1e-6, rtol=1e-4)
     for a, b in zip(ref.module.parameters(), model.parameters()):
         torch.testing.assert_close(b, a, **tol)
+    if ws is not None:
+        from fairscale_b200.utils.failure import check_device_status
+
+        check_device_status(dev)
+        assert ws.lanes[3].epoch >= 4 * 2, "reductions and broadcasts went over the NVLink lane"
+        if buffer_size > 0:
+            assert any(ws.offset_of(b.buffer) is not None for b in sdp._bucket_list), "gradient buckets live in the symmetric heap"
     dist.barrier()
 
 
 @pytest.mark.parametrize("reduce_fp16,buffer_size", [(False, 2**23), (False, 0), (True, 2**23)])
 def test_oss_sharded_ddp_matches_ddp_on_two_gpus(reduce_fp16, buffer_size):
     spawn_ranks(_oss_sdp_worker, 2, (reduce_fp16, buffer_size), backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("reduce_fp16,buffer_size", [(False, 2**23), (False, 0), (True, 0)])
+def test_oss_sharded_ddp_over_nvlink_matches_ddp(reduce_fp16, buffer_size):
+    spawn_ranks(_oss_sdp_worker, 2, (reduce_fp16, buffer_size, True), backend="nccl", timeout=300)
 
 
 def _async_pipe_worker(rank, world):
