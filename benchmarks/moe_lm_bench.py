@@ -114,7 +114,9 @@ def main():
         from fairscale_b200.parallel import nvlink
 
         if world > 1:
-            nvlink.enable(dist.group.WORLD, dev, staging_mb=64, heap_mb=512)
+            # three landing buffers of 2 * tokens rows per MoE layer (each layer keeps its own), plus room for the shared ones
+            per_buffer = 2 * args.batch * args.seq * args.d_model * 2
+            nvlink.enable(dist.group.WORLD, dev, staging_mb=64, heap_mb=((3 * args.layers + 4) * per_buffer >> 20) + 64)
         cfg = MoELMConfig(vocab_size=args.vocab, d_model=args.d_model, n_heads=args.heads, n_layers=args.layers, ffn=args.ffn,
                           max_seq=args.seq, num_local_experts=args.experts_per_gpu)
         model = MoELM(cfg).to(dev).to(torch.bfloat16)

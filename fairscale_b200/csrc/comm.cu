@@ -350,7 +350,8 @@ __global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM) all_reduce
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM) moe_scatter_rows_kernel(CommCtx c, PtrTable dst, const __nv_bfloat16* __restrict__ x,
                                                                         const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
-                                                                        const float* __restrict__ w, long long T, int rows_per_token, int M) {
+                                                                        const float* __restrict__ w, long long T, int rows_per_token, int M,
+                                                                        const int* __restrict__ counts, int E, int C, int n_local) {
   if (blockIdx.x == 0) signal_peers(c, c.channel);  // destinations are zeroed / free
   if (!wait_peers(c, c.channel)) return;
   const int lane = threadIdx.x & 31;
@@ -368,6 +369,22 @@ __global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM) moe_scatte
         for (int k = 0; k < 8; ++k) v.v[k] = __float2bfloat16_rn(__bfloat162float(v.v[k]) * scale);
       }
       st16(d + j, v);
+    }
+  }
+  // Rows that no token of this rank claimed: expert e took slots [0, counts[e] + counts[E + e]) of this rank's C-row
+  // segment in its owner's buffer (first choices, then second choices); the rest of the segment is zeroed here, so the
+  // owner needs no separate pass over its whole landing buffer.
+  if (counts != nullptr) {
+    Vec16<__nv_bfloat16> z;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) z.v[k] = __float2bfloat16_rn(0.f);
+    const long long rows = static_cast<long long>(E) * C;
+    for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; idx < rows; idx += warps) {
+      const int e = static_cast<int>(idx / C), slot = static_cast<int>(idx % C);
+      if (slot < counts[e] + counts[E + e]) continue;
+      const long long row = static_cast<long long>(e % n_local) * (static_cast<long long>(c.world) * C) + static_cast<long long>(c.rank) * C + slot;
+      __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dst.p[e / n_local])) + row * M;
+      for (int j = lane * 8; j < M; j += 256) st16(d + j, z);
     }
   }
   exit_barrier(c, c.channel + 1);  // all rows of all ranks have landed
@@ -721,12 +738,14 @@ FSB_API int fsb_comm_all_reduce(int rank, int world, unsigned epoch, int channel
 
 FSB_API int fsb_comm_moe_scatter_rows(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter,
                                       void* const* dst, const void* x, const int* dst_rank, const int* dst_row, const float* w,
-                                      long long T, int rows_per_token, int M, int* status, cudaStream_t stream) {
+                                      long long T, int rows_per_token, int M, const int* counts, int E, int C, int n_local,
+                                      int* status, cudaStream_t stream) {
   using namespace fsb;
   if (world > kMaxRanks || M % 8) return -1;
+  if (counts != nullptr && (E < 1 || C < 1 || n_local < 1 || E != n_local * world)) return -1;
   moe_scatter_rows_kernel<<<comm_grid(T * 32, kWideGrid), COMM_THREADS, 0, stream>>>(
       make_ctx(rank, world, epoch, channel, pads, counter, status), make_table(dst, world), static_cast<const __nv_bfloat16*>(x),
-      dst_rank, dst_row, w, T, rows_per_token, M);
+      dst_rank, dst_row, w, T, rows_per_token, M, counts, E, C, n_local);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -45,6 +45,52 @@ class _AllToAll(torch.autograd.Function):
         return (None, _AllToAll.apply(ctx.group, *grad_output))
 
 
+class _LayerBuffers:
+    """The symmetric-heap buffers of one MOELayer (landing buffer of the dispatch, expert outputs for the combine, and the
+    combine's gradient landing buffer).  A layer that uses its own buffers needs no defensive copies: what the dispatch
+    lands is read in place by the experts and kept for their backward, the expert outputs stay where the backward reads them
+    again.  That holds while at most one forward of the layer is waiting for its backward; a second forward in between
+    (micro-batches run forward first, backward later) falls back to shared buffers plus copies."""
+
+    _count = 0  # construction order is the same on every rank
+
+    def __init__(self) -> None:
+        self.index = _LayerBuffers._count
+        _LayerBuffers._count += 1
+        self.outstanding = 0
+        self.full = False
+        self.expect_backward = False
+
+    def _allocate(self, ws: Any, rows: int, M: int, dtype: torch.dtype) -> bool:
+        if self.full:
+            return False
+        try:
+            self.bufs = {w: ws.scratch(f"moe{self.index}:{w}", (rows, M), dtype) for w in ("in", "out", "grad")}
+            return True
+        except MemoryError:
+            self.full = True  # the heap has no room for per-layer buffers (the same on every rank): shared buffers + copies
+            return False
+
+    def claim(self, ws: Any, rows: int, M: int, dtype: torch.dtype) -> bool:
+        """Called by a dispatch forward: True if this forward may use the layer's own buffers (``self.bufs``).
+        ``self.expect_backward`` is set by the layer before the call (grad mode is off inside ``Function.forward``)."""
+        self._mine = False
+        if self.outstanding > 0 or not self._allocate(ws, rows, M, dtype):
+            return False
+        if self.expect_backward:
+            self.outstanding += 1  # released by the dispatch's backward
+        self._mine = True
+        return True
+
+    def holds(self) -> bool:
+        """For the combine of the same forward: did its dispatch get the layer's own buffers?"""
+        return bool(getattr(self, "_mine", False))
+
+    def release(self) -> None:
+        if self.outstanding > 0:
+            self.outstanding -= 1
+
+
 def _routes(route: Top2Route, world: int, n_local: int, rank: int) -> Tuple[Tensor, Tensor, Tensor]:
     """Per (token, choice): destination rank (-1 if dropped), row in the destination's
     ``[n_local, world * C, M]`` buffer, and flat slot ``expert * C + slot`` in the global ``[E, C, M]`` view."""
@@ -60,18 +106,27 @@ class _Dispatch(torch.autograd.Function):
     """tokens ``[S, M]`` -> expert inputs ``[n_local, world * C, M]`` on the owning ranks."""
 
     @staticmethod
-    def forward(ctx: Any, x: Tensor, route: Top2Route, group: Any, n_local: int) -> Tensor:  # type: ignore[override]
+    def forward(ctx: Any, x: Tensor, route: Top2Route, group: Any, n_local: int, owner: Optional[_LayerBuffers] = None) -> Tensor:  # type: ignore[override]
         world, rank = comm.group_size(group), comm.group_rank(group)
         C, E, M = route.capacity, route.num_experts, x.shape[1]
         dst_rank, dst_row, flat = _routes(route, world, n_local, rank)
         ctx.meta = (group, n_local, world, rank, C, E, M, x.dtype)
+        ctx.owner, ctx.claimed = owner, False
         ctx.save_for_backward(dst_rank, dst_row, flat, route.keep)
         ws = symm.workspace_for(group) if (x.is_cuda and comm.comm_mode() == "fused" and x.dtype == torch.bfloat16) else None
+        if owner is not None:
+            owner._mine = False
         if ws is not None:
-            buf = ws.scratch("moe_in", (n_local * world * C, M), x.dtype)
-            buf.zero_()
-            ws.moe_scatter_rows(buf, x.contiguous(), dst_rank.view(-1), dst_row.view(-1), None, 2)
-            return buf.view(n_local, world * C, M).clone()
+            private = owner is not None and owner.claim(ws, n_local * world * C, M, x.dtype)
+            ctx.claimed = private and owner.expect_backward
+            buf = owner.bufs["in"] if private else ws.scratch("moe_in", (n_local * world * C, M), x.dtype)
+            fill = (route.counts, E, C, n_local) if route.counts is not None else None
+            if fill is None:
+                buf.zero_()  # without per-expert counts the kernel cannot tell which rows stay unclaimed
+            ws.moe_scatter_rows(buf, x.contiguous(), dst_rank.view(-1), dst_row.view(-1), None, 2, fill=fill)
+            out = buf.view(n_local, world * C, M)
+            # the layer's own landing buffer stays untouched until its backward: the experts read it in place
+            return out if private else out.clone()
         local = x.new_zeros((E * C, M))
         for k in range(2):
             kept = route.keep[:, k]
@@ -85,13 +140,15 @@ class _Dispatch(torch.autograd.Function):
         group, n_local, world, rank, C, E, M, dtype = ctx.meta
         dst_rank, dst_row, flat, keep = ctx.saved_tensors
         S = dst_rank.shape[0]
+        if ctx.claimed:
+            ctx.owner.release()
         ws = symm.workspace_for(group) if (grad.is_cuda and comm.comm_mode() == "fused" and grad.dtype == torch.bfloat16) else None
         if ws is not None:
-            buf = ws.scratch("moe_grad", (n_local * world * C, M), grad.dtype)
+            buf = ws.scratch("moe_dgrad", (n_local * world * C, M), grad.dtype)
             buf.copy_(grad.reshape(-1, M))
             dx = torch.empty((S, M), dtype=grad.dtype, device=grad.device)
             ws.moe_gather_rows(buf, dx, dst_rank.view(-1), dst_row.view(-1), None, 2)
-            return dx, None, None, None
+            return dx, None, None, None, None
         g = grad.view(n_local, world, C, M).transpose(0, 1).contiguous().view(E * C, M)
         back = torch.empty_like(g)
         comm.all_to_all_single(back, g, group)
@@ -99,27 +156,32 @@ class _Dispatch(torch.autograd.Function):
         for k in range(2):
             kept = keep[:, k]
             dx[kept] += back[flat[kept, k]]
-        return dx, None, None, None
+        return dx, None, None, None, None
 
 
 class _Combine(torch.autograd.Function):
     """expert outputs ``[n_local, world * C, M]`` -> tokens ``[S, M]`` weighted by the gates."""
 
     @staticmethod
-    def forward(ctx: Any, expert_out: Tensor, gate: Tensor, route: Top2Route, group: Any, n_local: int) -> Tensor:  # type: ignore[override]
+    def forward(ctx: Any, expert_out: Tensor, gate: Tensor, route: Top2Route, group: Any, n_local: int,
+                owner: Optional[_LayerBuffers] = None) -> Tensor:  # type: ignore[override]
         world, rank = comm.group_size(group), comm.group_rank(group)
         C, E, M = route.capacity, route.num_experts, expert_out.shape[-1]
         dst_rank, dst_row, flat = _routes(route, world, n_local, rank)
         S = dst_rank.shape[0]
         w = (gate * route.keep).to(torch.float32).contiguous()
         ctx.meta = (group, n_local, world, rank, C, E, M)
+        ctx.fill = (route.counts, E, C, n_local) if route.counts is not None else None
         ws = symm.workspace_for(group) if (expert_out.is_cuda and comm.comm_mode() == "fused" and expert_out.dtype == torch.bfloat16) else None
+        ctx.private = ws is not None and owner is not None and owner.holds()
+        ctx.owner = owner
         if ws is not None:
-            buf = ws.scratch("moe_out", (n_local * world * C, M), expert_out.dtype)
+            buf = owner.bufs["out"] if ctx.private else ws.scratch("moe_out", (n_local * world * C, M), expert_out.dtype)
             buf.copy_(expert_out.reshape(-1, M))
             out = torch.empty((S, M), dtype=expert_out.dtype, device=expert_out.device)
             ws.moe_gather_rows(buf, out, dst_rank.view(-1), dst_row.view(-1), w.view(-1), 2)
-            ctx.save_for_backward(dst_rank, dst_row, flat, route.keep, w, expert_out)
+            # the layer's own buffer keeps the expert outputs until the backward reads them remotely again
+            ctx.save_for_backward(dst_rank, dst_row, flat, route.keep, w, buf if ctx.private else expert_out)
             return out
         eo = expert_out.view(n_local, world, C, M).transpose(0, 1).contiguous().view(E * C, M)
         home = torch.empty_like(eo)
@@ -138,16 +200,23 @@ class _Combine(torch.autograd.Function):
         ws = symm.workspace_for(group) if (dy.is_cuda and comm.comm_mode() == "fused" and dy.dtype == torch.bfloat16) else None
         if ws is not None:
             # d(expert_out): gate-weighted rows of dy pushed into the owners' gradient buffers
-            gbuf = ws.scratch("moe_grad", (n_local * world * C, M), dy.dtype)
-            gbuf.zero_()
-            ws.moe_scatter_rows(gbuf, dy, dst_rank.view(-1), dst_row.view(-1), w.view(-1), 2)
-            d_eo = gbuf.view(n_local, world * C, M).clone()
+            private = ctx.private
+            gbuf = ctx.owner.bufs["grad"] if private else ws.scratch("moe_grad", (n_local * world * C, M), dy.dtype)
+            if ctx.fill is None:
+                gbuf.zero_()
+            ws.moe_scatter_rows(gbuf, dy, dst_rank.view(-1), dst_row.view(-1), w.view(-1), 2, fill=ctx.fill)
+            d_eo = gbuf.view(n_local, world * C, M)
+            if not private:
+                d_eo = d_eo.clone()
             # d(gate): <expert_out row, dy row>, read remotely
-            obuf = ws.scratch("moe_out", (n_local * world * C, M), dy.dtype)
-            obuf.copy_(saved.reshape(-1, M))
+            if private:
+                obuf = saved  # still in place since the forward
+            else:
+                obuf = ws.scratch("moe_out", (n_local * world * C, M), dy.dtype)
+                obuf.copy_(saved.reshape(-1, M))
             dots = torch.zeros((S, 2), dtype=torch.float32, device=dy.device)
             ws.moe_gather_rows(obuf, None, dst_rank.view(-1), dst_row.view(-1), None, 2, grad=dy, dots=dots.view(-1))
-            return d_eo, (dots * keep).to(w.dtype), None, None, None
+            return d_eo, (dots * keep).to(w.dtype), None, None, None, None
         rows = saved  # [S, 2, M]
         d_gate = (rows.float() * dy.float().unsqueeze(1)).sum(-1) * keep
         contrib = dy.float().unsqueeze(1) * w.unsqueeze(-1)  # [S, 2, M]
@@ -159,7 +228,7 @@ class _Combine(torch.autograd.Function):
         back = torch.empty_like(home)
         comm.all_to_all_single(back, home, group)
         d_eo = back.view(world, n_local, C, M).transpose(0, 1).reshape(n_local, world * C, M)
-        return d_eo, d_gate.to(w.dtype), None, None, None
+        return d_eo, d_gate.to(w.dtype), None, None, None, None
 
 
 class MOELayer(Base):
@@ -183,6 +252,7 @@ class MOELayer(Base):
                 p.expert = True  # type: ignore[attr-defined]  # data-parallel reducers must skip these
         self.world_size = dist.get_world_size(self.group)
         self.num_local_experts = len(experts) if self._grouped else len(self.experts)  # type: ignore[arg-type]
+        self._heap_buffers = _LayerBuffers()
 
     def forward(self, *input: Tensor, **kwargs: Any) -> Tensor:
         assert len(input) == 1, "only single input Tensor supported"
@@ -195,7 +265,8 @@ class MOELayer(Base):
         if hasattr(self.gate, "route"):
             route: Top2Route = self.gate.route(tokens)
             self.l_aux = route.l_aux
-            expert_in = _Dispatch.apply(tokens, route, self.group, self.num_local_experts)  # [n_local, world*C, M]
+            self._heap_buffers.expect_backward = torch.is_grad_enabled()
+            expert_in = _Dispatch.apply(tokens, route, self.group, self.num_local_experts, self._heap_buffers)  # [n_local, world*C, M]
             if self._grouped:
                 expert_out = self.experts[0](expert_in)  # every local expert in one grouped launch
             else:
@@ -204,7 +275,7 @@ class MOELayer(Base):
                     chunk = expert_in[e].view(self.world_size, 1, route.capacity, d_model)
                     outs.append(expert(chunk).reshape(self.world_size * route.capacity, d_model))
                 expert_out = torch.stack(outs, dim=0)
-            combined = _Combine.apply(expert_out, route.gate, route, self.group, self.num_local_experts)
+            combined = _Combine.apply(expert_out, route.gate, route, self.group, self.num_local_experts, self._heap_buffers)
             return combined.reshape(x.shape)
 
         self.l_aux, combine_weights, dispatch_mask = self.gate(tokens)

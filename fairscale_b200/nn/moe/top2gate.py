@@ -54,6 +54,7 @@ class Top2Route(NamedTuple):
     gate: Tensor
     capacity: int
     num_experts: int
+    counts: Optional[Tensor] = None  # int32 [2 * E]: tokens per expert as first / second choice (CUDA index kernels only)
 
 
 def _route_indices_native(logits: Tensor, noise: Tensor) -> Optional[Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]]:
@@ -74,7 +75,7 @@ def _route_indices_native(logits: Tensor, noise: Tensor) -> Optional[Tuple[Tenso
     noise = noise.to(torch.float32).contiguous()
     _bind.call("fsb_top2_route", logits.data_ptr(), _bind.dtype_code(logits.dtype), noise.data_ptr(), S, E, out[0].data_ptr(),
                out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(), ws.data_ptr(), totals.data_ptr(), _bind.stream_ptr(dev), launches=3)
-    return out, totals[:E]
+    return out, totals
 
 
 class _GateValues(torch.autograd.Function):
@@ -130,16 +131,19 @@ def top2_route(logits: torch.Tensor, noise: Optional[Tensor] = None) -> Top2Rout
     assert S % E == 0
     if noise is None:
         noise = gumbel_rsample(logits.shape, device=logits.device)
+    if logits.is_cuda and not logits.is_contiguous():
+        logits = logits.contiguous()
     native = _route_indices_native(logits.detach(), noise) if logits.is_cuda else None
     if native is not None:
         # five launches in all: three for the indices, one for softmax + gate values + auxiliary loss, one memset
-        route, count1 = native
+        route, counts2 = native
+        count1 = counts2[:E]
         gate, l_aux = _GateValues.apply(logits, route, count1, capacity)
         r = route.long()
         keep = torch.stack([r[2] < capacity, r[3] < capacity], dim=1)
         expert = torch.stack([r[0], r[1]], dim=1)
         slot = torch.stack([r[2], r[3]], dim=1) * keep
-        return Top2Route(l_aux.to(logits.dtype), expert, slot, keep, gate, capacity, E)
+        return Top2Route(l_aux.to(logits.dtype), expert, slot, keep, gate, capacity, E, counts2)
     gates = F.softmax(logits, dim=1, dtype=torch.float)
     idx1 = torch.argmax(gates, dim=1)
     noisy = (logits + noise).scatter(1, idx1.unsqueeze(1), float("-inf"))
@@ -198,7 +202,8 @@ class _GateProjection(torch.autograd.Function):
         logits, _ = gemm_ops.linear_forward(x2, w_pad, None, out_dtype=torch.float32)
         ctx.save_for_backward(x2, w_pad)
         ctx.meta = (E, x.shape, w.dtype)
-        return logits[:, :E].reshape(*x.shape[:-1], E)
+        # contiguous: the routing kernels take dense [S, E] logits (a strided slice would send them down the eager path)
+        return logits[:, :E].contiguous().reshape(*x.shape[:-1], E)
 
     @staticmethod
     def backward(ctx, d_logits: Tensor):  # type: ignore[override]

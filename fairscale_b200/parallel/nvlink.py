@@ -51,7 +51,7 @@ def _sigs() -> None:
     S["fsb_comm_reduce_to"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
     S["fsb_comm_broadcast_dma"] = head + [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p]
     S["fsb_comm_all_reduce"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p]
-    S["fsb_comm_moe_scatter_rows"] = head + [c_void_p] * 6 + [c_longlong, c_int, c_int, c_void_p, c_void_p]
+    S["fsb_comm_moe_scatter_rows"] = head + [c_void_p] * 6 + [c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
     S["fsb_comm_moe_gather_rows"] = head + [c_void_p] * 8 + [c_longlong, c_int, c_int, c_void_p, c_void_p]
     _SIGS_DONE = True
 
@@ -128,7 +128,13 @@ class NvlinkWorkspace:
         n = 1
         for s in shape:
             n *= s
-        return self.alloc(n * torch.empty((), dtype=dtype).element_size()).view(dtype).view(shape)
+        window = self.alloc(n * torch.empty((), dtype=dtype).element_size())
+        # A tensor of its own on the heap's storage, not a view of the heap tensor: in-place operations on one window must
+        # not count as modifications of every other window (autograd refuses custom-Function outputs whose base changed).
+        esize = torch.empty((), dtype=dtype).element_size()
+        t = torch.empty(0, dtype=dtype, device=self.device)
+        t.set_(self.heap.untyped_storage(), (window.data_ptr() - self.heap.data_ptr() + self.heap.storage_offset()) // esize, tuple(shape))
+        return t
 
     # ------------------------------------------------------------------ gradient windows
     def enable_grad_windows(self, window_bytes: int, count: int = 3) -> None:
@@ -430,14 +436,18 @@ class NvlinkWorkspace:
 
     # ------------------------------------------------------------------ MoE routing (see nn/moe/moe_layer.py)
     def moe_scatter_rows(self, dst: torch.Tensor, x: torch.Tensor, dst_rank: torch.Tensor, dst_row: torch.Tensor,
-                         weights: Optional[torch.Tensor], rows_per_token: int, lane: int = 0) -> None:
-        """Store row ``t // rows_per_token`` of ``x`` into row ``dst_row[t]`` of rank ``dst_rank[t]``'s ``dst`` (heap tensor)."""
+                         weights: Optional[torch.Tensor], rows_per_token: int, lane: int = 0,
+                         fill: Optional[Tuple[torch.Tensor, int, int, int]] = None) -> None:
+        """Store row ``t // rows_per_token`` of ``x`` into row ``dst_row[t]`` of rank ``dst_rank[t]``'s ``dst`` (heap tensor).
+        ``fill = (counts[2E] int32, E, C, n_local)``: also zero the rows of this rank's segments that no token claimed
+        (``dst`` laid out ``[n_local, world, C, M]``, expert ``e`` having taken ``counts[e] + counts[E + e]`` slots)."""
         ln = self._lane(lane)
         off = self.offset_of(dst)
         assert off is not None, "destination must live in the symmetric heap"
         _bind.call("fsb_comm_moe_scatter_rows", *self._head(ln), self._counter(ln), self.peers(off), x.data_ptr(), dst_rank.data_ptr(),
                    dst_row.data_ptr(), _bind.ptr(weights), dst_rank.numel(), rows_per_token, x.shape[-1],
-                   _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
+                   None if fill is None else fill[0].data_ptr(), 0 if fill is None else fill[1], 0 if fill is None else fill[2],
+                   0 if fill is None else fill[3], _bind.status_ptr(self.device), _bind.stream_ptr(self.device))
 
     def moe_gather_rows(self, src: torch.Tensor, out: Optional[torch.Tensor], src_rank: torch.Tensor, src_row: torch.Tensor,
                         weights: Optional[torch.Tensor], rows_per_token: int, grad: Optional[torch.Tensor] = None,

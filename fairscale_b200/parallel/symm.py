@@ -53,10 +53,11 @@ def poison_all() -> None:
 
 def heap_allocator(group: Any, tag: str) -> Optional[Any]:
     """An ``allocator(numel, dtype, device)`` for flat buckets that places them in the symmetric heap of ``group``'s
-    workspace (so that peers can pull them directly), or None without a workspace.  Buffers are named by ``tag``, size and
-    dtype and reused: rebuilding the same bucket does not grow the heap.  Every rank must allocate the same buckets in the
-    same order (the heap hands out the same offsets on every rank); when the heap is full the bucket silently goes to
-    ordinary device memory on every rank alike (sizes are the same everywhere)."""
+    workspace (so that peers can pull them directly), or None without a workspace.  Every call hands out fresh memory: a
+    bucket that is rebuilt copies its members' values out of the old buffer, which therefore must not be recycled under
+    it.  Every rank must allocate the same buckets in the same order (the heap hands out the same offsets on every rank);
+    when the heap is full the bucket goes to ordinary device memory, on every rank alike since sizes are the same
+    everywhere.  ``tag`` only labels the allocation for debugging."""
     ws = workspace_for(group)
     if ws is None:
         return None
@@ -66,7 +67,7 @@ def heap_allocator(group: Any, tag: str) -> Optional[Any]:
         if torch.device(device) != ws.device or numel == 0:
             return torch.empty(numel, dtype=dtype, device=device)
         try:
-            return ws.scratch(f"{tag}:{numel}", (numel,), dtype)
+            return ws.alloc_tensor((numel,), dtype)
         except MemoryError:
             return torch.empty(numel, dtype=dtype, device=device)
 

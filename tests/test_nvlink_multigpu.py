@@ -375,6 +375,60 @@ def test_persistent_kernels_survive_a_foreign_kernel_holding_sms():
     spawn_ranks(_residency_worker, 2, (), backend="nccl", timeout=300)
 
 
+def _moe_layer_worker(rank, world):
+    """MOELayer with grouped bf16 experts over the NVLink scatter / gather kernels (per-layer heap buffers, unclaimed rows
+    zeroed by the scatter) against the same layer over NCCL all-to-all: outputs and every gradient, three iterations (the
+    buffers are reused), then two forwards before the backwards (the layer must fall back to shared buffers + copies)."""
+    import os
+
+    from fairscale_b200.nn.moe import MOELayer, Top2Gate
+    from fairscale_b200.nn.moe.experts import GroupedExperts
+    from fairscale_b200.parallel import nvlink
+    from fairscale_b200.utils.failure import check_device_status
+
+    dev = torch.device("cuda", rank)
+    nvlink.enable(None, dev, staging_mb=8, heap_mb=64)
+    d, ffn, n_local, tokens = 128, 256, 2, 512
+    torch.manual_seed(1)
+    gate = Top2Gate(d, n_local * world).to(dev)
+    torch.manual_seed(2 + rank)
+    experts = GroupedExperts(n_local, d, ffn).to(dev).bfloat16()
+    moe = MOELayer(gate, experts)
+
+    def run(mode, x, seeds):
+        os.environ["FSB200_COMM"] = mode
+        moe.zero_grad()
+        xs = [x.clone().requires_grad_() for _ in seeds]
+        ys = []
+        for s, xi in zip(seeds, xs):
+            torch.manual_seed(s)  # the gate draws its second-expert noise from the global generator
+            ys.append(moe(xi))
+        for y in ys:
+            (y.float().pow(2).mean() + moe.l_aux.float()).backward()
+        grads = [p.grad.float().clone() for p in moe.parameters()]
+        return [y.detach().float() for y in ys], [xi.grad.float() for xi in xs], grads
+
+    def close(a, b):
+        assert float((a - b).norm() / b.norm().clamp_min(1e-6)) < 2e-2
+
+    for it in range(3):
+        torch.manual_seed(100 + 10 * it + rank)
+        x = torch.randn(4, tokens // 4, d, device=dev).bfloat16()
+        for seeds in ([7 + it], [20 + it, 30 + it]):
+            fused, ref = run("fused", x, seeds), run("nccl", x, seeds)
+            for group_f, group_r in zip(fused, ref):
+                for a, b in zip(group_f, group_r):
+                    close(a, b)
+    os.environ["FSB200_COMM"] = "fused"
+    assert moe._heap_buffers.outstanding == 0 and not moe._heap_buffers.full
+    check_device_status(dev)
+    dist.barrier()
+
+
+def test_moe_layer_over_nvlink_matches_all_to_all():
+    spawn_ranks(_moe_layer_worker, 2, (), backend="nccl", timeout=300)
+
+
 def test_fused_tp_kernels():
     n = min(torch.cuda.device_count(), 8)
     spawn_ranks(_fused_tp_worker, 2 if n < 4 else (4 if n < 8 else 8), (), backend="nccl", timeout=300)
