@@ -167,8 +167,14 @@ class ParallelEmbedding(torch.nn.Module):
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
         input_parallel = copy_to_model_parallel_region(input_)
-        local = F.embedding(input_parallel, self.weight, self.padding_idx, self.max_norm, self.norm_type,
-                            self.scale_grad_by_freq, self.sparse)
+        plain = self.padding_idx is None and self.max_norm is None and not self.scale_grad_by_freq and not self.sparse
+        if plain and input_.is_cuda and self.weight.dtype == torch.bfloat16 and self.embedding_dim_per_partition % 8 == 0:
+            from ...ops.embedding import embedding
+
+            local = embedding(input_parallel, self.weight)  # native gather kernel; its backward scatters into the slice
+        else:
+            local = F.embedding(input_parallel, self.weight, self.padding_idx, self.max_norm, self.norm_type,
+                                self.scale_grad_by_freq, self.sparse)
         return gather_from_model_parallel_region(local)
 
 

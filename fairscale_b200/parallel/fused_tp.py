@@ -268,6 +268,14 @@ def _reduce_scatter_rows(x: torch.Tensor, group: Any) -> torch.Tensor:
     return out
 
 
+def _plain_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The local product of the unfused routes: the library's own tcgen05 GEMM for bf16 on the GPU (no autograd here, the
+    callers are autograd functions), ``F.linear`` for everything else (CPU, other dtypes)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+        return gemm_ops.linear_forward(x, w, bias)[0]
+    return F.linear(x, w, bias)
+
+
 # ---------------------------------------------------------------------------------------------- autograd
 class _AllGatherLinear(torch.autograd.Function):
     @staticmethod
@@ -279,7 +287,7 @@ class _AllGatherLinear(torch.autograd.Function):
             ctx.fused = True
         else:
             gathered = _all_gather_rows(x, group)
-            y = F.linear(gathered, w, bias)
+            y = _plain_linear(gathered, w, bias)
             ctx.fused = False
         ctx.save_for_backward(gathered, w)
         ctx.has_bias = bias is not None
@@ -312,7 +320,7 @@ class _LinearReduceScatter(torch.autograd.Function):
             out = gemm_rs(ws, x, w, bias)
             ctx.fused = True
         else:
-            out = _reduce_scatter_rows(F.linear(x, w), group)
+            out = _reduce_scatter_rows(_plain_linear(x, w), group)
             if bias is not None:
                 out = out + bias
             ctx.fused = False
@@ -375,7 +383,7 @@ class _LinearAllReduce(torch.autograd.Function):
         if world > 1 and x.shape[0] % world == 0 and gemm_rs_supported(ws, x.shape[0], x.shape[1], w.shape[0]):
             y = _all_gather_rows(gemm_rs(ws, x, w, bias), group)
         else:
-            y = F.linear(x, w)
+            y = _plain_linear(x, w)
             if world > 1:
                 comm.all_reduce(y, group=group)
             if bias is not None:

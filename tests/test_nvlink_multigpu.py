@@ -399,12 +399,13 @@ def _moe_layer_worker(rank, world):
         os.environ["FSB200_COMM"] = mode
         moe.zero_grad()
         xs = [x.clone().requires_grad_() for _ in seeds]
-        ys = []
+        ys, aux = [], []
         for s, xi in zip(seeds, xs):
             torch.manual_seed(s)  # the gate draws its second-expert noise from the global generator
             ys.append(moe(xi))
-        for y in ys:
-            (y.float().pow(2).mean() + moe.l_aux.float()).backward()
+            aux.append(moe.l_aux)
+        for y, la in zip(ys, aux):
+            (y.float().pow(2).mean() + la.float()).backward()
         grads = [p.grad.float().clone() for p in moe.parameters()]
         return [y.detach().float() for y in ys], [xi.grad.float() for xi in xs], grads
 
