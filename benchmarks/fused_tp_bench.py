@@ -37,6 +37,7 @@ def _time(fn, iters, flush):
         dist.barrier()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(3_000_000)  # ~1.5 ms of device time: the host enqueues fn() behind it, so a..b is device time only
         a.record()
         fn()
         b.record()
@@ -92,10 +93,11 @@ def main():
     flops = 2.0 * T * H * F
     nv_bytes = (world - 1) / world * T * H * 2
     ideal_us = max(flops / (peak * 1e12), nv_bytes / 770e9) * 1e6
-    for name, fused, unfused in (("ag_gemm", lambda: fused_tp.ag_gemm(ws, xs, w1, None), ag_unfused),
+    for name, fused, unfused in (("ag_gemm", lambda: fused_tp.ag_gemm(ws, xs, w1, None, engine="dma"), ag_unfused),
+                                 ("ag_gemm_sm_copy", lambda: fused_tp.ag_gemm(ws, xs, w1, None, engine="sm"), ag_unfused),
                                  ("gemm_rs", lambda: fused_tp.gemm_rs(ws, xa, w2, None), rs_unfused)):
         tf, tu = _time(fused, args.iters, flush), _time(unfused, args.iters, flush)
-        rows.append({"op": name, "world": world, "M": T, "N": F if name == "ag_gemm" else H, "K": H if name == "ag_gemm" else F,
+        rows.append({"op": name, "world": world, "M": T, "N": F if name.startswith("ag_gemm") else H, "K": H if name.startswith("ag_gemm") else F,
                      "fused_us": round(tf, 1), "unfused_us": round(tu, 1), "speedup": round(tu / tf, 3),
                      "fused_tflops": round(flops / tf / 1e6, 1), "roofline_us": round(ideal_us, 1),
                      "roofline_frac": round(ideal_us / tf, 3), "peak_source": src, "comm_ctas": os.environ.get("FSB200_FUSED_COMM_CTAS", "auto")})

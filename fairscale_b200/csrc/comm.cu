@@ -203,6 +203,46 @@ reduce_scatter_kernel(CommCtx c, PtrTable src, TO* __restrict__ out, long long n
   exit_barrier(c, c.channel + 1);
 }
 
+// The summation half of the copy-engine reduce-scatter: every addend already lies in this GPU's memory (src.p[q], q in rank
+// order: the own slice where the gradient was produced, the peers' slices where the copy engines put them).
+//   out[i] = (accumulate ? out[i] : 0) + scale * sum_q src_q[i]         (fp32 sum, fixed order: bitwise what the pull kernel gives)
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(COMM_THREADS, COMM_MIN_CTAS_PER_SM)
+local_sum_kernel(PtrTable src, int world, TO* __restrict__ out, long long n, float scale, int accumulate) {
+  constexpr int E = Acc8<TI>::N;
+  const long long nvec = n / E;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int g = 0; g < kMaxRanks; g += COMM_UNROLL) {
+      if (g < world) {
+        uint4 v[COMM_UNROLL];
+#pragma unroll
+        for (int q = 0; q < COMM_UNROLL; ++q)
+          if (g + q < world) v[q] = ld_peer16(reinterpret_cast<const TI*>(src.p[g + q]) + i * E);
+#pragma unroll
+        for (int q = 0; q < COMM_UNROLL; ++q)
+          if (g + q < world) Acc8<TI>::add(a, v[q]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      float r = a[e] * scale;
+      TO* o = out + i * E + e;
+      if (accumulate) r += to_f32<TO>(*o);
+      *o = from_f32<TO>(r);
+    }
+  }
+  for (long long i = nvec * E + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float a = 0.f;
+    for (int q = 0; q < world; ++q) a += to_f32<TI>(reinterpret_cast<const TI*>(src.p[q])[i]);
+    float r = a * scale;
+    if (accumulate) r += to_f32<TO>(out[i]);
+    out[i] = from_f32<TO>(r);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Reduce-scatter fused with the sharded Adam update (the gradient shard never exists in memory):
 //   g[i]  = scale * sum_p src_p[rank * n + i]                      (fp32, fixed summation order)
@@ -578,16 +618,16 @@ FSB_API int fsb_comm_stream_memops_available() { return stream_write_entry() != 
 //   phase 0 - the part of [prio_lo, prio_hi) that lies in this rank's own shard.  Enqueue it on the consumer's stream,
 //             before the consumer.
 //   phase 1 - on a side stream that waits for phase 0: the peers' parts of [prio_lo, prio_hi) with one flag store per
-//             piece, then the peers' parts of the rest, then the rest of the own shard (which may have to wait for the
+//             piece (cyclically from piece `first_piece` on, flags in sending order), then the peers' parts of the rest, then the rest of the own shard (which may have to wait for the
 //             consumer to leave the SMs).  Nothing the consumer waits for needs an SM.
 // The caller brackets the two calls with barriers (peers' shards final before / peers done reading after) on the
 // consumer's stream.  Returns -2 without stream memory operations.
 FSB_API int fsb_comm_gather_flagged_copies(int rank, int world, int phase, void* const* src, void* out, long long shard_bytes,
-                                           long long prio_lo, long long prio_hi, long long piece_bytes, unsigned int* flags,
-                                           unsigned int flag_value, cudaStream_t stream) {
+                                           long long prio_lo, long long prio_hi, long long piece_bytes, int first_piece,
+                                           unsigned int* flags, unsigned int flag_value, cudaStream_t stream) {
   const long long total = shard_bytes * world;
   if (world > fsb::kMaxRanks || rank < 0 || rank >= world || shard_bytes <= 0 || piece_bytes <= 0 || prio_lo < 0 || prio_hi > total ||
-      prio_lo > prio_hi)
+      prio_lo > prio_hi || first_piece < 0)
     return -1;
   const stream_write_fn write_u32 = stream_write_entry();
   if (write_u32 == nullptr) return -2;
@@ -606,17 +646,52 @@ FSB_API int fsb_comm_gather_flagged_copies(int rank, int world, int phase, void*
     return cudaSuccess;
   };
   if (phase == 0) return static_cast<int>(copy_range(prio_lo, prio_hi, true));
-  int piece = 0;
-  for (long long a = prio_lo; a < prio_hi; a += piece_bytes, ++piece) {
+  // pieces go out cyclically from `first_piece` on (ranks start at different pieces: they would otherwise all pull from the
+  // owner of the first bytes at once); flags are indexed in sending order
+  const int num_pieces = static_cast<int>((prio_hi - prio_lo + piece_bytes - 1) / piece_bytes);
+  for (int i = 0; i < num_pieces; ++i) {
+    const int q = (first_piece + i) % num_pieces;
+    const long long a = prio_lo + static_cast<long long>(q) * piece_bytes;
     cudaError_t e = copy_range(a, a + piece_bytes < prio_hi ? a + piece_bytes : prio_hi, false);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (write_u32(stream, reinterpret_cast<unsigned long long>(flags + piece), flag_value, 0u) != 0) return -3;
+    if (write_u32(stream, reinterpret_cast<unsigned long long>(flags + i), flag_value, 0u) != 0) return -3;
   }
   cudaError_t e = copy_range(0, prio_lo, false);
   if (e == cudaSuccess) e = copy_range(prio_hi, total, false);
   if (e == cudaSuccess) e = copy_range(0, prio_lo, true);
   if (e == cudaSuccess) e = copy_range(prio_hi, total, true);
   return static_cast<int>(e);
+}
+
+// All-gather of equal row blocks (`shard_bytes` each; block p of `out` is rank p's) whose progress a concurrently running
+// consumer follows: blocks arrive this rank's own first, then rank + 1, ... cyclically, each in pieces of `piece_bytes`, and
+// flags[k * pieces_per_block + j] = flag_value is stored in stream order once piece j of the k-th arriving block is in
+// place.  Two phases for the reason given above (copies within this GPU do not overlap a persistent kernel):
+//   phase 0 - own block + its flags, on the consumer's stream before the consumer;
+//   phase 1 - the peers' blocks on the copy engines of a side stream that waits for phase 0.
+// The caller provides the barriers around the two calls.  Returns -2 without stream memory operations.
+FSB_API int fsb_comm_gather_blocks_flagged(int rank, int world, int phase, void* const* src, void* out, long long shard_bytes,
+                                           long long piece_bytes, unsigned int* flags, unsigned int flag_value, cudaStream_t stream) {
+  if (world > fsb::kMaxRanks || rank < 0 || rank >= world || shard_bytes <= 0 || piece_bytes <= 0) return -1;
+  const stream_write_fn write_u32 = stream_write_entry();
+  if (write_u32 == nullptr) return -2;
+  const int pps = static_cast<int>((shard_bytes + piece_bytes - 1) / piece_bytes);
+  const int k_lo = phase == 0 ? 0 : 1, k_hi = phase == 0 ? 1 : world;
+  for (int k = k_lo; k < k_hi; ++k) {
+    const int p = (rank + k) % world;
+    char* dst = static_cast<char*>(out) + static_cast<long long>(p) * shard_bytes;
+    const char* from = static_cast<const char*>(src[p]);
+    for (int j = 0; j < pps; ++j) {
+      const long long a = static_cast<long long>(j) * piece_bytes;
+      const long long n = a + piece_bytes < shard_bytes ? piece_bytes : shard_bytes - a;
+      if (dst + a != from + a) {
+        cudaError_t e = cudaMemcpyAsync(dst + a, from + a, static_cast<size_t>(n), cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) return static_cast<int>(e);
+      }
+      if (write_u32(stream, reinterpret_cast<unsigned long long>(flags + k * pps + j), flag_value, 0u) != 0) return -3;
+    }
+  }
+  return 0;
 }
 
 FSB_API int fsb_comm_all_to_all(int rank, int world, unsigned epoch, int channel, void* const* pads, void* counter, void* const* src,
@@ -657,6 +732,48 @@ FSB_API int fsb_comm_reduce_scatter(int rank, int world, unsigned epoch, int cha
   if ((n * (in_dtype == FSB_F32 ? 4 : 2)) % 16) return -1;  // each rank's chunk must start 16-byte aligned
   return launch_reduce(rank, world, epoch, channel, pads, counter, src, in_dtype, out, out_dtype, n, scale, accumulate,
                        static_cast<long long>(rank) * n, 1, status, stream);
+}
+
+// Reduce-scatter with the transport on the copy engines: flag barrier (peers' gradients are final) -> one cudaMemcpyAsync
+// per peer that brings its copy of this rank's slice into `stage` ((world - 1) * n elements of in_dtype, ordinary device
+// memory) -> flag barrier (peers are done reading this rank's buffer) -> a short local kernel that sums the world addends
+// in rank order, scales, casts and accumulates exactly like the pull kernel.  While the slices travel no SM is involved, so
+// GEMMs of other streams keep the whole GPU; the sum touches the SMs for the time it takes to stream world * n elements
+// from local memory.  Uses epochs `epoch` and `epoch + 1` on `channel`.
+FSB_API int fsb_comm_reduce_scatter_dma(int rank, int world, unsigned epoch, int channel, void* const* pads, void* const* src,
+                                        int in_dtype, void* stage, void* out, int out_dtype, long long n, float scale, int accumulate,
+                                        int* status, cudaStream_t stream) {
+  using namespace fsb;
+  if (world > kMaxRanks) return -1;
+  const long long es = in_dtype == FSB_F32 ? 4 : 2;
+  if ((n * es) % 16) return -1;
+  barrier_kernel<<<1, COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch, channel, pads, nullptr, status));
+  const void* addend[kMaxRanks];
+  for (int k = 1; k < world; ++k) {
+    const int p = (rank + k) % world;  // the ring: at any moment the ranks read from different sources
+    char* dst = static_cast<char*>(stage) + static_cast<long long>(k - 1) * n * es;
+    cudaError_t e = cudaMemcpyAsync(dst, static_cast<const char*>(src[p]) + static_cast<long long>(rank) * n * es, static_cast<size_t>(n * es),
+                                    cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    addend[p] = dst;
+  }
+  addend[rank] = static_cast<const char*>(src[rank]) + static_cast<long long>(rank) * n * es;
+  barrier_kernel<<<1, COMM_THREADS, 0, stream>>>(make_ctx(rank, world, epoch + 1u, channel, pads, nullptr, status));
+  PtrTable t{};
+  for (int q = 0; q < world; ++q) t.p[q] = addend[q];
+  const int grid = comm_grid(n / 8, 148 * 4);
+#define FSB_LS(IC, IT, OC, OT)                                                                                          \
+  if (in_dtype == IC && out_dtype == OC) {                                                                              \
+    local_sum_kernel<IT, OT><<<grid, COMM_THREADS, 0, stream>>>(t, world, static_cast<OT*>(out), n, scale, accumulate); \
+    return static_cast<int>(cudaGetLastError());                                                                        \
+  }
+  FSB_LS(FSB_BF16, __nv_bfloat16, FSB_F32, float)
+  FSB_LS(FSB_BF16, __nv_bfloat16, FSB_BF16, __nv_bfloat16)
+  FSB_LS(FSB_F16, __half, FSB_F32, float)
+  FSB_LS(FSB_F16, __half, FSB_F16, __half)
+  FSB_LS(FSB_F32, float, FSB_F32, float)
+#undef FSB_LS
+  return -1;
 }
 
 // Sum of every rank's symmetric buffer bufs[p] (n elements of `dtype`) into rank `owner`'s buffer, in place and scaled; the

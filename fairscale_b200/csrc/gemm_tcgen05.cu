@@ -228,20 +228,32 @@ struct PairSmem {
 };
 
 __device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  if (p.b_ready != nullptr) {  // N-major: every M tile of the lowest outstanding weight rows first
-    tn = tile / tiles_m;
-    tm = tile - tn * tiles_m;
+  if (p.b_ready != nullptr) {  // N-major in sending order of the pieces of B: every M tile of the rows that arrive first
+    const int lin = tile / tiles_m;
+    tm = tile - lin * tiles_m;
+    // first tile that starts inside the first piece sent (rounded up: the tile before it needs the piece sent last)
+    const long long tile_bytes = static_cast<long long>(PAIR_BLOCK_N) * p.K * 2;
+    const int rot = static_cast<int>((static_cast<long long>(p.b_first_piece) * p.b_piece_bytes + tile_bytes - 1) / tile_bytes);
+    tn = (lin + rot) % tiles_n;
+  } else if (p.a_ready != nullptr) {  // M-major in arrival order of the row blocks of A, this rank's own block first
+    const int lin = tile / tiles_n;
+    tn = tile - lin * tiles_n;
+    const int rot = static_cast<int>((static_cast<long long>(p.a_first_shard) * p.a_shard_rows) / (2 * BLOCK_M));
+    tm = (lin + rot) % tiles_m;
   } else {
     tile_coords(tile, tiles_m, tiles_n, tm, tn);
   }
 }
 
-// Wait until bytes [lo, hi) of the B operand have arrived (see GemmParams::b_ready).  `upto` caches the highest piece
-// already seen.  Returns false when the wait limit ran out.
+// Wait until bytes [lo, hi) of the B operand have arrived (see GemmParams::b_ready).  Flags are raised in sending order by
+// one stream, so a raised flag vouches for every piece sent before it: `upto` caches the highest sending index seen.
+// Returns false when the wait limit ran out.
 __device__ __forceinline__ bool wait_b_pieces(const GemmParams& p, long long lo, long long hi, int& upto, volatile int* abort_flag) {
   const int first = static_cast<int>(lo / p.b_piece_bytes), last = static_cast<int>((hi - 1) / p.b_piece_bytes);
   bool waited = false;
-  for (int i = (first > upto + 1 ? first : upto + 1); i <= last; ++i) {
+  for (int q = first; q <= last; ++q) {
+    const int i = (q - p.b_first_piece + p.b_num_pieces) % p.b_num_pieces;  // sending index of piece q
+    if (i <= upto) continue;
     const uint64_t t0 = globaltimer_ns();
     unsigned int v;
     while (true) {
@@ -254,10 +266,46 @@ __device__ __forceinline__ bool wait_b_pieces(const GemmParams& p, long long lo,
       }
       __nanosleep(200);
     }
+    upto = i;
     waited = true;
   }
-  if (last > upto) upto = last;
   if (waited) asm volatile("fence.proxy.async;" ::: "memory");  // the arrived bytes before this thread's TMA reads of them
+  return true;
+}
+
+// Wait until rows [r0, r1) of the A operand have arrived (see GemmParams::a_ready).  Flags are raised in index order by
+// one stream, so a raised flag vouches for every lower index: `upto` caches the highest index seen.
+__device__ __forceinline__ bool wait_a_rows(const GemmParams& p, int r0, int r1, int& upto, volatile int* abort_flag) {
+  const int pps = (p.a_shard_rows + p.a_piece_rows - 1) / p.a_piece_rows;
+  bool waited = false;
+  int r = r0;
+  while (r < r1) {
+    const int shard = r / p.a_shard_rows, in_shard = r - shard * p.a_shard_rows;
+    const int k = (shard - p.a_first_shard + p.a_num_shards) % p.a_num_shards;
+    const int j = in_shard / p.a_piece_rows;
+    const int idx = k * pps + j;
+    if (idx > upto) {
+      const uint64_t t0 = globaltimer_ns();
+      unsigned int v;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.a_ready + idx) : "memory");
+        if (static_cast<int>(v - p.a_ready_epoch) >= 0) break;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > p.b_wait_ns) {
+          if (*abort_flag == 0) *abort_flag = 11;
+          return false;
+        }
+        __nanosleep(200);
+      }
+      upto = idx;
+      waited = true;
+    }
+    int next = shard * p.a_shard_rows + (j + 1) * p.a_piece_rows;  // first row of the next piece
+    const int shard_end = (shard + 1) * p.a_shard_rows;
+    if (next > shard_end) next = shard_end;
+    r = next;
+  }
+  if (waited) asm volatile("fence.proxy.async;" ::: "memory");  // the arrived rows before this thread's TMA reads of them
   return true;
 }
 
@@ -313,7 +361,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       // The first piece of B arrives only after every peer has entered the gather, which can be long after this kernel
       // started (rank skew).  Wait for it here, under the long limit, before any of the pipeline's short waits counts.
       int upto = -1;
-      wait_b_pieces(p, 0, 1, upto, abort_flag);
+      const long long first_byte = static_cast<long long>(p.b_first_piece) * p.b_piece_bytes;
+      wait_b_pieces(p, first_byte, first_byte + 1, upto, abort_flag);
     }
   }
   if (warp == 1) {
@@ -389,6 +438,9 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
           const long long row_bytes = static_cast<long long>(p.K) * 2;
           const int n1 = n0 + PAIR_HALF_N < p.N ? n0 + PAIR_HALF_N : p.N;
           if (!wait_b_pieces(p, n0 * row_bytes, n1 * row_bytes, b_upto, abort_flag)) break;
+        }
+        if (p.a_ready != nullptr && m0 < p.M) {
+          if (!wait_a_rows(p, m0, m0 + BLOCK_M < p.M ? m0 + BLOCK_M : p.M, b_upto, abort_flag)) break;
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 4)) { ok = false; break; }
@@ -556,7 +608,9 @@ static unsigned int* next_sched_slot(int di) {
 static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
                           int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
                           int epilogue, int out_f32, int accumulate_c, int max_ctas, int* status, cudaStream_t stream,
-                          const unsigned int* b_ready, unsigned int b_ready_epoch, long long b_piece_bytes, unsigned long long b_wait_ns);
+                          const unsigned int* b_ready, unsigned int b_ready_epoch, long long b_piece_bytes, unsigned long long b_wait_ns,
+                          const unsigned int* a_ready = nullptr, int a_shard_rows = 0, int a_piece_rows = 0, int a_first_shard = 0,
+                          int a_num_shards = 0, int b_first_piece = 0);
 
 FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
                           int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
@@ -567,20 +621,39 @@ FSB_API int fsb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
 
 // C[M, N] = epilogue(A[M, K] * B^T + bias) with B ([N, K], rows contiguous: ldb == K) arriving while the kernel runs:
 // ready[i] >= ready_epoch means bytes [i * piece_bytes, (i + 1) * piece_bytes) of B are in place (see GemmParams::b_ready).
+// Pieces are sent cyclically from `first_piece` on and flags are indexed in sending order.
 // Needs the CTA-pair kernel (M, N >= 256); returns -1 otherwise.  wait_ms bounds every wait for a piece.
 FSB_API int fsb_gemm_bf16_streamed_b(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
                                      int epilogue, const unsigned int* ready, unsigned int ready_epoch, long long piece_bytes,
-                                     long long wait_ms, int* status, cudaStream_t stream) {
+                                     int first_piece, long long wait_ms, int* status, cudaStream_t stream) {
   if (M < 256 || N < 256 || ready == nullptr || piece_bytes <= 0) return -1;
   if (epilogue != fsb::EPI_NONE && epilogue != fsb::EPI_BIAS) return -1;
+  if (first_piece < 0) return -1;
   return gemm_bf16_impl(A, B, C, bias, nullptr, nullptr, M, N, K, lda, K, ldc, ldc, 0, 0, epilogue, 0, 0, 0, status, stream, ready,
-                        ready_epoch, piece_bytes, static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 30000) * 1000000ull);
+                        ready_epoch, piece_bytes, static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 30000) * 1000000ull, nullptr, 0, 0,
+                        0, 0, first_piece);
+}
+
+// C[M, N] = epilogue(A * B^T + bias) with A ([M, K], rows contiguous) arriving while the kernel runs, row block by row block
+// (see GemmParams::a_ready): the all-gather of a sequence-parallel activation consumed by the product it feeds.
+// B is [N, K] (ldb) or, with b_mn_major, [K, N].  Needs the CTA-pair kernel (M, N >= 256); returns -1 otherwise.
+FSB_API int fsb_gemm_bf16_streamed_a(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int ldb, int ldc,
+                                     int b_mn_major, int epilogue, const unsigned int* ready, unsigned int ready_epoch, int shard_rows,
+                                     int piece_rows, int first_shard, int num_shards, long long wait_ms, int* status, cudaStream_t stream) {
+  if (M < 256 || N < 256 || ready == nullptr || shard_rows <= 0 || piece_rows <= 0 || num_shards <= 0 || shard_rows * num_shards != M) return -1;
+  if (first_shard < 0 || first_shard >= num_shards) return -1;
+  if (epilogue != fsb::EPI_NONE && epilogue != fsb::EPI_BIAS && epilogue != fsb::EPI_BIAS_GELU) return -1;
+  return gemm_bf16_impl(A, B, C, bias, nullptr, nullptr, M, N, K, K, ldb, ldc, ldc, 0, b_mn_major, epilogue, 0, 0, 0, status, stream, nullptr,
+                        ready_epoch, 0, static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 30000) * 1000000ull, ready, shard_rows,
+                        piece_rows, first_shard, num_shards);
 }
 
 static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, const void* aux, void* aux_out,
                           int M, int N, int K, int lda, int ldb, int ldc, int ld_aux, int a_mn_major, int b_mn_major,
                           int epilogue, int out_f32, int accumulate_c, int max_ctas, int* status, cudaStream_t stream,
-                          const unsigned int* b_ready, unsigned int b_ready_epoch, long long b_piece_bytes, unsigned long long b_wait_ns) {
+                          const unsigned int* b_ready, unsigned int b_ready_epoch, long long b_piece_bytes, unsigned long long b_wait_ns,
+                          const unsigned int* a_ready, int a_shard_rows, int a_piece_rows, int a_first_shard, int a_num_shards,
+                          int b_first_piece) {
   using namespace fsb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -1;
@@ -608,6 +681,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.batch = 1; p.stride_c = p.stride_aux = p.stride_bias = 0;
   p.sched = nullptr;
   p.b_ready = b_ready; p.b_ready_epoch = b_ready_epoch; p.b_piece_bytes = b_piece_bytes; p.b_wait_ns = b_wait_ns;
+  p.b_num_pieces = b_piece_bytes > 0 ? static_cast<int>((static_cast<long long>(N) * K * 2 + b_piece_bytes - 1) / b_piece_bytes) : 1;
+  p.b_first_piece = b_ready != nullptr ? b_first_piece % p.b_num_pieces : 0;
+  p.a_ready = a_ready; p.a_ready_epoch = b_ready_epoch; p.a_shard_rows = a_shard_rows; p.a_piece_rows = a_piece_rows;
+  p.a_first_shard = a_first_shard; p.a_num_shards = a_num_shards;
 
   int dev = 0;
   cudaGetDevice(&dev);
@@ -626,7 +703,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
     const char* e = getenv("FSB_GEMM_PAIR");
     pair_mode = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
-  if (b_ready != nullptr && !(pair_mode == 1 && M >= 256 && N >= 256 && max_ctas == 0)) return -1;
+  if ((b_ready != nullptr || a_ready != nullptr) && !(pair_mode == 1 && M >= 256 && N >= 256 && max_ctas == 0)) return -1;
   if (pair_mode == 1 && M >= 256 && N >= 256 && max_ctas == 0) {
     // the B map's box is this CTA's 128 columns (K-major) / 64 (MN-major, unchanged)
     if (!b_mn_major && !fsb_host::encode_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, PAIR_HALF_N)) return -1;
@@ -692,7 +769,8 @@ FSB_API int fsb_gemm_bf16_batched(const void* A, const void* B, void* C, const v
   p.epilogue = epilogue; p.out_f32 = out_f32; p.accumulate_c = accumulate_c;
   p.status = status;
   p.sched = nullptr;
-  p.b_ready = nullptr; p.b_ready_epoch = 0; p.b_piece_bytes = 0; p.b_wait_ns = 0;
+  p.b_ready = nullptr; p.b_ready_epoch = 0; p.b_piece_bytes = 0; p.b_wait_ns = 0; p.b_first_piece = 0; p.b_num_pieces = 1;
+  p.a_ready = nullptr; p.a_ready_epoch = 0; p.a_shard_rows = p.a_piece_rows = p.a_first_shard = p.a_num_shards = 0;
   p.batch = batch; p.stride_c = stride_c; p.stride_aux = stride_aux > 0 ? stride_aux : stride_c; p.stride_bias = stride_bias;
   int dev = 0, num_sms = 0;
   cudaGetDevice(&dev);

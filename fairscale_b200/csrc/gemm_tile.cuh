@@ -42,11 +42,22 @@ struct GemmParams {
   // Optional arrival flags of the B operand (CTA-pair kernel, B K-major with contiguous rows): the operand is being
   // written by somebody else (copy engines gathering a sharded weight) while the kernel runs.  Bytes
   // [i * b_piece_bytes, (i + 1) * b_piece_bytes) of B are valid once b_ready[i] >= b_ready_epoch (epochs only grow).
-  // Tiles are then visited N-major, rows ascending - the order in which the pieces are sent.
+  // Pieces are sent cyclically starting with piece b_first_piece (ranks start at different pieces, so that they do not
+  // all pull from the same source at once) and flags are indexed in sending order: piece q raises
+  // b_ready[(q - b_first_piece) mod b_num_pieces].  Tiles are visited N-major in the same cyclic order.
   const unsigned int* b_ready;
   unsigned int b_ready_epoch;
   long long b_piece_bytes;
   unsigned long long b_wait_ns;
+  int b_first_piece, b_num_pieces;
+  // Optional arrival flags of the A operand (CTA-pair kernel, A K-major): A is the concatenation of `a_num_shards` row
+  // blocks of `a_shard_rows` rows that arrive block by block, block `a_first_shard` first (it is this rank's own), then
+  // the following ones cyclically, each in pieces of `a_piece_rows` rows.  Piece j of the k-th arriving block is valid
+  // once a_ready[k * pieces_per_block + j] >= a_ready_epoch; flags are raised in that order.  Tiles are visited M-major
+  // in arrival order.  Waits are bounded by b_wait_ns.
+  const unsigned int* a_ready;
+  unsigned int a_ready_epoch;
+  int a_shard_rows, a_piece_rows, a_first_shard, a_num_shards;
 };
 
 // Parameters of problem `b` of a batch (pointers advanced; everything else shared).

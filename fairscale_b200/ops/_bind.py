@@ -14,7 +14,8 @@ _DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 _SIGNATURES = {
     "fsb_gemm_bf16": [c_void_p] * 6 + [c_int] * 13 + [c_void_p, c_void_p],
-    "fsb_gemm_bf16_streamed_b": [c_void_p] * 4 + [c_int] * 6 + [c_void_p, c_uint, c_longlong, c_longlong, c_void_p, c_void_p],
+    "fsb_gemm_bf16_streamed_a": [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_uint] + [c_int] * 4 + [c_longlong, c_void_p, c_void_p],
+    "fsb_gemm_bf16_streamed_b": [c_void_p] * 4 + [c_int] * 6 + [c_void_p, c_uint, c_longlong, c_int, c_longlong, c_void_p, c_void_p],
     "fsb_adam_chunk_size": [],
     "fsb_multi_tensor_adam": [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int] + [c_float] * 8 + [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "fsb_multi_tensor_sumsq": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p],

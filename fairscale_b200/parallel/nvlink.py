@@ -41,10 +41,12 @@ def _sigs() -> None:
     S["fsb_comm_gather_ranges_dma"] = head + [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     S["fsb_comm_all_gather_cols"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_all_gather_dma"] = head + [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
-    S["fsb_comm_gather_flagged_copies"] = [c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_uint,
-                                           c_void_p]
+    S["fsb_comm_gather_flagged_copies"] = [c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_int,
+                                           c_void_p, c_uint, c_void_p]
+    S["fsb_comm_gather_blocks_flagged"] = [c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_uint, c_void_p]
     S["fsb_comm_all_to_all"] = head + [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
     S["fsb_comm_reduce_scatter"] = head + [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
+    S["fsb_comm_reduce_scatter_dma"] = head + [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_float, c_int, c_void_p, c_void_p]
     S["fsb_comm_reduce_scatter_adam"] = head + [c_void_p, c_void_p, c_int, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                  c_float, c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p, c_void_p,
                                                  c_void_p, c_void_p]
@@ -84,6 +86,8 @@ class NvlinkWorkspace:
         self._peer_cache: Dict[int, Any] = {}
         # "kernel": one kernel pulls the shards with SM-issued loads; "dma": copy engines move them between two flag barriers
         self.all_gather_engine = os.environ.get("FSB200_AG", "dma").lower()
+        self.reduce_scatter_engine = os.environ.get("FSB200_RS", "dma").lower()  # "dma": copy engines + local sum; "kernel": pull kernel
+        self._rs_stage: Dict[int, torch.Tensor] = {}  # per lane: landing buffer of the peers' slices
         self.poisoned = False  # set when a kernel gave up a wait: flags and epochs can no longer be trusted
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
@@ -284,10 +288,11 @@ class NvlinkWorkspace:
                    _bind.stream_ptr(self.device))
 
     def gather_flagged_copies(self, out: torch.Tensor, shard: torch.Tensor, first: Tuple[int, int], piece_bytes: int,
-                              flags: torch.Tensor, flag_value: int, phase: int) -> None:
+                              flags: torch.Tensor, flag_value: int, phase: int, first_piece: int = 0) -> None:
         """The copies of an all-gather of heap-resident ``shard`` into ``out``, reporting progress: elements
         ``first = [lo, hi)`` of ``out`` go first, in pieces of ``piece_bytes``, and ``flags[i] = flag_value`` is stored by
-        the driver (in stream order) once piece ``i`` is in place; the rest follows.  ``phase=0`` (on the consumer's
+        the driver (in stream order) once the ``i``-th piece sent is in place (pieces go out cyclically from ``first_piece``
+        on); the rest follows.  ``phase=0`` (on the consumer's
         stream, before the consumer) copies this rank's own part of ``first``; ``phase=1`` (on a side stream that waits
         for phase 0) moves the peers' parts on the copy engines and stores the flags, then the remainder.  No kernel is
         launched, and nothing a persistent consumer waits for needs an SM.  The caller provides the barriers around the
@@ -298,7 +303,21 @@ class NvlinkWorkspace:
         n_pieces = -(-(first[1] - first[0]) * es // piece_bytes)
         assert flags.dtype == torch.int32 and flags.numel() >= n_pieces
         _bind.call("fsb_comm_gather_flagged_copies", self.rank, self.world, phase, self.peers(off), out.data_ptr(), shard.numel() * es, first[0] * es,
-                   first[1] * es, piece_bytes, flags.data_ptr(), flag_value, _bind.stream_ptr(self.device), launches=0)
+                   first[1] * es, piece_bytes, first_piece, flags.data_ptr(), flag_value, _bind.stream_ptr(self.device), launches=0)
+
+    def gather_blocks_flagged(self, out: torch.Tensor, block: torch.Tensor, piece_bytes: int, flags: torch.Tensor, flag_value: int,
+                              phase: int) -> None:
+        """The copies of an all-gather of equal blocks (``out`` = the ranks' heap-resident ``block``s in rank order), reporting
+        progress: blocks arrive this rank's own first, then rank + 1, ... cyclically, in pieces of ``piece_bytes``, and
+        ``flags[k * pieces_per_block + j] = flag_value`` is stored by the driver once piece ``j`` of the k-th arriving block
+        is in place.  ``phase=0`` (consumer's stream): own block; ``phase=1`` (side stream waiting for phase 0): the peers'
+        blocks on the copy engines.  See :meth:`gather_flagged_copies` for why, and for who provides the barriers."""
+        off = self.offset_of(block)
+        assert off is not None, "the block must live in the symmetric heap"
+        nbytes = block.numel() * block.element_size()
+        assert flags.dtype == torch.int32 and flags.numel() >= self.world * -(-nbytes // piece_bytes)
+        _bind.call("fsb_comm_gather_blocks_flagged", self.rank, self.world, phase, self.peers(off), out.data_ptr(), nbytes, piece_bytes,
+                   flags.data_ptr(), flag_value, _bind.stream_ptr(self.device), launches=0)
 
     def gather_ranges(self, out: torch.Tensor, shard: torch.Tensor, ranges: List[Tuple[int, int]], lane: int = 1) -> None:
         """Fetch only the element ranges ``[lo, hi)`` of the gathered flat buffer ``out`` (the shards' concatenation) from
@@ -341,9 +360,24 @@ class NvlinkWorkspace:
         window = self._window_of(flat_in) if off is not None else None
         if off is None or (flat_in.numel() != n * self.world and (window is None or need > self._gw_bytes)):
             off = self._stage(ln, flat_in, need)  # local copy into the lane's staging window (zero padded)
-        _bind.call("fsb_comm_reduce_scatter", *self._head(ln), self._counter(ln), self.peers(off), _bind.dtype_code(flat_in.dtype),
-                   out.data_ptr(), _bind.dtype_code(out.dtype), n, scale, int(accumulate), _bind.status_ptr(self.device),
-                   _bind.stream_ptr(self.device))
+        es = flat_in.element_size()
+        if self.reduce_scatter_engine == "dma" and self.world > 1 and n * es >= self.DMA_MIN_BYTES:
+            # the peers' copies of this rank's slice travel on the copy engines (no SM takes part) between two flag
+            # barriers; a short local kernel then sums them in rank order
+            stage = self._rs_stage.get(ln.index)
+            want = (self.world - 1) * n * es
+            if stage is None or stage.numel() < want:
+                stage = self._rs_stage[ln.index] = torch.empty(want, dtype=torch.uint8, device=self.device)
+            head = self._head(ln)
+            ln.epoch = (ln.epoch + 1) & 0x7FFFFFFF  # the exit barrier uses the next epoch
+            _bind.call("fsb_comm_reduce_scatter_dma", *head, self.peers(off), _bind.dtype_code(flat_in.dtype), stage.data_ptr(),
+                       out.data_ptr(), _bind.dtype_code(out.dtype), n, scale, int(accumulate), _bind.status_ptr(self.device),
+                       _bind.stream_ptr(self.device), launches=3)
+            stage.record_stream(torch.cuda.current_stream(self.device))
+        else:
+            _bind.call("fsb_comm_reduce_scatter", *self._head(ln), self._counter(ln), self.peers(off), _bind.dtype_code(flat_in.dtype),
+                       out.data_ptr(), _bind.dtype_code(out.dtype), n, scale, int(accumulate), _bind.status_ptr(self.device),
+                       _bind.stream_ptr(self.device))
         if window is not None:
             self.release_grad_window(flat_in)  # the kernel's exit barrier covers the peers' reads of this window
 

@@ -42,19 +42,27 @@ def _worker(rank, world):
         got = comm.all_gather_last_dim(part, None)
         assert torch.equal(got, torch.cat(parts, dim=-1))
 
-    # reduce-scatter with fused scale + fp32 cast + accumulate, incl. implicit zero padding
+    # reduce-scatter with fused scale + fp32 cast + accumulate, incl. implicit zero padding: the pull kernel, then the
+    # copy-engine transport + local sum, which must give the same bits (same fp32 summation order)
+    min_bytes = ws.DMA_MIN_BYTES
     for n, short in ((4096, 0), (1 << 18, 0), (1 << 14, 24)):
         full = (torch.randn(n * world - short, device=dev)).bfloat16()
         padded = torch.zeros(n * world, device=dev, dtype=torch.bfloat16)
         padded[: full.numel()] = full
         ref = torch.empty(n, device=dev, dtype=torch.float32)
         dist.reduce_scatter_tensor(ref, padded.float())
-        out = torch.full((n,), 3.0, device=dev)
-        ws.reduce_scatter(out, full, scale=0.5, accumulate=True)
-        torch.testing.assert_close(out, 3.0 + 0.5 * ref, atol=2e-2, rtol=2e-2)
-        out_b = torch.empty(n, device=dev, dtype=torch.bfloat16)
-        comm.reduce_scatter_into(out_b, padded, None)
-        torch.testing.assert_close(out_b.float(), ref, atol=6e-2, rtol=3e-2)
+        outs = {}
+        for engine in ("kernel", "dma"):
+            ws.reduce_scatter_engine, ws.DMA_MIN_BYTES = engine, 0
+            out = torch.full((n,), 3.0, device=dev)
+            ws.reduce_scatter(out, full, scale=0.5, accumulate=True)
+            torch.testing.assert_close(out, 3.0 + 0.5 * ref, atol=2e-2, rtol=2e-2)
+            out_b = torch.empty(n, device=dev, dtype=torch.bfloat16)
+            comm.reduce_scatter_into(out_b, padded, None)
+            torch.testing.assert_close(out_b.float(), ref, atol=6e-2, rtol=3e-2)
+            outs[engine] = (out, out_b)
+        assert torch.equal(outs["kernel"][0], outs["dma"][0]) and torch.equal(outs["kernel"][1], outs["dma"][1])
+    ws.DMA_MIN_BYTES = min_bytes
 
     # all-reduce, several dtypes and a ragged size
     for dtype, n in ((torch.bfloat16, 1 << 20), (torch.float32, 1000003), (torch.bfloat16, 8), (torch.float16, 4100)):
@@ -121,7 +129,7 @@ def _fsdp_worker(rank, world):
         model = build_fsdp_gpt(cfg, dev, nvlink_heap=(mode == "fused"), keep_low_precision_grads=False, bucket_cap_mb=0)
         ws = symm.workspace_for(model.process_group)
         if ws is not None:
-            ws.all_gather_engine = engine
+            ws.all_gather_engine = ws.reduce_scatter_engine = engine  # both collectives by pull kernels / by the copy engines
             ws.DMA_MIN_BYTES = 0
         opt = FusedAdam(model.parameters(), lr=1e-3, weight_decay=0.01)
         model.attach_optimizer(opt, fuse_step_into_reduce_scatter=fuse_step)
@@ -172,7 +180,7 @@ def _fsdp_worker(rank, world):
     # NCCL sums the bf16 gradients in bf16, the NVLink kernels in fp32
     for name in ("nvlink-kernel", "nvlink-dma", "nvlink-rs-adam"):
         same_training(name, "nccl", 2e-3, 0.05, 2e-2)
-    # the two all-gather engines move the same bytes: identical results
+    # the two transports move the same bytes and sum in the same order: identical results
     for k in ref_full:
         assert torch.equal(results["nvlink-kernel"][1][k], results["nvlink-dma"][1][k]), k
     # the fused reduce-scatter + Adam kernel follows the formulas of reduce-scatter followed by the Adam kernel; the two are
@@ -287,13 +295,19 @@ def _fused_tp_worker(rank, world):
         b = torch.randn(N, device=dev).bfloat16()
         full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
         dist.all_gather_into_tensor(full, x)
-        for _ in range(2):  # twice: epochs and monotonic counters must carry over
-            y, gathered = fused_tp.ag_gemm(ws, x, w, b)
-            torch.testing.assert_close(gathered, full)
-            torch.testing.assert_close(y.float(), full.float() @ w.float().t() + b.float(), atol=3e-2, rtol=3e-2)
-        wkn = w.t().contiguous()  # [K, N] storage
-        y2, _ = fused_tp.ag_gemm(ws, x, wkn, None, w_is_kn=True)
-        torch.testing.assert_close(y2.float(), full.float() @ w.float().t(), atol=3e-2, rtol=3e-2)
+        # copy CTAs inside the GEMM launch, then the copy-engine transport with arrival flags (one piece per block, then
+        # 128-row pieces); twice each: epochs and monotonic counters must carry over
+        for engine, piece in (("sm", None), ("dma", 4 << 20), ("dma", 128 * K * 2)):
+            if piece is not None:
+                fused_tp.AG_PIECE_BYTES = piece
+            for _ in range(2):
+                y, gathered = fused_tp.ag_gemm(ws, x, w, b, engine=engine)
+                torch.testing.assert_close(gathered, full)
+                torch.testing.assert_close(y.float(), full.float() @ w.float().t() + b.float(), atol=3e-2, rtol=3e-2)
+            wkn = w.t().contiguous()  # [K, N] storage
+            y2, _ = fused_tp.ag_gemm(ws, x, wkn, None, w_is_kn=True, engine=engine)
+            torch.testing.assert_close(y2.float(), full.float() @ w.float().t(), atol=3e-2, rtol=3e-2)
+        fused_tp.AG_PIECE_BYTES = 4 << 20
 
         xa = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
         partial = xa.float() @ w.float().t()
