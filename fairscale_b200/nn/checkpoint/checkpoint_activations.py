@@ -31,6 +31,7 @@ class _Flags(threading.local):
         self.is_checkpointing = False
         self.is_recomputing = False
         self.is_checkpointing_disabled = False
+        self.region_owners: List[Any] = []
 
 
 thread_local = _Flags()
@@ -44,6 +45,18 @@ def _flag(name: str, value: bool = True) -> Generator[None, None, None]:
         yield
     finally:
         setattr(thread_local, name, prev)
+
+
+@contextmanager
+def owning_checkpointed_regions(owner: Any) -> Generator[None, None, None]:
+    """While this context is active, every checkpointed region that starts a forward is counted in
+    ``owner._ckpt_outstanding`` until its backward (recomputation included) has run.  A parameter-sharding wrapper uses the
+    count to keep its full parameters until the last region that will recompute with them is done."""
+    thread_local.region_owners.append(owner)
+    try:
+        yield
+    finally:
+        thread_local.region_owners.pop()
 
 
 def disable_checkpointing() -> Any:
@@ -179,6 +192,22 @@ def autocast(enabled: bool) -> Generator:
         yield
 
 
+def _has_trainable_weights(module: nn.Module) -> bool:
+    """True if ``module`` or a sub-module holds a weight that requires grad: an ``nn.Parameter``, or - under a flattening
+    wrapper, which replaces parameters by plain tensor attributes that are views of its flat parameter - such a view.  The
+    wrapper records its views on the module it wraps (``_unflattened_param_views``); a checkpointed sub-module of that module
+    only sees them as attributes, so those are looked at as well."""
+    if any(p.requires_grad for p in module.parameters()):
+        return True
+    if any(v.requires_grad for v in getattr(module, "_unflattened_param_views", [])):
+        return True
+    for m in module.modules():
+        for v in vars(m).values():
+            if isinstance(v, torch.Tensor) and v.requires_grad:
+                return True
+    return False
+
+
 class CheckpointFunction(torch.autograd.Function):
     """Autograd node that runs ``run_function`` without grad and replays it in backward.
 
@@ -196,6 +225,9 @@ class CheckpointFunction(torch.autograd.Function):
         *args: Any,
     ) -> Any:
         torch_checkpoint.check_backward_validity(args)
+        ctx.region_owner = thread_local.region_owners[-1] if thread_local.region_owners else None
+        if ctx.region_owner is not None:
+            ctx.region_owner._ckpt_outstanding = getattr(ctx.region_owner, "_ckpt_outstanding", 0) + 1
         ctx.run_function = run_function
         ctx.kwarg_keys = kwarg_keys
         ctx.fwd_rng_state = get_rng_state()
@@ -218,11 +250,8 @@ class CheckpointFunction(torch.autograd.Function):
             outputs = run_function(*f_args, **f_kwargs)
             the_module = f_args[0]
 
-        # flattened modules expose their weights as plain views, not nn.Parameters
-        params: List[Any] = list(the_module.parameters())
-        params += getattr(the_module, "_unflattened_param_views", [])
         grad_src = ctx.grad_requirements if ctx.grad_requirements is not None else [t.requires_grad for t in tensor_inputs]
-        parent_ctx_dict["output_requires_grad"] = any(p.requires_grad for p in params) or any(grad_src)
+        parent_ctx_dict["output_requires_grad"] = _has_trainable_weights(the_module) or any(grad_src)
 
         if not isinstance(outputs, torch.Tensor):
             outputs, packed_outputs = split_non_tensors(outputs)
@@ -233,7 +262,15 @@ class CheckpointFunction(torch.autograd.Function):
     def backward(ctx: Any, *grads: Any) -> Tuple[Optional[Tensor], ...]:
         if not torch.autograd._is_checkpoint_valid():
             raise RuntimeError("Checkpointing is not compatible with .grad(), please use .backward() if possible")
+        try:
+            return CheckpointFunction._replay(ctx, *grads)
+        finally:
+            owner = ctx.region_owner
+            if owner is not None and getattr(owner, "_ckpt_outstanding", 0) > 0:
+                owner._ckpt_outstanding -= 1
 
+    @staticmethod
+    def _replay(ctx: Any, *grads: Any) -> Tuple[Optional[Tensor], ...]:
         saved: Tuple[Tensor, ...] = ctx.saved_tensors
         if ctx.fwd_device is not None:
             restored = []

@@ -70,6 +70,7 @@ from ...internal.reduce_scatter_bucketer import ReduceScatterBucketer
 from ...internal.state_dict import replace_by_prefix_
 from ...ops.cast import cast_into
 from ...parallel import comm, symm
+from ..checkpoint.checkpoint_activations import owning_checkpointed_regions
 from ...utils.failure import poll_device_status
 from ...utils.profiling import comm_range
 from ..misc import flatten_params_wrapper as _fpw
@@ -920,7 +921,8 @@ class FullyShardedDataParallel(nn.Module):
             self._allow_deferred_gather = False
         self._register_post_backward_hooks()
         self._prefetch_next_unit()
-        outputs = self.module(*args, **kwargs)
+        with owning_checkpointed_regions(self):
+            outputs = self.module(*args, **kwargs)
         self._finish_deferred_gathers()
 
         if self.reshard_after_forward:
@@ -1086,6 +1088,14 @@ class FullyShardedDataParallel(nn.Module):
             return
         if param.grad.requires_grad:
             raise RuntimeError("FSDP only works with gradients that don't require gradients")
+        if getattr(self, "_ckpt_outstanding", 0) >= 2:
+            # Checkpointed regions directly inside this unit (several of them, or one that was called several times) each
+            # run their own backward, and each accumulates into this parameter's gradient and lands here.  The ones still
+            # to come recompute their forward with the full parameters: keep them, and keep accumulating, until the last
+            # (the count includes the region whose backward is running now).
+            param._reduce_deferred = True  # type: ignore[attr-defined]
+            return
+        param._reduce_deferred = False  # type: ignore[attr-defined]
 
         if self._require_backward_grad_sync or self.reshard_after_forward:
             self._free_full_params([param])
@@ -1224,6 +1234,12 @@ class FullyShardedDataParallel(nn.Module):
         else:
             self.assert_state(TrainingState.BACKWARD_PRE)
 
+        for m in get_fsdp_instances(self):
+            # a count left over (a checkpointed forward whose backward never ran) must not keep gradients from being reduced
+            m._ckpt_outstanding = 0
+            for p in m.params:
+                if getattr(p, "_reduce_deferred", False):
+                    m._post_backward_hook(p)
         if self._require_backward_grad_sync:
             with _on_stream(self._streams["post_backward"]):
                 p_assert(self._reducer is not None, "WFPB: reducer is None")
@@ -1245,6 +1261,14 @@ class FullyShardedDataParallel(nn.Module):
                 # a unit whose parameters took no part in this backward never ran its post hook
                 m._free_full_params()
                 m._use_fp32_param_shard()
+            elif self._require_backward_grad_sync:
+                # the root keeps its parameters after forward; those without a gradient (frozen, or unused in this step)
+                # never ran the post hook that shards them again
+                stale = [p for p in m.params if p._is_sharded and p.data.shape == p._orig_size  # type: ignore[attr-defined]
+                         and p._orig_size != p._fp32_shard.shape]  # type: ignore[attr-defined]
+                if stale:
+                    m._free_full_params(stale)
+                    m._use_fp32_param_shard(stale)
             for p in m.params:
                 if not p.requires_grad or not self._require_backward_grad_sync:
                     continue

@@ -437,7 +437,7 @@ class _LinearAllReduce(torch.autograd.Function):
     def backward(ctx: Any, dy: torch.Tensor) -> Any:  # type: ignore[override]
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
-        dx = dy @ w if ctx.needs_input_grad[0] else None
+        dx = gemm_ops.linear_dgrad(dy, w) if ctx.needs_input_grad[0] else None  # tcgen05 GEMM on the GPU, matmul elsewhere
         dw = gemm_ops.linear_wgrad(dy, x).to(w.dtype) if ctx.needs_input_grad[1] else None
         db = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
