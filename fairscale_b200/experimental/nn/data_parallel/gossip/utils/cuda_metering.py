@@ -1,23 +1,36 @@
-"""Named CUDA-event timers with a mean / std report (parity: .../gossip/utils/cuda_metering.py:27-115)."""
+"""Named CUDA-event timers with a mean / std report (interface of .../gossip/utils/cuda_metering.py:27-115).
+
+A recorder stamps a start event when it is created and an end event on ``stop()``.  Nothing synchronises in the training
+loop: elapsed times are resolved only when a report is asked for.  Recorders are kept in two registries of bounded
+length per name - one that ``reset()`` empties (``event_recorders``) and one that covers the whole run
+(``all_event_recorders``).
+"""
 
 from __future__ import annotations
 
 from abc import ABC, abstractmethod
 from collections import defaultdict, deque
-from functools import partial
 import statistics
 from typing import ClassVar, Deque, Dict, Optional
 
 import torch
 
 MAX_LEN_DEQUEUE = 10**4
-deque_with_max_len_fixed = partial(deque, maxlen=MAX_LEN_DEQUEUE)
+
+
+def deque_with_max_len_fixed() -> "Deque[CudaEventRecorder]":
+    return deque(maxlen=MAX_LEN_DEQUEUE)
+
+
+def _registry() -> "Dict[str, Deque[CudaEventRecorder]]":
+    return defaultdict(deque_with_max_len_fixed)
 
 
 def create_and_record_event() -> torch.cuda.Event:
-    ev = torch.cuda.Event(enable_timing=True)
-    ev.record()
-    return ev
+    """A timing event stamped on the current stream."""
+    stamp = torch.cuda.Event(enable_timing=True)
+    stamp.record()
+    return stamp
 
 
 class EventRecorder(ABC):
@@ -26,28 +39,29 @@ class EventRecorder(ABC):
         ...
 
 
-def create_event_recorder(event_name: str, dummy: bool = False) -> EventRecorder:
-    return DummyCudaEventRecorder() if dummy or not torch.cuda.is_available() else CudaEventRecorder(event_name)
+class DummyCudaEventRecorder(EventRecorder):
+    """Stands in where timing is off or there is no GPU."""
+
+    def stop(self) -> None:
+        return None
 
 
 class CudaEventRecorder(EventRecorder):
-    """Records a start event when created and an end event on ``stop()``; elapsed times are resolved lazily (no
-    synchronisation in the training loop) when a report is requested."""
-
-    event_recorders: ClassVar[Dict[str, Deque["CudaEventRecorder"]]] = defaultdict(deque_with_max_len_fixed)  # type: ignore[arg-type]
-    all_event_recorders: ClassVar[Dict[str, Deque["CudaEventRecorder"]]] = defaultdict(deque_with_max_len_fixed)  # type: ignore[arg-type]
+    event_recorders: ClassVar[Dict[str, Deque["CudaEventRecorder"]]] = _registry()
+    all_event_recorders: ClassVar[Dict[str, Deque["CudaEventRecorder"]]] = _registry()
 
     def __init__(self, event_name: str) -> None:
         self.event_name = event_name
         self.start_event = create_and_record_event()
         self.end_event: Optional[torch.cuda.Event] = None
-        CudaEventRecorder.event_recorders[event_name].append(self)
-        CudaEventRecorder.all_event_recorders[event_name].append(self)
+        for registry in (CudaEventRecorder.event_recorders, CudaEventRecorder.all_event_recorders):
+            registry[event_name].append(self)
 
     def stop(self) -> None:
         self.end_event = create_and_record_event()
 
     def find_time_elapsed(self) -> float:
+        """Milliseconds between creation and ``stop()``; waits for the end event."""
         if self.end_event is None:
             raise Exception(f"stopEvent was not called for event with name {self.event_name}")
         self.end_event.synchronize()
@@ -55,16 +69,18 @@ class CudaEventRecorder(EventRecorder):
 
     @classmethod
     def reset(cls) -> None:
-        cls.event_recorders = defaultdict(deque_with_max_len_fixed)  # type: ignore[arg-type]
+        cls.event_recorders = _registry()
+
+    @staticmethod
+    def _line(name: str, recorders: "Deque[CudaEventRecorder]") -> str:
+        ms = [r.find_time_elapsed() for r in recorders]
+        spread = statistics.pstdev(ms) if len(ms) > 1 else 0.0
+        return f"{name} = {statistics.mean(ms)} +/- {spread}"
 
     @classmethod
     def get_common_timings(cls, event_recorders: Dict[str, Deque["CudaEventRecorder"]], description: str) -> str:
-        lines = [f"{description}:"]
-        for name in sorted(event_recorders):
-            times = [r.find_time_elapsed() for r in event_recorders[name]]
-            std = statistics.pstdev(times) if len(times) > 1 else 0.0
-            lines.append(f"{name} = {statistics.mean(times)} +/- {std}")
-        return "\n".join(lines) + "\n"
+        body = [cls._line(name, event_recorders[name]) for name in sorted(event_recorders)]
+        return "\n".join([f"{description}:"] + body) + "\n"
 
     @classmethod
     def get_all_timings(cls) -> str:
@@ -74,11 +90,10 @@ class CudaEventRecorder(EventRecorder):
     @classmethod
     def get_timings(cls) -> str:
         """Report since the last ``reset()`` followed by the report over the whole run."""
-        out = cls.get_common_timings(cls.event_recorders, "Timings since last reset")
-        out += cls.get_common_timings(cls.all_event_recorders, "All timings")
-        return out
+        return cls.get_common_timings(cls.event_recorders, "Timings since last reset") + cls.get_all_timings()
 
 
-class DummyCudaEventRecorder(EventRecorder):
-    def stop(self) -> None:
-        pass
+def create_event_recorder(event_name: str, dummy: bool = False) -> EventRecorder:
+    if dummy or not torch.cuda.is_available():
+        return DummyCudaEventRecorder()
+    return CudaEventRecorder(event_name)

@@ -1,33 +1,30 @@
-"""state_dict key utilities (parity: fairscale/internal/state_dict.py:16-75)."""
+"""state_dict key utilities (interface of fairscale/internal/state_dict.py:16-75)."""
 
 from __future__ import annotations
 
-from typing import TYPE_CHECKING, Dict, List, Tuple, Type, Union
+from typing import TYPE_CHECKING, Dict, Iterator, List, Tuple, Type, Union
 
-import torch
 from torch import Tensor, nn
 
 if TYPE_CHECKING:
     from collections import OrderedDict
 
 
-def find_module_instances(module: nn.Module, search_class: Type[nn.Module]) -> List[Tuple[str, nn.Module]]:
-    """Return ``(state_dict_prefix, instance)`` for each ``search_class`` instance under ``module``.
+def _walk(module: nn.Module, prefix: str = "") -> Iterator[Tuple[str, nn.Module]]:
+    """Depth-first, parents before children, with the state-dict prefix of every module (``""`` for the root, otherwise
+    ending in a dot)."""
+    yield prefix, module
+    for name, child in module.named_children():
+        yield from _walk(child, f"{prefix}{name}.")
 
-    Prefixes end with ``"."`` (or are empty for the root) and follow the key names the
-    module tree produces *after* wrapper prefixes were cleaned, which is what
+
+def find_module_instances(module: nn.Module, search_class: Type[nn.Module]) -> List[Tuple[str, nn.Module]]:
+    """``(state_dict_prefix, instance)`` for each ``search_class`` instance under ``module`` (itself included).
+
+    The prefixes are those of the keys the module tree produces once wrapper prefixes have been cleaned, which is what
     state-dict hooks need.
     """
-    found: List[Tuple[str, nn.Module]] = []
-
-    def visit(mod: nn.Module, prefix: str) -> None:
-        if isinstance(mod, search_class):
-            found.append((prefix, mod))
-        for name, child in mod.named_children():
-            visit(child, f"{prefix}{name}.")
-
-    visit(module, "")
-    return found
+    return [(prefix, m) for prefix, m in _walk(module) if isinstance(m, search_class)]
 
 
 def replace_by_prefix_(
@@ -36,6 +33,6 @@ def replace_by_prefix_(
     """Rename, in place, every key starting with ``old_prefix`` to start with ``new_prefix``."""
     if old_prefix == new_prefix:
         raise ValueError("old_prefix and new_prefix must be distinct")
-    for key in list(state_dict.keys()):
-        if key.startswith(old_prefix):
-            state_dict[new_prefix + key[len(old_prefix):]] = state_dict.pop(key)
+    cut = len(old_prefix)
+    for key in [k for k in state_dict if k.startswith(old_prefix)]:
+        state_dict[new_prefix + key[cut:]] = state_dict.pop(key)

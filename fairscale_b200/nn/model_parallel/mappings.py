@@ -1,16 +1,18 @@
 """Autograd-aware collectives between "replicated" and "tensor-parallel" regions.
 
-Parity: fairscale/nn/model_parallel/mappings.py:30-156 (the Megatron f / g operators and the
-scatter / gather pair).  Collectives go through :mod:`fairscale_b200.parallel.comm`, i.e. the NVLink
-kernels when a symmetric workspace exists for the model-parallel group and NCCL / gloo otherwise.
-The gather along the last dimension is :func:`fairscale_b200.parallel.comm.all_gather_last_dim`: over NVLink the pulling
-kernel writes every rank's slice straight into its column window of the output; over NCCL / gloo it is one all-gather
-along a leading axis plus one transposing copy (the reference uses ``all_gather`` into a list + ``torch.cat``).
+Behaviour of fairscale/nn/model_parallel/mappings.py:30-156 (the Megatron f / g operators and the scatter / gather
+pair), built from one table: each region operator is a (forward primitive, backward primitive) pair out of the three
+primitives ``identity``, ``sum over the group``, ``slice / concatenate the last dimension``, and one generic autograd
+function applies a pair.  Collectives go through :mod:`fairscale_b200.parallel.comm`, i.e. the NVLink kernels when a
+symmetric workspace exists for the model-parallel group and NCCL / gloo otherwise.  The gather along the last dimension
+is :func:`fairscale_b200.parallel.comm.all_gather_last_dim`: over NVLink the pulling kernel writes every rank's slice
+straight into its column window of the output; over NCCL / gloo it is one all-gather along a leading axis plus one
+transposing copy (the reference uses ``all_gather`` into a list + ``torch.cat``).
 """
 
 from __future__ import annotations
 
-from typing import Any
+from typing import Any, Callable, Dict, Tuple
 
 import torch
 import torch.distributed as dist
@@ -19,95 +21,88 @@ from ...parallel import comm
 from .initialize import get_model_parallel_group
 from .utils import split_tensor_along_last_dim
 
+Primitive = Callable[[torch.Tensor], torch.Tensor]
 
-def _reduce(ctx: Any, input_: torch.Tensor) -> torch.Tensor:
-    """In-place sum over the model-parallel group."""
+
+def _group_and_size() -> Tuple[Any, int]:
     group = get_model_parallel_group()
-    if ctx is not None:
-        ctx.mark_dirty(input_)
-    if dist.get_world_size(group=group) == 1:
-        return input_
-    comm.all_reduce(input_, group=group)
-    return input_
+    return group, dist.get_world_size(group=group)
 
 
-def _split(input_: torch.Tensor) -> torch.Tensor:
-    """Keep this rank's slice of the last dimension."""
-    group = get_model_parallel_group()
-    world = dist.get_world_size(group=group)
+# ---------------------------------------------------------------------------------------------------------- primitives
+def _identity(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def _sum_over_group(t: torch.Tensor) -> torch.Tensor:
+    """In place: every rank ends up with the sum."""
+    group, world = _group_and_size()
+    if world > 1:
+        comm.all_reduce(t, group=group)
+    return t
+
+
+def _own_slice(t: torch.Tensor) -> torch.Tensor:
+    """This rank's slice of the last dimension."""
+    group, world = _group_and_size()
     if world == 1:
-        return input_
-    return split_tensor_along_last_dim(input_, world)[dist.get_rank(group=group)].contiguous()
+        return t
+    return split_tensor_along_last_dim(t, world)[dist.get_rank(group=group)].contiguous()
 
 
-def _gather(input_: torch.Tensor) -> torch.Tensor:
-    """Concatenate every rank's tensor along the last dimension."""
-    group = get_model_parallel_group()
-    world = dist.get_world_size(group=group)
+def _concat_slices(t: torch.Tensor) -> torch.Tensor:
+    """Every rank's tensor side by side along the last dimension."""
+    group, world = _group_and_size()
     if world == 1:
-        return input_
-    return comm.all_gather_last_dim(input_, group=group)
+        return t
+    return comm.all_gather_last_dim(t, group=group)
 
 
-class _CopyToModelParallelRegion(torch.autograd.Function):
-    """Identity forward, all-reduce backward (Megatron's ``f``)."""
+# the names the reference's helpers go by
+_reduce = lambda ctx, t: _sum_over_group(t)  # noqa: E731
+_split = _own_slice
+_gather = _concat_slices
 
-    @staticmethod
-    def forward(ctx, input_):  # type: ignore[override]
-        return input_
+# operator -> (forward, backward, forward works in place)
+_REGION_OPS: Dict[str, Tuple[Primitive, Primitive, bool]] = {
+    "copy": (_identity, _sum_over_group, False),      # f: replicated activations enter a parallel region
+    "reduce": (_sum_over_group, _identity, True),     # g: partial results leave it
+    "scatter": (_own_slice, _concat_slices, False),
+    "gather": (_concat_slices, _own_slice, False),
+}
 
-    @staticmethod
-    def backward(ctx, grad_output):  # type: ignore[override]
-        return _reduce(None, grad_output)
 
-
-class _ReduceFromModelParallelRegion(torch.autograd.Function):
-    """All-reduce forward, identity backward (Megatron's ``g``)."""
-
-    @staticmethod
-    def forward(ctx, input_):  # type: ignore[override]
-        return _reduce(ctx, input_)
+class _RegionOp(torch.autograd.Function):
+    """Applies the forward primitive of ``kind``; its backward applies the paired primitive to the gradient."""
 
     @staticmethod
-    def backward(ctx, grad_output):  # type: ignore[override]
-        return grad_output
-
-
-class _ScatterToModelParallelRegion(torch.autograd.Function):
-    """Slice forward, gather backward."""
-
-    @staticmethod
-    def forward(ctx, input_):  # type: ignore[override]
-        return _split(input_)
+    def forward(ctx: Any, kind: str, t: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
+        fwd, _, in_place = _REGION_OPS[kind]
+        ctx.kind = kind
+        if in_place:
+            ctx.mark_dirty(t)
+        return fwd(t)
 
     @staticmethod
-    def backward(ctx, grad_output):  # type: ignore[override]
-        return _gather(grad_output)
-
-
-class _GatherFromModelParallelRegion(torch.autograd.Function):
-    """Gather forward, slice backward."""
-
-    @staticmethod
-    def forward(ctx, input_):  # type: ignore[override]
-        return _gather(input_)
-
-    @staticmethod
-    def backward(ctx, grad_output):  # type: ignore[override]
-        return _split(grad_output)
+    def backward(ctx: Any, grad: torch.Tensor) -> Tuple[None, torch.Tensor]:  # type: ignore[override]
+        return None, _REGION_OPS[ctx.kind][1](grad)
 
 
 def copy_to_model_parallel_region(input_: torch.Tensor) -> torch.Tensor:
-    return _CopyToModelParallelRegion.apply(input_)
+    """Identity forward, all-reduce backward (Megatron's ``f``)."""
+    return _RegionOp.apply("copy", input_)
 
 
 def reduce_from_model_parallel_region(input_: torch.Tensor) -> torch.Tensor:
-    return _ReduceFromModelParallelRegion.apply(input_)
+    """All-reduce forward (in place), identity backward (Megatron's ``g``)."""
+    return _RegionOp.apply("reduce", input_)
 
 
 def scatter_to_model_parallel_region(input_: torch.Tensor) -> torch.Tensor:
-    return _ScatterToModelParallelRegion.apply(input_)
+    """Slice of the last dimension forward, gather backward."""
+    return _RegionOp.apply("scatter", input_)
 
 
 def gather_from_model_parallel_region(input_: torch.Tensor) -> torch.Tensor:
-    return _GatherFromModelParallelRegion.apply(input_)
+    """Gather along the last dimension forward, slice backward."""
+    return _RegionOp.apply("gather", input_)
