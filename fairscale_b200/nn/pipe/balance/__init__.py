@@ -18,18 +18,22 @@ TensorOrTensors = Union[Tensor, Tensors]
 
 
 def balance_cost(cost: List[int], partitions: int) -> List[int]:
-    return [len(block) for block in blockpartition.solve(cost, partitions)]
+    """Layers per partition when consecutive layers with these costs are cut into ``partitions`` blocks of similar cost."""
+    return list(map(len, blockpartition.solve(cost, partitions)))
+
+
+def _on(device: Device) -> torch.device:
+    return device if isinstance(device, torch.device) else torch.device(device)
 
 
 def balance_by_time(partitions: int, module: nn.Sequential, sample: TensorOrTensors, *, timeout: float = 1.0,
                     device: Device = torch.device("cuda")) -> List[int]:
-    """Balance so that every partition takes about the same forward+backward time on ``sample``."""
-    times = profile_times(module, sample, timeout, torch.device(device))
-    return balance_cost(times, partitions)
+    """Cut so that every partition takes about the same forward + backward time on ``sample`` (profiled for ``timeout`` s)."""
+    return balance_cost(profile_times(module, sample, timeout, _on(device)), partitions)
 
 
 def balance_by_size(partitions: int, module: nn.Sequential, input: TensorOrTensors, *, chunks: int = 1, param_scale: float = 2.0,
                     device: Device = torch.device("cuda")) -> List[int]:
-    """Balance by memory: activations of one micro-batch plus ``param_scale`` x parameters (2 for SGD, 4 for Adam...)."""
-    sizes = profile_sizes(module, input, chunks, param_scale, torch.device(device))
-    return balance_cost(sizes, partitions)
+    """Cut by memory: activations of one of ``chunks`` micro-batches plus ``param_scale`` x parameter bytes (2 for SGD: weight +
+    gradient; 4 for Adam: two moments more)."""
+    return balance_cost(profile_sizes(module, input, chunks, param_scale, _on(device)), partitions)

@@ -1,8 +1,7 @@
-"""Shared types of the multi-process pipeline (parity: fairscale/nn/pipe/types.py:13-69)."""
+"""Shared types of the multi-process pipeline (names of fairscale/nn/pipe/types.py:13-69)."""
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
 from typing import Any, Callable, List, Optional, Tuple, Union
 
 import torch
@@ -12,10 +11,21 @@ Tensors = Tuple[Tensor, ...]
 TensorOrTensors = Union[Tensor, Tensors]
 
 MESSAGE_GENERATION_START = 0
-
-# globally unique tag space for p2p messages of one step
-_message_generation = MESSAGE_GENERATION_START
 MESSAGE_TENSOR_SIZE = 1024  # reserved width of a header; headers here are small fixed int64 tensors
+
+
+class _TagSpace:
+    """Tags of p2p messages, unique within the process: every message reserves one tag per tensor it carries."""
+
+    def __init__(self, start: int) -> None:
+        self.next = start
+
+    def reserve(self, count: int) -> int:
+        first, self.next = self.next, self.next + count
+        return first
+
+
+_tags = _TagSpace(MESSAGE_GENERATION_START)
 
 
 class LazyModule:
@@ -28,27 +38,20 @@ class LazyModule:
         return self.function()
 
 
-@dataclass(init=False)
 class PipeMessage:
-    """Envelope of one activation / gradient transfer between neighbouring stages."""
+    """Envelope of one activation / gradient transfer between neighbouring stages: who sends to whom, which queue of the
+    receiver it is for, small Python arguments, and the tensors (whose shapes and dtypes the sender fills in)."""
 
-    src: int
-    dest: int
-    queue_name: int
-    args: Any
-    tensors: Tensors
-    tensor_shapes: List[torch.Size]
-    tensor_dtypes: List[torch.dtype]
-    tag: int = 0
+    __slots__ = ("src", "dest", "queue_name", "args", "tensors", "tensor_shapes", "tensor_dtypes", "tag")
 
     def __init__(self, src: int, dest: int, queue_name: int, args: Any = None, tensors: Optional[Tensors] = None, tensor_count: int = 0):
-        self.src = src
-        self.dest = dest
-        self.queue_name = queue_name
-        self.args = args
-        self.tensors = tensors or tuple()
-        self.tensor_shapes = []
-        self.tensor_dtypes = []
-        global _message_generation
-        self.tag = _message_generation
-        _message_generation += len(self.tensors) if tensors is not None else tensor_count
+        self.src, self.dest, self.queue_name, self.args = src, dest, queue_name, args
+        self.tensors: Tensors = tuple(tensors) if tensors else tuple()
+        self.tensor_shapes: List[torch.Size] = []
+        self.tensor_dtypes: List[torch.dtype] = []
+        self.tag = _tags.reserve(len(self.tensors) if tensors is not None else tensor_count)
+
+    def __repr__(self) -> str:
+        return f"PipeMessage({self.src}->{self.dest}, queue {self.queue_name}, {len(self.tensors)} tensors, tag {self.tag})"
+
+
