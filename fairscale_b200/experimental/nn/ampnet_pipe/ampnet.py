@@ -12,7 +12,7 @@ through the asynchronous-send transport of ``AsyncPipe``.
 
 from __future__ import annotations
 
-from typing import Any, Dict, Iterator, Optional, Tuple
+from typing import Any, Dict, Iterator, Tuple
 
 import torch
 from torch import nn

@@ -8,7 +8,7 @@ broadcast per edge.
 from __future__ import annotations
 
 import logging
-from typing import Any, Iterator, List, Optional, Tuple
+from typing import Any, Iterator, Optional, Tuple
 
 from enum import Enum
 

@@ -12,7 +12,7 @@ from torch.distributed import rpc
 from ....nn.pipe import microbatch
 from .data import DataConsumer
 from .graph import Node, PipelineModulesGraph
-from .partition_handler import DistributedPipelineRecord, PartitionHandler
+from .partition_handler import PartitionHandler
 
 Device = Union[torch.device, int, str]
 MOVING_DENIED = TypeError("denied to move parameters and buffers, because DistributedPipeline should manage device placement")

@@ -16,7 +16,7 @@ from dataclasses import dataclass
 from enum import Enum, auto
 from functools import lru_cache
 import json
-from typing import Any, Callable, Dict, List, NamedTuple, Optional, Sequence, Set, Tuple, Union
+from typing import Any, Callable, Dict, List, NamedTuple, Optional, Set, Tuple, Union
 
 from contextlib import contextmanager
 

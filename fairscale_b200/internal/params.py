@@ -5,7 +5,7 @@ from __future__ import annotations
 from collections import abc
 from dataclasses import dataclass
 from math import inf
-from typing import Any, Callable, Dict, List, Optional, Union
+from typing import Any, Callable, List, Optional, Union
 
 import torch
 import torch.distributed as dist

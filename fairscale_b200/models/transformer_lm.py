@@ -11,7 +11,7 @@ otherwise) instead of ``nn.MultiheadAttention`` with a dense additive mask.
 from __future__ import annotations
 
 import math
-from typing import Any, Optional
+from typing import Any
 
 import torch
 import torch.distributed as dist

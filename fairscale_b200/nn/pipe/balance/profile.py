@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import copy
 import time
-from typing import Any, Generator, List, Sequence, Tuple, Union
+from typing import Generator, List, Tuple, Union
 
 import torch
 from torch import Tensor, nn

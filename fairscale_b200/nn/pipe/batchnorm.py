@@ -7,7 +7,7 @@ match what an un-piped model would have tracked.  Contract of fairscale/nn/pipe/
 
 from __future__ import annotations
 
-from typing import List, Optional, TypeVar, cast
+from typing import Optional, TypeVar, cast
 
 import torch
 from torch import Tensor, nn

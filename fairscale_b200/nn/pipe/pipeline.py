@@ -20,7 +20,7 @@ from __future__ import annotations
 import sys
 from dataclasses import dataclass, field
 from types import TracebackType
-from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple, Type, Union
+from typing import Callable, Iterable, List, Optional, Tuple, Type, Union
 
 import torch
 from torch import Tensor, nn

@@ -8,7 +8,7 @@ native library; otherwise (and on CPU) a PyTorch formulation is used and :data:`
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

@@ -10,7 +10,6 @@ one multi-tensor sum of squares on CUDA instead of two reductions per parameter.
 
 from __future__ import annotations
 
-import logging
 from typing import Any, Dict, List, Tuple
 
 import torch

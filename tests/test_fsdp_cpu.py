@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
-from fairscale_b200.fair_dev.testing.testing import DummyProcessGroup, objects_are_equal, spawn_ranks
+from fairscale_b200.fair_dev.testing.testing import DummyProcessGroup, spawn_ranks
 from fairscale_b200.nn import FullyShardedDataParallel as FSDP
 from fairscale_b200.nn import auto_wrap, default_auto_wrap_policy, enable_wrap, wrap
 from fairscale_b200.nn.data_parallel import TrainingState, get_fsdp_instances
