@@ -227,6 +227,13 @@ class ShardedDataParallel(nn.Module):
                 "Grads waiting to be reduced. If this is on purpose (grad accumulation), please use a no_sync() context"
             )
         with profiler.record_function("fairscale::sdp::refresh_trainable"):
+            # A parameter that has just been frozen may still carry last step's gradient as a view of a bucket that is
+            # about to be rebuilt without it; zero_grad() only visits trainable parameters, so that stale value would be
+            # applied by the optimizer again and again.  (A gradient set by hand on a frozen parameter is left alone.)
+            for bucket in self._bucket_list:
+                for p in bucket._params:
+                    if not p.requires_grad and p.grad is not None:
+                        p.grad = None
             self._trainable_params = sorted((p for p in self._all_params if p.requires_grad), key=lambda t: t.numel())
             self._trainable_param_to_rank = {}
             for optim in self._sharded_optimizers:
