@@ -12,7 +12,6 @@ host→device copy is issued ahead of the recomputation.
 
 from __future__ import annotations
 
-import functools
 import threading
 import weakref
 from contextlib import contextmanager, nullcontext
@@ -92,11 +91,27 @@ def checkpoint_wrapper(module: nn.Module, offload_to_cpu: bool = False) -> nn.Mo
     """
     patch_batchnorm(module)
     module._fsb_checkpointed = True  # type: ignore[assignment]  # wrappers may rely on the forward being replayed in backward
-    # a weak reference avoids the module ↔ bound-partial cycle that would keep it alive forever
-    module.forward = functools.partial(  # type: ignore[method-assign]
-        _checkpointed_forward, type(module).forward, weakref.ref(module), offload_to_cpu
-    )
+    module.forward = _CheckpointedForward(type(module).forward, module, offload_to_cpu)  # type: ignore[method-assign]
     return module
+
+
+class _CheckpointedForward:
+    """The ``forward`` of a wrapped module.  It reaches its module through a weak reference (a strong one would form a
+    module <-> forward cycle that keeps the module alive until the garbage collector runs), and a deep copy of the
+    module gets a forward that points at the copy, not at the original."""
+
+    def __init__(self, original_forward: Any, module: nn.Module, offload_to_cpu: bool) -> None:
+        self.original_forward = original_forward
+        self.weak_self = weakref.ref(module)
+        self.offload_to_cpu = offload_to_cpu
+
+    def __call__(self, *args: Any, **kwargs: Any) -> Any:
+        return _checkpointed_forward(self.original_forward, self.weak_self, self.offload_to_cpu, *args, **kwargs)
+
+    def __deepcopy__(self, memo: Dict[int, Any]) -> "_CheckpointedForward":
+        original = self.weak_self()
+        owner = memo.get(id(original)) if original is not None else None  # the copy under construction, if we are part of one
+        return _CheckpointedForward(self.original_forward, owner if owner is not None else original, self.offload_to_cpu)
 
 
 def _checkpointed_forward(original_forward: Any, weak_self: Any, offload_to_cpu: bool, *args: Any, **kwargs: Any) -> Any:
