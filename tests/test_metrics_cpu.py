@@ -53,3 +53,26 @@ def _timer(rank, world):
 
 def test_device_timer_reports_the_slowest_rank():
     spawn_ranks(_timer, 2, (), backend="gloo")
+
+
+def test_ncu_summary_reads_a_raw_page_csv():
+    """The profile summariser on a hand-made raw-page CSV: units row, per-launch rows, kernel filter, achieved rates."""
+    from fairscale_b200.utils import ncu_summary
+
+    header = ["ID", "Kernel Name", "gpu__time_duration.sum", "launch__grid_size", "dram__bytes_read.sum",
+              "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active",
+              "smsp__average_warps_issue_stalled_long_scoreboard_per_issue_active.ratio",
+              "smsp__average_warps_issue_stalled_selected_per_issue_active.ratio"]
+    units = ["", "", "us", "", "Mbyte", "%", "inst", "inst"]
+    rows = [["0", "gemm_kernel(Params)", "200.0", "148", "100.5", "79.25", "11.5", "1.0"],
+            ["1", "copy_kernel(void *)", "50,000", "296", "2,048.0", "0", "30.25", "1.0"]]
+    text = "==PROF== noise before the table\n" + "\n".join(",".join(f'"{c}"' for c in r) for r in [header, units] + rows) + "\n"
+    h, u, launches = ncu_summary.parse_csv(text)
+    assert h == header and u == units and len(launches) == 2
+    report = ncu_summary.summarise(h, u, launches, kernel="gemm", flops=2 * 8192 * 8192 * 2048, peaks={"bf16_tflops": 1600.0})
+    assert "gemm_kernel" in report and "copy_kernel" not in report
+    assert "200.0 us" in report and "79.2 %" in report and "100.5 MB" in report
+    assert "long_scoreboard 11.50" in report and "selected" not in report
+    assert "1374.4 TFLOP/s = 0.86 of measured" in report
+    everything = ncu_summary.summarise(h, u, launches, nbytes=2048e6 * 2)
+    assert "50000.0 us" in everything and "81.9 GB/s" in everything
