@@ -238,7 +238,9 @@ __device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, 
   } else if (p.a_ready != nullptr) {  // M-major in arrival order of the row blocks of A, this rank's own block first
     const int lin = tile / tiles_n;
     tn = tile - lin * tiles_n;
-    const int rot = static_cast<int>((static_cast<long long>(p.a_first_shard) * p.a_shard_rows) / (2 * BLOCK_M));
+    // first tile that starts inside this rank's own block (rounded up: a tile that straddles the block's start also needs
+    // rows of the block that arrives last, so it is visited last)
+    const int rot = static_cast<int>((static_cast<long long>(p.a_first_shard) * p.a_shard_rows + 2 * BLOCK_M - 1) / (2 * BLOCK_M));
     tm = (lin + rot) % tiles_m;
   } else {
     tile_coords(tile, tiles_m, tiles_n, tm, tn);
