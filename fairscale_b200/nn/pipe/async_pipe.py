@@ -268,6 +268,8 @@ class AsyncPipe(nn.Module):
                 x = batches[i]
             else:
                 x = self.transport.recv(self.rank - 1, slot=i)
+                if i + 1 < n:
+                    self.transport.prefetch(self.rank - 1, i + 1)  # the next activation travels while this one is computed on
                 if x.requires_grad and torch.is_grad_enabled():
                     x = _RecvBoundary.apply(x, self.transport, self.rank - 1, n + i)  # gradient slots follow the activation slots
             y = self._run_stage(x, i < stop)
@@ -293,10 +295,14 @@ class AsyncPipe(nn.Module):
             return
         outs = self._outputs if output is None else output
         n = len(outs)
-        # the next stage emits the gradients in its backward order: last micro-batch first
-        grads = [self.transport.recv(self.rank + 1, slot=n + (n - 1 - k)) for k in range(n)]
-        # the final stage back-propagates torch.cat(outs): gradients arrive in autograd's (reverse) order
-        for y, g in zip(reversed(outs), grads):
+        # the next stage emits the gradients in its backward order (the final stage back-propagates torch.cat(outs), i.e. in
+        # autograd's reverse order): last micro-batch first.  The receive of the following gradient is posted before the
+        # backward of the current one.
+        slots = [n + (n - 1 - k) for k in range(n)]
+        for k, y in enumerate(reversed(outs)):
+            g = self.transport.recv(self.rank + 1, slot=slots[k])
+            if k + 1 < n:
+                self.transport.prefetch(self.rank + 1, slots[k + 1])
             if y.requires_grad:
                 torch.autograd.backward(y, g)
         self.transport.flush()

@@ -46,6 +46,11 @@ class Transport:
     def flush(self) -> None:
         raise NotImplementedError
 
+    def prefetch(self, src: int, slot: Optional[int]) -> bool:
+        """Optionally start receiving the next message from ``src`` ahead of the ``recv`` that will ask for it; the default
+        does nothing."""
+        return False
+
 
 Signature = Tuple[Tuple[int, ...], torch.dtype, bool]  # shape, dtype, requires_grad
 
@@ -62,6 +67,8 @@ class SendRecvTransport(Transport):
         self._expected: Dict[Tuple[int, int], Signature] = {}  # (source, slot) -> contract
         self.headers_sent = 0      # instrumentation: how many messages carried a header ...
         self.headers_received = 0  # ... and how many receives had to read one on the host
+        self._prefetched: Dict[Tuple[int, Optional[int]], Tuple[Tensor, Any]] = {}  # (source, slot) -> (buffer, pending receive)
+        self.prefetches = 0        # receives that were posted ahead of their use
 
     def _global(self, group_rank: int) -> int:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None and self.group is not dist.group.WORLD else group_rank
@@ -89,7 +96,27 @@ class SendRecvTransport(Transport):
         self._pending.append(dist.isend(t.detach(), self._global(dst), group=self.group))
         self._pending.append(keep)  # the buffers stay alive until the sends have completed
 
+    def prefetch(self, src: int, slot: Optional[int]) -> bool:
+        """Post the receive of the next message from ``src`` now, so that the transfer runs while the caller computes.
+        Possible when the message's shape is known (static-shape contract already established for ``(src, slot)``); the
+        caller must ask for this message next among those from ``src``.  Returns whether a receive was posted."""
+        contract = self._expected.get((src, slot)) if (self.static_shapes and slot is not None) else None
+        if contract is None or (src, slot) in self._prefetched:
+            return False
+        shape, dtype, _ = contract
+        buf = torch.empty(shape, dtype=dtype, device=self.device)
+        self._prefetched[(src, slot)] = (buf, dist.irecv(buf, self._global(src), group=self.group))
+        self.prefetches += 1
+        return True
+
     def recv(self, src: int, slot: Optional[int] = None) -> Tensor:
+        pending = self._prefetched.pop((src, slot), None)
+        if pending is not None:
+            out, work = pending
+            work.wait()
+            if self._expected[(src, slot)][2] and out.is_floating_point():
+                out.requires_grad_()
+            return out
         contract = self._expected.get((src, slot)) if (self.static_shapes and slot is not None) else None
         if contract is None:
             head = torch.zeros(_HEADER, dtype=torch.int64, device=self.device)

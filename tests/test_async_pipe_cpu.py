@@ -54,7 +54,7 @@ def _static_worker(rank, world):
     pipe.transport.static_shapes = True
     torch.manual_seed(5)
     x = torch.randn(6, 6)
-    counts = []
+    counts, posted_ahead = [], []
     for _ in range(3):
         out = pipe(x if rank == 0 else None)
         if rank == 2:
@@ -63,6 +63,7 @@ def _static_worker(rank, world):
         elif rank < 2:
             pipe.back_helper(out)
         counts.append((pipe.transport.headers_sent, pipe.transport.headers_received))
+        posted_ahead.append(pipe.transport.prefetches)
         dist.barrier()
     if rank < 3:
         assert counts[1] != counts[0] or rank == 3  # the chunk-count message has no slot and keeps its header
@@ -71,6 +72,10 @@ def _static_worker(rank, world):
         assert per_step_after_first[0] < first_step[0] or first_step[0] == 0
         assert per_step_after_first[1] < first_step[1] or first_step[1] == 0
         assert per_step_after_first[0] <= 1 and per_step_after_first[1] <= 1  # only the chunk-count message
+    # once the shapes are known, receives are posted one message ahead: activations on every stage but the first, gradients
+    # on every stage but the last (chunks - 1 of each per step)
+    if rank in (1, 2):
+        assert posted_ahead[0] == 0 and posted_ahead[2] > posted_ahead[1] > 0, posted_ahead
     if rank == 1:
         # a tensor that breaks the contract is refused by the sender
         with pytest.raises(RuntimeError, match="static contract"):
