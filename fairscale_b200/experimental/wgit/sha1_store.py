@@ -133,7 +133,8 @@ class SHA1_Store:
                     else:
                         shutil.copyfile(src, dest)
                     csize = dest.stat().st_size
-                    entry = {ENTRY_RF_KEY: 0, ENTRY_COMP_KEY: compress, ENTRY_OS_KEY: orig, ENTRY_DS_KEY: orig,
+                    # the original size of an entry counts every reference, the other two count the stored copy once
+                    entry = {ENTRY_RF_KEY: 0, ENTRY_COMP_KEY: compress, ENTRY_OS_KEY: 0, ENTRY_DS_KEY: orig,
                              ENTRY_CS_KEY: csize, ENTRY_NAMES_KEY: {}}
                     self._json[sha1] = entry
                     self._json[STORE_DS_KEY] += orig
@@ -141,6 +142,7 @@ class SHA1_Store:
                 elif entry[ENTRY_COMP_KEY] != compress:
                     raise ValueError(f"{sha1} was stored with compress={entry[ENTRY_COMP_KEY]}; cannot add it with compress={compress}")
                 entry[ENTRY_RF_KEY] += 1
+                entry[ENTRY_OS_KEY] += orig
                 if name:
                     entry[ENTRY_NAMES_KEY][name] = entry[ENTRY_NAMES_KEY].get(name, 0) + 1
                 self._json[STORE_OS_KEY] += orig
@@ -169,8 +171,10 @@ class SHA1_Store:
             entry = self._json.get(sha1)
             if entry is None:
                 raise ValueError(f"Try to delete SHA1 {sha1} but it is not found")
+            one = entry[ENTRY_OS_KEY] // max(1, entry[ENTRY_RF_KEY])
             entry[ENTRY_RF_KEY] -= 1
-            self._json[STORE_OS_KEY] -= entry[ENTRY_OS_KEY]
+            entry[ENTRY_OS_KEY] -= one
+            self._json[STORE_OS_KEY] -= one
             if entry[ENTRY_RF_KEY] <= 0:
                 (self._sha1_to_dir(sha1) / sha1).unlink(missing_ok=True)
                 self._json[STORE_DS_KEY] -= entry[ENTRY_DS_KEY]
