@@ -140,6 +140,10 @@ class Adam(Optimizer):
         self._optim_scale_update_freq = 2000
         if amsgrad:
             raise RuntimeError("FusedAdam does not support the AMSGrad variant.")
+        if lr < 0.0 or eps < 0.0 or weight_decay < 0.0:
+            raise ValueError(f"lr, eps and weight_decay must not be negative (got lr={lr}, eps={eps}, weight_decay={weight_decay})")
+        if not (0.0 <= betas[0] < 1.0 and 0.0 <= betas[1] < 1.0):
+            raise ValueError(f"betas must lie in [0, 1), got {betas}")
         defaults = dict(lr=lr, bias_correction=bias_correction, betas=betas, eps=eps, weight_decay=weight_decay,
                         max_grad_norm=max_grad_norm)
         super().__init__(parameters, defaults)
@@ -187,12 +191,17 @@ class Adam(Optimizer):
         scale = state_dict.pop("optim_scale", self._optim_scale)
         super().load_state_dict(state_dict)
         self._optim_scale = scale
-        for group in self.param_groups:
-            for p in group["params"]:
-                st = self.state.get(p)
-                if st and "exp_avg" in st:
-                    st["exp_avg"] = st["exp_avg"].to(self.optim_type)
-                    st["exp_avg_sq"] = st["exp_avg_sq"].to(self.optim_type)
+        # torch casts loaded state to the dtype of its parameter, which would round fp32 moments of fp16 / bf16 parameters
+        # (the reference accepts that loss, fairscale/optim/adam.py:169-181): take the moments from the saved tensors instead
+        saved_state = state_dict.get("state", {})
+        for group, saved_group in zip(self.param_groups, state_dict["param_groups"]):
+            for p, saved_id in zip(group["params"], saved_group["params"]):
+                st, saved = self.state.get(p), saved_state.get(saved_id)
+                if not st or "exp_avg" not in st:
+                    continue
+                for key in ("exp_avg", "exp_avg_sq"):
+                    src = saved[key] if saved is not None and torch.is_tensor(saved.get(key)) else st[key]
+                    st[key] = src.detach().to(device=p.device, dtype=self.optim_type, copy=True)
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
