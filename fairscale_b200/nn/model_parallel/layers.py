@@ -129,8 +129,12 @@ class VocabParallelEmbedding(torch.nn.Module):
             outside = (input_ < self.vocab_start_index) | (input_ >= self.vocab_end_index)
             local = input_.clone() - self.vocab_start_index
             local[outside] = 0
-            partial = F.embedding(local, self.weight, self.padding_idx, self.max_norm, self.norm_type,
-                                  self.scale_grad_by_freq, self.sparse)
+            # padding_idx names a row of the whole vocabulary: only the rank that holds the row passes it on, renumbered
+            pad = self.padding_idx
+            if pad is not None:
+                pad = pad + self.num_embeddings if pad < 0 else pad
+                pad = pad - self.vocab_start_index if self.vocab_start_index <= pad < self.vocab_end_index else None
+            partial = F.embedding(local, self.weight, pad, self.max_norm, self.norm_type, self.scale_grad_by_freq, self.sparse)
             partial[outside, :] = 0.0
         return reduce_from_model_parallel_region(partial)
 

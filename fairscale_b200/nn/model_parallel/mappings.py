@@ -80,7 +80,10 @@ class _RegionOp(torch.autograd.Function):
         fwd, _, in_place = _REGION_OPS[kind]
         ctx.kind = kind
         if in_place:
-            ctx.mark_dirty(t)
+            if t.is_leaf and t.requires_grad:
+                t = t.detach().clone()  # autograd refuses to overwrite a leaf that wants a gradient: reduce a copy
+            else:
+                ctx.mark_dirty(t)
         return fwd(t)
 
     @staticmethod
