@@ -26,6 +26,7 @@ class DistributedPipelineRecord:
         self.tensors: List[List[Optional[Tensor]]] = [[None] * num_inputs for _ in range(chunks)]
         self.recv_events: List[List[Any]] = [[None] * num_inputs for _ in range(chunks)]
         self.outputs: List[Any] = [None] * chunks
+        self.chunks = chunks  # micro-batches of THIS mini-batch: fewer than the pipeline's setting when the batch is small
         self.consumers = consumers
         self.rank = rank
         self.device = device
@@ -57,7 +58,26 @@ class DistributedPipelineRecord:
     def forward_results(self, chunk: int) -> None:
         out = self.outputs[chunk]
         for c in self.consumers:
-            self.pending.append(c.consumer.rpc_async().feed(chunk, c.consumer_input_idx, out[c.output_idx]))
+            if c.consumer.is_owner():
+                # the next partition lives in this process: hand the tensor over directly (no copy, no RPC to oneself, and
+                # the autograd graph of the two partitions stays one local graph)
+                c.consumer.local_value().feed(chunk, c.consumer_input_idx, out[c.output_idx])
+            else:
+                self.pending.append(feed_record_async(c.consumer, chunk, c.consumer_input_idx, out[c.output_idx]))
+
+
+def _feed_record(record_rref: rpc.RRef, chunk: int, input_idx: int, tensor: Tensor) -> None:
+    record_rref.local_value().feed(chunk, input_idx, tensor)
+
+
+def feed_record_async(record_rref: rpc.RRef, chunk: int, input_idx: int, tensor: Tensor) -> Any:
+    """Send ``tensor`` to the record behind ``record_rref``; returns the future of the call.
+
+    The call is issued with ``rpc.rpc_async`` from the calling thread.  ``record_rref.rpc_async().feed(...)`` would not do: the
+    RRef proxy first fetches the type of the remote object and issues the real call from the callback of that fetch, on a
+    thread that does not carry the caller's distributed-autograd context - the first tensors of a mini-batch then travel
+    without their autograd edge, arrive as leaves, and the backward pass waits for gradients that never come."""
+    return rpc.rpc_async(record_rref.owner(), _feed_record, args=(record_rref, chunk, input_idx, tensor))
 
 
 class PartitionHandler:
@@ -77,16 +97,21 @@ class PartitionHandler:
     def local_parameter_rrefs(self) -> List[rpc.RRef]:
         return [rpc.RRef(p) for p in self.module.parameters()]
 
-    def make_pipeline_record(self, consumers: List[DataConsumer]) -> DistributedPipelineRecord:
-        return DistributedPipelineRecord(self.device, self.rank, self.chunks, self.num_inputs, self.num_outputs, consumers)
+    def make_pipeline_record(self, consumers: List[DataConsumer], chunks: Optional[int] = None) -> DistributedPipelineRecord:
+        """``chunks``: how many micro-batches the driver will feed (a mini-batch with fewer rows than the configured number of
+        chunks gives fewer; waiting for the configured number would never end)."""
+        n = self.chunks if chunks is None else min(int(chunks), self.chunks)
+        return DistributedPipelineRecord(self.device, self.rank, n, self.num_inputs, self.num_outputs, consumers)
 
-    def _compute(self, inputs: List[Tensor], chunk: int) -> Any:
+    def _compute(self, inputs: List[Tensor], chunk: int, chunks: Optional[int] = None) -> Any:
         def fn(*xs: Tensor) -> Any:
             with record_function("chunk%d-rank%d" % (chunk, self.rank)):
                 y = self.module(*xs)
             return tuple(y) if self.num_outputs is not None else (y,)
 
-        stop = self.checkpoint_stop if self.module.training else 0
+        # "except_last" leaves the last micro-batch of this mini-batch alone, however many there are
+        missing = self.chunks - (self.chunks if chunks is None else chunks)
+        stop = max(0, self.checkpoint_stop - missing) if self.module.training else 0
         if chunk < stop and torch.is_grad_enabled() and any(x.requires_grad for x in inputs):
             from torch.utils.checkpoint import checkpoint
 
@@ -96,10 +121,10 @@ class PartitionHandler:
     def run_pipeline(self, pipeline_record_rref: rpc.RRef) -> Optional[Tensor]:
         """Process every chunk of the mini-batch; the last partition returns the concatenated model output."""
         rec: DistributedPipelineRecord = pipeline_record_rref.local_value()
-        for chunk in range(self.chunks):
+        for chunk in range(rec.chunks):
             with record_function("feed"):
                 inputs = rec.wait_for(chunk)
-            rec.outputs[chunk] = self._compute(inputs, chunk)
+            rec.outputs[chunk] = self._compute(inputs, chunk, rec.chunks)
             rec.forward_results(chunk)
         for f in rec.pending:
             f.wait()

@@ -12,7 +12,7 @@ from torch.distributed import rpc
 from ....nn.pipe import microbatch
 from .data import DataConsumer
 from .graph import Node, PipelineModulesGraph
-from .partition_handler import PartitionHandler
+from .partition_handler import PartitionHandler, feed_record_async
 
 Device = Union[torch.device, int, str]
 MOVING_DENIED = TypeError("denied to move parameters and buffers, because DistributedPipeline should manage device placement")
@@ -31,6 +31,9 @@ class DistributedPipeline(nn.Module):
     Args: ``graph`` (:class:`PipelineModulesGraph`), ``chunks`` micro-batches per mini-batch, ``checkpoint`` in
     ``'always' | 'except_last' | 'never'``.  ``forward`` returns an RRef to the output on the last partition's
     worker; train with ``torch.distributed.autograd`` and ``DistributedOptimizer(parameter_rrefs())``.
+
+    Every worker process should import this package before ``rpc.init_rpc``: an RPC agent unpickles incoming calls on
+    several threads, and letting those threads perform the first import concurrently can fail inside the import lock.
     """
 
     DataConsumer = DataConsumer  # the edge record type, reachable from the class as in the reference
@@ -92,14 +95,14 @@ class DistributedPipeline(nn.Module):
             for c in part.nodes[-1].output_consumers:
                 cp = next(p for p in self.partitions if p.nodes[0] is c.consumer)
                 consumers.append(DataConsumer(records[cp], c.consumer_input_idx, c.output_idx))
-            records[part] = h.make_pipeline_record(consumers)
+            records[part] = h.make_pipeline_record(consumers, len(batches[0]))
             r = h.run_pipeline(records[part])
             if part is self.partitions[-1]:
                 result = r
         futs = []
         for i, mb in enumerate(zip(*batches)):
             for ic in self.input_consumers:
-                futs.append(records[ic.consumer].rpc_async().feed(i, ic.consumer_input_idx, mb[ic.output_idx].tensor))
+                futs.append(feed_record_async(records[ic.consumer], i, ic.consumer_input_idx, mb[ic.output_idx].tensor))
         for f in futs:
             f.wait()
         assert result is not None
