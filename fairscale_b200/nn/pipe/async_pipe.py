@@ -125,9 +125,7 @@ class AsyncPipe(nn.Module):
         self.world = dist.get_world_size(group)
         if len(self.balance) > self.world:
             raise IndexError(f"too few ranks to hold given partitions (ranks: {self.world}, partitions: {len(self.balance)})")
-        n_layers = len(module)
-        if sum(self.balance) != n_layers:
-            raise ValueError(f"module and sum of balance have different length (module: {n_layers}, sum of balance: {sum(self.balance)})")
+        check_balance(module, self.balance)
         self.final_stage = len(self.balance) - 1
         self.pipeline: Optional[AsyncPipeline] = None
         entries = list(module)
@@ -237,9 +235,9 @@ class AsyncPipe(nn.Module):
     def _run_stage(self, x: TensorOrTensors, use_checkpoint: bool) -> TensorOrTensors:
         assert self.partition is not None
         if use_checkpoint and torch.is_grad_enabled():
-            from torch.utils.checkpoint import checkpoint as torch_ckpt
+            from .checkpoint import recomputed_in_backward
 
-            return torch_ckpt(self.partition, x, use_reentrant=False)
+            return recomputed_in_backward(self.partition, x)
         return self.partition(x)
 
     def forward(self, input: Optional[TensorOrTensors] = None) -> Optional[TensorOrTensors]:  # type: ignore[override]

@@ -125,9 +125,9 @@ class AsyncEventLoop:
 
     def _run_module(self, w: ModuleWrapper, x: Tensor, mb: int) -> Tensor:
         if mb < self.checkpoint_stop and torch.is_grad_enabled() and x.requires_grad:
-            from torch.utils.checkpoint import checkpoint as torch_ckpt
+            from .checkpoint import recomputed_in_backward
 
-            return torch_ckpt(w.module, x, use_reentrant=False)
+            return recomputed_in_backward(w.module, x)
         return w.module(x)
 
     # ------------------------------------------------------------------ forward

@@ -97,6 +97,23 @@ def enable_recomputing() -> Generator[None, None, None]:
         thread_local.is_recomputing = prev
 
 
+def recomputed_in_backward(function: Callable[[Any], Any], input: Any) -> Any:
+    """``function(input)`` through ``torch.utils.checkpoint`` (no activations kept; the call is repeated in backward), with the
+    flags of this module raised around the two calls: :func:`is_checkpointing` during the first, :func:`is_recomputing` during
+    the repetition, so that layers with side effects (running statistics, counters) can tell them apart.  Used by the
+    multi-process pipeline, whose stages checkpoint whole micro-batches."""
+    from torch.utils.checkpoint import checkpoint as torch_checkpoint
+
+    calls = [0]
+
+    def flagged(x: Any) -> Any:
+        calls[0] += 1
+        with (enable_checkpointing() if calls[0] == 1 else enable_recomputing()):
+            return function(x)
+
+    return torch_checkpoint(flagged, input, use_reentrant=False)
+
+
 def is_checkpointing() -> bool:
     """True inside the no-grad forward of a checkpointed stage."""
     return thread_local.is_checkpointing
