@@ -1771,6 +1771,10 @@ class FullyShardedDataParallel(nn.Module):
             assert len(full_optim_state_dict["state"]) <= len(instances), (
                 f'{len(full_optim_state_dict["state"])}, {len(instances)}'
             )
+            # one flat parameter per instance that owns parameters, whether or not the optimizer keeps state for it (the
+            # saved map cannot tell instances without state apart: plain SGD, frozen or unused units)
+            for group in full_optim_state_dict["param_groups"]:
+                group["params"] = list(range(len(instances)))
         for pid, per_param in full_optim_state_dict["state"].items():
             for name, v in per_param.items():
                 if ou.is_singleton_tensor(v):
