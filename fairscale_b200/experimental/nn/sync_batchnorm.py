@@ -97,6 +97,7 @@ class SyncBatchNorm(torch.nn.BatchNorm2d):
             raise ValueError(f"expected at least 2D input (got {input.dim()}D input)")
 
     def forward(self, input: Tensor) -> Tensor:  # type: ignore[override]
+        self._check_input_dim(input)
         if not dist.is_initialized() or not self.training:
             return super().forward(input)
         group = self._process_group if self._process_group is not None else dist.group.WORLD
