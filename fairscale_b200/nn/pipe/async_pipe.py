@@ -23,6 +23,7 @@ from .async_pipeline import AsyncPipeline
 from .async_schedule import Invocation, Location, ModuleWrapper
 from .batchnorm import DeferredBatchNorm
 from .messages import SendRecvTransport, get_transport
+from .skip.skippable import Skippable
 from .types import LazyModule
 
 Tensors = Tuple[Tensor, ...]
@@ -67,6 +68,12 @@ class PartitionInfo:
 
     def __len__(self) -> int:
         return len(self.modules)
+
+
+def _refuse_lazy_skippables(module: Any, layers: Iterable[nn.Module]) -> None:
+    """Skip connections are resolved against the whole sequence, which a rank that only builds its own layers never sees."""
+    if not isinstance(module, nn.Sequential) and any(isinstance(layer, Skippable) for layer in layers):
+        raise ValueError("Can't use Skippable layers with multi-process pipe and lazy construction")
 
 
 def plan_invocations(layers: Sequence[Any], balance: Sequence[int]) -> Tuple[List[Location], List[Invocation]]:
@@ -132,6 +139,7 @@ class AsyncPipe(nn.Module):
         if len({id(l) for l in entries}) < len(entries):
             # a layer object that appears more than once: event-loop schedule, data may revisit a stage
             self._init_event_loop(entries, input_device, deferred_batch_norm)
+            _refuse_lazy_skippables(module, [] if self.partition is None else [layer for seq in self.partition for layer in seq])
             return
         if self.rank >= len(self.balance):
             logging.warning(f"AsyncPipe: rank {self.rank} has no partition and stays idle")
@@ -140,6 +148,7 @@ class AsyncPipe(nn.Module):
             lo = sum(self.balance[: self.rank])
             layers = list(module)[lo : lo + self.balance[self.rank]] if isinstance(module, nn.Sequential) else module[lo : lo + self.balance[self.rank]]
             built = [l() if isinstance(l, LazyModule) else l for l in layers]
+            _refuse_lazy_skippables(module, built)
             part = nn.Sequential(*built)
             if deferred_batch_norm:
                 part = DeferredBatchNorm.convert_deferred_batch_norm(part, chunks)

@@ -116,6 +116,33 @@ def _lazy(rank, world):
     dist.barrier()
 
 
+def _lazy_skippable(rank, world):
+    from fairscale_b200.nn.pipe.skip import pop, skippable, stash
+
+    @skippable(stash=["skip"])
+    class Stash(nn.Module):
+        def forward(self, x):
+            yield stash("skip", x)
+            return x * 2
+
+    @skippable(pop=["skip"])
+    class Pop(nn.Module):
+        def forward(self, x):
+            skip = yield pop("skip")
+            return x + skip
+
+    with pytest.raises(ValueError, match="Skippable layers with multi-process pipe and lazy construction"):
+        AsyncPipe([LazyModule(lambda: Stash()), LazyModule(lambda: Pop())], balance=[2], chunks=1)
+    # built eagerly and kept inside one stage, the pair works
+    pipe = AsyncPipe(nn.Sequential(Stash(), Pop()), balance=[2], chunks=2)
+    x = torch.rand(4, 3)
+    torch.testing.assert_close(pipe(x), x * 3)
+
+
+def test_skippable_layers_are_refused_with_lazy_construction():
+    spawn_ranks(_lazy_skippable, 1, (), backend="gloo")
+
+
 def test_lazy_construction_builds_only_the_local_layers():
     spawn_ranks(_lazy, 2, (), backend="gloo")
 
