@@ -159,7 +159,11 @@ def _start_context() -> Any:
     method = os.environ.get("FSB_TEST_START_METHOD", "spawn" if torch.cuda.is_available() else "forkserver")
     ctx = mp.get_context(method)
     if method == "forkserver":
-        ctx.set_forkserver_preload(["torch", "torch.distributed", "torch.distributed.rpc", "numpy", "fairscale_b200", "fairscale_b200.nn", "fairscale_b200.optim"])
+        # torch._dynamo is pulled in by the first non-reentrant torch.utils.checkpoint call and torch.distributed.optim by
+        # DistributedOptimizer: seconds each, paid once in the server instead of in every rank of every test
+        ctx.set_forkserver_preload(["torch", "torch.distributed", "torch.distributed.rpc", "torch.distributed.autograd", "torch.distributed.optim",
+                                    "torch.utils.checkpoint", "torch._dynamo", "numpy", "fairscale_b200", "fairscale_b200.nn", "fairscale_b200.optim",
+                                    "fairscale_b200.experimental.nn"])
     return ctx
 
 
