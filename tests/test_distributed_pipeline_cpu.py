@@ -3,8 +3,9 @@ import os
 
 import pytest
 import torch
-import torch.multiprocessing as mp
 from torch import nn
+
+from fairscale_b200.fair_dev.testing.testing import find_free_port, spawn_ranks
 
 
 def _run(rank, world, port, mode):
@@ -64,11 +65,4 @@ def _run(rank, world, port, mode):
 
 @pytest.mark.parametrize("mode", ["graph", "trace"])
 def test_distributed_pipeline_two_workers(mode):
-    port = 29700 + os.getpid() % 200 + (0 if mode == "graph" else 1)
-    ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_run, args=(r, 2, port, mode)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(180)
-        assert p.exitcode == 0
+    spawn_ranks(_run, 2, (find_free_port(), mode), backend="gloo", timeout=180.0)

@@ -6,8 +6,9 @@ import os
 
 import pytest
 import torch
-import torch.multiprocessing as mp
 from torch import nn
+
+from fairscale_b200.fair_dev.testing.testing import find_free_port, spawn_ranks
 
 
 class ConcatenateTensors(nn.Module):
@@ -175,15 +176,4 @@ def _worker(rank, world, port, case):
 
 @pytest.mark.parametrize("case", list(_CASES))
 def test_distributed_pipeline_case(case):
-    world = _CASES[case][1]
-    port = 29950 + os.getpid() % 150 + 150 * list(_CASES).index(case) % 600
-    ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_worker, args=(r, world, port, case)) for r in range(world)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(240)
-    for p in procs:
-        if p.is_alive():
-            p.kill()
-    assert [p.exitcode for p in procs] == [0] * world
+    spawn_ranks(_worker, _CASES[case][1], (find_free_port(), case), backend="gloo", timeout=240.0)
