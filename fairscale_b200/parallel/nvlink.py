@@ -115,10 +115,36 @@ class NvlinkWorkspace:
     def alloc(self, nbytes: int, align: int = 256) -> torch.Tensor:
         """Persistent uint8 window of the symmetric heap (same offset on every rank when called collectively)."""
         off = (self._bump + align - 1) // align * align
-        if off + nbytes > self.heap_bytes:
+        guards = self._guards()
+        taken = nbytes if guards is None else guards.reserve(nbytes)
+        if off + taken > self.heap_bytes:
             raise MemoryError("symmetric heap exhausted; pass a larger heap_mb to nvlink.enable()")
-        self._bump = off + nbytes
+        self._bump = off + taken
+        if guards is not None:
+            guards.plant(off, nbytes)
         return self.heap[off : off + nbytes]
+
+    def _guards(self) -> Optional[Any]:
+        """Guard words behind every heap window when ``FSB200_HEAP_CANARY=1`` (see :mod:`fairscale_b200.parallel.heap_guard`)."""
+        from . import heap_guard
+
+        if not heap_guard.enabled():
+            return None
+        if getattr(self, "_heap_guards", None) is None:
+            self._heap_guards = heap_guard.HeapGuards(self.heap)
+        return self._heap_guards
+
+    def check_canaries(self) -> None:
+        """Raise if a guard behind a heap window was overwritten (debug aid; synchronises the device).  A no-op unless the
+        workspace was created with ``FSB200_HEAP_CANARY=1``."""
+        guards = getattr(self, "_heap_guards", None)
+        if guards is None:
+            return
+        torch.cuda.synchronize(self.device)
+        bad = guards.corrupted()
+        if bad:
+            guards.replant()
+            raise RuntimeError("symmetric heap overrun on rank %d:\n  " % self.rank + "\n  ".join(bad))
 
     def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """Named, reusable heap tensor (allocated on first use; the same name and size returns the same window)."""
