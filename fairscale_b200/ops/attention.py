@@ -8,6 +8,7 @@ native library; otherwise (and on CPU) a PyTorch formulation is used and :data:`
 from __future__ import annotations
 
 import math
+import warnings
 from typing import Optional
 
 import torch
@@ -15,6 +16,7 @@ import torch
 from . import _bind
 
 BACKEND = "unset"
+_WARNED_LIBRARY_PATH = False  # the fall-back to the library kernel is announced once
 
 
 def _reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
@@ -46,6 +48,14 @@ def causal_attention(qkv: torch.Tensor, n_heads: int, scale: Optional[float] = N
         return flash_attention_packed(qkv, n_heads, scale)
     q, k, v = qkv.view(B, S, 3, n_heads, D).permute(2, 0, 3, 1, 4)
     if qkv.is_cuda:
+        global _WARNED_LIBRARY_PATH
+        if not _WARNED_LIBRARY_PATH:
+            _WARNED_LIBRARY_PATH = True
+            warnings.warn(
+                f"causal_attention: the tcgen05 kernels take bf16 with head size 64 or 128 and a sequence length that is a multiple "
+                f"of 128 (got {qkv.dtype}, head size {D}, length {S}); this call runs torch's scaled_dot_product_attention instead",
+                stacklevel=2,
+            )
         BACKEND = "torch-sdpa"
         o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale)
     else:
