@@ -16,7 +16,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from ...nn.checkpoint import is_checkpointing, is_recomputing
+from ...nn.checkpoint import checkpoint_invocations, is_checkpointing, is_recomputing
 
 
 def _reduce_dims(x: Tensor) -> List[int]:
@@ -101,19 +101,33 @@ class SyncBatchNorm(torch.nn.BatchNorm2d):
         if not dist.is_initialized() or not self.training:
             return super().forward(input)
         group = self._process_group if self._process_group is not None else dist.group.WORLD
-        first_pass = not is_recomputing()
-        if first_pass:
+        # Statistics of a checkpointed call are handed to the repetition of that same call: they are kept in the call's own
+        # scratch (one layer may run several times inside one call, and a step may have several calls that autograd
+        # repeats in reverse order), or in this module's list when the checkpoint in use has no scratch.
+        running = checkpoint_invocations()
+        key = ("sync_batchnorm", id(self))
+        stats = None
+        if is_recomputing():
+            for scratch in reversed(running):
+                if scratch.get("_mode") == "replay" and scratch.get(key):
+                    stats = scratch[key].pop(0)
+                    break
+            if stats is None and not running and self.saved_for_2nd_fwd:
+                stats = self.saved_for_2nd_fwd.pop(0)
+        if stats is None:
             with torch.no_grad():
                 mean, var, invstd, total = _calculate_stats(input, self.eps, group)
-                if self.track_running_stats:
+                if self.track_running_stats and not is_recomputing():
                     m = self.momentum if self.momentum is not None else 1.0 / float(self.num_batches_tracked + 1)
                     self.running_mean += m * (mean.to(self.running_mean.dtype) - self.running_mean)
                     self.running_var += m * ((var * (total / (total - 1))).to(self.running_var.dtype) - self.running_var)
                     self.num_batches_tracked += 1
-            if is_checkpointing():
-                self.saved_for_2nd_fwd.append((mean, invstd, total))
-        else:
-            mean, invstd, total = self.saved_for_2nd_fwd.pop(0)
+            stats = (mean, invstd, total)
+        if running and running[-1].get("_mode") == "first":
+            running[-1].setdefault(key, []).append(stats)  # the innermost call is in its forward: its repetition will ask
+        elif not running and is_checkpointing() and not is_recomputing():
+            self.saved_for_2nd_fwd.append(stats)
+        mean, invstd, total = stats
         w = self.weight if self.affine else None
         b = self.bias if self.affine else None
         return _SyncBatchNormFunction.apply(input, w, b, mean, invstd, total, group)

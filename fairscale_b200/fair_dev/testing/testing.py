@@ -138,6 +138,10 @@ def _rank_entry(rank: int, fn: Callable, world_size: int, url: str, backend: Opt
                 env: Optional[Dict[str, str]] = None) -> None:
     if env:
         os.environ.update(env)  # a forkserver child starts from the server's environment, not from the caller's
+    if not torch.cuda.is_available():
+        # CPU ranks: several processes with a full-size OpenMP pool each oversubscribe the cores, and the tiny tensors of the
+        # tests then spend their time in thread hand-offs (a 3-step conv net: 2 s with 8 threads per rank, 0.04 s with one)
+        torch.set_num_threads(int(os.environ.get("FSB_TEST_THREADS", "1")))
     try:
         ok = dist_init(rank, world_size, url, backend=backend)
         if not ok:

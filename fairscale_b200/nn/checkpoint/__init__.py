@@ -1,4 +1,5 @@
 from .checkpoint_activations import (  # noqa: F401
+    checkpoint_invocations,
     checkpoint_wrapper,
     disable_checkpointing,
     is_checkpointing,

@@ -31,9 +31,28 @@ class _Flags(threading.local):
         self.is_recomputing = False
         self.is_checkpointing_disabled = False
         self.region_owners: List[Any] = []
+        self.invocations: List[Dict[str, Any]] = []  # one scratch dict per checkpointed call that is running, innermost last
 
 
 thread_local = _Flags()
+
+
+@contextmanager
+def _running_invocation(scratch: Dict[str, Any], mode: str) -> Generator[None, None, None]:
+    scratch["_mode"] = mode  # "first": the no-grad forward; "replay": its repetition in backward
+    thread_local.invocations.append(scratch)
+    try:
+        yield
+    finally:
+        thread_local.invocations.pop()
+
+
+def checkpoint_invocations() -> List[Dict[str, Any]]:
+    """Scratch dicts of the checkpointed calls that are running in this thread, innermost last.  One dict belongs to one call
+    of a checkpointed module: it is current during the call's forward (``scratch["_mode"] == "first"``) and again during the
+    repetition of exactly that call in backward (``"replay"``), whatever the order in which autograd gets to the calls of a
+    step.  Layers with side effects keep what the repetition has to reuse there (e.g. SyncBatchNorm its batch statistics)."""
+    return thread_local.invocations
 
 
 @contextmanager
@@ -259,8 +278,9 @@ class CheckpointFunction(torch.autograd.Function):
             ctx.fwd_device, ctx.grad_requirements, ctx.park_events = None, None, None
         ctx.save_for_backward(*tensor_inputs)
         ctx.packed_non_tensor_inputs = packed_inputs
+        ctx.scratch = {}
 
-        with torch.no_grad(), enable_checkpointing():
+        with torch.no_grad(), enable_checkpointing(), _running_invocation(ctx.scratch, "first"):
             f_args, f_kwargs = unpack_kwargs(kwarg_keys, args)
             outputs = run_function(*f_args, **f_kwargs)
             the_module = f_args[0]
@@ -302,7 +322,7 @@ class CheckpointFunction(torch.autograd.Function):
         rng_now = get_rng_state()
         set_rng_state(ctx.fwd_rng_state)
         amp = torch.autocast(**ctx.autocast) if ctx.autocast is not None else nullcontext()
-        with torch.enable_grad(), enable_recomputing(), amp:
+        with torch.enable_grad(), enable_recomputing(), amp, _running_invocation(ctx.scratch, "replay"):
             f_args, f_kwargs = unpack_kwargs(ctx.kwarg_keys, inputs)
             outputs = ctx.run_function(*f_args, **f_kwargs)
             tensor_outputs, _ = split_non_tensors(outputs)

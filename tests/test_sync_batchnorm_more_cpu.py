@@ -129,3 +129,63 @@ def _conversion(rank, world):
 
 def test_conversion_keeps_settings_and_statistics():
     spawn_ranks(_conversion, 2, (), backend="gloo")
+
+
+def _several_calls_per_step(rank, world, nested):
+    """The same checkpointed block runs three times in one step (autograd repeats the calls last first), optionally inside an
+    outer checkpointed block: every repetition gets the statistics of its own first run."""
+    from fairscale_b200.nn.checkpoint import checkpoint_invocations
+
+    torch.manual_seed(0)
+    plain = nn.Sequential(nn.Conv2d(3, 3, 1), nn.BatchNorm2d(3))
+    sync = SyncBatchNorm.convert_sync_batchnorm(copy.deepcopy(plain))
+    block = checkpoint_wrapper(sync)
+    if nested:
+        outer = checkpoint_wrapper(nn.Sequential(block))
+        run = lambda t: outer(t)  # noqa: E731
+    else:
+        run = block
+    per = 4
+    g = torch.Generator().manual_seed(1)
+    xs = [torch.randn(8, 3, 4, 4, generator=g) * (i + 1) + i for i in range(3)]  # very different statistics per call
+    a = [x.clone().requires_grad_() for x in xs]
+    sum(plain(t).pow(2).sum() for t in a).backward()
+    b = [x[rank * per:(rank + 1) * per].clone().requires_grad_() for x in xs]
+    sum(run(t).pow(2).sum() for t in b).backward()
+    for got, want in zip(b, a):
+        torch.testing.assert_close(got.grad, want.grad[rank * per:(rank + 1) * per], atol=1e-3, rtol=1e-3)
+    assert int(sync[1].num_batches_tracked) == int(plain[1].num_batches_tracked) == 3
+    torch.testing.assert_close(sync[1].running_var, plain[1].running_var, atol=1e-4, rtol=1e-4)
+    assert checkpoint_invocations() == []  # nothing is left running
+
+
+@pytest.mark.parametrize("nested", [False, True])
+def test_block_called_several_times_per_step(nested):
+    spawn_ranks(_several_calls_per_step, 2, (nested,), backend="gloo")
+
+
+def test_every_checkpointed_call_has_its_own_scratch():
+    from fairscale_b200.nn.checkpoint import checkpoint_invocations
+
+    seen = []
+
+    class Probe(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(2, 2)
+
+        def forward(self, x):
+            stack = checkpoint_invocations()
+            scratch = stack[-1]
+            scratch.setdefault("visits", []).append(scratch["_mode"])
+            seen.append((id(scratch), scratch["_mode"], len(stack)))
+            return self.lin(x)
+
+    probe = checkpoint_wrapper(Probe())
+    x = torch.randn(3, 2, requires_grad=True)
+    (probe(x).sum() + probe(x * 2).sum()).backward()
+    first_a, first_b, replay_1, replay_2 = seen
+    assert first_a[1] == first_b[1] == "first" and replay_1[1] == replay_2[1] == "replay"
+    assert first_a[0] != first_b[0]                      # two calls, two scratch dicts
+    assert {replay_1[0], replay_2[0]} == {first_a[0], first_b[0]}  # each repetition finds the dict of its own call
+    assert all(depth == 1 for _, _, depth in seen) and checkpoint_invocations() == []
