@@ -177,7 +177,10 @@ class OSS(Optimizer):
         """Clip the *global* gradient norm; must be called on all ranks.
 
         Each rank only holds the gradients of its shard (with ShardedDataParallel), so
-        the local norm is combined across ranks before the common scale is applied.
+        the local norm is combined across ranks before the common scale is applied.  The combination runs over the WORLD
+        group, not over this optimizer's group (as in the reference, fairscale/optim/oss.py:283-297): with model parallelism
+        the ranks outside the data-parallel group hold other parameters of the same model.  Every rank of the world has to
+        make the call.
         """
         max_norm = float(max_norm)
         norm_type = float(norm_type)
