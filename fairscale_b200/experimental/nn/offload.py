@@ -15,8 +15,9 @@ checkpointing with micro-batches, profiler range names).  Design differences:
 
 from __future__ import annotations
 
+import contextlib
 import logging
-from typing import Any, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 from torch import nn
@@ -178,6 +179,14 @@ def _to(t: Any, device: torch.device) -> Any:
     return t.to(device, non_blocking=True) if isinstance(t, torch.Tensor) else t
 
 
+def _autocast_snapshot() -> Optional[Dict[str, Any]]:
+    """Arguments that re-create the autocast context that is active now (None when there is none)."""
+    for device_type in ("cuda", "cpu"):
+        if torch.is_autocast_enabled(device_type):
+            return {"device_type": device_type, "dtype": torch.get_autocast_dtype(device_type)}
+    return None
+
+
 class OffloadFunction(torch.autograd.Function):
     """Checkpointed execution: forward runs every slice under ``no_grad`` and keeps only the slice-boundary
     activations (on the offload device); backward reloads slices in reverse, recomputes with grad per micro-batch
@@ -187,6 +196,7 @@ class OffloadFunction(torch.autograd.Function):
     def forward(ctx: Any, dummy: torch.Tensor, model: "OffloadModel", *inputs: Any) -> Any:  # type: ignore[override]
         ctx.model = model
         ctx.n_inputs = len(inputs)
+        ctx.autocast = _autocast_snapshot()  # the recomputation in backward runs under the autocast state of this forward
         slices = model.model_slices
         acts: List[Tuple[Any, ...]] = [tuple(inputs)]
         ctx.inputs_require_grad = [isinstance(i, torch.Tensor) and i.requires_grad for i in inputs]
@@ -228,7 +238,8 @@ class OffloadFunction(torch.autograd.Function):
             in_grads: List[List[Any]] = []
             for mb, gmb in zip(model._microbatches(acts), model._microbatches(grads)):
                 leaves = tuple(a.detach().requires_grad_(a.is_floating_point()) if isinstance(a, torch.Tensor) else a for a in mb)
-                with record_function(_NS + "forward_pass_with_enable_grad"), torch.enable_grad():
+                amp = torch.autocast(**ctx.autocast) if ctx.autocast is not None else contextlib.nullcontext()
+                with record_function(_NS + "forward_pass_with_enable_grad"), torch.enable_grad(), amp:
                     o = s(*leaves)
                     o = o if isinstance(o, tuple) else (o,)
                 with record_function(_NS + "backward_pass"):
