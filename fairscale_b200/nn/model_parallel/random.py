@@ -129,6 +129,7 @@ class CheckpointFunction(torch.autograd.Function):
         ctx.fwd_cpu_rng_state = torch.get_rng_state()
         ctx.fwd_dev_rng_state = _get_state()
         ctx.fwd_tracker = get_cuda_rng_tracker().get_states()
+        ctx.autocast = next(({"device_type": d, "dtype": torch.get_autocast_dtype(d)} for d in ("cuda", "cpu") if torch.is_autocast_enabled(d)), None)
         ctx.save_for_backward(*args)
         with torch.no_grad():
             return run_function(*args)
@@ -143,7 +144,8 @@ class CheckpointFunction(torch.autograd.Function):
         _set_cuda_rng_state(ctx.fwd_dev_rng_state)
         get_cuda_rng_tracker().set_states(ctx.fwd_tracker)
         detached = detach_variable(inputs)
-        with torch.enable_grad():
+        amp = torch.autocast(**ctx.autocast) if ctx.autocast is not None else contextlib.nullcontext()
+        with torch.enable_grad(), amp:  # the forward's autocast state, as well as its random states
             outputs = ctx.run_function(*detached)
         torch.set_rng_state(now_cpu)
         _set_cuda_rng_state(now_dev)

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import threading
 from collections import deque
-from contextlib import contextmanager
+from contextlib import contextmanager, nullcontext
 from typing import Any, Callable, Deque, Generator, List, Optional, Tuple, Union
 
 import torch
@@ -36,6 +36,7 @@ class _Mailbox:
     def __init__(self) -> None:
         self.recomputed: Deque[Recomputed] = deque(maxlen=1)
         self.rng_states: Deque[RNGStates] = deque(maxlen=1)
+        self.autocast: Optional[dict] = None  # arguments of the autocast context the forward ran under
 
 
 class Checkpointing:
@@ -147,6 +148,7 @@ class Checkpoint(torch.autograd.Function):
     def forward(ctx: Any, phony: Tensor, box: _Mailbox, function: Function, input_atomic: bool, *input: Tensor) -> TensorOrTensors:  # type: ignore[override]
         ctx.box = box
         save_rng_states(input[0].device, box.rng_states)
+        box.autocast = next(({"device_type": d, "dtype": torch.get_autocast_dtype(d)} for d in ("cuda", "cpu") if torch.is_autocast_enabled(d)), None)
         ctx.save_for_backward(*input)
         with torch.no_grad(), enable_checkpointing():
             return function(input[0] if input_atomic else input)
@@ -174,8 +176,11 @@ class Recompute(torch.autograd.Function):
     def backward(ctx: Any, *grad_output: Tensor) -> Tuple[None, ...]:  # type: ignore[override]
         inputs = ctx.saved_tensors
         leaves = tuple(x.detach().requires_grad_(x.requires_grad) for x in inputs)
+        # the repetition runs under the random state and the autocast state of the forward (backward passes start with
+        # autocast off, and a stage that got low-precision activations then meets its own fp32 weights)
+        amp = torch.autocast(**ctx.box.autocast) if ctx.box.autocast is not None else nullcontext()
         with restore_rng_states(inputs[0].device, ctx.box.rng_states):
-            with torch.enable_grad(), enable_recomputing():
+            with torch.enable_grad(), enable_recomputing(), amp:
                 output = ctx.function(leaves[0] if ctx.input_atomic else leaves)
         ctx.box.recomputed.append((output, leaves))
         return (None, None, None, None) + tuple(None for _ in inputs)

@@ -366,3 +366,32 @@ def _random_streams(rank, world):
 
 def test_two_random_streams_and_the_checkpoint_that_replays_them():
     spawn_ranks(_random_streams, 2, (), backend="gloo")
+
+
+def _checkpoint_under_autocast(rank, world):
+    mpu.initialize_model_parallel(world)
+    mpu.model_parallel_cuda_manual_seed(1)
+    lin1, lin2 = torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)
+
+    def block(t):
+        return lin2(torch.tanh(lin1(t)))
+
+    x = torch.randn(4, 8)
+    a, b = x.clone().requires_grad_(), x.clone().requires_grad_()
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        kept = block(a)
+        replayed = mpu.checkpoint(block, b)
+    assert replayed.dtype == torch.bfloat16
+    kept.float().sum().backward()
+    grads = [p.grad.clone() for p in (*lin1.parameters(), *lin2.parameters())]
+    for p in (*lin1.parameters(), *lin2.parameters()):
+        p.grad = None
+    replayed.float().sum().backward()  # the repetition runs with autocast on again
+    for p, g in zip((*lin1.parameters(), *lin2.parameters()), grads):
+        torch.testing.assert_close(p.grad, g, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(b.grad, a.grad, atol=1e-6, rtol=1e-5)
+    mpu.destroy_model_parallel()
+
+
+def test_checkpoint_replays_under_the_forwards_autocast_state():
+    spawn_ranks(_checkpoint_under_autocast, 1, (), backend="gloo")

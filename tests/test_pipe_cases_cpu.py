@@ -695,3 +695,21 @@ def test_skippables_are_verified_before_anything_runs():
     x = torch.rand(4, 2)
     torch.testing.assert_close(pipe(x), (x * 4 + x * 2) + x)
     assert "Stash" in repr(Stash())
+
+
+@pytest.mark.parametrize("mode", ["always", "except_last"])
+def test_recomputation_runs_under_the_autocast_state_of_the_forward(mode):
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(4, 8), nn.Tanh(), nn.Linear(8, 8), nn.Tanh(), nn.Linear(8, 2))
+    plain = deepcopy(model)
+    pipe = Pipe(model, [2, 2, 1], devices=["cpu"] * 3, chunks=2, checkpoint=mode)
+    x = torch.randn(4, 4, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_()
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        out, want = pipe(x), plain(x2)
+    assert out.dtype == torch.bfloat16
+    out.float().sum().backward()  # backward starts with autocast off; the stages got bf16 activations from their predecessors
+    want.float().sum().backward()
+    torch.testing.assert_close(x.grad, x2.grad, atol=2e-2, rtol=2e-2)
+    for a, b in zip(pipe.parameters(), plain.parameters()):
+        torch.testing.assert_close(a.grad, b.grad, atol=2e-2, rtol=2e-2)
