@@ -1,15 +1,21 @@
 """fairseq-style dynamic loss scaler that also works on CPU tensors.
 
-Capability parity with fairscale/experimental/optim/dynamic_loss_scaler.py:32-208: overflow is detected through
-the gradient norm (inf / nan), the scale shrinks by ``scale_factor`` when the share of overflowing steps since
-the last rescale reaches ``tolerance``, grows every ``scale_window`` overflow-free steps, and training stops
-with ``FloatingPointError`` once the scale would fall to ``min_loss_scale``.  On CUDA the norm of all gradients
-is one multi-tensor launch and one host read per step, not one ``torch.norm`` per parameter.
+Same behaviour and public names as fairscale/experimental/optim/dynamic_loss_scaler.py:32-208, organised as two parts: a
+small schedule object that only counts steps and decides when the scale moves (it never sees a tensor), and the scaler
+proper that measures gradient norms, drives the schedule and talks to the optimizer.
+
+Rules of the schedule: a step whose gradient norm is inf or nan is an overflow.  Overflows are counted since the last
+change of the scale; once their share of the steps since then reaches ``tolerance`` the scale is divided by
+``scale_factor`` (not below ``threshold``).  After ``scale_window`` steps without overflow the scale is multiplied by
+``scale_factor``.  A scale that would reach ``min_loss_scale`` stops training with ``FloatingPointError``.
+
+On CUDA the norm of a parameter group's gradients is one multi-tensor launch and one host read, not one norm per tensor.
 """
 
 from __future__ import annotations
 
-from collections import defaultdict
+import math
+from dataclasses import dataclass, field
 from enum import Enum
 from typing import Any, Dict, List, Optional
 
@@ -24,6 +30,48 @@ class OptState(Enum):
     STEPPED = 2
 
 
+@dataclass
+class _Schedule:
+    """Step counters of the scaler.  ``step`` counts calls of ``update`` (and overflowing steps), the other two remember at
+    which step the scale last changed and last overflowed."""
+
+    window: int
+    tolerance: float
+    step: int = 0
+    last_overflow: int = -1
+    last_change: int = -1
+    overflows_since_change: int = 0
+
+    def overflow_forces_decrease(self) -> bool:
+        """Register an overflow at the current step; True when the tolerated share is used up."""
+        self.last_overflow = self.step
+        self.overflows_since_change += 1
+        share = self.overflows_since_change / float(self.step - self.last_change)
+        if share < self.tolerance:
+            return False
+        self.last_change, self.overflows_since_change = self.step, 0
+        return True
+
+    def clean_step_allows_increase(self) -> bool:
+        """Called once per finished step: True every ``window`` steps after the last overflow."""
+        grow = (self.step - self.last_overflow) % self.window == 0
+        if grow:
+            self.last_change = self.step
+        self.step += 1
+        return grow
+
+
+@dataclass
+class _PerOptimizer:
+    stage: Dict[int, OptState] = field(default_factory=dict)
+
+    def of(self, optimizer: Any) -> OptState:
+        return self.stage.get(id(optimizer), OptState.READY)
+
+    def set(self, optimizer: Any, value: OptState) -> None:
+        self.stage[id(optimizer)] = value
+
+
 class DynamicLossScaler:
     def __init__(self, init_scale: float = 2.0**15, scale_factor: float = 2.0, scale_window: int = 2000,
                  tolerance: float = 0.0, threshold: Optional[float] = None, min_loss_scale: float = 1e-4):
@@ -33,17 +81,29 @@ class DynamicLossScaler:
         self.tolerance = tolerance
         self.threshold = threshold
         self.min_loss_scale = min_loss_scale
-        self._iter = 0
-        self._last_overflow_iter = -1
-        self._last_rescale_iter = -1
-        self._overflows_since_rescale = 0
-        self._stage: Dict[int, OptState] = defaultdict(lambda: OptState.READY)
+        self._schedule = _Schedule(window=scale_window, tolerance=tolerance)
+        self._optimizers = _PerOptimizer()
 
+    # ------------------------------------------------------------------ scaling
     def scale(self, outputs: Any) -> Any:
+        """``outputs`` (a tensor, or a list / tuple of tensors) times the current scale."""
         if isinstance(outputs, (list, tuple)):
-            return type(outputs)(self.loss_scale * o for o in outputs)
-        return self.loss_scale * outputs
+            return type(outputs)(o * self.loss_scale for o in outputs)
+        return outputs * self.loss_scale
 
+    @torch.no_grad()
+    def unscale_(self, optimizer: Any) -> None:
+        stage = self._optimizers.of(optimizer)
+        if stage is OptState.UNSCALED:
+            raise RuntimeError("unscale_() has already been called on this optimizer since the last update().")
+        if stage is OptState.STEPPED:
+            raise RuntimeError("unscale_() is being called after step().")
+        grads = [p.grad for group in optimizer.param_groups for p in group["params"] if p.grad is not None]
+        if grads:
+            torch._foreach_mul_(grads, 1.0 / float(self.loss_scale))
+        self._optimizers.set(optimizer, OptState.UNSCALED)
+
+    # ------------------------------------------------------------------ overflow handling
     @torch.no_grad()
     def _get_gradients_norm(self, params: List[torch.nn.Parameter]) -> float:
         grads = [p.grad.detach() for p in params if p.grad is not None]
@@ -51,74 +111,56 @@ class DynamicLossScaler:
             return 0.0
         if multi_tensor.supported(grads):
             return float(multi_tensor.l2_norm(grads))
-        return float(torch.linalg.vector_norm(torch.stack([torch.linalg.vector_norm(g.float()) for g in grads])))
+        per_tensor = torch.stack([torch.linalg.vector_norm(g.float()) for g in grads])
+        return float(torch.linalg.vector_norm(per_tensor))
 
     def _decrease_loss_scale(self) -> None:
-        self.loss_scale /= self.scale_factor
-        if self.threshold is not None:
-            self.loss_scale = max(self.loss_scale, self.threshold)
+        lowered = self.loss_scale / self.scale_factor
+        self.loss_scale = lowered if self.threshold is None else max(lowered, self.threshold)
 
     def _check_overflow(self, grad_norm: float) -> None:
-        if grad_norm != float("inf") and grad_norm == grad_norm:
+        """Raises ``OverflowError`` (after adjusting the scale) when ``grad_norm`` is not finite."""
+        if math.isfinite(grad_norm):
             return
-        prev = self.loss_scale
-        since = self._iter - self._last_rescale_iter
-        self._last_overflow_iter = self._iter
-        self._overflows_since_rescale += 1
-        if self._overflows_since_rescale / float(since) >= self.tolerance:
+        before = self.loss_scale
+        if self._schedule.overflow_forces_decrease():
             self._decrease_loss_scale()
-            self._last_rescale_iter = self._iter
-            self._overflows_since_rescale = 0
         if self.loss_scale <= self.min_loss_scale:
-            self.loss_scale = prev
+            self.loss_scale = before  # leave the scale usable for whoever catches the error
             raise FloatingPointError(
                 f"Minimum loss scale reached ({self.min_loss_scale}). Your loss is probably exploding. Try lowering the "
                 "learning rate, using gradient clipping or increasing the batch size."
             )
-        self._iter += 1
+        self._schedule.step += 1
         raise OverflowError("setting loss scale to: " + str(self.loss_scale))
 
-    def update(self) -> None:
-        if (self._iter - self._last_overflow_iter) % self.scale_window == 0:
-            self.loss_scale *= self.scale_factor
-            self._last_rescale_iter = self._iter
-        self._iter += 1
-        self._stage.clear()
-
+    # ------------------------------------------------------------------ the training-loop calls
     def step(self, optimizer: Any, *args: Any, **kwargs: Any) -> Any:
         """Unscale (if not done yet) and step; returns None and skips the step when the gradients overflowed."""
         if "closure" in kwargs:
             raise RuntimeError("Closure use is not currently supported if DynamicLossScaler is enabled.")
-        if self._stage[id(optimizer)] is OptState.STEPPED:
+        if self._optimizers.of(optimizer) is OptState.STEPPED:
             raise RuntimeError("step() has already been called since the last update().")
-        for group in optimizer.param_groups:
-            try:
+        try:
+            for group in optimizer.param_groups:
                 self._check_overflow(self._get_gradients_norm(group["params"]))
-            except OverflowError:
-                return None
-        if self._stage[id(optimizer)] is OptState.READY:
+        except OverflowError:
+            return None
+        if self._optimizers.of(optimizer) is OptState.READY:
             self.unscale_(optimizer)
-        ret = optimizer.step(*args, **kwargs)
-        self._stage[id(optimizer)] = OptState.STEPPED
-        return ret
+        result = optimizer.step(*args, **kwargs)
+        self._optimizers.set(optimizer, OptState.STEPPED)
+        return result
 
-    @torch.no_grad()
-    def unscale_(self, optimizer: Any) -> None:
-        stage = self._stage[id(optimizer)]
-        if stage is OptState.UNSCALED:
-            raise RuntimeError("unscale_() has already been called on this optimizer since the last update().")
-        if stage is OptState.STEPPED:
-            raise RuntimeError("unscale_() is being called after step().")
-        inv = 1.0 / float(self.loss_scale)
-        for group in optimizer.param_groups:
-            for p in group["params"]:
-                if p.grad is not None:
-                    p.grad.mul_(inv)
-        self._stage[id(optimizer)] = OptState.UNSCALED
+    def update(self) -> None:
+        """End of a step: grow the scale when the window without overflow is complete, forget per-optimizer stages."""
+        if self._schedule.clean_step_allows_increase():
+            self.loss_scale *= self.scale_factor
+        self._optimizers.stage.clear()
 
+    # ------------------------------------------------------------------ checkpointing
     def state_dict(self) -> Optional[Dict[str, float]]:
-        return {"loss_scale": self.loss_scale} if self.loss_scale is not None else None
+        return None if self.loss_scale is None else {"loss_scale": self.loss_scale}
 
     def load_state_dict(self, state_dict: Dict[str, float]) -> None:
-        if "loss_scale" in state_dict:
-            self.loss_scale = state_dict["loss_scale"]
+        self.loss_scale = state_dict.get("loss_scale", self.loss_scale)

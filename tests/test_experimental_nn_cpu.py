@@ -213,3 +213,59 @@ def test_auto_shard_transformer_reference_split():
     shards = shard_model(TransformerModel(28783, 200, 2, 200, 1, 0.2))
     assert len(shards) == 2
     assert [sum(p.numel() for p in s.parameters()) for s in shards] == [5998600, 5785383]
+
+
+def test_dynamic_loss_scaler_schedule_window_tolerance_and_floor():
+    model = nn.Linear(2, 1)
+    opt = torch.optim.SGD(model.parameters(), lr=0.0)
+
+    def run(scaler, overflow):
+        opt.zero_grad()
+        scaler.scale(model(torch.ones(1, 2)).sum()).backward()
+        if overflow:
+            model.weight.grad[0, 0] = float("nan")
+        stepped = scaler.step(opt) is not None or not overflow
+        if not overflow:
+            scaler.update()
+        return stepped
+
+    # grows every `scale_window` clean steps
+    s = DynamicLossScaler(init_scale=4.0, scale_window=3)
+    scales = []
+    for _ in range(7):
+        run(s, False)
+        scales.append(s.loss_scale)
+    assert scales == [4.0, 4.0, 8.0, 8.0, 8.0, 16.0, 16.0], scales
+    # with a tolerance, single overflows among many clean steps do not lower the scale; a burst does
+    s = DynamicLossScaler(init_scale=64.0, scale_window=1000, tolerance=0.5)
+    for _ in range(4):
+        run(s, False)
+    run(s, True)
+    assert s.loss_scale == 64.0  # one overflow in five steps since the last change: below one half
+    s2 = DynamicLossScaler(init_scale=64.0, scale_window=1000, tolerance=0.5)
+    run(s2, False)
+    run(s2, True)
+    assert s2.loss_scale == 32.0  # one in two
+    # the threshold is a floor for decreases; lists and tuples are scaled element-wise; state round trip
+    s = DynamicLossScaler(init_scale=4.0, threshold=3.0)
+    run(s, True)
+    assert s.loss_scale == 3.0
+    a, b = s.scale([torch.ones(1), torch.ones(1) * 2])
+    assert float(a) == 3.0 and float(b) == 6.0 and isinstance(s.scale((torch.ones(1),)), tuple)
+    other = DynamicLossScaler()
+    other.load_state_dict(s.state_dict())
+    assert other.loss_scale == 3.0
+    # misuse is reported
+    run(s, False)
+    opt.zero_grad()
+    s.scale(model(torch.ones(1, 2)).sum()).backward()
+    s.unscale_(opt)
+    with pytest.raises(RuntimeError):
+        s.unscale_(opt)
+    s.step(opt)
+    with pytest.raises(RuntimeError):
+        s.step(opt)
+    with pytest.raises(RuntimeError):
+        s.unscale_(opt)
+    with pytest.raises(RuntimeError):
+        DynamicLossScaler().step(opt, closure=lambda: 0)
