@@ -20,6 +20,11 @@ from .initialize import get_model_parallel_group, get_model_parallel_rank, get_m
 from .utils import VocabUtility
 
 
+__all__ = [
+    "vocab_parallel_cross_entropy",
+]
+
+
 class _VocabParallelCrossEntropy(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, vocab_parallel_logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:  # type: ignore[override]

@@ -18,6 +18,27 @@ import torch.distributed as dist
 
 from .utils import ensure_divisibility
 
+__all__ = [
+    "initialize_model_parallel",
+    "model_parallel_is_initialized",
+    "destroy_model_parallel",
+    "get_model_parallel_group",
+    "get_model_parallel_rank",
+    "get_model_parallel_src_rank",
+    "get_model_parallel_world_size",
+    "get_data_parallel_group",
+    "get_data_parallel_rank",
+    "get_data_parallel_ranks",
+    "get_data_parallel_world_size",
+    "get_pipeline_parallel_group",
+    "get_pipeline_parallel_ranks",
+    "get_context_parallel_group",
+    "get_context_parallel_rank",
+    "get_context_parallel_ranks",
+    "get_context_parallel_world_size",
+]
+
+
 _AXES = ("data", "pipeline", "context", "model")
 
 

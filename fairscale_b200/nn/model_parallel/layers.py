@@ -34,6 +34,14 @@ from .mappings import (
 from .utils import VocabUtility, divide_and_check_no_remainder
 
 
+__all__ = [
+    "ColumnParallelLinear",
+    "RowParallelLinear",
+    "VocabParallelEmbedding",
+    "ParallelEmbedding",
+]
+
+
 def _local_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -> torch.Tensor:
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
         return _gemm.linear(x, w, b)

@@ -21,6 +21,14 @@ from ...parallel import comm
 from .initialize import get_model_parallel_group
 from .utils import split_tensor_along_last_dim
 
+__all__ = [
+    "copy_to_model_parallel_region",
+    "reduce_from_model_parallel_region",
+    "scatter_to_model_parallel_region",
+    "gather_from_model_parallel_region",
+]
+
+
 Primitive = Callable[[torch.Tensor], torch.Tensor]
 
 

@@ -18,6 +18,13 @@ from torch.utils.checkpoint import detach_variable
 
 from .initialize import get_data_parallel_rank, get_model_parallel_rank
 
+__all__ = [
+    "checkpoint",
+    "get_cuda_rng_tracker",
+    "model_parallel_cuda_manual_seed",
+]
+
+
 _MODEL_PARALLEL_RNG_TRACKER_NAME = "model-parallel-rng"
 
 
