@@ -20,37 +20,41 @@ def _is_namedtuple(x: Any) -> bool:
     return isinstance(x, tuple) and hasattr(x, "_fields") and hasattr(x, "_make")
 
 
-def apply_to_type(type_fn: Callable[[Any], bool], fn: Callable, container: Any) -> Any:
-    """Map ``fn`` over every leaf for which ``type_fn(leaf)`` is true.
+def _rebuild_ordered(x: "OrderedDict", walk: Callable) -> "OrderedDict":
+    # subclasses of OrderedDict (model outputs of some libraries) carry attributes beside their items: both are kept
+    out = type(x)()
+    for key in x:
+        out[key] = walk(x[key])
+    vars(out).update(vars(x))
+    return out
 
-    Containers are rebuilt with the same concrete type; other leaves are returned
-    unchanged.  Dict values are mutated through ``__dict__`` for objects that are
-    themselves dict-like holders (``OrderedDict`` subclasses keep extra attributes).
-    """
+
+# (test, how to rebuild around the mapped children), tried from top to bottom: the order matters where one kind is a special
+# case of another (OrderedDict before dict, PackedSequence and namedtuples before tuple)
+_KINDS: List[Tuple[Callable[[Any], bool], Callable[[Any, Callable], Any]]] = [
+    (lambda x: isinstance(x, OrderedDict), _rebuild_ordered),
+    # a PackedSequence is an immutable named tuple: rebuild it around the mapped data (the reference calls fn for its side
+    # effects only and returns the input, which loses casts and device moves)
+    (lambda x: isinstance(x, PackedSequence), lambda x, walk: x._replace(data=walk(x.data))),
+    (lambda x: isinstance(x, dict), lambda x, walk: {key: walk(x[key]) for key in x}),
+    (_is_namedtuple, lambda x, walk: type(x)(*map(walk, x))),
+    (lambda x: isinstance(x, list), lambda x, walk: list(map(walk, x))),
+    (lambda x: isinstance(x, tuple), lambda x, walk: tuple(map(walk, x))),
+    (lambda x: isinstance(x, set), lambda x, walk: set(map(walk, x))),
+]
+
+
+def apply_to_type(type_fn: Callable[[Any], bool], fn: Callable, container: Any) -> Any:
+    """``container`` rebuilt with ``fn(leaf)`` in the place of every leaf that ``type_fn`` accepts.  Dicts, ordered dicts (and
+    their subclasses, attributes included), lists, tuples, named tuples, sets and packed sequences are walked and come back
+    as the same kind; every other object is a leaf and, unless ``type_fn`` accepts it, is returned untouched."""
 
     def walk(x: Any) -> Any:
         if type_fn(x):
             return fn(x)
-        if isinstance(x, OrderedDict):
-            out = x.__class__()
-            for k, v in x.items():
-                out[k] = walk(v)
-            out.__dict__.update(x.__dict__)
-            return out
-        if isinstance(x, PackedSequence):
-            # a PackedSequence is an immutable named tuple: rebuild it around the mapped data (the reference calls fn for
-            # its side effects only and returns the input, which loses casts and device moves)
-            return x._replace(data=walk(x.data))
-        if isinstance(x, dict):
-            return {k: walk(v) for k, v in x.items()}
-        if _is_namedtuple(x):
-            return type(x)(*(walk(v) for v in x))
-        if isinstance(x, list):
-            return [walk(v) for v in x]
-        if isinstance(x, tuple):
-            return tuple(walk(v) for v in x)
-        if isinstance(x, set):
-            return {walk(v) for v in x}
+        for is_kind, rebuild in _KINDS:
+            if is_kind(x):
+                return rebuild(x, walk)
         return x
 
     return walk(container)

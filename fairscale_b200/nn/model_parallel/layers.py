@@ -93,7 +93,27 @@ def _initialize_affine_weight(
     return master if return_master_weight else None
 
 
-class VocabParallelEmbedding(torch.nn.Module):
+class _ShardedEmbedding(torch.nn.Module):
+    """What both sharded embeddings take over from ``torch.nn.Embedding``: its settings, and the library lookup that honours
+    all of them."""
+
+    weight: Parameter
+
+    def _keep_settings(self, num_embeddings, embedding_dim, padding_idx, max_norm, norm_type, scale_grad_by_freq, sparse) -> None:
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.padding_idx, self.max_norm, self.norm_type = padding_idx, max_norm, norm_type
+        self.scale_grad_by_freq, self.sparse = scale_grad_by_freq, sparse
+        self._weight = None
+
+    def _is_plain_lookup(self) -> bool:
+        """No setting asks for more than ``weight[ids]``."""
+        return self.padding_idx is None and self.max_norm is None and not (self.scale_grad_by_freq or self.sparse)
+
+    def _torch_lookup(self, ids: torch.Tensor, padding_idx: Optional[int]) -> torch.Tensor:
+        return F.embedding(ids, self.weight, padding_idx, self.max_norm, self.norm_type, self.scale_grad_by_freq, self.sparse)
+
+
+class VocabParallelEmbedding(_ShardedEmbedding):
     """Embedding whose vocabulary rows are split across the model-parallel group.
 
     Tokens outside the local range contribute zeros; the partial results are summed with an all-reduce.
@@ -111,14 +131,7 @@ class VocabParallelEmbedding(torch.nn.Module):
         init_method: Callable[[torch.Tensor], torch.Tensor] = init.xavier_normal_,
     ) -> None:
         super().__init__()
-        self.num_embeddings = num_embeddings
-        self.embedding_dim = embedding_dim
-        self.padding_idx = padding_idx
-        self.max_norm = max_norm
-        self.norm_type = norm_type
-        self.scale_grad_by_freq = scale_grad_by_freq
-        self.sparse = sparse
-        self._weight = None
+        self._keep_settings(num_embeddings, embedding_dim, padding_idx, max_norm, norm_type, scale_grad_by_freq, sparse)
         self.vocab_start_index, self.vocab_end_index = VocabUtility.vocab_range_from_global_vocab_size(
             num_embeddings, get_model_parallel_rank(), get_model_parallel_world_size()
         )
@@ -127,8 +140,7 @@ class VocabParallelEmbedding(torch.nn.Module):
         _initialize_affine_weight(self.weight, num_embeddings, embedding_dim, self.num_embeddings_per_partition, 0, init_method)
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
-        plain = self.padding_idx is None and self.max_norm is None and not self.scale_grad_by_freq and not self.sparse
-        if plain and input_.is_cuda and self.weight.dtype == torch.bfloat16 and self.embedding_dim % 8 == 0:
+        if self._is_plain_lookup() and input_.is_cuda and self.weight.dtype == torch.bfloat16 and self.embedding_dim % 8 == 0:
             from ...ops.embedding import embedding
 
             # the kernel masks out-of-range ids itself (no index clone / masked writes)
@@ -142,12 +154,12 @@ class VocabParallelEmbedding(torch.nn.Module):
             if pad is not None:
                 pad = pad + self.num_embeddings if pad < 0 else pad
                 pad = pad - self.vocab_start_index if self.vocab_start_index <= pad < self.vocab_end_index else None
-            partial = F.embedding(local, self.weight, pad, self.max_norm, self.norm_type, self.scale_grad_by_freq, self.sparse)
+            partial = self._torch_lookup(local, pad)
             partial[outside, :] = 0.0
         return reduce_from_model_parallel_region(partial)
 
 
-class ParallelEmbedding(torch.nn.Module):
+class ParallelEmbedding(_ShardedEmbedding):
     """Embedding whose embedding dimension is split across the model-parallel group (outputs are gathered)."""
 
     def __init__(
@@ -163,14 +175,7 @@ class ParallelEmbedding(torch.nn.Module):
         keep_master_weight_for_test: bool = False,
     ) -> None:
         super().__init__()
-        self.num_embeddings = num_embeddings
-        self.embedding_dim = embedding_dim
-        self.padding_idx = padding_idx
-        self.max_norm = max_norm
-        self.norm_type = norm_type
-        self.scale_grad_by_freq = scale_grad_by_freq
-        self.sparse = sparse
-        self._weight = None
+        self._keep_settings(num_embeddings, embedding_dim, padding_idx, max_norm, norm_type, scale_grad_by_freq, sparse)
         world = get_model_parallel_world_size()
         self.embedding_dim_per_partition = divide_and_check_no_remainder(embedding_dim, world)
         self.weight = Parameter(torch.empty(num_embeddings, self.embedding_dim_per_partition))
@@ -179,14 +184,12 @@ class ParallelEmbedding(torch.nn.Module):
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
         input_parallel = copy_to_model_parallel_region(input_)
-        plain = self.padding_idx is None and self.max_norm is None and not self.scale_grad_by_freq and not self.sparse
-        if plain and input_.is_cuda and self.weight.dtype == torch.bfloat16 and self.embedding_dim_per_partition % 8 == 0:
+        if self._is_plain_lookup() and input_.is_cuda and self.weight.dtype == torch.bfloat16 and self.embedding_dim_per_partition % 8 == 0:
             from ...ops.embedding import embedding
 
             local = embedding(input_parallel, self.weight)  # native gather kernel; its backward scatters into the slice
         else:
-            local = F.embedding(input_parallel, self.weight, self.padding_idx, self.max_norm, self.norm_type,
-                                self.scale_grad_by_freq, self.sparse)
+            local = self._torch_lookup(input_parallel, self.padding_idx)
         return gather_from_model_parallel_region(local)
 
 
