@@ -13,7 +13,6 @@ import contextlib
 import functools
 import gc
 import logging
-import multiprocessing
 import os
 import random
 import socket

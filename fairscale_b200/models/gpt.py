@@ -141,8 +141,6 @@ def build_fsdp_gpt(cfg: GPTConfig, device: torch.device, process_group: Any = No
     from ..nn.checkpoint import checkpoint_wrapper
     from ..nn.data_parallel import FullyShardedDataParallel as FSDP
 
-    import torch.distributed as dist
-
     from ..internal.parallel import ProcessGroupName, get_process_group_cached
     from ..parallel import nvlink, symm
 

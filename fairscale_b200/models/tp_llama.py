@@ -17,7 +17,6 @@ from dataclasses import dataclass
 from typing import Any, Optional
 
 import torch
-import torch.distributed as dist
 from torch import nn
 
 from ..nn.model_parallel import (
@@ -25,7 +24,6 @@ from ..nn.model_parallel import (
     RowParallelLinear,
     VocabParallelEmbedding,
     get_model_parallel_group,
-    get_model_parallel_rank,
     get_model_parallel_world_size,
     vocab_parallel_cross_entropy,
 )

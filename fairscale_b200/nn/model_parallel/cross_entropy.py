@@ -12,7 +12,6 @@ from __future__ import annotations
 from typing import Any
 
 import torch
-import torch.distributed as dist
 
 from ...ops.loss import ce_backward, ce_forward
 from ...parallel import comm
