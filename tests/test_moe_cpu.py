@@ -231,3 +231,27 @@ def test_gate_takes_low_precision_activations_and_routes_in_fp32():
     assert combine.dtype == torch.float32 and mask.dtype == torch.bool
     (l_aux + combine.sum()).backward()
     assert x.grad is not None and gate.wg.weight.grad is not None
+
+
+def _identity_backward(rank, world):
+    """fairscale tests/nn/moe/test_moe_layer.py `backward`: one identity expert per rank and as many experts as ranks; every
+    token finds room (capacity is 2 * tokens / experts), so the layer returns its input and an MSE loss against the input
+    leaves no gradient on the expert."""
+    torch.manual_seed(2)
+    d = 8
+    x = torch.randn(4, 16, d)
+    expert = nn.Linear(d, d, bias=False)
+    expert.weight = nn.Parameter(torch.eye(d))
+    gate = Top2Gate(d, world)
+    dist.broadcast(gate.wg.weight.data, 0)
+    moe = MOELayer(gate, expert)
+    y = moe(x)
+    assert y.shape == x.shape
+    torch.testing.assert_close(y, x, atol=1e-5, rtol=1e-5)
+    nn.functional.mse_loss(y, x).backward()
+    torch.testing.assert_close(expert.weight.grad, torch.zeros_like(expert.weight), atol=1e-6, rtol=0)
+    assert moe.l_aux is not None and moe.l_aux.requires_grad
+
+
+def test_moe_identity_expert_gets_no_gradient_from_a_loss_against_the_input():
+    spawn_ranks(_identity_backward, 2, (), backend="gloo")
