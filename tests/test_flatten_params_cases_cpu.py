@@ -204,3 +204,25 @@ def test_unflatten_params_over_tensors_from_outside(build):
     module.load_state_dict(during)
     for fp, ref in zip(module.flat_params, outside):
         torch.testing.assert_close(fp.detach(), ref)
+
+
+def test_a_flat_parameter_is_not_flattened_again():
+    """An outer wrapper asked to take every parameter of a module that already holds a wrapper refuses; with a parameter list
+    that leaves the inner wrapper's flat parameter out, both work side by side."""
+    inner = FlattenParamsWrapper(nn.Linear(4, 4))
+    with pytest.raises(ValueError, match="Nesting"):
+        FlattenParamsWrapper(nn.Sequential(inner, nn.Linear(4, 2)))
+
+    torch.manual_seed(0)
+    plain = nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 2))
+    want_state = {k: v.clone() for k, v in plain.state_dict().items()}
+    x = torch.rand(3, 4)
+    want = plain(x)
+    plain[0] = FlattenParamsWrapper(plain[0])
+    outer = FlattenParamsWrapper(plain, param_list=list(plain[1].parameters()))
+    torch.testing.assert_close(outer(x), want)
+    got_state = outer.state_dict()
+    assert got_state.keys() == want_state.keys()
+    for k, v in want_state.items():
+        torch.testing.assert_close(got_state[k], v)
+    assert sorted(p.numel() for p in outer.parameters()) == [4 * 2 + 2, 4 * 4 + 4]
