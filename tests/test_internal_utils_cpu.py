@@ -81,6 +81,30 @@ def test_calc_grad_norm():
     assert torch.isclose(calc_grad_norm(ps, 2.0), torch.tensor(30.0).sqrt())
     assert calc_grad_norm(ps, float("inf")) == 3.0
     assert calc_grad_norm([ps[2]], 2.0) == 0.0
+    # a bare tensor, another order, an integer order, and the dtype of the first parameter that counts
+    assert torch.isclose(calc_grad_norm(ps[0], 1), torch.tensor(6.0))
+    assert torch.isclose(calc_grad_norm(ps, 1.0), torch.tensor(12.0))
+    half = nn.Parameter(torch.ones(4, dtype=torch.bfloat16))
+    half.grad = torch.full((4,), 0.5, dtype=torch.bfloat16)
+    norm = calc_grad_norm([ps[2], half, ps[0]], 2.0)  # ps[2] has no gradient
+    assert norm.dtype == torch.bfloat16 and torch.isclose(norm.float(), torch.tensor(13.0).sqrt(), rtol=1e-2)
+    assert calc_grad_norm(iter(ps), 2.0) > 5  # any iterable of parameters
+
+
+def test_recursive_copy_to_device_walks_containers_and_leaves_the_rest():
+    from collections import OrderedDict, namedtuple
+
+    from fairscale_b200.internal.params import get_global_rank, recursive_copy_to_device
+
+    Pair = namedtuple("Pair", "a b")
+    value = {"t": torch.ones(2, dtype=torch.float64), "l": [torch.zeros(1), "text", 3], "tup": (torch.ones(1), None),
+             "od": OrderedDict(x=torch.ones(1)), "np": Pair(torch.ones(1), 2)}
+    moved = recursive_copy_to_device(value, non_blocking=False, device=torch.device("cpu"))
+    assert moved["t"].dtype == torch.float64 and moved["l"][1:] == ["text", 3] and moved["tup"][1] is None
+    assert isinstance(moved["l"], list) and isinstance(moved["tup"], tuple) and isinstance(moved["od"], dict)
+    assert isinstance(moved["np"], tuple) and torch.equal(moved["np"][0], torch.ones(1)) and moved["np"][1] == 2
+    assert recursive_copy_to_device(5, non_blocking=True, device=torch.device("cpu")) == 5
+    assert get_global_rank(None, 3) == 3  # no group: ranks are already global
 
 
 def test_param_and_grad_buckets():
